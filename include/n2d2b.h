@@ -1,0 +1,199 @@
+/*
+ * n2d2b.h - C ABI of the B200-native quantized integer inference path of N2D2.
+ *
+ * This is the whole boundary between host code (the C++ classes that keep N2D2's Cell / Scaling /
+ * DeepNet names, a test harness, another language's FFI) and the CUDA kernels.  Plain pointers and
+ * sizes only; every function returns 0 on success or a negative n2d2b_status, and
+ * n2d2b_last_error() gives the message for the calling thread.  Nothing here throws, resets the
+ * device or falls back to the CPU: without a usable GPU the calls fail.
+ *
+ * Citations give the interface of the reference project (CEA-LIST/N2D2) each entry point replaces.
+ *
+ * Data layouts
+ *   activations  NHWC, int8 (signed or unsigned per tensor) or int32 (cells whose Scaling is NONE)
+ *   conv weights [Cout][kH][kW][Cin/groups] int8, or packed int4 (two per byte, even element in the
+ *                high nibble, each output channel's row padded to a whole byte)
+ *   fc weights   [Cout][K], K running over the input tensor in NHWC order
+ *   biases       int32 per output channel
+ */
+#ifndef N2D2B_H
+#define N2D2B_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct n2d2b_net n2d2b_net;
+typedef void* n2d2b_stream; /* a cudaStream_t; NULL = the legacy default stream the reference uses */
+
+typedef enum n2d2b_status {
+    N2D2B_OK = 0,
+    N2D2B_ERR_INVALID = -1,     /* bad argument or unsupported configuration (std::runtime_error / domain_error in N2D2) */
+    N2D2B_ERR_CUDA = -2,        /* a CUDA call failed (CHECK_CUDA_STATUS in N2D2, include/CudaUtils.hpp:52-66, minus the device reset) */
+    N2D2B_ERR_STATE = -3,       /* call made in the wrong state (e.g. forward before finalize) */
+    N2D2B_ERR_TIMEOUT = -4,     /* a device-side bounded wait gave up; the context stays usable */
+    N2D2B_ERR_TOO_LARGE = -5    /* a size exceeds a documented maximum */
+} n2d2b_status;
+
+/* include/ScalingMode.hpp:27-34 */
+typedef enum n2d2b_scaling_mode {
+    N2D2B_SCALING_NONE = 0,
+    N2D2B_SCALING_FLOAT_MULT = 1,
+    N2D2B_SCALING_FIXED_MULT16 = 2,
+    N2D2B_SCALING_FIXED_MULT32 = 3,
+    N2D2B_SCALING_SINGLE_SHIFT = 4,
+    N2D2B_SCALING_DOUBLE_SHIFT = 5
+} n2d2b_scaling_mode;
+
+/* include/Activation/{Linear,Rectifier,Saturation}Activation_Frame.hpp */
+typedef enum n2d2b_activation {
+    N2D2B_ACT_LINEAR = 0,
+    N2D2B_ACT_RECTIFIER = 1,
+    N2D2B_ACT_SATURATION = 2
+} n2d2b_activation;
+
+typedef enum n2d2b_pooling { N2D2B_POOL_MAX = 0, N2D2B_POOL_AVERAGE = 1 } n2d2b_pooling;
+typedef enum n2d2b_dtype { N2D2B_I8 = 0, N2D2B_I32 = 1 } n2d2b_dtype;
+
+/*
+ * Per-output-channel rescale: the payload of N2D2's Scaling value type (include/Scaling.hpp:45-427;
+ * factories :339-373).  All arrays have nb_channels entries and are host pointers, copied by the call.
+ *   FLOAT_MULT    fscale                      y = round(Clip?(x) * fscale[c])
+ *   FIXED_MULT*   mult, frac_bits             y = (round(Clip?(x)) * mult[c] + 2^(f-1)) >> f
+ *   SINGLE_SHIFT  shift0                      y = (x + 2^(s-1)) >> s[c]
+ *   DOUBLE_SHIFT  shift0 (a), shift1 (b)      y = (x + (x << a[c]) + 2^(b-1)) >> b[c]
+ * frac_bits_per_channel (optional) overrides frac_bits channel by channel; the reference API has one
+ * nbFractionalBits per Scaling object (include/Scaling.hpp:129-193), so this is an extension.
+ * Clipping happens before the rescale and, as on the reference's CPU path, only in the FLOAT and FIXED
+ * modes (src/Scaling_Kernels.cpp:41-53,135-136).
+ */
+typedef struct n2d2b_scaling {
+    int32_t mode; /* n2d2b_scaling_mode */
+    int32_t nb_channels;
+    const float* fscale;
+    const int32_t* mult;
+    int32_t frac_bits;
+    const uint8_t* frac_bits_per_channel;
+    const uint8_t* shift0;
+    const uint8_t* shift1;
+    int32_t is_clipped;
+    const float* clip;
+} n2d2b_scaling;
+
+/*
+ * What a cell does to its accumulators on the way out: Activation::propagate =
+ * Scaling (with saturation to out_bits, signed or unsigned) then the activation
+ * (include/Activation/RectifierActivation_Frame.hpp:54-87).  out_unsigned is what
+ * DeepNetExport::isCellOutputUnsigned (src/Export/DeepNetExport.cpp:370-388) derives from the graph;
+ * here it is explicit.
+ */
+typedef struct n2d2b_quant {
+    n2d2b_scaling scaling;
+    int32_t activation;   /* n2d2b_activation */
+    int32_t out_bits;     /* 1..8; ignored when scaling.mode is NONE (the output stays int32) */
+    int32_t out_unsigned;
+    int32_t saturation_threshold; /* N2D2B_ACT_SATURATION only */
+} n2d2b_quant;
+
+/* ConvCell creation arguments (include/Cell/ConvCell.hpp:45-55) + input wiring */
+typedef struct n2d2b_conv_desc {
+    int32_t input;        /* tensor id */
+    int32_t nb_outputs;
+    int32_t kernel_h, kernel_w;
+    int32_t stride_y, stride_x;
+    int32_t pad_top, pad_left, pad_bottom, pad_right;
+    int32_t dilation_y, dilation_x;
+    int32_t groups;       /* 1 = dense, nb_channels = depthwise */
+    int32_t weight_bits;  /* 8, or 4 for packed int4 weights */
+} n2d2b_conv_desc;
+
+/* PoolCell creation arguments (include/Cell/PoolCell.hpp) */
+typedef struct n2d2b_pool_desc {
+    int32_t input;
+    int32_t pooling;      /* n2d2b_pooling */
+    int32_t pool_h, pool_w;
+    int32_t stride_y, stride_x;
+    int32_t pad_y, pad_x;
+} n2d2b_pool_desc;
+
+typedef struct n2d2b_tensor_info {
+    int32_t channels, height, width;
+    int32_t dtype;        /* n2d2b_dtype */
+    int32_t is_unsigned;
+    int32_t producer;     /* index of the producing cell, -1 for the network input */
+    int32_t readable;     /* 1 when n2d2b_net_read_tensor can return it after a forward */
+} n2d2b_tensor_info;
+
+/* n2d2b_net_finalize flags */
+#define N2D2B_KEEP_ALL_OUTPUTS 1u /* every cell keeps its own output buffer (layer-by-layer parity; DeepNet::logOutputs, src/DeepNet.cpp:1729-1759) */
+#define N2D2B_NO_FUSION 2u        /* do not fold ElemWise sums into the producing convolution's epilogue */
+#define N2D2B_FORCE_SIMT 4u       /* CUDA-core kernels everywhere (cross-check of the tensor-core path) */
+#define N2D2B_FORCE_IM2COL 8u     /* tensor-core convolutions always load activations through the im2col map */
+
+const char* n2d2b_last_error(void);
+int n2d2b_version(void);
+/* Number of CUDA devices, or a negative status. Replaces CudaContext device enumeration. */
+int n2d2b_device_count(void);
+
+/* A quantized network on one GPU: the cells DeepNetQuantization::quantizeNetwork leaves behind
+ * (src/DeepNetQuantization.cpp:285-388), executed in insertion order like DeepNet::propagate
+ * (src/DeepNet.cpp:2660-2743).  One net per GPU; a net is not thread-safe, different nets are. */
+int n2d2b_net_create(int device, n2d2b_net** net);
+void n2d2b_net_destroy(n2d2b_net* net);
+
+/* The stimuli tensor (StimuliProvider batch after the x255 / x127 range transform,
+ * src/DeepNetQuantization.cpp:359-370): channels x height x width of 8-bit values. Returns tensor id 0. */
+int n2d2b_net_set_input(n2d2b_net* net, int channels, int height, int width, int is_unsigned, int* tensor_id);
+
+/* ConvCell_Frame_CUDA (src/Cell/ConvCell_Frame_CUDA.cpp:1169-1270). bias may be NULL (NoBias). */
+int n2d2b_net_add_conv(n2d2b_net* net, const n2d2b_conv_desc* desc, const void* weights, const int32_t* bias,
+                       const n2d2b_quant* quant, int* tensor_id);
+/* FcCell_Frame_CUDA (src/Cell/FcCell_Frame_CUDA.cpp:308-427) */
+int n2d2b_net_add_fc(n2d2b_net* net, int input, int nb_outputs, int weight_bits, const void* weights,
+                     const int32_t* bias, const n2d2b_quant* quant, int* tensor_id);
+/* PoolCell_Frame_CUDA (src/Cell/PoolCell_Frame_CUDA.cpp:234-272); average pooling truncates like the
+ * quantized CPU cell (src/Cell/PoolCell_Frame_Kernels.cpp:93-95) */
+int n2d2b_net_add_pool(n2d2b_net* net, const n2d2b_pool_desc* desc, int* tensor_id);
+/* ElemWiseCell_Frame_CUDA, Sum with unit weights (src/Cell/ElemWiseCell_Frame_CUDA.cpp:135-228) */
+int n2d2b_net_add_elemwise_sum(n2d2b_net* net, const int* inputs, int nb_inputs, const n2d2b_quant* quant,
+                               int* tensor_id);
+/* ScalingCell_Frame_CUDA (src/Cell/ScalingCell_Frame_CUDA.cpp:67-76) */
+int n2d2b_net_add_scaling(n2d2b_net* net, int input, const n2d2b_quant* quant, int* tensor_id);
+
+/* Allocates activations for up to max_batch images, lays weights out for the kernels, builds the TMA
+ * descriptors.  Replaces Cell::initialize() + the cuDNN descriptor/algorithm set-up
+ * (src/Cell/ConvCell_Frame_CUDA.cpp:153-330,786-1094). */
+int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags);
+
+/* DeepNet::propagate(inference = true) on device buffers: d_input is batch x H x W x C 8-bit values,
+ * d_output receives the last cell's output (batch x its size). Asynchronous on `stream`. */
+int n2d2b_net_forward(n2d2b_net* net, const void* d_input, int batch, void* d_output, n2d2b_stream stream);
+/* The same with host buffers (the reference's mInputs.synchronizeHToD / mOutputs.synchronizeDToH):
+ * copies in, runs, copies out and synchronises the stream. */
+int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream);
+
+int n2d2b_net_num_tensors(const n2d2b_net* net);
+int n2d2b_net_tensor_info(const n2d2b_net* net, int tensor_id, n2d2b_tensor_info* info);
+/* Copies a tensor of the last forward (first `batch` images) to the host. */
+int n2d2b_net_read_tensor(n2d2b_net* net, int tensor_id, int batch, void* host_dst, size_t bytes);
+/* Number of kernel launches one forward of `batch` images issues. */
+int n2d2b_net_launches_per_forward(const n2d2b_net* net);
+/* Name of the kernel family cell `cell` runs on ("tcgen05", "simt", "depthwise", "pool", "sum", "fused"). */
+const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell);
+/* Device time of every cell of one forward, in milliseconds (CUDA events on `stream`), like the
+ * per-cell timings of DeepNet::propagate (src/DeepNet.cpp:2705-2717). ms has one entry per cell. */
+int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_output, float* ms, int nb_cells,
+                      n2d2b_stream stream);
+
+/* Stand-alone Scaling::propagate on device buffers (cuda*Scaling_propagate,
+ * src/Scaling_CUDA_Kernels.cu:209-430): d_in is int32 NHWC (nb_pixels x channels), d_out int8. */
+int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t nb_pixels,
+                            const n2d2b_quant* quant, n2d2b_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* N2D2B_H */

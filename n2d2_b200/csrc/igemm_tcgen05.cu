@@ -1,0 +1,513 @@
+// Implicit-GEMM convolution / fully-connected kernel on the Blackwell tensor cores.
+//
+//   D[M x N] (int32, in TMEM) = A[M x K] (u8 or s8 activations, NHWC) * B[N x K]^T (s8 weights, OHWI)
+//   M = output pixels (batch * oH * oW), N = output channels, K = taps * Cin walked tap by tap.
+//
+// One persistent CTA per SM loops over 128 x BN output tiles.  Warp 0 issues TMA loads into a
+// multi-stage shared-memory ring (A tile through a 2-D tiled map for a plain GEMM, or through an
+// im2col map that applies stride / padding / dilation and zero-fills the halo; B tile through a 2-D
+// map), warp 1 issues tcgen05.mma kind::i8 into one of two TMEM accumulators, warps 2-5 drain the
+// other accumulator with tcgen05.ld and run the fused epilogue (bias, per-channel rescale, rounding,
+// saturation, ReLU, optional residual add + second rescale) straight to int8 NHWC.  This replaces
+// the reference's cudnnConvolutionForward + cudnnAddTensor + Scaling kernel + cudnnActivationForward
+// sequence (src/Cell/ConvCell_Frame_CUDA.cpp:1169-1270) and its cublasGemm FC
+// (src/Cell/FcCell_Frame_CUDA.cpp:308-427).
+//
+// Every wait on an mbarrier is bounded: a wait that does not complete within about a second sets
+// *status_word and makes the whole CTA drain and exit, so a wrong descriptor cannot hang the GPU.
+#include <cstdio>
+#include <cstring>
+#include "kernels.h"
+
+namespace n2d2b {
+
+static constexpr int BM = 128;
+static constexpr int NUM_THREADS = 192;
+static constexpr int EPI_WARP0 = 2;
+static constexpr unsigned long long WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
+
+struct IgemmArgs {
+    int M, N, Cin, taps, BK, BN, stages, a_im2col;
+    int oW, oH, kW, sX, sY, pL, pT, dX, dY;
+    int num_m_tiles, num_n_tiles;
+    unsigned idesc;
+    unsigned tmem_cols;
+    int out_dtype;
+    void* out;
+    int* status;
+    QuantDev q;
+    Residual r;
+};
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
+{
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait. Returns false (and raises the CTA-wide abort flag) on time-out or when another
+// role already aborted.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
+                                          int* status, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* tm, unsigned bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(unsigned dst, const CUtensorMap* tm, unsigned bar, int c,
+                                                   int w, int h, int n, unsigned short off_w,
+                                                   unsigned short off_h)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are `swz` bytes wide (swz = 32, 64 or
+// 128, equal to the TMA swizzle span): 8-row groups are swz*8 bytes apart.
+__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr, int swz)
+{
+    const unsigned long long layout = (swz == 128) ? 2ull : (swz == 64 ? 4ull : 6ull);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)(((unsigned)(swz * 8)) >> 4) << 32;  // stride byte offset
+    d |= 1ull << 46;                                               // descriptor version (sm_100)
+    d |= layout << 61;
+    return d;
+}
+
+// ----------------------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const IgemmArgs a)
+{
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment of the tile ring (required by the 128-byte swizzle)
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int a_stage_bytes = BM * a.BK;
+    const int b_stage_bytes = a.BN * a.BK;
+    const int stage_bytes = a_stage_bytes + b_stage_bytes;
+    unsigned char* tiles = smem;
+    unsigned long long* bars = (unsigned long long*)(smem + (size_t)a.stages * stage_bytes);
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
+    const unsigned full0 = smem_u32(bars);
+    const unsigned empty0 = full0 + 8u * a.stages;
+    const unsigned tfull0 = empty0 + 8u * a.stages;
+    const unsigned tempty0 = tfull0 + 16u;
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    int* epi_params = (int*)(tmem_slot + 4);  // [4][BN]: bias, p0, p1, aux
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull0 + 8u * s, 1);
+            mbar_init(tempty0 + 8u * s, 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const int num_tiles = a.num_m_tiles * a.num_n_tiles;
+    const int kchunks = (a.Cin + a.BK - 1) / a.BK;
+    const int num_kb = a.taps * kchunks;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int n_tile = tile % a.num_n_tiles;
+                const int m_tile = tile / a.num_n_tiles;
+                const int m0 = m_tile * BM, n0 = n_tile * a.BN;
+                int iw0 = 0, ih0 = 0, in0 = 0;
+                if (a.a_im2col) {
+                    const int ox = m0 % a.oW;
+                    const int t = m0 / a.oW;
+                    const int oy = t % a.oH;
+                    in0 = t / a.oH;
+                    iw0 = ox * a.sX - a.pL;
+                    ih0 = oy * a.sY - a.pT;
+                }
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % a.stages;
+                    const unsigned ph = (it / a.stages) & 1u;
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+                    const int tap = kb / kchunks;
+                    const int kc = kb - tap * kchunks;
+                    const unsigned bar = full0 + 8u * s;
+                    const unsigned dstA = smem_u32(tiles + (size_t)s * stage_bytes);
+                    const unsigned dstB = dstA + a_stage_bytes;
+                    mbar_expect_tx(bar, (unsigned)stage_bytes);
+                    if (a.a_im2col) {
+                        const int ky = tap / a.kW, kx = tap - ky * a.kW;
+                        tma_load_im2col_4d(dstA, &tmA, bar, kc * a.BK, iw0, ih0, in0,
+                                           (unsigned short)(kx * a.dX), (unsigned short)(ky * a.dY));
+                    } else {
+                        tma_load_2d(dstA, &tmA, bar, tap * a.Cin + kc * a.BK, m0);
+                    }
+                    tma_load_2d(dstB, &tmB, bar, tap * a.Cin + kc * a.BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            unsigned it = 0;
+            unsigned acc_it = 0;
+            bool ok = true;
+            const int ksteps = a.BK / 32;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
+                const unsigned as = acc_it & 1u;
+                const unsigned aph = (acc_it >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % a.stages;
+                    const unsigned ph = (it / a.stages) & 1u;
+                    if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned sa = smem_u32(tiles + (size_t)s * stage_bytes);
+                    const unsigned long long adesc = make_smem_desc(sa, a.BK);
+                    const unsigned long long bdesc = make_smem_desc(sa + a_stage_bytes, a.BK);
+                    for (int k = 0; k < ksteps; ++k) {
+                        // advancing K by 32 bytes inside the swizzle span = +2 in the 16-byte address field
+                        tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k),
+                                  a.idesc, (kb | k) ? 1u : 0u);
+                    }
+                    tc_commit(empty0 + 8u * s);  // frees the stage once these MMAs have read it
+                }
+                if (ok) tc_commit(tfull0 + 8u * as);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const int row = quad * 32 + lane;
+        const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
+        unsigned acc_it = 0;
+        bool ok = true;
+        const bool vec_ok = (a.out_dtype == DT_I8) && (a.N % 16 == 0);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
+            const int n_tile = tile % a.num_n_tiles;
+            const int m_tile = tile / a.num_n_tiles;
+            const int m0 = m_tile * BM, n0 = n_tile * a.BN;
+            const unsigned as = acc_it & 1u;
+            const unsigned aph = (acc_it >> 1) & 1u;
+            if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const int m = m0 + row;
+            const bool m_ok = m < a.M;
+            for (int c0 = 0; c0 < a.BN; c0 += 32) {
+                unsigned v[32];
+                const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)c0;
+                tc_ld32(taddr, v);
+                tc_wait_ld();
+                if (!m_ok) continue;
+                const int nbase = n0 + c0;
+                if (nbase >= a.N) continue;
+                int y[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int n = nbase + j;
+                    if (n < a.N) {
+                        const long long x = (long long)(int)v[j] + (a.q.bias ? (long long)a.q.bias[n] : 0ll);
+                        int t = requant64(x, n, a.q);
+                        if (a.r.ptr) {
+                            const long long u = (long long)t
+                                + (long long)load_i8(a.r.ptr, (size_t)m * a.N + n, a.r.is_unsigned != 0);
+                            t = requant64(u, n, a.r.q2);
+                        }
+                        y[j] = t;
+                    } else {
+                        y[j] = 0;
+                    }
+                }
+                if (a.out_dtype == DT_I8) {
+                    uint8_t* op = (uint8_t*)a.out + (size_t)m * a.N + nbase;
+                    if (vec_ok && nbase + 32 <= a.N) {
+                        unsigned wds[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            wds[i] = ((unsigned)y[4 * i] & 0xffu) | (((unsigned)y[4 * i + 1] & 0xffu) << 8)
+                                   | (((unsigned)y[4 * i + 2] & 0xffu) << 16) | (((unsigned)y[4 * i + 3] & 0xffu) << 24);
+                        ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                        ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+                    } else {
+                        for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = (uint8_t)y[j];
+                    }
+                } else {
+                    int32_t* op = (int32_t*)a.out + (size_t)m * a.N + nbase;
+                    for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = y[j];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8u * as);
+        }
+        (void)epi_tid;
+        (void)epi_params;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn g_encode_tiled = nullptr;
+static EncodeIm2colFn g_encode_im2col = nullptr;
+
+static int load_driver_entry_points(const char** why)
+{
+    if (g_encode_tiled && g_encode_im2col) return 0;
+    cudaDriverEntryPointQueryResult qr;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn) {
+        *why = "cuTensorMapEncodeTiled is not available from the CUDA driver";
+        return -1;
+    }
+    g_encode_tiled = (EncodeTiledFn)fn;
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn) {
+        *why = "cuTensorMapEncodeIm2col is not available from the CUDA driver";
+        return -1;
+    }
+    g_encode_im2col = (EncodeIm2colFn)fn;
+    return 0;
+}
+
+static CUtensorMapSwizzle swizzle_for(int bk)
+{
+    return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+static size_t igemm_smem_bytes(int stages, int BK, int BN)
+{
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 4) * 8 + 16 + 4 * 256 * 4 + 64;
+}
+
+int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned,
+                    int force_im2col, int force_bn, int num_sms, const char** why)
+{
+    static const char* kWhy = "";
+    *why = kWhy;
+    if (load_driver_entry_points(why)) return -1;
+    if (g.groups != 1) { *why = "grouped convolution is not a dense contraction"; return -1; }
+    if (g.C % 16 != 0) { *why = "input channels must be a multiple of 16 for the TMA path"; return -1; }
+    if (((uintptr_t)in & 15) || ((uintptr_t)w & 15)) { *why = "operands must be 16-byte aligned"; return -1; }
+    memset(plan, 0, sizeof(*plan));
+    const bool plain = (g.kH == 1 && g.kW == 1 && g.sY == 1 && g.sX == 1 && g.pT == 0 && g.pL == 0
+                        && g.oH == g.H && g.oW == g.W);
+    plan->a_im2col = (plain && !force_im2col) ? 0 : 1;
+    plan->M = g.B * g.oH * g.oW;
+    plan->N = g.O;
+    plan->Cin = g.C;
+    plan->taps = g.kH * g.kW;
+    // widest K slab (= swizzle span) that divides the channel count; a channel count that is only a
+    // multiple of 16 uses 32-byte slabs whose tail the TMA unit zero-fills
+    plan->BK = (g.C % 128 == 0) ? 128 : (g.C % 64 == 0 ? 64 : 32);
+    int bn = force_bn;
+    if (bn == 0) bn = (g.O >= 256) ? 256 : (g.O > 64 ? 128 : 64);
+    plan->BN = bn;
+    plan->a_unsigned = in_unsigned;
+    plan->oW = g.oW; plan->oH = g.oH; plan->kW = g.kW;
+    plan->sX = g.sX; plan->sY = g.sY; plan->pL = g.pL; plan->pT = g.pT; plan->dX = g.dX; plan->dY = g.dY;
+    // pipeline depth: fill up to ~200 KB of shared memory, at most 8 stages
+    int stages = 8;
+    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN) > 200 * 1024) --stages;
+    plan->stages = stages;
+    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN);
+    const int num_m_tiles = (plan->M + BM - 1) / BM;
+    const int num_n_tiles = (plan->N + plan->BN - 1) / plan->BN;
+    const long long tiles = (long long)num_m_tiles * num_n_tiles;
+    plan->grid = (int)(tiles < num_sms ? tiles : num_sms);
+    if (plan->grid < 1) plan->grid = 1;
+
+    const CUtensorMapSwizzle swz = swizzle_for(plan->BK);
+    CUresult rc;
+    // B: weights [N][Ktot], K fastest
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)plan->taps * g.C, (cuuint64_t)g.O};
+        const cuuint64_t strides[1] = {(cuuint64_t)plan->taps * g.C};
+        const cuuint32_t box[2] = {(cuuint32_t)plan->BK, (cuuint32_t)plan->BN};
+        const cuuint32_t estr[2] = {1, 1};
+        rc = g_encode_tiled(&plan->tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the weight matrix"; return -1; }
+    }
+    if (!plan->a_im2col) {
+        const cuuint64_t dims[2] = {(cuuint64_t)g.C, (cuuint64_t)plan->M};
+        const cuuint64_t strides[1] = {(cuuint64_t)g.C};
+        const cuuint32_t box[2] = {(cuuint32_t)plan->BK, (cuuint32_t)BM};
+        const cuuint32_t estr[2] = {1, 1};
+        rc = g_encode_tiled(&plan->tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)in, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the activation matrix"; return -1; }
+    } else {
+        // NHWC activations as a (C, W, H, N) tensor; the base pixel of output (ox, oy) is
+        // (ox*sX - pL, oy*sY - pT) and the filter tap is passed as an offset per load.
+        const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)g.C, (cuuint64_t)g.C * g.W, (cuuint64_t)g.C * g.W * g.H};
+        const int lower[2] = {-g.pL, -g.pT};
+        // last base pixel = (oW-1)*sX - pL  ->  upper corner relative to the tensor edge
+        const int upper[2] = {(g.oW - 1) * g.sX - g.pL - (g.W - 1), (g.oH - 1) * g.sY - g.pT - (g.H - 1)};
+        const cuuint32_t estr[4] = {1, (cuuint32_t)g.sX, (cuuint32_t)g.sY, 1};
+        rc = g_encode_im2col(&plan->tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)in, dims, strides, lower, upper,
+                             (cuuint32_t)plan->BK, (cuuint32_t)BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeIm2col failed for the activation tensor"; return -1; }
+        // Drivers up to CUDA 13.1 encode im2col maps of tensors smaller than 128 KiB with a flag
+        // (bit 21 of the second 64-bit word) that makes the load misbehave; clearing it is the
+        // documented remedy used by NVIDIA's own open-source templates.
+        int drv = 0;
+        if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010) {
+            const size_t bytes = (size_t)g.C * g.W * g.H * g.B;
+            if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
+        }
+    }
+    return 0;
+}
+
+cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, void* out, int out_dtype,
+                         int* status_word, cudaStream_t s)
+{
+    if (plan.M == 0 || plan.N == 0) return cudaSuccess;
+    IgemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.M = plan.M; a.N = plan.N; a.Cin = plan.Cin; a.taps = plan.taps; a.BK = plan.BK; a.BN = plan.BN;
+    a.stages = plan.stages; a.a_im2col = plan.a_im2col;
+    a.oW = plan.oW; a.oH = plan.oH; a.kW = plan.kW; a.sX = plan.sX; a.sY = plan.sY;
+    a.pL = plan.pL; a.pT = plan.pT; a.dX = plan.dX; a.dY = plan.dY;
+    a.num_m_tiles = (plan.M + BM - 1) / BM;
+    a.num_n_tiles = (plan.N + plan.BN - 1) / plan.BN;
+    // instruction descriptor: D = s32, A = u8/s8, B = s8, both K-major, N and M extents
+    a.idesc = (2u << 4) | ((plan.a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
+            | ((unsigned)(BM >> 4) << 24);
+    unsigned cols = 2u * plan.BN;
+    unsigned p2 = 32;
+    while (p2 < cols) p2 <<= 1;
+    a.tmem_cols = p2;
+    a.out_dtype = out_dtype;
+    a.out = out;
+    a.status = status_word;
+    a.q = q;
+    a.r = r;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(igemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    int tiles = a.num_m_tiles * a.num_n_tiles;
+    int grid = plan.grid < tiles ? plan.grid : tiles;
+    igemm_i8_tcgen05_kernel<<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
+    return cudaGetLastError();
+}
+
+}  // namespace n2d2b

@@ -1,0 +1,74 @@
+// Host-side launch interface of the CUDA kernels (internal to the library).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "common.cuh"
+
+namespace n2d2b {
+
+struct ConvGeom {
+    int B, H, W, C;      // input, NHWC
+    int oH, oW, O;       // output, NHWC
+    int kH, kW, sY, sX, pT, pL, dY, dX;
+    int groups, Cg, Og;  // channels / outputs per group
+};
+
+struct PoolGeom {
+    int B, H, W, C, oH, oW;
+    int pH, pW, sY, sX, padY, padX;
+    int is_max;
+};
+
+struct SumInputs {
+    const void* ptr[4];
+    int dtype[4];
+    int is_unsigned[4];
+    int n;
+};
+
+// Fused residual: after the cell's own requantisation t, out = requant2(t + res)
+struct Residual {
+    const void* ptr;   // int8 NHWC, same shape as the output; nullptr = none
+    int is_unsigned;
+    QuantDev q2;
+};
+
+// CUDA-core direct convolution (any geometry, groups, dilation); weights OHWI int8.
+cudaError_t launch_conv_direct(const void* in, int in_unsigned, const int8_t* w, const ConvGeom& g,
+                               const QuantDev& q, const Residual& r, void* out, int out_dtype,
+                               cudaStream_t s);
+// Depthwise convolution, C % 16 == 0; weights re-laid as [kH][kW][C].
+cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc,
+                                  const ConvGeom& g, const QuantDev& q, void* out, cudaStream_t s);
+cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void* out, cudaStream_t s);
+cudaError_t launch_pool_i32(const void* in, const PoolGeom& g, void* out, cudaStream_t s);
+cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, const QuantDev& q,
+                                void* out, int out_dtype, cudaStream_t s);
+// Fully connected on CUDA cores: in [B][K], w [O][K] int8.
+cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, int B, int K, int O,
+                             const QuantDev& q, void* out, int out_dtype, cudaStream_t s);
+
+// ---- tensor-core implicit GEMM (tcgen05 kind::i8) ----
+struct IgemmPlan {
+    CUtensorMap tmA;      // activations: 2-D tiled [M][K] or 4-D im2col NHWC
+    CUtensorMap tmB;      // weights [N][Ktot], K-major
+    int a_im2col;         // 0: 2-D tiled, 1: im2col
+    int M, N;             // GEMM extents (output pixels, output channels)
+    int Cin, taps;        // K = taps * Cin, walked tap by tap
+    int BK;               // bytes of K per pipeline stage: 32, 64 or 128 (also the swizzle width)
+    int BN;               // tile N: 64, 128 or 256
+    int stages;
+    int a_unsigned;
+    // im2col geometry
+    int oW, oH, kW, sX, sY, pL, pT, dX, dY;
+    int grid;             // CTAs to launch
+    size_t smem_bytes;
+};
+// Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
+int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g,
+                    int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
+cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, void* out,
+                         int out_dtype, int* status_word, cudaStream_t s);
+
+}  // namespace n2d2b

@@ -1,0 +1,862 @@
+// C ABI (include/n2d2b.h) and the static executor behind it: a quantized network is a list of cells
+// in execution order, every tensor an NHWC buffer in HBM, every cell one kernel launch (a residual
+// sum is folded into the producing convolution's epilogue when the graph allows it).
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/n2d2b.h"
+#include "kernels.h"
+
+using namespace n2d2b;
+
+// ------------------------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                        \
+    do {                                                                                      \
+        cudaError_t e_ = (expr);                                                              \
+        if (e_ != cudaSuccess)                                                                \
+            return fail(N2D2B_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                  \
+    } while (0)
+
+// ------------------------------------------------------------------------------------ model
+enum CellType { CELL_CONV, CELL_FC, CELL_POOL, CELL_SUM, CELL_SCALING };
+enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED };
+
+struct TensorRec {
+    int C = 0, H = 0, W = 0;
+    int dtype = DT_I8;
+    int is_unsigned = 0;
+    int producer = -1;
+    int buffer = -1;      // index into Net::buffers, -1 for the network input
+    bool readable = true;
+    size_t elems() const { return (size_t)C * H * W; }
+    size_t bytes_per_image() const { return elems() * (dtype == DT_I32 ? 4 : 1); }
+};
+
+struct QuantHost {
+    int mode = SC_NONE, act = ACT_LINEAR, out_bits = 8, out_unsigned = 0, sat_thr = 0;
+    int is_clipped = 0;
+    int nb_channels = 0;
+    std::vector<int32_t> bias, p0, p1, clip_thr, clip_val;
+    std::vector<float> fscale, clip_f;
+    bool has_bias = false;
+    // device copy
+    void* d_blob = nullptr;
+    QuantDev dev{};
+};
+
+struct CellRec {
+    CellType type;
+    std::vector<int> inputs;
+    int output = -1;
+    n2d2b_conv_desc conv{};
+    n2d2b_pool_desc pool{};
+    ConvGeom geom{};
+    PoolGeom pgeom{};
+    QuantHost q;
+    std::vector<int8_t> weights;  // host copy, OHWI int8 (int4 already widened)
+    int8_t* d_weights = nullptr;
+    Engine engine = ENG_SIMT;
+    // fused residual sum
+    int residual = -1;
+    QuantHost q2;
+    bool has_q2 = false;
+    bool skipped = false;  // folded into another cell
+    // tensor-core plan
+    IgemmPlan plan{};
+    bool has_plan = false;
+    const void* plan_input = nullptr;
+};
+
+struct n2d2b_net {
+    int device = 0;
+    int num_sms = 148;
+    bool finalized = false;
+    int max_batch = 0;
+    unsigned flags = 0;
+    std::vector<TensorRec> tensors;
+    std::vector<CellRec> cells;
+    std::vector<void*> buffers;
+    std::vector<size_t> buffer_bytes;
+    int* d_status = nullptr;
+    int launches = 0;
+    const void* last_input = nullptr;
+    void* d_stage_in = nullptr;   // device staging of the host-buffer entry point
+    void* d_stage_out = nullptr;
+};
+
+static int validate_quant(const n2d2b_quant* qu, int channels, bool accumulators_have_bias, QuantHost& q,
+                          const int32_t* bias)
+{
+    if (!qu) return fail(N2D2B_ERR_INVALID, "quant must not be NULL");
+    const n2d2b_scaling& s = qu->scaling;
+    q.mode = s.mode;
+    q.act = qu->activation;
+    q.out_bits = qu->out_bits;
+    q.out_unsigned = qu->out_unsigned ? 1 : 0;
+    q.sat_thr = qu->saturation_threshold;
+    q.is_clipped = s.is_clipped ? 1 : 0;
+    q.nb_channels = channels;
+    if (q.mode < SC_NONE || q.mode > SC_DOUBLE_SHIFT) return fail(N2D2B_ERR_INVALID, "unknown scaling mode %d", q.mode);
+    if (q.act < ACT_LINEAR || q.act > ACT_SATURATION) return fail(N2D2B_ERR_INVALID, "unknown activation %d", q.act);
+    if (q.mode != SC_NONE) {
+        if (s.nb_channels != channels)
+            return fail(N2D2B_ERR_INVALID, "scaling has %d channels, the cell has %d outputs", s.nb_channels, channels);
+        // the integer modes throw on a non-quantized cell in the reference; a float-mode cell with
+        // nbBits == 0 would produce fractional values, which this integer path cannot carry
+        if (q.out_bits < 1 || q.out_bits > 8)
+            return fail(N2D2B_ERR_INVALID, "out_bits must be in 1..8 (got %d)", q.out_bits);
+    }
+    q.p0.assign(channels, 0);
+    q.p1.assign(channels, 0);
+    q.fscale.assign(channels, 1.0f);
+    q.clip_thr.assign(channels, 0);
+    q.clip_val.assign(channels, 0);
+    q.clip_f.assign(channels, 0.0f);
+    switch (q.mode) {
+    case SC_FLOAT_MULT:
+        if (!s.fscale) return fail(N2D2B_ERR_INVALID, "FLOAT_MULT scaling needs fscale");
+        for (int c = 0; c < channels; ++c) q.fscale[c] = s.fscale[c];
+        break;
+    case SC_FIXED_MULT16:
+    case SC_FIXED_MULT32:
+        if (!s.mult) return fail(N2D2B_ERR_INVALID, "FIXED_MULT scaling needs mult");
+        for (int c = 0; c < channels; ++c) {
+            const int f = s.frac_bits_per_channel ? s.frac_bits_per_channel[c] : s.frac_bits;
+            if (f < 0 || f > 62) return fail(N2D2B_ERR_INVALID, "fractional bits %d out of range", f);
+            q.p0[c] = s.mult[c];
+            q.p1[c] = f;
+        }
+        break;
+    case SC_SINGLE_SHIFT:
+        if (!s.shift0) return fail(N2D2B_ERR_INVALID, "SINGLE_SHIFT scaling needs shift0");
+        for (int c = 0; c < channels; ++c) {
+            if (s.shift0[c] > 62) return fail(N2D2B_ERR_INVALID, "shift %d out of range", s.shift0[c]);
+            q.p0[c] = s.shift0[c];
+        }
+        break;
+    case SC_DOUBLE_SHIFT:
+        if (!s.shift0 || !s.shift1) return fail(N2D2B_ERR_INVALID, "DOUBLE_SHIFT scaling needs shift0 and shift1");
+        for (int c = 0; c < channels; ++c) {
+            if (s.shift0[c] > 30 || s.shift1[c] > 62) return fail(N2D2B_ERR_INVALID, "shift pair out of range");
+            q.p0[c] = s.shift0[c];
+            q.p1[c] = s.shift1[c];
+        }
+        break;
+    default:
+        break;
+    }
+    // clipping only acts in the FLOAT and FIXED modes (CPU path of the reference)
+    if (q.is_clipped && (q.mode == SC_FLOAT_MULT || q.mode == SC_FIXED_MULT16 || q.mode == SC_FIXED_MULT32)) {
+        if (!s.clip) return fail(N2D2B_ERR_INVALID, "is_clipped needs clip values");
+        for (int c = 0; c < channels; ++c) {
+            const float cl = s.clip[c];
+            if (!std::isfinite(cl)) return fail(N2D2B_ERR_INVALID, "clip[%d] is not finite", c);
+            q.clip_f[c] = cl;
+            q.clip_thr[c] = (int32_t)(cl > 0.0f ? std::floor(cl) : std::ceil(cl));
+            q.clip_val[c] = (int32_t)std::round(cl);
+        }
+    } else {
+        q.is_clipped = 0;
+    }
+    q.has_bias = accumulators_have_bias && bias != nullptr;
+    q.bias.assign(channels, 0);
+    if (q.has_bias)
+        for (int c = 0; c < channels; ++c) q.bias[c] = bias[c];
+    return 0;
+}
+
+static void quant_output_type(const QuantHost& q, int* dtype, int* is_unsigned)
+{
+    if (q.mode == SC_NONE) {
+        *dtype = DT_I32;
+        *is_unsigned = 0;
+    } else {
+        *dtype = DT_I8;
+        *is_unsigned = q.out_unsigned;
+    }
+}
+
+static int upload_quant(QuantHost& q)
+{
+    const int C = q.nb_channels;
+    const size_t words = (size_t)C * 7;
+    std::vector<int32_t> blob(words);
+    memcpy(&blob[0 * C], q.bias.data(), C * 4);
+    memcpy(&blob[1 * C], q.p0.data(), C * 4);
+    memcpy(&blob[2 * C], q.p1.data(), C * 4);
+    memcpy(&blob[3 * C], q.fscale.data(), C * 4);
+    memcpy(&blob[4 * C], q.clip_thr.data(), C * 4);
+    memcpy(&blob[5 * C], q.clip_val.data(), C * 4);
+    memcpy(&blob[6 * C], q.clip_f.data(), C * 4);
+    CUDA_TRY(cudaMalloc(&q.d_blob, words * 4 + 16));
+    CUDA_TRY(cudaMemcpy(q.d_blob, blob.data(), words * 4, cudaMemcpyHostToDevice));
+    int32_t* d = (int32_t*)q.d_blob;
+    QuantDev& v = q.dev;
+    v.mode = q.mode;
+    v.act = q.act;
+    v.saturate = (q.mode != SC_NONE) ? 1 : 0;
+    if (q.out_unsigned) { v.out_lo = 0; v.out_hi = (1 << q.out_bits) - 1; }
+    else { v.out_lo = -(1 << (q.out_bits - 1)); v.out_hi = (1 << (q.out_bits - 1)) - 1; }
+    v.is_clipped = q.is_clipped;
+    v.sat_thr = q.sat_thr;
+    v.bias = q.has_bias ? d + 0 * C : nullptr;
+    v.p0 = d + 1 * C;
+    v.p1 = d + 2 * C;
+    v.fscale = (const float*)(d + 3 * C);
+    v.clip_thr = d + 4 * C;
+    v.clip_val = d + 5 * C;
+    v.clip_f = (const float*)(d + 6 * C);
+    return 0;
+}
+
+static void unpack_weights(const void* src, int weight_bits, size_t rows, size_t row_elems, std::vector<int8_t>& dst)
+{
+    dst.resize(rows * row_elems);
+    if (weight_bits == 8) {
+        memcpy(dst.data(), src, rows * row_elems);
+        return;
+    }
+    // packed int4: element 2i in the high nibble of byte i, element 2i+1 in the low nibble
+    const size_t row_bytes = (row_elems + 1) / 2;
+    const uint8_t* p = (const uint8_t*)src;
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t i = 0; i < row_elems; ++i) {
+            const uint8_t byte = p[r * row_bytes + i / 2];
+            const int nib = (i % 2 == 0) ? (byte >> 4) : (byte & 0xF);
+            dst[r * row_elems + i] = (int8_t)((nib & 8) ? nib - 16 : nib);
+        }
+}
+
+// ------------------------------------------------------------------------------------ C ABI
+extern "C" {
+
+const char* n2d2b_last_error(void) { return g_err; }
+int n2d2b_version(void) { return 100; }
+
+int n2d2b_device_count(void)
+{
+    int n = 0;
+    CUDA_TRY(cudaGetDeviceCount(&n));
+    return n;
+}
+
+int n2d2b_net_create(int device, n2d2b_net** net)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    *net = nullptr;
+    int n = 0;
+    CUDA_TRY(cudaGetDeviceCount(&n));
+    if (device < 0 || device >= n) return fail(N2D2B_ERR_INVALID, "device %d out of range (%d devices)", device, n);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(N2D2B_ERR_INVALID, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                    prop.minor);
+    n2d2b_net* p = new n2d2b_net();
+    p->device = device;
+    p->num_sms = prop.multiProcessorCount;
+    *net = p;
+    return 0;
+}
+
+void n2d2b_net_destroy(n2d2b_net* net)
+{
+    if (!net) return;
+    cudaSetDevice(net->device);
+    for (void* b : net->buffers) cudaFree(b);
+    for (CellRec& c : net->cells) {
+        cudaFree(c.d_weights);
+        cudaFree(c.q.d_blob);
+        cudaFree(c.q2.d_blob);
+    }
+    cudaFree(net->d_status);
+    cudaFree(net->d_stage_in);
+    cudaFree(net->d_stage_out);
+    delete net;
+}
+
+int n2d2b_net_set_input(n2d2b_net* net, int channels, int height, int width, int is_unsigned, int* tensor_id)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (net->finalized || !net->tensors.empty()) return fail(N2D2B_ERR_STATE, "input already set");
+    if (channels < 1 || height < 1 || width < 1) return fail(N2D2B_ERR_INVALID, "input dimensions must be positive");
+    TensorRec t;
+    t.C = channels; t.H = height; t.W = width; t.dtype = DT_I8; t.is_unsigned = is_unsigned ? 1 : 0;
+    net->tensors.push_back(t);
+    if (tensor_id) *tensor_id = 0;
+    return 0;
+}
+
+static int check_tensor(const n2d2b_net* net, int id)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (net->finalized) return fail(N2D2B_ERR_STATE, "the network is already finalized");
+    if (id < 0 || id >= (int)net->tensors.size()) return fail(N2D2B_ERR_INVALID, "unknown tensor id %d", id);
+    return 0;
+}
+
+static int conv_out(int in, int k, int stride, int pad0, int pad1, int dil)
+{
+    // ConvCell_Frame_Kernels.cpp:37-45
+    return (int)((in + pad0 + pad1 - dil * (k - 1) - 1 + stride) / (double)stride);
+}
+
+int n2d2b_net_add_conv(n2d2b_net* net, const n2d2b_conv_desc* d, const void* weights, const int32_t* bias,
+                       const n2d2b_quant* quant, int* tensor_id)
+{
+    if (!d || !weights) return fail(N2D2B_ERR_INVALID, "desc and weights must not be NULL");
+    if (int rc = check_tensor(net, d->input)) return rc;
+    const TensorRec in = net->tensors[d->input];
+    if (in.dtype != DT_I8) return fail(N2D2B_ERR_INVALID, "a convolution needs an 8-bit input tensor");
+    if (d->nb_outputs < 1 || d->kernel_h < 1 || d->kernel_w < 1 || d->stride_y < 1 || d->stride_x < 1
+        || d->dilation_y < 1 || d->dilation_x < 1 || d->groups < 1 || d->pad_top < 0 || d->pad_left < 0
+        || d->pad_bottom < 0 || d->pad_right < 0)
+        return fail(N2D2B_ERR_INVALID, "invalid convolution geometry");
+    if (in.C % d->groups || d->nb_outputs % d->groups)
+        return fail(N2D2B_ERR_INVALID, "groups (%d) must divide channels (%d) and outputs (%d)", d->groups, in.C,
+                    d->nb_outputs);
+    if (d->weight_bits != 8 && d->weight_bits != 4) return fail(N2D2B_ERR_INVALID, "weight_bits must be 8 or 4");
+    CellRec c;
+    c.type = CELL_CONV;
+    c.inputs = {d->input};
+    c.conv = *d;
+    ConvGeom& g = c.geom;
+    g.H = in.H; g.W = in.W; g.C = in.C;
+    g.O = d->nb_outputs;
+    g.kH = d->kernel_h; g.kW = d->kernel_w; g.sY = d->stride_y; g.sX = d->stride_x;
+    g.pT = d->pad_top; g.pL = d->pad_left; g.dY = d->dilation_y; g.dX = d->dilation_x;
+    g.groups = d->groups; g.Cg = in.C / d->groups; g.Og = d->nb_outputs / d->groups;
+    g.oH = conv_out(in.H, g.kH, g.sY, d->pad_top, d->pad_bottom, g.dY);
+    g.oW = conv_out(in.W, g.kW, g.sX, d->pad_left, d->pad_right, g.dX);
+    if (g.oH < 1 || g.oW < 1) return fail(N2D2B_ERR_INVALID, "convolution output would be empty");
+    if (int rc = validate_quant(quant, g.O, true, c.q, bias)) return rc;
+    unpack_weights(weights, d->weight_bits, (size_t)g.O, (size_t)g.kH * g.kW * g.Cg, c.weights);
+    TensorRec t;
+    t.C = g.O; t.H = g.oH; t.W = g.oW;
+    quant_output_type(c.q, &t.dtype, &t.is_unsigned);
+    t.producer = (int)net->cells.size();
+    c.output = (int)net->tensors.size();
+    net->tensors.push_back(t);
+    net->cells.push_back(std::move(c));
+    if (tensor_id) *tensor_id = net->cells.back().output;
+    return 0;
+}
+
+int n2d2b_net_add_fc(n2d2b_net* net, int input, int nb_outputs, int weight_bits, const void* weights,
+                     const int32_t* bias, const n2d2b_quant* quant, int* tensor_id)
+{
+    if (!weights) return fail(N2D2B_ERR_INVALID, "weights must not be NULL");
+    if (int rc = check_tensor(net, input)) return rc;
+    const TensorRec in = net->tensors[input];
+    if (in.dtype != DT_I8) return fail(N2D2B_ERR_INVALID, "a fully-connected cell needs an 8-bit input tensor");
+    if (nb_outputs < 1) return fail(N2D2B_ERR_INVALID, "nb_outputs must be positive");
+    if (weight_bits != 8 && weight_bits != 4) return fail(N2D2B_ERR_INVALID, "weight_bits must be 8 or 4");
+    CellRec c;
+    c.type = CELL_FC;
+    c.inputs = {input};
+    // a fully-connected cell is a 1x1 convolution over the flattened input
+    ConvGeom& g = c.geom;
+    g.H = 1; g.W = 1; g.C = (int)in.elems();
+    g.O = nb_outputs; g.kH = g.kW = 1; g.sY = g.sX = 1; g.pT = g.pL = 0; g.dY = g.dX = 1;
+    g.groups = 1; g.Cg = g.C; g.Og = g.O; g.oH = g.oW = 1;
+    if (int rc = validate_quant(quant, g.O, true, c.q, bias)) return rc;
+    unpack_weights(weights, weight_bits, (size_t)g.O, (size_t)g.C, c.weights);
+    TensorRec t;
+    t.C = g.O; t.H = 1; t.W = 1;
+    quant_output_type(c.q, &t.dtype, &t.is_unsigned);
+    t.producer = (int)net->cells.size();
+    c.output = (int)net->tensors.size();
+    net->tensors.push_back(t);
+    net->cells.push_back(std::move(c));
+    if (tensor_id) *tensor_id = net->cells.back().output;
+    return 0;
+}
+
+int n2d2b_net_add_pool(n2d2b_net* net, const n2d2b_pool_desc* d, int* tensor_id)
+{
+    if (!d) return fail(N2D2B_ERR_INVALID, "desc must not be NULL");
+    if (int rc = check_tensor(net, d->input)) return rc;
+    const TensorRec in = net->tensors[d->input];
+    if (d->pool_h < 1 || d->pool_w < 1 || d->stride_y < 1 || d->stride_x < 1 || d->pad_y < 0 || d->pad_x < 0
+        || (d->pooling != N2D2B_POOL_MAX && d->pooling != N2D2B_POOL_AVERAGE))
+        return fail(N2D2B_ERR_INVALID, "invalid pooling geometry");
+    CellRec c;
+    c.type = CELL_POOL;
+    c.inputs = {d->input};
+    c.pool = *d;
+    PoolGeom& g = c.pgeom;
+    g.H = in.H; g.W = in.W; g.C = in.C;
+    g.pH = d->pool_h; g.pW = d->pool_w; g.sY = d->stride_y; g.sX = d->stride_x; g.padY = d->pad_y; g.padX = d->pad_x;
+    g.is_max = (d->pooling == N2D2B_POOL_MAX);
+    // PoolCell.cpp:233-239
+    g.oH = (int)((in.H + 2 * d->pad_y - d->pool_h + d->stride_y) / (double)d->stride_y);
+    g.oW = (int)((in.W + 2 * d->pad_x - d->pool_w + d->stride_x) / (double)d->stride_x);
+    if (g.oH < 1 || g.oW < 1) return fail(N2D2B_ERR_INVALID, "pooling output would be empty");
+    TensorRec t;
+    t.C = in.C; t.H = g.oH; t.W = g.oW; t.dtype = in.dtype; t.is_unsigned = in.is_unsigned;
+    t.producer = (int)net->cells.size();
+    c.output = (int)net->tensors.size();
+    net->tensors.push_back(t);
+    net->cells.push_back(std::move(c));
+    if (tensor_id) *tensor_id = net->cells.back().output;
+    return 0;
+}
+
+int n2d2b_net_add_elemwise_sum(n2d2b_net* net, const int* inputs, int nb_inputs, const n2d2b_quant* quant,
+                               int* tensor_id)
+{
+    if (!inputs || nb_inputs < 1 || nb_inputs > 4)
+        return fail(N2D2B_ERR_INVALID, "an element-wise sum takes 1 to 4 inputs");
+    for (int k = 0; k < nb_inputs; ++k)
+        if (int rc = check_tensor(net, inputs[k])) return rc;
+    const TensorRec a = net->tensors[inputs[0]];
+    for (int k = 1; k < nb_inputs; ++k) {
+        const TensorRec& b = net->tensors[inputs[k]];
+        if (b.C != a.C || b.H != a.H || b.W != a.W)
+            return fail(N2D2B_ERR_INVALID, "element-wise inputs differ in shape");
+    }
+    CellRec c;
+    c.type = CELL_SUM;
+    c.inputs.assign(inputs, inputs + nb_inputs);
+    if (int rc = validate_quant(quant, a.C, false, c.q, nullptr)) return rc;
+    TensorRec t;
+    t.C = a.C; t.H = a.H; t.W = a.W;
+    quant_output_type(c.q, &t.dtype, &t.is_unsigned);
+    t.producer = (int)net->cells.size();
+    c.output = (int)net->tensors.size();
+    net->tensors.push_back(t);
+    net->cells.push_back(std::move(c));
+    if (tensor_id) *tensor_id = net->cells.back().output;
+    return 0;
+}
+
+int n2d2b_net_add_scaling(n2d2b_net* net, int input, const n2d2b_quant* quant, int* tensor_id)
+{
+    const int ids[1] = {input};
+    int rc = n2d2b_net_add_elemwise_sum(net, ids, 1, quant, tensor_id);
+    if (rc == 0) net->cells.back().type = CELL_SCALING;
+    return rc;
+}
+
+// ---- finalize -------------------------------------------------------------------------------
+static void fuse_residuals(n2d2b_net* net)
+{
+    const int nc = (int)net->cells.size();
+    std::vector<int> consumers(net->tensors.size(), 0);
+    for (const CellRec& c : net->cells)
+        for (int i : c.inputs) consumers[i]++;
+    for (int si = 0; si < nc; ++si) {
+        CellRec& s = net->cells[si];
+        if (s.type != CELL_SUM || s.inputs.size() != 2) continue;
+        if (s.q.mode == SC_NONE) continue;
+        int best = -1;
+        for (int k = 0; k < 2; ++k) {
+            const int t = s.inputs[k], other = s.inputs[1 - k];
+            const TensorRec& tt = net->tensors[t];
+            const TensorRec& ot = net->tensors[other];
+            if (tt.producer < 0 || consumers[t] != 1) continue;
+            CellRec& p = net->cells[tt.producer];
+            if (p.type != CELL_CONV || p.geom.groups != 1 || p.residual >= 0 || p.skipped) continue;
+            if (tt.dtype != DT_I8 || ot.dtype != DT_I8) continue;
+            if (ot.producer >= tt.producer) continue;  // the other operand must exist when p runs
+            if (best < 0 || tt.producer > net->tensors[s.inputs[best]].producer) best = k;
+        }
+        if (best < 0) continue;
+        const int t = s.inputs[best], other = s.inputs[1 - best];
+        CellRec& p = net->cells[net->tensors[t].producer];
+        p.residual = other;
+        p.q2 = s.q;
+        p.has_q2 = true;
+        p.inputs.push_back(other);  // keeps the operand alive for the buffer planner
+        net->tensors[t].readable = false;
+        net->tensors[t].buffer = -2;  // never materialised
+        p.output = s.output;
+        net->tensors[s.output].producer = net->tensors[t].producer;
+        s.skipped = true;
+        s.engine = ENG_FUSED;
+    }
+}
+
+static int plan_buffers(n2d2b_net* net)
+{
+    const bool keep_all = (net->flags & N2D2B_KEEP_ALL_OUTPUTS) != 0;
+    const int nt = (int)net->tensors.size();
+    std::vector<int> last_use(nt, -1);
+    for (int ci = 0; ci < (int)net->cells.size(); ++ci) {
+        const CellRec& c = net->cells[ci];
+        if (c.skipped) continue;
+        for (int i : c.inputs) last_use[i] = std::max(last_use[i], ci);
+    }
+    int final_tensor = -1;
+    for (int ci = (int)net->cells.size() - 1; ci >= 0; --ci)
+        if (!net->cells[ci].skipped) { final_tensor = net->cells[ci].output; break; }
+    std::vector<size_t> sizes;
+    std::vector<int> free_list;
+    for (int ci = 0; ci < (int)net->cells.size(); ++ci) {
+        CellRec& c = net->cells[ci];
+        if (c.skipped) continue;
+        TensorRec& t = net->tensors[c.output];
+        const size_t need = ((t.bytes_per_image() * (size_t)net->max_batch + 255) / 256) * 256 + 256;
+        int pick = -1;
+        if (!keep_all) {
+            for (size_t f = 0; f < free_list.size(); ++f) {
+                const int b = free_list[f];
+                if (sizes[b] >= need && (pick < 0 || sizes[b] < sizes[free_list[pick]])) pick = (int)f;
+            }
+        }
+        if (pick >= 0) {
+            t.buffer = free_list[pick];
+            free_list.erase(free_list.begin() + pick);
+        } else {
+            t.buffer = (int)sizes.size();
+            sizes.push_back(need);
+        }
+        if (!keep_all) {
+            // release the inputs that die with this cell (never the network input or the final output)
+            for (int i : c.inputs) {
+                if (i == 0 || i == final_tensor) continue;
+                if (last_use[i] == ci && net->tensors[i].buffer >= 0) {
+                    if (std::find(free_list.begin(), free_list.end(), net->tensors[i].buffer) == free_list.end())
+                        free_list.push_back(net->tensors[i].buffer);
+                }
+            }
+            // a tensor nobody reads (other than the final one) can be reused at once
+            if (last_use[c.output] < 0 && c.output != final_tensor) free_list.push_back(t.buffer);
+        }
+    }
+    if (!keep_all)
+        for (int i = 1; i < nt; ++i)
+            if (net->tensors[i].buffer >= 0 && i != final_tensor) net->tensors[i].readable = false;
+    net->buffers.assign(sizes.size(), nullptr);
+    net->buffer_bytes = sizes;
+    for (size_t b = 0; b < sizes.size(); ++b) {
+        CUDA_TRY(cudaMalloc(&net->buffers[b], sizes[b]));
+        CUDA_TRY(cudaMemset(net->buffers[b], 0, sizes[b]));
+    }
+    return 0;
+}
+
+static void* tensor_ptr(const n2d2b_net* net, int id, const void* d_input)
+{
+    if (id == 0) return (void*)d_input;
+    const TensorRec& t = net->tensors[id];
+    return t.buffer >= 0 ? net->buffers[t.buffer] : nullptr;
+}
+
+static int final_tensor_of(const n2d2b_net* net)
+{
+    for (int ci = (int)net->cells.size() - 1; ci >= 0; --ci)
+        if (!net->cells[ci].skipped) return net->cells[ci].output;
+    return -1;
+}
+
+int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (net->finalized) return fail(N2D2B_ERR_STATE, "the network is already finalized");
+    if (net->cells.empty()) return fail(N2D2B_ERR_STATE, "the network has no cells");
+    if (max_batch < 1) return fail(N2D2B_ERR_INVALID, "max_batch must be positive");
+    CUDA_TRY(cudaSetDevice(net->device));
+    net->max_batch = max_batch;
+    net->flags = flags;
+    if (!(flags & N2D2B_NO_FUSION)) fuse_residuals(net);
+    if (int rc = plan_buffers(net)) return rc;
+    CUDA_TRY(cudaMalloc(&net->d_status, 64));
+    CUDA_TRY(cudaMemset(net->d_status, 0, 64));
+    net->launches = 0;
+    for (CellRec& c : net->cells) {
+        if (c.skipped) continue;
+        net->launches++;
+        if (c.type == CELL_POOL) { c.engine = ENG_POOL; continue; }
+        if (int rc = upload_quant(c.q)) return rc;
+        if (c.has_q2)
+            if (int rc = upload_quant(c.q2)) return rc;
+        if (c.type == CELL_SUM || c.type == CELL_SCALING) { c.engine = ENG_SUM; continue; }
+        // conv / fc: choose the kernel family and lay the weights out for it
+        const ConvGeom& g = c.geom;
+        const bool depthwise = (c.type == CELL_CONV && g.groups == g.C && g.Cg == 1 && g.Og == 1 && g.C % 16 == 0
+                                && g.groups > 1 && c.residual < 0
+                                && net->tensors[c.output].dtype == DT_I8);
+        std::vector<int8_t> laid = c.weights;
+        if (depthwise) {
+            c.engine = ENG_DEPTHWISE;
+            // [C][kH][kW] -> [kH][kW][C] so that 16 channels of a tap are one 128-bit load
+            const int taps = g.kH * g.kW;
+            for (int ch = 0; ch < g.C; ++ch)
+                for (int t = 0; t < taps; ++t) laid[(size_t)t * g.C + ch] = c.weights[(size_t)ch * taps + t];
+        } else {
+            c.engine = ENG_SIMT;
+        }
+        CUDA_TRY(cudaMalloc((void**)&c.d_weights, laid.size() + 256));
+        CUDA_TRY(cudaMemset(c.d_weights, 0, laid.size() + 256));
+        CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
+        if (!depthwise && !(flags & N2D2B_FORCE_SIMT) && g.groups == 1 && g.C % 16 == 0) {
+            ConvGeom gb = g;
+            gb.B = max_batch;
+            const char* why = "";
+            const void* in_ptr = tensor_ptr(net, c.inputs[0], nullptr);
+            // the network input pointer is only known at forward time; plan against a placeholder
+            // that is re-encoded on first use
+            static char placeholder[16] __attribute__((aligned(16)));
+            const void* enc_ptr = in_ptr ? in_ptr : (const void*)placeholder;
+            if (igemm_make_plan(&c.plan, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
+                                (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why) == 0) {
+                c.engine = ENG_TCGEN05;
+                c.has_plan = true;
+                c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
+            }
+        }
+    }
+    CUDA_TRY(cudaMalloc(&net->d_stage_in, net->tensors[0].bytes_per_image() * (size_t)max_batch + 256));
+    CUDA_TRY(cudaMalloc(&net->d_stage_out,
+                        net->tensors[final_tensor_of(net)].bytes_per_image() * (size_t)max_batch + 256));
+    net->finalized = true;
+    return 0;
+}
+
+// ---- forward --------------------------------------------------------------------------------
+static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, cudaStream_t s)
+{
+    const void* in0 = tensor_ptr(net, c.inputs[0], d_input);
+    void* out = tensor_ptr(net, c.output, d_input);
+    const TensorRec& tin = net->tensors[c.inputs[0]];
+    const TensorRec& tout = net->tensors[c.output];
+    if (!in0 || !out) return fail(N2D2B_ERR_STATE, "internal: tensor without a buffer");
+    Residual r{};
+    if (c.residual >= 0) {
+        r.ptr = tensor_ptr(net, c.residual, d_input);
+        r.is_unsigned = net->tensors[c.residual].is_unsigned;
+        r.q2 = c.q2.dev;
+    }
+    switch (c.engine) {
+    case ENG_TCGEN05: {
+        if (c.plan_input != in0) {
+            ConvGeom gb = c.geom;
+            gb.B = net->max_batch;
+            const char* why = "";
+            if (igemm_make_plan(&c.plan, in0, c.d_weights, gb, tin.is_unsigned,
+                                (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why))
+                return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
+            c.plan_input = in0;
+        }
+        IgemmPlan p = c.plan;
+        p.M = batch * c.geom.oH * c.geom.oW;
+        CUDA_TRY(launch_igemm(p, c.q.dev, r, out, tout.dtype, net->d_status, s));
+        break;
+    }
+    case ENG_SIMT: {
+        ConvGeom g = c.geom;
+        g.B = batch;
+        if (c.type == CELL_FC && c.residual < 0)
+            CUDA_TRY(launch_fc_direct(in0, tin.is_unsigned, c.d_weights, batch, g.C, g.O, c.q.dev, out, tout.dtype, s));
+        else
+            CUDA_TRY(launch_conv_direct(in0, tin.is_unsigned, c.d_weights, g, c.q.dev, r, out, tout.dtype, s));
+        break;
+    }
+    case ENG_DEPTHWISE: {
+        ConvGeom g = c.geom;
+        g.B = batch;
+        CUDA_TRY(launch_conv_depthwise(in0, tin.is_unsigned, c.d_weights, g, c.q.dev, out, s));
+        break;
+    }
+    case ENG_POOL: {
+        PoolGeom g = c.pgeom;
+        g.B = batch;
+        if (tin.dtype == DT_I32) CUDA_TRY(launch_pool_i32(in0, g, out, s));
+        else CUDA_TRY(launch_pool(in0, tin.is_unsigned, g, out, s));
+        break;
+    }
+    case ENG_SUM: {
+        SumInputs ins{};
+        ins.n = (int)c.inputs.size();
+        for (int k = 0; k < ins.n; ++k) {
+            ins.ptr[k] = tensor_ptr(net, c.inputs[k], d_input);
+            ins.dtype[k] = net->tensors[c.inputs[k]].dtype;
+            ins.is_unsigned[k] = net->tensors[c.inputs[k]].is_unsigned;
+        }
+        CUDA_TRY(launch_elemwise_sum(ins, (size_t)batch * tout.H * tout.W, tout.C, c.q.dev, out, tout.dtype, s));
+        break;
+    }
+    case ENG_FUSED:
+        break;
+    }
+    return 0;
+}
+
+static int forward_impl(n2d2b_net* net, const void* d_input, int batch, void* d_output, cudaStream_t s, float* ms,
+                        int nb_cells)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "forward before finalize");
+    if (batch < 0 || batch > net->max_batch)
+        return fail(N2D2B_ERR_TOO_LARGE, "batch %d exceeds the finalized maximum %d", batch, net->max_batch);
+    if (batch == 0) return 0;
+    if (!d_input) return fail(N2D2B_ERR_INVALID, "d_input must not be NULL");
+    CUDA_TRY(cudaSetDevice(net->device));
+    std::vector<cudaEvent_t> ev;
+    if (ms) {
+        if (nb_cells != (int)net->cells.size())
+            return fail(N2D2B_ERR_INVALID, "ms must have one entry per cell (%d)", (int)net->cells.size());
+        ev.resize(net->cells.size() + 1);
+        for (auto& e : ev) CUDA_TRY(cudaEventCreate(&e));
+        CUDA_TRY(cudaEventRecord(ev[0], s));
+    }
+    for (size_t ci = 0; ci < net->cells.size(); ++ci) {
+        CellRec& c = net->cells[ci];
+        if (!c.skipped)
+            if (int rc = run_cell(net, c, d_input, batch, s)) return rc;
+        if (ms) CUDA_TRY(cudaEventRecord(ev[ci + 1], s));
+    }
+    const int ft = final_tensor_of(net);
+    if (d_output) {
+        const TensorRec& t = net->tensors[ft];
+        CUDA_TRY(cudaMemcpyAsync(d_output, tensor_ptr(net, ft, d_input), t.bytes_per_image() * (size_t)batch,
+                                 cudaMemcpyDeviceToDevice, s));
+    }
+    net->last_input = d_input;
+    if (ms) {
+        CUDA_TRY(cudaStreamSynchronize(s));
+        for (size_t ci = 0; ci < net->cells.size(); ++ci) CUDA_TRY(cudaEventElapsedTime(&ms[ci], ev[ci], ev[ci + 1]));
+        for (auto& e : ev) cudaEventDestroy(e);
+    }
+    return 0;
+}
+
+static int check_status(n2d2b_net* net)
+{
+    int st = 0;
+    CUDA_TRY(cudaMemcpy(&st, net->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(net->d_status, 0, sizeof(int));
+        return fail(N2D2B_ERR_TIMEOUT, "a tensor-core kernel gave up waiting on a pipeline barrier (role %d)", st);
+    }
+    return 0;
+}
+
+int n2d2b_net_forward(n2d2b_net* net, const void* d_input, int batch, void* d_output, n2d2b_stream stream)
+{
+    return forward_impl(net, d_input, batch, d_output, (cudaStream_t)stream, nullptr, 0);
+}
+
+int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_output, float* ms, int nb_cells,
+                      n2d2b_stream stream)
+{
+    if (!ms) return fail(N2D2B_ERR_INVALID, "ms must not be NULL");
+    if (int rc = forward_impl(net, d_input, batch, d_output, (cudaStream_t)stream, ms, nb_cells)) return rc;
+    return check_status(net);
+}
+
+int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "forward before finalize");
+    if (batch < 0 || batch > net->max_batch)
+        return fail(N2D2B_ERR_TOO_LARGE, "batch %d exceeds the finalized maximum %d", batch, net->max_batch);
+    if (batch == 0) return 0;
+    if (!h_input || !h_output) return fail(N2D2B_ERR_INVALID, "host buffers must not be NULL");
+    CUDA_TRY(cudaSetDevice(net->device));
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t in_bytes = net->tensors[0].bytes_per_image() * (size_t)batch;
+    const int ft = final_tensor_of(net);
+    const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
+    void* d_in = net->d_stage_in;
+    void* d_out = net->d_stage_out;
+    CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
+    if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0)) return rc;
+    CUDA_TRY(cudaMemcpyAsync(h_output, d_out, out_bytes, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return check_status(net);
+}
+
+int n2d2b_net_num_tensors(const n2d2b_net* net) { return net ? (int)net->tensors.size() : fail(N2D2B_ERR_INVALID, "net must not be NULL"); }
+
+int n2d2b_net_tensor_info(const n2d2b_net* net, int id, n2d2b_tensor_info* info)
+{
+    if (!net || !info) return fail(N2D2B_ERR_INVALID, "net and info must not be NULL");
+    if (id < 0 || id >= (int)net->tensors.size()) return fail(N2D2B_ERR_INVALID, "unknown tensor id %d", id);
+    const TensorRec& t = net->tensors[id];
+    info->channels = t.C; info->height = t.H; info->width = t.W;
+    info->dtype = t.dtype; info->is_unsigned = t.is_unsigned; info->producer = t.producer;
+    info->readable = (t.readable && (id == 0 || t.buffer >= 0 || !net->finalized)) ? 1 : 0;
+    return 0;
+}
+
+int n2d2b_net_read_tensor(n2d2b_net* net, int id, int batch, void* host_dst, size_t bytes)
+{
+    if (!net || !host_dst) return fail(N2D2B_ERR_INVALID, "net and host_dst must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "read before finalize");
+    if (id < 0 || id >= (int)net->tensors.size()) return fail(N2D2B_ERR_INVALID, "unknown tensor id %d", id);
+    const TensorRec& t = net->tensors[id];
+    if (batch < 0 || batch > net->max_batch) return fail(N2D2B_ERR_TOO_LARGE, "batch out of range");
+    const size_t need = t.bytes_per_image() * (size_t)batch;
+    if (bytes < need) return fail(N2D2B_ERR_INVALID, "destination holds %zu bytes, the tensor needs %zu", bytes, need);
+    const void* src = tensor_ptr(net, id, net->last_input);
+    if (!src || !t.readable) return fail(N2D2B_ERR_STATE, "tensor %d is not kept (finalize with N2D2B_KEEP_ALL_OUTPUTS)", id);
+    CUDA_TRY(cudaSetDevice(net->device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpy(host_dst, src, need, cudaMemcpyDeviceToHost));
+    return check_status(net);
+}
+
+int n2d2b_net_launches_per_forward(const n2d2b_net* net)
+{
+    if (!net || !net->finalized) return fail(N2D2B_ERR_STATE, "the network is not finalized");
+    return net->launches;
+}
+
+const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
+{
+    if (!net || cell < 0 || cell >= (int)net->cells.size()) return "";
+    switch (net->cells[cell].engine) {
+    case ENG_TCGEN05: return "tcgen05";
+    case ENG_SIMT: return "simt";
+    case ENG_DEPTHWISE: return "depthwise";
+    case ENG_POOL: return "pool";
+    case ENG_SUM: return "sum";
+    case ENG_FUSED: return "fused";
+    }
+    return "";
+}
+
+int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t nb_pixels, const n2d2b_quant* quant,
+                            n2d2b_stream stream)
+{
+    if (!quant) return fail(N2D2B_ERR_INVALID, "quant must not be NULL");
+    if (!d_in || !d_out) return fail(N2D2B_ERR_INVALID, "device buffers must not be NULL");
+    if (quant->scaling.mode == SC_NONE) return fail(N2D2B_ERR_INVALID, "a NONE scaling has nothing to do");
+    CUDA_TRY(cudaSetDevice(device));
+    QuantHost q;
+    if (int rc = validate_quant(quant, quant->scaling.nb_channels, false, q, nullptr)) return rc;
+    if (int rc = upload_quant(q)) return rc;
+    SumInputs ins{};
+    ins.n = 1;
+    ins.ptr[0] = d_in;
+    ins.dtype[0] = DT_I32;
+    cudaError_t e = launch_elemwise_sum(ins, nb_pixels, q.nb_channels, q.dev, d_out, DT_I8, (cudaStream_t)stream);
+    cudaError_t e2 = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(q.d_blob);
+    if (e != cudaSuccess) return fail(N2D2B_ERR_CUDA, "scaling kernel launch failed: %s", cudaGetErrorString(e));
+    if (e2 != cudaSuccess) return fail(N2D2B_ERR_CUDA, "scaling kernel failed: %s", cudaGetErrorString(e2));
+    return 0;
+}
+
+}  // extern "C"

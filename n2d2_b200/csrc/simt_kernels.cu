@@ -1,0 +1,385 @@
+// CUDA-core kernels of the quantized integer path: the layers that are not dense contractions
+// (depthwise convolution, pooling, element-wise sum, stand-alone rescale) plus a direct convolution
+// and a direct fully-connected kernel that accept any geometry.  Every kernel ends in the same
+// requantisation epilogue (common.cuh), so no float tensor or separate Scaling pass exists between
+// layers.  Activations are NHWC int8 (signed or unsigned per tensor) or int32.
+#include "kernels.h"
+
+namespace n2d2b {
+
+static inline unsigned grid_for(size_t n, int block)
+{
+    size_t g = (n + block - 1) / block;
+    const size_t cap = 148u * 32u * 64u;
+    return (unsigned)(g < cap ? (g ? g : 1) : cap);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_out(void* out, size_t i, int v);
+template <>
+__device__ __forceinline__ void store_out<int8_t>(void* out, size_t i, int v)
+{
+    ((int8_t*)out)[i] = (int8_t)v;  // the low byte is the value for both u8 and s8 tensors
+}
+template <>
+__device__ __forceinline__ void store_out<int32_t>(void* out, size_t i, int v)
+{
+    ((int32_t*)out)[i] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Direct convolution: one thread per output value, output channel fastest (NHWC).  Replaces the
+// reference's ConvCell_Frame_Kernels::forward + forwardBias + Scaling + activation for geometries
+// the tensor-core kernel does not take (few input channels, groups, dilation).
+// ---------------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void conv_direct_kernel(const uint8_t* __restrict__ in, int in_unsigned,
+                                   const int8_t* __restrict__ w, ConvGeom g, QuantDev q,
+                                   Residual r, void* __restrict__ out, size_t total)
+{
+    const bool vec4 = (g.Cg % 4 == 0);
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int o = (int)(idx % g.O);
+        size_t p = idx / g.O;
+        const int ox = (int)(p % g.oW); p /= g.oW;
+        const int oy = (int)(p % g.oH);
+        const int b = (int)(p / g.oH);
+        const int grp = o / g.Og;
+        const int iy0 = oy * g.sY - g.pT, ix0 = ox * g.sX - g.pL;
+        const int8_t* wo = w + (size_t)o * g.kH * g.kW * g.Cg;
+        int acc = 0;
+        for (int ky = 0; ky < g.kH; ++ky) {
+            const int iy = iy0 + ky * g.dY;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.kW; ++kx) {
+                const int ix = ix0 + kx * g.dX;
+                if (ix < 0 || ix >= g.W) continue;
+                const uint8_t* ip = in + (((size_t)b * g.H + iy) * g.W + ix) * g.C + (size_t)grp * g.Cg;
+                const int8_t* wp = wo + (size_t)(ky * g.kW + kx) * g.Cg;
+                if (vec4 && ((((uintptr_t)ip) | ((uintptr_t)wp)) & 3) == 0) {
+                    const unsigned* ip4 = (const unsigned*)ip;
+                    const int* wp4 = (const int*)wp;
+                    if (in_unsigned)
+                        for (int c = 0; c < g.Cg / 4; ++c) acc = dp4a_us(ip4[c], wp4[c], acc);
+                    else
+                        for (int c = 0; c < g.Cg / 4; ++c) acc = dp4a_ss((int)ip4[c], wp4[c], acc);
+                } else {
+                    for (int c = 0; c < g.Cg; ++c)
+                        acc += load_i8(ip, c, in_unsigned) * (int)wp[c];
+                }
+            }
+        }
+        long long x = (long long)acc + (q.bias ? (long long)q.bias[o] : 0ll);
+        int y = requant64(x, o, q);
+        if (r.ptr) {
+            const long long u = (long long)y + (long long)load_i8(r.ptr, idx, r.is_unsigned);
+            y = requant64(u, o, r.q2);
+        }
+        store_out<OutT>(out, idx, y);
+    }
+}
+
+cudaError_t launch_conv_direct(const void* in, int in_unsigned, const int8_t* w, const ConvGeom& g,
+                               const QuantDev& q, const Residual& r, void* out, int out_dtype,
+                               cudaStream_t s)
+{
+    const size_t total = (size_t)g.B * g.oH * g.oW * g.O;
+    if (total == 0) return cudaSuccess;
+    const int block = 256;
+    const unsigned grid = grid_for(total, block);
+    if (out_dtype == DT_I8)
+        conv_direct_kernel<int8_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, g, q, r, out, total);
+    else
+        conv_direct_kernel<int32_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, g, q, r, out, total);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Depthwise convolution: HBM-bound (one multiply-add per loaded byte and tap), so it stays on the
+// CUDA cores.  One thread owns 16 consecutive channels of one output pixel: every tap is one
+// 128-bit load of the input and one of the weights, the result one 128-bit store.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack16(const uint4& v, bool is_unsigned, int* x)
+{
+    const unsigned wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned byte = (wds[i] >> (8 * j)) & 0xffu;
+            x[i * 4 + j] = is_unsigned ? (int)byte : (int)(int8_t)byte;
+        }
+}
+
+__device__ __forceinline__ uint4 pack16(const int* y)
+{
+    unsigned wds[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        wds[i] = ((unsigned)y[i * 4] & 0xffu) | (((unsigned)y[i * 4 + 1] & 0xffu) << 8)
+               | (((unsigned)y[i * 4 + 2] & 0xffu) << 16) | (((unsigned)y[i * 4 + 3] & 0xffu) << 24);
+    return make_uint4(wds[0], wds[1], wds[2], wds[3]);
+}
+
+__global__ void conv_depthwise_kernel(const uint8_t* __restrict__ in, int in_unsigned,
+                                      const int8_t* __restrict__ w_hwc, ConvGeom g, QuantDev q,
+                                      uint8_t* __restrict__ out, size_t total_vec)
+{
+    const int cv = g.C / 16;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int c16 = (int)(idx % cv);
+        size_t p = idx / cv;
+        const int ox = (int)(p % g.oW); p /= g.oW;
+        const int oy = (int)(p % g.oH);
+        const int b = (int)(p / g.oH);
+        const int c0 = c16 * 16;
+        int acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0;
+        const int iy0 = oy * g.sY - g.pT, ix0 = ox * g.sX - g.pL;
+        for (int ky = 0; ky < g.kH; ++ky) {
+            const int iy = iy0 + ky * g.dY;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.kW; ++kx) {
+                const int ix = ix0 + kx * g.dX;
+                if (ix < 0 || ix >= g.W) continue;
+                const uint4 xv = *(const uint4*)(in + (((size_t)b * g.H + iy) * g.W + ix) * g.C + c0);
+                const uint4 wv = __ldg((const uint4*)(w_hwc + (size_t)(ky * g.kW + kx) * g.C + c0));
+                int xs[16], ws[16];
+                unpack16(xv, in_unsigned != 0, xs);
+                unpack16(wv, false, ws);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] += xs[i] * ws[i];
+            }
+        }
+        int y[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const long long x = (long long)acc[i] + (q.bias ? (long long)q.bias[c0 + i] : 0ll);
+            y[i] = requant64(x, c0 + i, q);
+        }
+        *(uint4*)(out + idx * 16) = pack16(y);
+    }
+}
+
+cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc,
+                                  const ConvGeom& g, const QuantDev& q, void* out, cudaStream_t s)
+{
+    const size_t total = (size_t)g.B * g.oH * g.oW * (g.C / 16);
+    if (total == 0) return cudaSuccess;
+    const int block = 256;
+    conv_depthwise_kernel<<<grid_for(total, block), block, 0, s>>>((const uint8_t*)in, in_unsigned, w_hwc, g, q,
+                                                                   (uint8_t*)out, total);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pooling (PoolCell): max over the in-image taps (0 for an all-padding window); average with the
+// full window as divisor and truncation toward zero, as the reference's quantized PoolCell does.
+// Vector path: 16 channels per thread when C % 16 == 0 and the tensor is int8.
+// ---------------------------------------------------------------------------------------------
+__global__ void pool_vec_kernel(const uint8_t* __restrict__ in, int in_unsigned, PoolGeom g,
+                                uint8_t* __restrict__ out, size_t total_vec)
+{
+    const int cv = g.C / 16;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int c16 = (int)(idx % cv);
+        size_t p = idx / cv;
+        const int ox = (int)(p % g.oW); p /= g.oW;
+        const int oy = (int)(p % g.oH);
+        const int b = (int)(p / g.oH);
+        const int iy0 = oy * g.sY - g.padY, ix0 = ox * g.sX - g.padX;
+        int v[16];
+        bool valid = false;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0;
+        for (int ky = 0; ky < g.pH; ++ky) {
+            const int iy = iy0 + ky;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.pW; ++kx) {
+                const int ix = ix0 + kx;
+                if (ix < 0 || ix >= g.W) continue;
+                const uint4 xv = *(const uint4*)(in + (((size_t)b * g.H + iy) * g.W + ix) * g.C + c16 * 16);
+                int xs[16];
+                unpack16(xv, in_unsigned != 0, xs);
+                if (g.is_max) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = (!valid || xs[i] > v[i]) ? xs[i] : v[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] += xs[i];
+                }
+                valid = true;
+            }
+        }
+        if (!g.is_max) {
+            const int count = g.pH * g.pW;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v[i] / count;  // C division truncates toward zero
+        }
+        *(uint4*)(out + idx * 16) = pack16(v);
+    }
+}
+
+template <typename ElemT>
+__global__ void pool_scalar_kernel(const void* __restrict__ in, int in_unsigned, PoolGeom g,
+                                   void* __restrict__ out, size_t total)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % g.C);
+        size_t p = idx / g.C;
+        const int ox = (int)(p % g.oW); p /= g.oW;
+        const int oy = (int)(p % g.oH);
+        const int b = (int)(p / g.oH);
+        const int iy0 = oy * g.sY - g.padY, ix0 = ox * g.sX - g.padX;
+        long long v = 0;
+        bool valid = false;
+        for (int ky = 0; ky < g.pH; ++ky) {
+            const int iy = iy0 + ky;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.pW; ++kx) {
+                const int ix = ix0 + kx;
+                if (ix < 0 || ix >= g.W) continue;
+                const size_t ii = (((size_t)b * g.H + iy) * g.W + ix) * g.C + c;
+                long long x;
+                if (sizeof(ElemT) == 4) x = ((const int32_t*)in)[ii];
+                else x = load_i8(in, ii, in_unsigned != 0);
+                if (g.is_max) v = (!valid || x > v) ? x : v;
+                else v += x;
+                valid = true;
+            }
+        }
+        if (!g.is_max) v = v / (long long)(g.pH * g.pW);
+        if (sizeof(ElemT) == 4) ((int32_t*)out)[idx] = (int32_t)v;
+        else ((int8_t*)out)[idx] = (int8_t)v;
+    }
+}
+
+cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void* out, cudaStream_t s)
+{
+    // int8 tensors; int32 tensors go through launch_pool_i32
+    const int block = 256;
+    if (g.C % 16 == 0) {
+        const size_t total = (size_t)g.B * g.oH * g.oW * (g.C / 16);
+        if (total == 0) return cudaSuccess;
+        pool_vec_kernel<<<grid_for(total, block), block, 0, s>>>((const uint8_t*)in, in_unsigned, g, (uint8_t*)out, total);
+    } else {
+        const size_t total = (size_t)g.B * g.oH * g.oW * g.C;
+        if (total == 0) return cudaSuccess;
+        pool_scalar_kernel<int8_t><<<grid_for(total, block), block, 0, s>>>(in, in_unsigned, g, out, total);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pool_i32(const void* in, const PoolGeom& g, void* out, cudaStream_t s)
+{
+    const size_t total = (size_t)g.B * g.oH * g.oW * g.C;
+    if (total == 0) return cudaSuccess;
+    pool_scalar_kernel<int32_t><<<grid_for(total, 256), 256, 0, s>>>(in, 0, g, out, total);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Element-wise sum of up to four tensors (ElemWiseCell, Sum, unit weights) followed by the cell's
+// own requantisation; with a single input it is the stand-alone ScalingCell.
+// ---------------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void elemwise_sum_kernel(SumInputs ins, size_t total, int C, QuantDev q, void* __restrict__ out)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % C);
+        long long x = 0;
+        for (int k = 0; k < ins.n; ++k) {
+            if (ins.dtype[k] == DT_I32) x += ((const int32_t*)ins.ptr[k])[idx];
+            else x += load_i8(ins.ptr[k], idx, ins.is_unsigned[k] != 0);
+        }
+        if (q.bias) x += q.bias[c];
+        store_out<OutT>(out, idx, requant64(x, c, q));
+    }
+}
+
+// Fast path: two int8 inputs, int8 output, 16 values per thread.
+__global__ void elemwise_sum2_vec_kernel(const uint8_t* __restrict__ a, int a_unsigned,
+                                         const uint8_t* __restrict__ b, int b_unsigned, size_t total_vec,
+                                         int C, QuantDev q, uint8_t* __restrict__ out)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const uint4 av = *(const uint4*)(a + idx * 16);
+        const uint4 bv = *(const uint4*)(b + idx * 16);
+        int xa[16], xb[16], y[16];
+        unpack16(av, a_unsigned != 0, xa);
+        unpack16(bv, b_unsigned != 0, xb);
+        const int c0 = (int)((idx * 16) % C);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = requant64((long long)xa[i] + xb[i], c0 + i, q);
+        *(uint4*)(out + idx * 16) = pack16(y);
+    }
+}
+
+cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, const QuantDev& q,
+                                void* out, int out_dtype, cudaStream_t s)
+{
+    const size_t total = pixels * (size_t)C;
+    if (total == 0) return cudaSuccess;
+    const int block = 256;
+    if (ins.n == 2 && out_dtype == DT_I8 && ins.dtype[0] == DT_I8 && ins.dtype[1] == DT_I8 && C % 16 == 0
+        && !q.bias) {
+        elemwise_sum2_vec_kernel<<<grid_for(total / 16, block), block, 0, s>>>(
+            (const uint8_t*)ins.ptr[0], ins.is_unsigned[0], (const uint8_t*)ins.ptr[1], ins.is_unsigned[1],
+            total / 16, C, q, (uint8_t*)out);
+    } else if (out_dtype == DT_I8) {
+        elemwise_sum_kernel<int8_t><<<grid_for(total, block), block, 0, s>>>(ins, total, C, q, out);
+    } else {
+        elemwise_sum_kernel<int32_t><<<grid_for(total, block), block, 0, s>>>(ins, total, C, q, out);
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fully connected on CUDA cores: one warp per (image, output), lanes stride over K, shuffle-reduce.
+// ---------------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void fc_direct_kernel(const uint8_t* __restrict__ in, int in_unsigned,
+                                 const int8_t* __restrict__ w, int B, int K, int O, QuantDev q,
+                                 void* __restrict__ out)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t idx = warp; idx < (size_t)B * O; idx += nwarps) {
+        const int o = (int)(idx % O);
+        const int b = (int)(idx / O);
+        const uint8_t* ip = in + (size_t)b * K;
+        const int8_t* wp = w + (size_t)o * K;
+        int acc = 0;
+        for (int k = lane; k < K; k += 32) acc += load_i8(ip, k, in_unsigned != 0) * (int)wp[k];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+            const long long x = (long long)acc + (q.bias ? (long long)q.bias[o] : 0ll);
+            store_out<OutT>(out, idx, requant64(x, o, q));
+        }
+    }
+}
+
+cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, int B, int K, int O,
+                             const QuantDev& q, void* out, int out_dtype, cudaStream_t s)
+{
+    const size_t total = (size_t)B * O;
+    if (total == 0) return cudaSuccess;
+    const int block = 256;
+    const unsigned grid = grid_for(total * 32, block);
+    if (out_dtype == DT_I8)
+        fc_direct_kernel<int8_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, B, K, O, q, out);
+    else
+        fc_direct_kernel<int32_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, B, K, O, q, out);
+    return cudaGetLastError();
+}
+
+}  // namespace n2d2b
