@@ -15,7 +15,7 @@ int n2d2o_num_threads(void);
     void n2d2o_conv_##S(const T* in, int inW, int inH, int inC, int B, const T* w, int kW, int kH, \
                         int wC, int O, const uint8_t* maps, int nbGroups, int strideX, int strideY, \
                         int padL, int padT, int padR, int padB, int dilX, int dilY, int accumulate, \
-                        T* out);                                                                   \
+                        int refQuirks, T* out);                                                                   \
     void n2d2o_add_bias_##S(T* out, int oW, int oH, int O, int B, const T* bias);                  \
     void n2d2o_fc_##S(const T* in, int K, int B, const T* w, const T* bias, int O, T* out);        \
     void n2d2o_pool_max_##S(const T* in, int inW, int inH, int C, int B, int pW, int pH,           \

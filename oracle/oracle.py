@@ -70,7 +70,7 @@ def group_map(O, Cin, groups):
 
 
 def conv(x, w_oihw, flavour, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), groups=1, maps=None, bias=None,
-         accumulate_into=None):
+         accumulate_into=None, ref_quirks=False):
     """x: [B][C][H][W]; w_oihw: [O][Cg][kH][kW]; pad = (top, left, bottom, right). Returns [B][O][oH][oW]."""
     t = _np_t(flavour)
     x = np.ascontiguousarray(x, t)
@@ -85,7 +85,8 @@ def conv(x, w_oihw, flavour, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), groups
     out = accumulate_into if accumulate_into is not None else np.zeros((B, O, oH, oW), t)
     _fn('n2d2o_conv', flavour)(
         _p(x), W, H, Cin, B, _p(w), kW, kH, wC, O, _p(maps), nb_groups, stride[1], stride[0],
-        pad[1], pad[0], pad[3], pad[2], dil[1], dil[0], 1 if accumulate_into is not None else 0, _p(out))
+        pad[1], pad[0], pad[3], pad[2], dil[1], dil[0], 1 if accumulate_into is not None else 0,
+        1 if ref_quirks else 0, _p(out))
     if bias is not None:
         bb = np.ascontiguousarray(bias, t)
         _fn('n2d2o_add_bias', flavour)(_p(out), oW, oH, O, B, _p(bb))

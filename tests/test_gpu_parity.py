@@ -1,0 +1,140 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, bit for bit (integer work: no
+tolerance).  Every network is compared cell by cell (KEEP_ALL_OUTPUTS | NO_FUSION) and again in the
+shipped configuration (residual sums folded into the convolution epilogue, buffers reused)."""
+import numpy as np
+import pytest
+
+from n2d2_b200 import netdesc, runtime
+from oracle import oracle
+
+from gpu_common import KEEP, compare_net, single_conv_net
+
+pytestmark = pytest.mark.gpu
+R = runtime
+
+
+def test_config1_mnist24_single_shift_batch64():
+    n, eng = compare_net(netdesc.mnist24(), 64)
+    assert n == 4
+    n, eng = compare_net(netdesc.mnist24(), 64, flags=KEEP | R.FORCE_SIMT)
+    assert set(eng) == {'simt'}
+    # the fp32-accumulating flavour (what the reference's CPU cells compute) gives the same integers here
+    compare_net(netdesc.mnist24(), 64, flavour='f32')
+
+
+@pytest.mark.parametrize('force', [0, R.FORCE_SIMT], ids=['tensor-core', 'cuda-core'])
+@pytest.mark.parametrize('name', ['resnet50_double', 'resnet18_fixed', 'mobilenet_single', 'resnet18_w4_clipped_fixed',
+                                  'resnet18_float_clipped', 'resnet18_signed', 'resnet18_per_channel_frac'])
+def test_small_networks_cell_by_cell(name, force):
+    net = {
+        'resnet50_double': lambda: netdesc.resnet50(size=64, classes=100),
+        'resnet18_fixed': lambda: netdesc.resnet18(size=64, classes=100),
+        'mobilenet_single': lambda: netdesc.mobilenet_v1(size=64, classes=100),
+        'resnet18_w4_clipped_fixed': lambda: netdesc.resnet18(size=64, classes=100, weight_bits=4, clipped=True),
+        'resnet18_float_clipped': lambda: netdesc.resnet18(size=48, classes=10, scaling='float', clipped=True),
+        'resnet18_signed': lambda: netdesc.resnet18(size=48, classes=10, unsigned_relu=False),
+        'resnet18_per_channel_frac': lambda: netdesc.resnet18(size=48, classes=10, per_channel_frac=True),
+    }[name]()
+    n, eng = compare_net(net, 3, flags=KEEP | force)
+    assert n == len(net['layers'])
+    if not force and 'resnet' in name:
+        assert 'tcgen05' in eng
+
+
+@pytest.mark.parametrize('name', ['resnet50', 'resnet18', 'mobilenet'])
+def test_small_networks_shipped_configuration(name):
+    net = {'resnet50': lambda: netdesc.resnet50(size=64, classes=100),
+           'resnet18': lambda: netdesc.resnet18(size=64, classes=100),
+           'mobilenet': lambda: netdesc.mobilenet_v1(size=64, classes=100)}[name]()
+    n, eng = compare_net(net, 5, flags=0)
+    if name != 'mobilenet':
+        assert 'fused' in eng     # residual sums ride in the convolution epilogue
+
+
+# (C, H, O, k, stride, pad, input unsigned, flags)
+TC_CASES = [
+    (64, 8, 64, 1, 1, 0, True, 0), (128, 8, 256, 1, 1, 0, True, 0), (256, 9, 64, 1, 1, 0, False, 0),
+    (32, 8, 64, 1, 1, 0, True, 0), (16, 9, 32, 1, 1, 0, True, 0), (48, 9, 32, 3, 1, 1, True, 0),
+    (512, 7, 2048, 1, 1, 0, True, 0), (64, 8, 64, 1, 1, 0, True, R.FORCE_IM2COL), (64, 8, 64, 3, 1, 1, True, 0),
+    (128, 15, 128, 3, 2, 1, True, 0), (256, 14, 512, 1, 2, 0, False, 0), (64, 55, 64, 3, 1, 1, True, 0),
+    (64, 28, 1000, 1, 1, 0, True, 0), (64, 13, 72, 3, 1, 1, True, 0), (192, 7, 96, 5, 2, 2, True, 0),
+    (64, 12, 64, 3, 1, 2, True, 0),
+]
+
+
+@pytest.mark.parametrize('case', TC_CASES, ids=lambda c: 'C%d_H%d_O%d_k%d_s%d_p%d_%s_f%d' % (
+    c[0], c[1], c[2], c[3], c[4], c[5], 'u8' if c[6] else 's8', c[7]))
+def test_tensor_core_convolutions(case):
+    C, H, O, k, s, p, uns, flags = case
+    net = single_conv_net(C, H, H, O, k, s, p, in_unsigned=uns)
+    compare_net(net, 3, flags=KEEP | flags, want_engine='tcgen05')
+
+
+def test_tensor_core_dilated_convolution():
+    net = single_conv_net(64, 15, 15, 64, 3, 1, 2, dil=2)
+    compare_net(net, 2, want_engine='tcgen05')
+
+
+@pytest.mark.parametrize('mode', ['single', 'double', 'fixed', 'float'])
+@pytest.mark.parametrize('act', ['relu', 'linear'])
+def test_every_scaling_mode_on_both_kernel_families(mode, act):
+    for flags in (KEEP, KEEP | R.FORCE_SIMT):
+        net = single_conv_net(64, 9, 9, 80, 3, 1, 1, mode=mode, act=act, clipped=(mode in ('fixed', 'float')))
+        compare_net(net, 2, flags=flags)
+
+
+def test_direct_kernels_odd_geometries():
+    # few channels, groups, no bias, rectangular pooling, odd channel counts
+    for net in (single_conv_net(3, 17, 13, 5, 3, 2, 1), single_conv_net(6, 9, 9, 9, 3, 1, 1, groups=3),
+                single_conv_net(16, 9, 9, 16, 3, 1, 1, groups=16), single_conv_net(5, 8, 8, 7, 2, 2, 0, bias=False),
+                single_conv_net(1, 24, 24, 16, 4, 2, 0)):
+        compare_net(net, 2)
+    b = netdesc.NetBuilder('pools', 5, 11, 9, 3, 'single')
+    x = b.conv(-1, 7, 3, pad=1)
+    b.pool(x, 'max', (3, 2), 2, pad=1)
+    b.pool(x, 'avg', (2, 3), 1)
+    compare_net(b.net, 2)
+
+
+def test_scaling_cell_and_int32_outputs():
+    # a cell without Scaling leaves int32 accumulators; a ScalingCell brings them back to 8 bits
+    b = netdesc.NetBuilder('raw', 32, 6, 6, 11, 'fixed')
+    x = b.conv(-1, 32, 3, pad=1, act='linear')
+    b.net['layers'][0]['quant'] = {'mode': 'none', 'act': 'linear'}
+    y = b.scaling(x, act='relu')
+    b.net['layers'][1]['quant']['mult'] = (b.net['layers'][1]['quant']['mult'] // 4096).astype(np.int32) + 1
+    b.net['layers'][1]['quant']['frac_bits'] = 14
+    compare_net(b.net, 2)
+
+
+def test_batch_edges_and_errors():
+    net = netdesc.resnet18(size=32, classes=10)
+    qn = runtime.QuantizedNet(net, 4)
+    x = netdesc.make_input(net, 4)
+    ref = oracle.run_net(net, x, 'i64')[-1].reshape(4, -1)
+    full = qn.forward_host(x).astype(np.int64)
+    assert np.array_equal(full, ref)
+    one = qn.forward_host(x[:1]).astype(np.int64)           # ragged: fewer images than max_batch
+    assert np.array_equal(one, ref[:1])
+    assert qn.forward_host(x[:0]).shape[0] == 0              # empty batch is a no-op
+    with pytest.raises(runtime.N2D2BError, match='exceeds'):
+        qn.forward_host(netdesc.make_input(net, 5))
+    qn.close()
+    bad = netdesc.mnist24()
+    bad['layers'][0]['quant']['shift0'] = bad['layers'][0]['quant']['shift0'][:3]
+    with pytest.raises(runtime.N2D2BError):
+        runtime.QuantizedNet(bad, 1)
+
+
+def test_batch_invariance_at_a_large_batch():
+    # size-independent property: an image's logits do not depend on what else is in the batch, so a
+    # large batch can be checked image by image against small-batch oracle runs
+    net = netdesc.resnet50(size=96, classes=100)
+    big = 300
+    x = netdesc.make_input(net, big)
+    qn = runtime.QuantizedNet(net, big)
+    out = qn.forward_host(x).astype(np.int64)
+    qn.close()
+    picks = [0, 1, 127, 128, 255, 299]
+    ref = oracle.run_net(net, x[picks], 'i64')[-1].reshape(len(picks), -1)
+    assert np.array_equal(out[picks], ref)
