@@ -132,6 +132,7 @@ typedef struct n2d2b_tensor_info {
 #define N2D2B_NO_FUSION 2u        /* do not fold ElemWise sums into the producing convolution's epilogue */
 #define N2D2B_FORCE_SIMT 4u       /* CUDA-core kernels everywhere (cross-check of the tensor-core path) */
 #define N2D2B_FORCE_IM2COL 8u     /* tensor-core convolutions always load activations through the im2col map */
+#define N2D2B_EXACT64_EPILOGUE 16u /* tensor-core cells always use the 64-bit requantisation (cross-check of the 32-bit form) */
 
 const char* n2d2b_last_error(void);
 int n2d2b_version(void);

@@ -22,8 +22,10 @@
 namespace n2d2b {
 
 static constexpr int BM = 128;
-static constexpr int NUM_THREADS = 192;
 static constexpr int EPI_WARP0 = 2;
+static constexpr int NUM_EPI_WARPS = 8;       // two per TMEM lane quadrant, each takes half of the tile's columns
+static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
+static constexpr int FAST_NP = 5;             // words per channel of a fast requantisation: lo, hi, mult, add, shift
 static constexpr unsigned long long WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
 
 struct IgemmArgs {
@@ -37,6 +39,12 @@ struct IgemmArgs {
     int* status;
     QuantDev q;
     Residual r;
+    // fast 32-bit epilogue: y = (clamp(acc, lo, hi) * mult + add) >> shift, rows of cpad entries
+    const int* fq;      // [FAST_NP][cpad] of the cell
+    const int* fq2;     // [FAST_NP][cpad] of the fused residual sum (nullptr without one)
+    int cpad;
+    int t_lo, t_hi;     // saturation range of the cell's own output (before the residual add)
+    int out_unsigned;   // final 8-bit range: 1 = [0,255], 0 = [-128,127]
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -147,11 +155,92 @@ __device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr,
     return d;
 }
 
+// Packs four 32-bit values into four bytes with saturation to the unsigned or signed 8-bit range
+// (y0 in the low byte).
+__device__ __forceinline__ unsigned pack4_sat(int y0, int y1, int y2, int y3, bool is_unsigned)
+{
+    unsigned t, d;
+    if (is_unsigned) {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
+    } else {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
+    }
+    return d;
+}
+__device__ __forceinline__ int byte_of(unsigned w, int j, bool is_unsigned)
+{
+    return is_unsigned ? (int)((w >> (8 * j)) & 0xffu) : ((int)(w << (24 - 8 * j)) >> 24);
+}
+// One 32-column chunk of one accumulator row through the 32-bit epilogue.
+//   RES   : add the residual operand and requantise a second time
+//   CLAMP : keep the overflow / ReLU clamps (the host drops them when every product provably fits)
+// par points at the staged constants: rows of 256 words: lo, hi, mult, add, shift (+ the same five
+// of the residual stage).
+template <bool RES, bool CLAMP>
+__device__ __forceinline__ void fast_chunk(const unsigned* v, const int* par, int c0, const uint4& rv0, const uint4& rv1,
+                                           bool res_unsigned, bool out_unsigned, int t_lo, int t_hi, uint8_t* op)
+{
+    const unsigned rw[8] = {rv0.x, rv0.y, rv0.z, rv0.w, rv1.x, rv1.y, rv1.z, rv1.w};
+    unsigned wds[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int4 mu4 = *(const int4*)&par[2 * 256 + c0 + 4 * g];
+        const int4 ad4 = *(const int4*)&par[3 * 256 + c0 + 4 * g];
+        const int4 sh4 = *(const int4*)&par[4 * 256 + c0 + 4 * g];
+        const int mu[4] = {mu4.x, mu4.y, mu4.z, mu4.w}, ad[4] = {ad4.x, ad4.y, ad4.z, ad4.w};
+        const int sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
+        int y[4];
+        if (CLAMP) {
+            const int4 lo4 = *(const int4*)&par[0 * 256 + c0 + 4 * g];
+            const int4 hi4 = *(const int4*)&par[1 * 256 + c0 + 4 * g];
+            const int lo[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] = (min(max((int)v[4 * g + j], lo[j]), hi[j]) * mu[j] + ad[j]) >> sh[j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] = ((int)v[4 * g + j] * mu[j] + ad[j]) >> sh[j];
+        }
+        if (RES) {
+            const int4 mu2 = *(const int4*)&par[(FAST_NP + 2) * 256 + c0 + 4 * g];
+            const int4 ad2 = *(const int4*)&par[(FAST_NP + 3) * 256 + c0 + 4 * g];
+            const int4 sh2 = *(const int4*)&par[(FAST_NP + 4) * 256 + c0 + 4 * g];
+            const int m2[4] = {mu2.x, mu2.y, mu2.z, mu2.w}, a2[4] = {ad2.x, ad2.y, ad2.z, ad2.w};
+            const int s2[4] = {sh2.x, sh2.y, sh2.z, sh2.w};
+            int l2[4] = {0, 0, 0, 0}, h2[4] = {0, 0, 0, 0};
+            if (CLAMP) {
+                const int4 lo2 = *(const int4*)&par[(FAST_NP + 0) * 256 + c0 + 4 * g];
+                const int4 hi2 = *(const int4*)&par[(FAST_NP + 1) * 256 + c0 + 4 * g];
+                l2[0] = lo2.x; l2[1] = lo2.y; l2[2] = lo2.z; l2[3] = lo2.w;
+                h2[0] = hi2.x; h2[1] = hi2.y; h2[2] = hi2.z; h2[3] = hi2.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int t = min(max(y[j], t_lo), t_hi);
+                // one byte of the residual word, zero- or sign-extended by a single byte permute
+                const int r = res_unsigned ? (int)__byte_perm(rw[g], 0, 0x4440 + j)
+                                           : (int)__byte_perm(rw[g], 0, 0x8880 + 0x1110 * j + j);
+                int u = t + r;
+                if (CLAMP) u = min(max(u, l2[j]), h2[j]);
+                y[j] = (u * m2[j] + a2[j]) >> s2[j];
+            }
+        }
+        wds[g] = pack4_sat(y[0], y[1], y[2], y[3], out_unsigned);
+    }
+    ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+}
+
 // ----------------------------------------------------------------------------- the kernel
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const IgemmArgs a)
 {
+    constexpr bool FAST = MODE != 0;
+    constexpr bool RES = (MODE == 2 || MODE == 4);
+    constexpr bool CLAMP = (MODE == 1 || MODE == 2);
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment of the tile ring (required by the 128-byte swizzle)
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -160,14 +249,15 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int stage_bytes = a_stage_bytes + b_stage_bytes;
     unsigned char* tiles = smem;
     unsigned long long* bars = (unsigned long long*)(smem + (size_t)a.stages * stage_bytes);
-    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2]
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
     const unsigned tfull0 = empty0 + 8u * a.stages;
     const unsigned tempty0 = tfull0 + 16u;
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 4);
+    const unsigned pready0 = tempty0 + 16u;
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    int* epi_params = (int*)(tmem_slot + 4);  // [4][BN]: bias, p0, p1, aux
+    int* epi_params = (int*)(tmem_slot + 4);  // [2 accumulator stages][2 quant sets][FAST_NP][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -179,7 +269,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(tfull0 + 8u * s, 1);
-            mbar_init(tempty0 + 8u * s, 4);
+            mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
+            mbar_init(pready0 + 8u * s, 32 * NUM_EPI_WARPS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -270,71 +361,138 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int half = (warp - EPI_WARP0) >> 2;        // which half of the tile's columns
         const int row = quad * 32 + lane;
         const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
+        const int cols_per_warp = a.BN / 2;
         unsigned acc_it = 0;
+        unsigned stage_it = 0;
+        int staged_n_tile = -1;
+        int* par = epi_params;
         bool ok = true;
-        const bool vec_ok = (a.out_dtype == DT_I8) && (a.N % 16 == 0);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
             const int n_tile = tile % a.num_n_tiles;
             const int m_tile = tile / a.num_n_tiles;
             const int m0 = m_tile * BM, n0 = n_tile * a.BN;
             const unsigned as = acc_it & 1u;
             const unsigned aph = (acc_it >> 1) & 1u;
-            if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
-            tc_fence_after();
+            if (FAST && n_tile != staged_n_tile) {
+                // stage this column block's per-channel constants (once per CTA when the grid is a
+                // multiple of the number of column blocks).  Two buffers: the other one may still be
+                // read by slower warps, this one is free once everybody passed the previous barrier.
+                par = epi_params + (size_t)(stage_it & 1u) * (2 * FAST_NP * 256);
+                const int nq = a.fq2 ? 2 : 1;
+                for (int i = epi_tid; i < nq * FAST_NP * a.BN; i += 32 * NUM_EPI_WARPS) {
+                    const int set = i / (FAST_NP * a.BN);
+                    const int rem = i - set * FAST_NP * a.BN;
+                    const int prm = rem / a.BN, c = rem - prm * a.BN;
+                    const int* src = set ? a.fq2 : a.fq;
+                    par[(set * FAST_NP + prm) * 256 + c] = __ldg(src + (size_t)prm * a.cpad + n0 + c);
+                }
+                const unsigned pb = pready0 + 8u * (stage_it & 1u);
+                mbar_arrive(pb);
+                if (!mbar_wait(pb, (stage_it >> 1) & 1u, abort_flag, a.status, 5)) { ok = false; break; }
+                staged_n_tile = n_tile;
+                ++stage_it;
+            }
             const int m = m0 + row;
             const bool m_ok = m < a.M;
-            for (int c0 = 0; c0 < a.BN; c0 += 32) {
-                unsigned v[32];
-                const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)c0;
-                tc_ld32(taddr, v);
-                tc_wait_ld();
-                if (!m_ok) continue;
-                const int nbase = n0 + c0;
-                if (nbase >= a.N) continue;
-                int y[32];
+            const int nchunks = cols_per_warp / 32;
+            const int cbase = half * cols_per_warp;
+            if (FAST) {
+                // the residual operand does not depend on the accumulator: fetch it while the MMAs run
+                uint4 rres[8];
+                if (RES) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int n = nbase + j;
-                    if (n < a.N) {
-                        const long long x = (long long)(int)v[j] + (a.q.bias ? (long long)a.q.bias[n] : 0ll);
-                        int t = requant64(x, n, a.q);
-                        if (a.r.ptr) {
-                            const long long u = (long long)t
-                                + (long long)load_i8(a.r.ptr, (size_t)m * a.N + n, a.r.is_unsigned != 0);
-                            t = requant64(u, n, a.r.q2);
+                    for (int i = 0; i < 4; ++i) {
+                        rres[2 * i] = make_uint4(0, 0, 0, 0);
+                        rres[2 * i + 1] = rres[2 * i];
+                        const int nb = n0 + cbase + 32 * i;
+                        if (i < nchunks && m_ok && nb < a.N) {
+                            const uint4* rp = (const uint4*)((const uint8_t*)a.r.ptr + (size_t)m * a.N + nb);
+                            rres[2 * i] = rp[0];
+                            rres[2 * i + 1] = rp[1];
                         }
-                        y[j] = t;
-                    } else {
-                        y[j] = 0;
                     }
                 }
-                if (a.out_dtype == DT_I8) {
-                    uint8_t* op = (uint8_t*)a.out + (size_t)m * a.N + nbase;
-                    if (vec_ok && nbase + 32 <= a.N) {
-                        unsigned wds[8];
+                if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)cbase;
+                const bool res_unsigned = a.r.is_unsigned != 0;
+                const bool out_unsigned = a.out_unsigned != 0;
+                uint8_t* orow = (uint8_t*)a.out + (size_t)m * a.N + n0 + cbase;
+                unsigned vA[32], vB[32];
+                tc_ld32(tbase, vA);
+                // two chunks per trip: the next chunk's TMEM load is in flight while this one is computed
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            wds[i] = ((unsigned)y[4 * i] & 0xffu) | (((unsigned)y[4 * i + 1] & 0xffu) << 8)
-                                   | (((unsigned)y[4 * i + 2] & 0xffu) << 16) | (((unsigned)y[4 * i + 3] & 0xffu) << 24);
-                        ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-                        ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
-                    } else {
-                        for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = (uint8_t)y[j];
+                for (int i = 0; i < 4; i += 2) {
+                    if (i < nchunks) {
+                        tc_wait_ld();
+                        if (i + 1 < nchunks) tc_ld32(tbase + 32u * (i + 1), vB);
+                        if (m_ok && n0 + cbase + 32 * i < a.N)
+                            fast_chunk<RES, CLAMP>(vA, par, cbase + 32 * i, rres[2 * i], rres[2 * i + 1], res_unsigned,
+                                                   out_unsigned, a.t_lo, a.t_hi, orow + 32 * i);
                     }
-                } else {
-                    int32_t* op = (int32_t*)a.out + (size_t)m * a.N + nbase;
-                    for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = y[j];
+                    if (i + 1 < nchunks) {
+                        tc_wait_ld();
+                        if (i + 2 < nchunks) tc_ld32(tbase + 32u * (i + 2), vA);
+                        if (m_ok && n0 + cbase + 32 * (i + 1) < a.N)
+                            fast_chunk<RES, CLAMP>(vB, par, cbase + 32 * (i + 1), rres[2 * i + 2], rres[2 * i + 3],
+                                                   res_unsigned, out_unsigned, a.t_lo, a.t_hi, orow + 32 * (i + 1));
+                    }
+                }
+            } else {
+                if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
+                tc_fence_after();
+                for (int cc = 0; cc < cols_per_warp; cc += 32) {
+                    const int c0 = cbase + cc;
+                    unsigned v[32];
+                    const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)c0;
+                    const int nbase = n0 + c0;
+                    tc_ld32(taddr, v);
+                    tc_wait_ld();
+                    if (!m_ok || nbase >= a.N) continue;
+                    int y[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int n = nbase + j;
+                        if (n < a.N) {
+                            const long long x = (long long)(int)v[j] + (a.q.bias ? (long long)a.q.bias[n] : 0ll);
+                            int t = requant64(x, n, a.q);
+                            if (a.r.ptr) {
+                                const long long u = (long long)t
+                                    + (long long)load_i8(a.r.ptr, (size_t)m * a.N + n, a.r.is_unsigned != 0);
+                                t = requant64(u, n, a.r.q2);
+                            }
+                            y[j] = t;
+                        } else {
+                            y[j] = 0;
+                        }
+                    }
+                    if (a.out_dtype == DT_I8) {
+                        uint8_t* op = (uint8_t*)a.out + (size_t)m * a.N + nbase;
+                        if ((a.N % 16 == 0) && nbase + 32 <= a.N) {
+                            unsigned wds[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                wds[i] = ((unsigned)y[4 * i] & 0xffu) | (((unsigned)y[4 * i + 1] & 0xffu) << 8)
+                                       | (((unsigned)y[4 * i + 2] & 0xffu) << 16) | (((unsigned)y[4 * i + 3] & 0xffu) << 24);
+                            ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                            ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+                        } else {
+                            for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = (uint8_t)y[j];
+                        }
+                    } else {
+                        int32_t* op = (int32_t*)a.out + (size_t)m * a.N + nbase;
+                        for (int j = 0; j < 32 && nbase + j < a.N; ++j) op[j] = y[j];
+                    }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8u * as);
         }
-        (void)epi_tid;
-        (void)epi_params;
     }
 
     tc_fence_before();
@@ -384,7 +542,7 @@ static CUtensorMapSwizzle swizzle_for(int bk)
 
 static size_t igemm_smem_bytes(int stages, int BK, int BN)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 4) * 8 + 16 + 4 * 256 * 4 + 64;
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 6) * 8 + 16 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned,
@@ -415,7 +573,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const Conv
     plan->sX = g.sX; plan->sY = g.sY; plan->pL = g.pL; plan->pT = g.pT; plan->dX = g.dX; plan->dY = g.dY;
     // pipeline depth: fill up to ~200 KB of shared memory, at most 8 stages
     int stages = 8;
-    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN) > 200 * 1024) --stages;
+    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN) > 224 * 1024) --stages;
     plan->stages = stages;
     plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN);
     const int num_m_tiles = (plan->M + BM - 1) / BM;
@@ -471,8 +629,8 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const Conv
     return 0;
 }
 
-cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, void* out, int out_dtype,
-                         int* status_word, cudaStream_t s)
+cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast, void* out,
+                         int out_dtype, int* status_word, cudaStream_t s)
 {
     if (plan.M == 0 || plan.N == 0) return cudaSuccess;
     IgemmArgs a;
@@ -495,18 +653,35 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.status = status_word;
     a.q = q;
     a.r = r;
+    a.fq = fast.fq; a.fq2 = fast.fq2; a.cpad = fast.cpad; a.t_lo = fast.t_lo; a.t_hi = fast.t_hi;
+    a.out_unsigned = fast.out_unsigned;
+    const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2);
+    const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : 4) : (fast.need_clamp ? 1 : 3));
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024);
-        if (e != cudaSuccess) return e;
+        const void* variants[5] = {(const void*)igemm_i8_tcgen05_kernel<0>, (const void*)igemm_i8_tcgen05_kernel<1>,
+                                   (const void*)igemm_i8_tcgen05_kernel<2>, (const void*)igemm_i8_tcgen05_kernel<3>,
+                                   (const void*)igemm_i8_tcgen05_kernel<4>};
+        for (const void* fn : variants) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return e;
+        }
         attr_set[dev] = true;
     }
     int tiles = a.num_m_tiles * a.num_n_tiles;
     int grid = plan.grid < tiles ? plan.grid : tiles;
-    igemm_i8_tcgen05_kernel<<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
+    // a grid that is a multiple of the number of column blocks keeps every CTA on one column block,
+    // so its per-channel constants are staged once
+    if (tiles > grid && a.num_n_tiles > 1 && grid > a.num_n_tiles) grid -= grid % a.num_n_tiles;
+    switch (mode) {
+    case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    case 3: igemm_i8_tcgen05_kernel<3><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    case 4: igemm_i8_tcgen05_kernel<4><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    default: igemm_i8_tcgen05_kernel<0><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    }
     return cudaGetLastError();
 }
 

@@ -49,6 +49,18 @@ cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, cons
 cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, int B, int K, int O,
                              const QuantDev& q, void* out, int out_dtype, cudaStream_t s);
 
+// Per-channel constants of the 32-bit epilogue y = (clamp(acc, lo, hi) * mult + add) >> shift, which is
+// exact whenever the host could bound every intermediate to 32 bits (see build_fast_quant in net.cu).
+struct FastQuant {
+    const int* fq = nullptr;    // [5][cpad]: lo, hi, mult, add, shift of the cell
+    const int* fq2 = nullptr;   // the same for a fused residual sum
+    int cpad = 0;
+    int t_lo = 0, t_hi = 0;     // range the cell's own output saturates to
+    int out_unsigned = 0;       // final 8-bit range
+    bool need_clamp = true;     // false: no product can leave 32 bits and saturation is the final pack's
+    bool enabled = false;
+};
+
 // ---- tensor-core implicit GEMM (tcgen05 kind::i8) ----
 struct IgemmPlan {
     CUtensorMap tmA;      // activations: 2-D tiled [M][K] or 4-D im2col NHWC
@@ -68,7 +80,7 @@ struct IgemmPlan {
 // Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g,
                     int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
-cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, void* out,
-                         int out_dtype, int* status_word, cudaStream_t s);
+cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,
+                         void* out, int out_dtype, int* status_word, cudaStream_t s);
 
 }  // namespace n2d2b

@@ -79,6 +79,9 @@ struct CellRec {
     QuantHost q2;
     bool has_q2 = false;
     bool skipped = false;  // folded into another cell
+    // 32-bit epilogue constants (tensor-core cells)
+    FastQuant fast{};
+    int* d_fast = nullptr;
     // tensor-core plan
     IgemmPlan plan{};
     bool has_plan = false;
@@ -227,6 +230,104 @@ static int upload_quant(QuantHost& q)
     return 0;
 }
 
+// ---- 32-bit epilogue constants ----------------------------------------------------------------
+// For the shift and fixed-point modes the rescale of channel c is f(x) = (x * m + half) >> s with
+// m >= 0, a non-decreasing function of x.  Saturating f(x) to [out_lo, out_hi] (and a ReLU) equals
+// evaluating f on x clamped to [L, H], where H is the smallest x with f(x) >= out_hi and L the
+// largest x with f(x) <= out_lo: the clamp bounds every product, so 32-bit arithmetic is exact.
+// Clipping to [0, clip] before the rescale tightens the same clamp, and the bias is folded in:
+//   y = (clamp(acc, L - b, H - b) * m + (b * m + half)) >> s.
+// Returns false when some intermediate could leave 32 bits or the configuration is outside this
+// form (float mode, negative multipliers, clip <= 0, out_bits != 8, Saturation activation); the
+// exact 64-bit epilogue is used then.
+static long long ceil_div(long long a, long long b)  // b > 0
+{
+    return (a >= 0) ? (a + b - 1) / b : -((-a) / b);
+}
+
+static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int* eff_lo,
+                             int* eff_hi, bool* need_clamp)
+{
+    if (q.mode != SC_SINGLE_SHIFT && q.mode != SC_DOUBLE_SHIFT && q.mode != SC_FIXED_MULT16 && q.mode != SC_FIXED_MULT32)
+        return false;
+    if (q.out_bits != 8 || q.act == ACT_SATURATION) return false;
+    const int C = q.nb_channels;
+    const long long out_hi = q.out_unsigned ? 255 : 127;
+    long long out_lo = q.out_unsigned ? 0 : -128;
+    if (q.act == ACT_RECTIFIER && out_lo < 0) out_lo = 0;
+    *eff_lo = (int)out_lo;
+    *eff_hi = (int)out_hi;
+    out.assign((size_t)5 * cpad, 0);
+    const long long LIM = (1ll << 31) - 1;
+    // without the clamps the final 8-bit pack does the saturation (and, for unsigned outputs, the ReLU)
+    if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned)) *need_clamp = true;
+    for (int c = 0; c < C; ++c) {
+        long long m, s;
+        if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
+        else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
+        else { m = q.p0[c]; s = q.p1[c]; }
+        if (m < 0 || s > 30) return false;
+        const long long half = s > 0 ? (1ll << (s - 1)) : 0;
+        long long L = 0, H = 0;
+        if (m > 0) {
+            H = ceil_div((out_hi << s) - half, m);
+            L = ceil_div(((out_lo + 1) << s) - half, m) - 1;
+        }
+        if (q.is_clipped) {
+            if (!(q.clip_f[c] > 0.0f)) return false;
+            L = std::max(L, 0ll);
+            H = std::min(H, (long long)q.clip_val[c]);
+        }
+        if (H < L) L = H;   // everything saturates to the same value
+        const long long b = q.has_bias ? q.bias[c] : 0;
+        long long lo = L - b, hi = H - b;
+        const long long add = b * m + half;
+        // |x| never exceeds x_bound, so clamp bounds beyond it are equivalent to it (min(max(x, lo), hi)
+        // with lo > hi yields hi, which is then on the saturating side as well)
+        lo = std::max(lo, -x_bound);
+        hi = std::min(hi, x_bound);
+        const long long p0 = lo * m + add, p1 = hi * m + add;
+        if (std::llabs(add) > LIM || std::llabs(p0) > LIM || std::llabs(p1) > LIM) return false;
+        if (x_bound * m + std::llabs(add) > LIM) *need_clamp = true;   // an unclamped product could overflow
+        out[(size_t)0 * cpad + c] = (int32_t)lo;
+        out[(size_t)1 * cpad + c] = (int32_t)hi;
+        out[(size_t)2 * cpad + c] = (int32_t)m;
+        out[(size_t)3 * cpad + c] = (int32_t)add;
+        out[(size_t)4 * cpad + c] = (int32_t)s;
+    }
+    return true;
+}
+
+static int upload_fast(CellRec& c, const TensorRec& tout)
+{
+    c.fast = FastQuant{};
+    if (tout.dtype != DT_I8) return 0;
+    const int C = c.q.nb_channels;
+    const int cpad = ((C + 255) / 256) * 256;
+    std::vector<int32_t> f1, f2;
+    int lo1, hi1, lo2 = 0, hi2 = 0;
+    // |accumulator| <= K * 255 * 128; the residual stage adds two 8-bit values
+    const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * 128ll;
+    if (acc_bound > (1ll << 30)) return 0;
+    bool need_clamp = false;
+    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) return 0;
+    bool with_res = c.residual >= 0;
+    if (with_res && !build_fast_quant(c.q2, cpad, 512, f2, &lo2, &hi2, &need_clamp)) return 0;
+    const size_t words = f1.size() + f2.size();
+    CUDA_TRY(cudaMalloc((void**)&c.d_fast, words * 4 + 16));
+    CUDA_TRY(cudaMemcpy(c.d_fast, f1.data(), f1.size() * 4, cudaMemcpyHostToDevice));
+    if (with_res) CUDA_TRY(cudaMemcpy(c.d_fast + f1.size(), f2.data(), f2.size() * 4, cudaMemcpyHostToDevice));
+    c.fast.fq = c.d_fast;
+    c.fast.fq2 = with_res ? c.d_fast + f1.size() : nullptr;
+    c.fast.cpad = cpad;
+    c.fast.t_lo = lo1;
+    c.fast.t_hi = hi1;
+    c.fast.out_unsigned = with_res ? c.q2.out_unsigned : c.q.out_unsigned;
+    c.fast.need_clamp = need_clamp;
+    c.fast.enabled = true;
+    return 0;
+}
+
 static void unpack_weights(const void* src, int weight_bits, size_t rows, size_t row_elems, std::vector<int8_t>& dst)
 {
     dst.resize(rows * row_elems);
@@ -287,6 +388,7 @@ void n2d2b_net_destroy(n2d2b_net* net)
         cudaFree(c.d_weights);
         cudaFree(c.q.d_blob);
         cudaFree(c.q2.d_blob);
+        cudaFree(c.d_fast);
     }
     cudaFree(net->d_status);
     cudaFree(net->d_stage_in);
@@ -623,6 +725,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
                 c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
+                if (!(flags & N2D2B_EXACT64_EPILOGUE))
+                    if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
             }
         }
     }
@@ -660,7 +764,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         }
         IgemmPlan p = c.plan;
         p.M = batch * c.geom.oH * c.geom.oW;
-        CUDA_TRY(launch_igemm(p, c.q.dev, r, out, tout.dtype, net->d_status, s));
+        CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, net->d_status, s));
         break;
     }
     case ENG_SIMT: {

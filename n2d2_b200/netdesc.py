@@ -67,7 +67,7 @@ class NetBuilder:
         self.net = {'name': name, 'input': {'C': C, 'H': H, 'W': W, 'unsigned': bool(input_unsigned)},
                     'layers': []}
         self.rng = np.random.Generator(np.random.PCG64(seed))
-        self.scaling = scaling
+        self.scaling_mode = scaling
         self.unsigned_relu = unsigned_relu
         self.weight_dist = weight_dist
         self.weight_bits = weight_bits
@@ -96,7 +96,7 @@ class NetBuilder:
         return p / math.sqrt(3.0) if kind == 'uniform' else float(p)
 
     def _quant(self, channels, act, acc_sigma, target_rms=45.0, mode=None):
-        mode = mode or self.scaling
+        mode = mode or self.scaling_mode
         out_unsigned = bool(self.unsigned_relu and act == 'relu')
         q = {'mode': None, 'act': act, 'out_bits': 8, 'out_unsigned': out_unsigned}
         want = target_rms / max(acc_sigma, 1.0)   # desired multiplicative scale

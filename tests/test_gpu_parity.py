@@ -70,6 +70,23 @@ def test_tensor_core_convolutions(case):
     compare_net(net, 3, flags=KEEP | flags, want_engine='tcgen05')
 
 
+def test_exact64_epilogue_matches_too():
+    # the tensor-core cells default to the 32-bit epilogue wherever it is provably exact; the 64-bit
+    # form must give the same integers
+    for net in (netdesc.resnet50(size=64, classes=100), netdesc.resnet18(size=64, classes=100, clipped=True)):
+        compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='tcgen05')
+        compare_net(net, 3, flags=R.EXACT64_EPILOGUE)
+
+
+def test_wide_shifts_fall_back_to_the_exact_epilogue():
+    # fractional bits beyond what 32-bit products can hold
+    net = single_conv_net(64, 9, 9, 64, 3, 1, 1, mode='fixed')
+    q = net['layers'][0]['quant']
+    q['mult'] = (q['mult'].astype(np.int64) << 14).astype(np.int32)
+    q['frac_bits'] = int(q['frac_bits']) + 14
+    compare_net(net, 2, want_engine='tcgen05')
+
+
 def test_tensor_core_dilated_convolution():
     net = single_conv_net(64, 15, 15, 64, 3, 1, 2, dil=2)
     compare_net(net, 2, want_engine='tcgen05')
@@ -121,8 +138,12 @@ def test_batch_edges_and_errors():
         qn.forward_host(netdesc.make_input(net, 5))
     qn.close()
     bad = netdesc.mnist24()
-    bad['layers'][0]['quant']['shift0'] = bad['layers'][0]['quant']['shift0'][:3]
-    with pytest.raises(runtime.N2D2BError):
+    bad['layers'][0]['groups'] = 3                           # does not divide 1 channel / 16 outputs
+    with pytest.raises(runtime.N2D2BError, match='groups'):
+        runtime.QuantizedNet(bad, 1)
+    bad = netdesc.mnist24()
+    bad['layers'][0]['quant']['out_bits'] = 12               # beyond what an 8-bit tensor holds
+    with pytest.raises(runtime.N2D2BError, match='out_bits'):
         runtime.QuantizedNet(bad, 1)
 
 
