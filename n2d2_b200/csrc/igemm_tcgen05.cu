@@ -141,6 +141,20 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* v)
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// tcgen05.ld fills its destination registers asynchronously; the compiler only sees them as outputs of
+// the load statement and is free to schedule their consumers ahead of the wait.  Passing the
+// registers through an empty volatile statement placed after the wait ties every later use to it.
+__device__ __forceinline__ void tc_wait_ld_into(unsigned* v)
+{
+    tc_wait_ld();
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                      "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :: "memory");
+    asm volatile("" : "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
+                      "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
+                      "+r"(v[30]), "+r"(v[31])
+                 :: "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are `swz` bytes wide (swz = 32, 64 or
 // 128, equal to the TMA swizzle span): 8-row groups are swz*8 bytes apart.
@@ -168,6 +182,16 @@ __device__ __forceinline__ unsigned pack4_sat(int y0, int y1, int y2, int y3, bo
         asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
     }
     return d;
+}
+// Byte j of w, zero- or sign-extended, in one permute: a selector nibble with its top bit set
+// replicates the sign of the selected byte (the __byte_perm intrinsic only honours 3 bits per nibble,
+// hence the PTX form).
+__device__ __forceinline__ int byte_extend(unsigned w, int j, bool is_unsigned)
+{
+    unsigned d;
+    const unsigned sel = is_unsigned ? (0x4440u + j) : (0x8880u + 0x1110u * j + j);
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(sel));
+    return (int)d;
 }
 __device__ __forceinline__ int byte_of(unsigned w, int j, bool is_unsigned)
 {
@@ -219,8 +243,7 @@ __device__ __forceinline__ void fast_chunk(const unsigned* v, const int* par, in
             for (int j = 0; j < 4; ++j) {
                 const int t = min(max(y[j], t_lo), t_hi);
                 // one byte of the residual word, zero- or sign-extended by a single byte permute
-                const int r = res_unsigned ? (int)__byte_perm(rw[g], 0, 0x4440 + j)
-                                           : (int)__byte_perm(rw[g], 0, 0x8880 + 0x1110 * j + j);
+                const int r = byte_extend(rw[g], j, res_unsigned);
                 int u = t + r;
                 if (CLAMP) u = min(max(u, l2[j]), h2[j]);
                 y[j] = (u * m2[j] + a2[j]) >> s2[j];
@@ -422,24 +445,19 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 const bool res_unsigned = a.r.is_unsigned != 0;
                 const bool out_unsigned = a.out_unsigned != 0;
                 uint8_t* orow = (uint8_t*)a.out + (size_t)m * a.N + n0 + cbase;
-                unsigned vA[32], vB[32];
-                tc_ld32(tbase, vA);
-                // two chunks per trip: the next chunk's TMEM load is in flight while this one is computed
+                // The asynchronous TMEM load is waited for at once: its destination registers must not
+                // stay live across other code (a compiler-inserted move or spill between the load and
+                // the wait would capture stale values).  The second warp on each scheduler hides the
+                // load latency instead.
 #pragma unroll
-                for (int i = 0; i < 4; i += 2) {
+                for (int i = 0; i < 4; ++i) {
                     if (i < nchunks) {
-                        tc_wait_ld();
-                        if (i + 1 < nchunks) tc_ld32(tbase + 32u * (i + 1), vB);
+                        unsigned v[32];
+                        tc_ld32(tbase + 32u * i, v);
+                        tc_wait_ld_into(v);
                         if (m_ok && n0 + cbase + 32 * i < a.N)
-                            fast_chunk<RES, CLAMP>(vA, par, cbase + 32 * i, rres[2 * i], rres[2 * i + 1], res_unsigned,
+                            fast_chunk<RES, CLAMP>(v, par, cbase + 32 * i, rres[2 * i], rres[2 * i + 1], res_unsigned,
                                                    out_unsigned, a.t_lo, a.t_hi, orow + 32 * i);
-                    }
-                    if (i + 1 < nchunks) {
-                        tc_wait_ld();
-                        if (i + 2 < nchunks) tc_ld32(tbase + 32u * (i + 2), vA);
-                        if (m_ok && n0 + cbase + 32 * (i + 1) < a.N)
-                            fast_chunk<RES, CLAMP>(vB, par, cbase + 32 * (i + 1), rres[2 * i + 2], rres[2 * i + 3],
-                                                   res_unsigned, out_unsigned, a.t_lo, a.t_hi, orow + 32 * (i + 1));
                     }
                 }
             } else {
@@ -451,7 +469,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)c0;
                     const int nbase = n0 + c0;
                     tc_ld32(taddr, v);
-                    tc_wait_ld();
+                    tc_wait_ld_into(v);
                     if (!m_ok || nbase >= a.N) continue;
                     int y[32];
 #pragma unroll
