@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstring>
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace n2d2b {
 
@@ -25,8 +26,6 @@ static constexpr int BM = 128;
 static constexpr int EPI_WARP0 = 2;
 static constexpr int NUM_EPI_WARPS = 8;       // two per TMEM lane quadrant, each takes half of the tile's columns
 static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
-static constexpr int FAST_NP = 5;             // words per channel of a fast requantisation: lo, hi, mult, add, shift
-static constexpr unsigned long long WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
@@ -46,214 +45,6 @@ struct IgemmArgs {
     int t_lo, t_hi;     // saturation range of the cell's own output (before the residual add)
     int out_unsigned;   // final 8-bit range: 1 = [0,255], 0 = [-128,127]
 };
-
-// ----------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
-{
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait. Returns false (and raises the CTA-wide abort flag) on time-out or when another
-// role already aborted.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
-                                          int* status, int code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            atomicCAS(status, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* tm, unsigned bar, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_load_im2col_4d(unsigned dst, const CUtensorMap* tm, unsigned bar, int c,
-                                                   int w, int h, int n, unsigned short off_w,
-                                                   unsigned short off_h)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
-        ::"r"(dst), "l"(tm), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
-                                          unsigned idesc, unsigned accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(unsigned bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* v)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// tcgen05.ld fills its destination registers asynchronously; the compiler only sees them as outputs of
-// the load statement and is free to schedule their consumers ahead of the wait.  Passing the
-// registers through an empty volatile statement placed after the wait ties every later use to it.
-__device__ __forceinline__ void tc_wait_ld_into(unsigned* v)
-{
-    tc_wait_ld();
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                      "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
-                 :: "memory");
-    asm volatile("" : "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
-                      "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
-                      "+r"(v[30]), "+r"(v[31])
-                 :: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are `swz` bytes wide (swz = 32, 64 or
-// 128, equal to the TMA swizzle span): 8-row groups are swz*8 bytes apart.
-__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr, int swz)
-{
-    const unsigned long long layout = (swz == 128) ? 2ull : (swz == 64 ? 4ull : 6ull);
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)(((unsigned)(swz * 8)) >> 4) << 32;  // stride byte offset
-    d |= 1ull << 46;                                               // descriptor version (sm_100)
-    d |= layout << 61;
-    return d;
-}
-
-// Packs four 32-bit values into four bytes with saturation to the unsigned or signed 8-bit range
-// (y0 in the low byte).
-__device__ __forceinline__ unsigned pack4_sat(int y0, int y1, int y2, int y3, bool is_unsigned)
-{
-    unsigned t, d;
-    if (is_unsigned) {
-        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
-        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
-    } else {
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
-    }
-    return d;
-}
-// Byte j of w, zero- or sign-extended, in one permute: a selector nibble with its top bit set
-// replicates the sign of the selected byte (the __byte_perm intrinsic only honours 3 bits per nibble,
-// hence the PTX form).
-__device__ __forceinline__ int byte_extend(unsigned w, int j, bool is_unsigned)
-{
-    unsigned d;
-    const unsigned sel = is_unsigned ? (0x4440u + j) : (0x8880u + 0x1110u * j + j);
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(sel));
-    return (int)d;
-}
-__device__ __forceinline__ int byte_of(unsigned w, int j, bool is_unsigned)
-{
-    return is_unsigned ? (int)((w >> (8 * j)) & 0xffu) : ((int)(w << (24 - 8 * j)) >> 24);
-}
-// One 32-column chunk of one accumulator row through the 32-bit epilogue.
-//   RES   : add the residual operand and requantise a second time
-//   CLAMP : keep the overflow / ReLU clamps (the host drops them when every product provably fits)
-// par points at the staged constants: rows of 256 words: lo, hi, mult, add, shift (+ the same five
-// of the residual stage).
-template <bool RES, bool CLAMP>
-__device__ __forceinline__ void fast_chunk(const unsigned* v, const int* par, int c0, const uint4& rv0, const uint4& rv1,
-                                           bool res_unsigned, bool out_unsigned, int t_lo, int t_hi, uint8_t* op)
-{
-    const unsigned rw[8] = {rv0.x, rv0.y, rv0.z, rv0.w, rv1.x, rv1.y, rv1.z, rv1.w};
-    unsigned wds[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        const int4 mu4 = *(const int4*)&par[2 * 256 + c0 + 4 * g];
-        const int4 ad4 = *(const int4*)&par[3 * 256 + c0 + 4 * g];
-        const int4 sh4 = *(const int4*)&par[4 * 256 + c0 + 4 * g];
-        const int mu[4] = {mu4.x, mu4.y, mu4.z, mu4.w}, ad[4] = {ad4.x, ad4.y, ad4.z, ad4.w};
-        const int sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
-        int y[4];
-        if (CLAMP) {
-            const int4 lo4 = *(const int4*)&par[0 * 256 + c0 + 4 * g];
-            const int4 hi4 = *(const int4*)&par[1 * 256 + c0 + 4 * g];
-            const int lo[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] = (min(max((int)v[4 * g + j], lo[j]), hi[j]) * mu[j] + ad[j]) >> sh[j];
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] = ((int)v[4 * g + j] * mu[j] + ad[j]) >> sh[j];
-        }
-        if (RES) {
-            const int4 mu2 = *(const int4*)&par[(FAST_NP + 2) * 256 + c0 + 4 * g];
-            const int4 ad2 = *(const int4*)&par[(FAST_NP + 3) * 256 + c0 + 4 * g];
-            const int4 sh2 = *(const int4*)&par[(FAST_NP + 4) * 256 + c0 + 4 * g];
-            const int m2[4] = {mu2.x, mu2.y, mu2.z, mu2.w}, a2[4] = {ad2.x, ad2.y, ad2.z, ad2.w};
-            const int s2[4] = {sh2.x, sh2.y, sh2.z, sh2.w};
-            int l2[4] = {0, 0, 0, 0}, h2[4] = {0, 0, 0, 0};
-            if (CLAMP) {
-                const int4 lo2 = *(const int4*)&par[(FAST_NP + 0) * 256 + c0 + 4 * g];
-                const int4 hi2 = *(const int4*)&par[(FAST_NP + 1) * 256 + c0 + 4 * g];
-                l2[0] = lo2.x; l2[1] = lo2.y; l2[2] = lo2.z; l2[3] = lo2.w;
-                h2[0] = hi2.x; h2[1] = hi2.y; h2[2] = hi2.z; h2[3] = hi2.w;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int t = min(max(y[j], t_lo), t_hi);
-                // one byte of the residual word, zero- or sign-extended by a single byte permute
-                const int r = byte_extend(rw[g], j, res_unsigned);
-                int u = t + r;
-                if (CLAMP) u = min(max(u, l2[j]), h2[j]);
-                y[j] = (u * m2[j] + a2[j]) >> s2[j];
-            }
-        }
-        wds[g] = pack4_sat(y[0], y[1], y[2], y[3], out_unsigned);
-    }
-    ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-    ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
-}
 
 // ----------------------------------------------------------------------------- the kernel
 template <int MODE>

@@ -83,4 +83,23 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const Conv
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,
                          void* out, int out_dtype, int* status_word, cudaStream_t s);
 
+// ---- first-layer convolution (<= 4 input channels) on the tensor cores ----
+struct StemPlan {
+    CUtensorMap tmB;      // arranged weights [O][nkb*128]
+    int nkb;
+    int stages;
+    int in_unsigned;
+    int num_sms;
+    size_t smem_bytes;
+};
+bool stem_eligible(const ConvGeom& g);
+size_t stem_weight_bytes(const ConvGeom& g);
+void stem_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* dst);
+int stem_make_plan(StemPlan* plan, const int8_t* d_w_arranged, const ConvGeom& g, int in_unsigned, int num_sms,
+                   const char** why);
+// Re-lays [pixels][C] (C <= 4) as [pixels][4] with zero fill.
+cudaError_t launch_pad_channels(const void* in, int C, size_t pixels, void* out, cudaStream_t s);
+cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g, const FastQuant& fast, void* out,
+                        int* status_word, cudaStream_t s);
+
 }  // namespace n2d2b

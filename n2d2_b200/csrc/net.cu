@@ -37,7 +37,7 @@ static int fail(int code, const char* fmt, ...)
 
 // ------------------------------------------------------------------------------------ model
 enum CellType { CELL_CONV, CELL_FC, CELL_POOL, CELL_SUM, CELL_SCALING };
-enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED };
+enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED, ENG_STEM };
 
 struct TensorRec {
     int C = 0, H = 0, W = 0;
@@ -82,6 +82,9 @@ struct CellRec {
     // 32-bit epilogue constants (tensor-core cells)
     FastQuant fast{};
     int* d_fast = nullptr;
+    // first-layer tensor-core kernel
+    StemPlan stem{};
+    void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel
     // tensor-core plan
     IgemmPlan plan{};
     bool has_plan = false;
@@ -389,6 +392,7 @@ void n2d2b_net_destroy(n2d2b_net* net)
         cudaFree(c.q.d_blob);
         cudaFree(c.q2.d_blob);
         cudaFree(c.d_fast);
+        cudaFree(c.d_pad4);
     }
     cudaFree(net->d_status);
     cudaFree(net->d_stage_in);
@@ -699,6 +703,31 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                                 && g.groups > 1 && c.residual < 0
                                 && net->tensors[c.output].dtype == DT_I8);
         std::vector<int8_t> laid = c.weights;
+        const bool stem = !depthwise && c.type == CELL_CONV && !(flags & N2D2B_FORCE_SIMT) && c.residual < 0
+                          && stem_eligible(g) && net->tensors[c.output].dtype == DT_I8 && !(flags & N2D2B_EXACT64_EPILOGUE);
+        if (stem) {
+            if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+            if (c.fast.enabled) {
+                std::vector<int8_t> arranged(stem_weight_bytes(g));
+                stem_arrange_weights(g, c.weights.data(), arranged.data());
+                CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
+                CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
+                const char* why = "";
+                if (stem_make_plan(&c.stem, c.d_weights, g, net->tensors[c.inputs[0]].is_unsigned, net->num_sms, &why) == 0) {
+                    if (g.C != 4) {
+                        CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * g.H * g.W * 4 + 256));
+                        net->launches++;
+                    }
+                    c.engine = ENG_STEM;
+                    continue;
+                }
+                cudaFree(c.d_weights);
+                c.d_weights = nullptr;
+            }
+            cudaFree(c.d_fast);
+            c.d_fast = nullptr;
+            c.fast = FastQuant{};
+        }
         if (depthwise) {
             c.engine = ENG_DEPTHWISE;
             // [C][kH][kW] -> [kH][kW][C] so that 16 channels of a tap are one 128-bit load
@@ -765,6 +794,17 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         IgemmPlan p = c.plan;
         p.M = batch * c.geom.oH * c.geom.oW;
         CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, net->d_status, s));
+        break;
+    }
+    case ENG_STEM: {
+        ConvGeom g = c.geom;
+        g.B = batch;
+        const void* in4 = in0;
+        if (c.d_pad4) {
+            CUDA_TRY(launch_pad_channels(in0, g.C, (size_t)batch * g.H * g.W, c.d_pad4, s));
+            in4 = c.d_pad4;
+        }
+        CUDA_TRY(launch_stem(c.stem, in4, g, c.fast, out, net->d_status, s));
         break;
     }
     case ENG_SIMT: {
@@ -937,6 +977,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
     case ENG_POOL: return "pool";
     case ENG_SUM: return "sum";
     case ENG_FUSED: return "fused";
+    case ENG_STEM: return "stem-tcgen05";
     }
     return "";
 }

@@ -87,6 +87,20 @@ def test_wide_shifts_fall_back_to_the_exact_epilogue():
     compare_net(net, 2, want_engine='tcgen05')
 
 
+# (C, H, W, O, k, stride, pad, input unsigned)
+STEM_CASES = [(3, 32, 32, 64, 7, 2, 3, True), (3, 224, 224, 64, 7, 2, 3, True), (3, 33, 29, 32, 3, 2, 1, True),
+              (1, 24, 24, 32, 4, 2, 0, True), (4, 17, 19, 64, 5, 1, 2, False), (2, 16, 16, 96, 8, 3, 0, True),
+              (3, 20, 20, 256, 3, 1, 1, True)]
+
+
+@pytest.mark.parametrize('case', STEM_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_s%d_p%d' % c[:7])
+@pytest.mark.parametrize('mode', ['double', 'fixed'])
+def test_first_layer_tensor_core_kernel(case, mode):
+    C, H, W, O, k, s, p, uns = case
+    net = single_conv_net(C, H, W, O, k, s, p, in_unsigned=uns, mode=mode)
+    compare_net(net, 3, want_engine='stem-tcgen05')
+
+
 def test_tensor_core_dilated_convolution():
     net = single_conv_net(64, 15, 15, 64, 3, 1, 2, dil=2)
     compare_net(net, 2, want_engine='tcgen05')
