@@ -71,7 +71,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const unsigned pready0 = tempty0 + 16u;
     unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    int* epi_params = (int*)(tmem_slot + 4);  // [2 accumulator stages][2 quant sets][FAST_NP][BN]
+    // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
+    int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -351,7 +352,7 @@ static CUtensorMapSwizzle swizzle_for(int bk)
 
 static size_t igemm_smem_bytes(int stages, int BK, int BN)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 6) * 8 + 16 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 6) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned,

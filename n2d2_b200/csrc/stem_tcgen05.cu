@@ -73,7 +73,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const StemArgs
     const unsigned wbar = tempty0 + 16u;
     unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 5);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    int* par = (int*)(tmem_slot + 4);                      // [FAST_NP][256]
+    int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256], 16-byte aligned for vector loads
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -267,7 +267,7 @@ int stem_make_plan(StemPlan* plan, const int8_t* d_w_arranged, const ConvGeom& g
     const size_t b_bytes = (((size_t)plan->nkb * g.O * 128) + 1023) & ~(size_t)1023;
     const size_t a_stage = (size_t)plan->nkb * SBM * 128;
     int stages = 4;
-    auto smem_for = [&](int st) { return 1024 + b_bytes + st * a_stage + (2 * st + 5) * 8 + 16 + FAST_NP * 256 * 4 + 64; };
+    auto smem_for = [&](int st) { return 1024 + b_bytes + st * a_stage + (2 * st + 5) * 8 + 32 + FAST_NP * 256 * 4 + 64; };
     while (stages > 2 && smem_for(stages) > 200 * 1024) --stages;
     plan->stages = stages;
     plan->smem_bytes = smem_for(stages);
