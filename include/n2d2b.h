@@ -194,6 +194,40 @@ int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_ou
 int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t nb_pixels,
                             const n2d2b_quant* quant, n2d2b_stream stream);
 
+/*
+ * First-layer convolution that allocates no device memory.  It has no counterpart in the reference.
+ *
+ * For callers that cannot call cudaMalloc where they need the result: plugins inside a host
+ * framework that owns the device heap, latency-bound loops that cannot afford an allocation's
+ * device-wide synchronisation, processes at their memory budget.  The scratch the kernel needs
+ * (the input re-laid with 4 bytes per pixel, the re-ordered weights, the per-channel constants)
+ * lives in a fixed array inside the library's device image instead of in allocated memory.
+ *
+ *   d_input / d_output  device buffers: batch x height x width x channels 8-bit values in, batch x
+ *                       oH x oW x nb_outputs 8-bit values out (same layout and arithmetic as a conv
+ *                       cell added with n2d2b_net_add_conv)
+ *   desc, weights, bias, quant   host data, as for n2d2b_net_add_conv (desc->input is ignored);
+ *                       8-bit weights; <= 4 channels, kernel <= 8x8, no dilation or groups, nb_outputs
+ *                       a multiple of 32 and <= 256; a shift or fixed-point scaling whose products
+ *                       fit 32 bits, 8-bit output
+ *
+ * Limits and sharing
+ *   - batch x height x width must not exceed N2D2B_NOALLOC_MAX_PIXELS (else N2D2B_ERR_TOO_LARGE).
+ *   - Every GPU that loads the library holds N2D2B_NOALLOC_SCRATCH_BYTES for this array until the
+ *     process exits, whether or not this function is ever called.
+ *   - All calls on a device share the one array: calls whose GPU work overlaps (different streams,
+ *     different threads) race on it.  Issue them on one stream, or order them yourself.
+ *   - The first call on a device looks up the array's device address; make that call before any
+ *     stream capture begins.  The call copies the small layer constants and waits for that copy
+ *     (a stream synchronisation), then enqueues the kernels asynchronously.
+ *   - It calls no cudaMalloc, cudaFree or other allocating CUDA routine.
+ */
+#define N2D2B_NOALLOC_MAX_PIXELS (8u * 1024u * 1024u)
+#define N2D2B_NOALLOC_SCRATCH_BYTES (128u * 1024u + 4u * N2D2B_NOALLOC_MAX_PIXELS)
+int n2d2b_first_conv_noalloc(int device, const void* d_input, int batch, int height, int width, int channels,
+                             int in_unsigned, const n2d2b_conv_desc* desc, const int8_t* weights, const int32_t* bias,
+                             const n2d2b_quant* quant, void* d_output, n2d2b_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

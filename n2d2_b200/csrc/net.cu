@@ -12,6 +12,7 @@
 
 #include "../../include/n2d2b.h"
 #include "kernels.h"
+#include "host_internal.h"
 
 using namespace n2d2b;
 
@@ -348,6 +349,31 @@ static void unpack_weights(const void* src, int weight_bits, size_t rows, size_t
             dst[r * row_elems + i] = (int8_t)((nib & 8) ? nib - 16 : nib);
         }
 }
+
+// ---- helpers exported to the other translation units (host_internal.h) -------------------------
+namespace n2d2b {
+int set_error(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int prepare_fast_constants(const n2d2b_quant* quant, int channels, const int32_t* bias, long long acc_bound,
+                           std::vector<int32_t>& consts, int* cpad, int* out_unsigned, bool* need_clamp)
+{
+    QuantHost q;
+    if (int rc = validate_quant(quant, channels, true, q, bias)) return rc;
+    *cpad = ((channels + 255) / 256) * 256;
+    int lo = 0, hi = 0;
+    *need_clamp = false;
+    if (q.mode == SC_NONE || !build_fast_quant(q, *cpad, acc_bound, consts, &lo, &hi, need_clamp)) return 1;
+    *out_unsigned = q.out_unsigned;
+    return 0;
+}
+}  // namespace n2d2b
 
 // ------------------------------------------------------------------------------------ C ABI
 extern "C" {

@@ -13,6 +13,7 @@
 #include <cstring>
 #include "kernels.h"
 #include "tc_common.cuh"
+#include "host_internal.h"
 
 namespace n2d2b {
 
@@ -319,3 +320,132 @@ cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g
 }
 
 }  // namespace n2d2b
+
+// ------------------------------------------------------------------------------------------------
+// First-layer convolution for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a result: a plugin
+// running inside a framework that owns the whole device heap and forbids foreign allocations, a
+// real-time inference loop where an allocation's unbounded latency (and its implicit device-wide
+// synchronisation) is not acceptable, or a process near its memory budget.  The normal path
+// (n2d2b_net_finalize) allocates the scratch the first-layer kernel needs - the input re-laid with
+// four bytes per pixel, the weights in the kernel's K order, the per-channel epilogue constants.
+// This entry point keeps all three in one fixed array that lives in the library's device image:
+// every GPU that loads the library holds N2D2B_NOALLOC_SCRATCH_BYTES of it until the process exits,
+// which is why the size is modest and the batch it can take is bounded.
+// ------------------------------------------------------------------------------------------------
+static constexpr size_t NA_WEIGHT_BYTES = 256 * 256;                 // 256 outputs x 2 K blocks of 128 bytes
+static constexpr size_t NA_CONST_OFFSET = NA_WEIGHT_BYTES;           // [5][256] words
+static constexpr size_t NA_PAD_OFFSET = 128 * 1024;                  // re-laid input starts here
+static constexpr size_t NA_SCRATCH_BYTES = NA_PAD_OFFSET + (size_t)N2D2B_NOALLOC_MAX_PIXELS * 4;
+static_assert(NA_SCRATCH_BYTES == N2D2B_NOALLOC_SCRATCH_BYTES, "header and implementation disagree on the scratch size");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle; its device address comes from the runtime, once per
+// device, with that device current.
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+static int noalloc_scratch_for(int device, unsigned char** ptr)
+{
+    if (device < 0 || device >= 64) return n2d2b::set_error(N2D2B_ERR_INVALID, "device %d out of range", device);
+    if (!g_noalloc_ptr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return n2d2b::set_error(N2D2B_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[device] = (unsigned char*)p;
+    }
+    *ptr = g_noalloc_ptr[device];
+    return 0;
+}
+
+extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int batch, int height, int width, int channels,
+                                        int in_unsigned, const n2d2b_conv_desc* desc, const int8_t* weights,
+                                        const int32_t* bias, const n2d2b_quant* quant, void* d_output,
+                                        n2d2b_stream stream)
+{
+    using namespace n2d2b;
+    if (!d_input || !d_output || !desc || !weights || !quant)
+        return set_error(N2D2B_ERR_INVALID, "input, output, desc, weights and quant must not be NULL");
+    if (batch < 0 || height < 1 || width < 1 || channels < 1)
+        return set_error(N2D2B_ERR_INVALID, "invalid input dimensions");
+    if (batch == 0) return 0;
+    if (desc->weight_bits != 8) return set_error(N2D2B_ERR_INVALID, "this entry point takes 8-bit weights");
+    if (desc->nb_outputs < 1 || desc->kernel_h < 1 || desc->kernel_w < 1 || desc->stride_y < 1 || desc->stride_x < 1
+        || desc->pad_top < 0 || desc->pad_left < 0 || desc->pad_bottom < 0 || desc->pad_right < 0)
+        return set_error(N2D2B_ERR_INVALID, "invalid convolution geometry");
+    ConvGeom g;
+    memset(&g, 0, sizeof(g));
+    g.B = batch; g.H = height; g.W = width; g.C = channels;
+    g.O = desc->nb_outputs; g.kH = desc->kernel_h; g.kW = desc->kernel_w;
+    g.sY = desc->stride_y; g.sX = desc->stride_x; g.pT = desc->pad_top; g.pL = desc->pad_left;
+    g.dY = desc->dilation_y; g.dX = desc->dilation_x;
+    g.groups = desc->groups; g.Cg = channels; g.Og = g.O;
+    g.oH = (int)((height + desc->pad_top + desc->pad_bottom - (g.kH - 1) - 1 + g.sY) / (double)g.sY);
+    g.oW = (int)((width + desc->pad_left + desc->pad_right - (g.kW - 1) - 1 + g.sX) / (double)g.sX);
+    if (g.oH < 1 || g.oW < 1) return set_error(N2D2B_ERR_INVALID, "convolution output would be empty");
+    if (!stem_eligible(g))
+        return set_error(N2D2B_ERR_INVALID,
+                         "outside the first-layer kernel: needs <= 4 channels, kernel <= 8x8, no dilation or groups, "
+                         "outputs a multiple of 32 and <= 256");
+    const size_t pixels = (size_t)batch * height * width;
+    if (pixels > (size_t)N2D2B_NOALLOC_MAX_PIXELS)
+        return set_error(N2D2B_ERR_TOO_LARGE, "batch x height x width = %zu input pixels exceeds the fixed scratch of %u pixels",
+                         pixels, (unsigned)N2D2B_NOALLOC_MAX_PIXELS);
+    if (stem_weight_bytes(g) > NA_WEIGHT_BYTES)
+        return set_error(N2D2B_ERR_TOO_LARGE, "arranged weights exceed the fixed scratch");
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(e));
+    int sms = 148;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+    unsigned char* scratch = nullptr;
+    if (int rc = noalloc_scratch_for(device, &scratch)) return rc;
+
+    // host-side preparation: epilogue constants and weights in the kernel's K order
+    std::vector<int32_t> consts;
+    int cpad = 0, out_unsigned = 0;
+    bool need_clamp = false;
+    const long long acc_bound = (long long)g.kH * g.kW * g.C * 255ll * 128ll;
+    const int prc = prepare_fast_constants(quant, g.O, bias, acc_bound, consts, &cpad, &out_unsigned, &need_clamp);
+    if (prc < 0) return prc;
+    if (prc > 0 || cpad != 256)
+        return set_error(N2D2B_ERR_INVALID,
+                         "this entry point takes shift or fixed-point scalings whose products fit 32 bits and 8-bit outputs");
+    std::vector<int8_t> arranged(stem_weight_bytes(g));
+    stem_arrange_weights(g, weights, arranged.data());
+
+    cudaStream_t s = (cudaStream_t)stream;
+    // both copies are ordered on the caller's stream behind any earlier call that still reads the scratch;
+    // the host buffers are released when this function returns, hence the synchronisation
+    e = cudaMemcpyAsync(scratch, arranged.data(), arranged.size(), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(scratch + NA_CONST_OFFSET, consts.data(), consts.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "copy of the layer constants failed: %s", cudaGetErrorString(e));
+
+    StemPlan plan;
+    const char* why = "";
+    if (stem_make_plan(&plan, (const int8_t*)scratch, g, in_unsigned ? 1 : 0, sms, &why))
+        return set_error(N2D2B_ERR_INVALID, "first-layer plan failed: %s", why);
+    const void* in4 = d_input;
+    if (channels != 4) {
+        // every pixel of the region is rewritten in full, so nothing of an earlier call survives
+        e = launch_pad_channels(d_input, channels, pixels, scratch + NA_PAD_OFFSET, s);
+        if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "re-layout launch failed: %s", cudaGetErrorString(e));
+        in4 = scratch + NA_PAD_OFFSET;
+    }
+    FastQuant fq;
+    fq.fq = (const int*)(scratch + NA_CONST_OFFSET);
+    fq.cpad = cpad;
+    fq.out_unsigned = out_unsigned;
+    fq.need_clamp = need_clamp;
+    fq.enabled = true;
+    // the status word of the bounded waits also lives in the scratch (last 16 bytes of the constants area)
+    int* status = (int*)(scratch + NA_PAD_OFFSET - 16);
+    e = cudaMemsetAsync(status, 0, sizeof(int), s);
+    if (e == cudaSuccess) e = launch_stem(plan, in4, g, fq, d_output, status, s);
+    if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "first-layer launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+

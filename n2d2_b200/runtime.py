@@ -90,6 +90,9 @@ def load():
                                           C.c_void_p]
         lib.n2d2b_scaling_propagate.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(Quant),
                                                 C.c_void_p]
+        lib.n2d2b_first_conv_noalloc.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                 C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.POINTER(Quant),
+                                                 C.c_void_p, C.c_void_p]
         _lib = lib
     return _lib
 
@@ -247,3 +250,20 @@ class QuantizedNet:
 def scaling_propagate(x_i32_dev_ptr, out_dev_ptr, nb_pixels, q, channels, device=0, stream=0):
     qq, keep = make_quant(q, channels)
     check(load().n2d2b_scaling_propagate(device, x_i32_dev_ptr, out_dev_ptr, nb_pixels, C.byref(qq), stream))
+
+
+NOALLOC_MAX_PIXELS = 8 * 1024 * 1024
+
+
+def first_conv_noalloc(d_in_ptr, batch, height, width, channels, in_unsigned, layer, d_out_ptr, device=0, stream=0):
+    """First-layer convolution through the entry point that allocates no device memory (its scratch is
+    a fixed array inside the library; see include/n2d2b.h for the limits).  `layer` is a conv layer
+    dict of netdesc.py; d_in_ptr / d_out_ptr are raw device pointers."""
+    w = np.ascontiguousarray(layer['weights'], np.int8)
+    b = None if layer.get('bias') is None else np.ascontiguousarray(layer['bias'], np.int32)
+    q, keep = make_quant(layer['quant'], layer['Cout'])
+    d = ConvDesc(0, layer['Cout'], layer['kH'], layer['kW'], layer['stride'][0], layer['stride'][1], layer['pad'][0],
+                 layer['pad'][1], layer['pad'][2], layer['pad'][3], layer['dil'][0], layer['dil'][1], layer['groups'],
+                 int(layer.get('weight_bits', 8)))
+    check(load().n2d2b_first_conv_noalloc(device, d_in_ptr, batch, height, width, channels, 1 if in_unsigned else 0,
+                                          C.byref(d), _ptr(w), _ptr(b), C.byref(q), d_out_ptr, stream))
