@@ -1,0 +1,449 @@
+// Host-side C++ mirror of the part of N2D2's API that the quantized inference path uses, on top of
+// the C ABI (include/n2d2b.h).  Class, factory and method names follow the reference so that code
+// written against its Cell / Scaling / DeepNet interface reads the same here:
+//
+//   Scaling, ScalingMode               include/Scaling.hpp:339-373, include/ScalingMode.hpp:27-34
+//   Activation and its three kinds     include/Activation/Activation.hpp:36-110
+//   Cell::setQuantized & co            include/Cell/Cell.hpp:75-85
+//   ConvCell creation arguments        include/Cell/ConvCell.hpp:45-55
+//   DeepNet::addCell / getCell /
+//     getLayers / test                 src/DeepNet.cpp:74-290,2622-2768
+//   DeepNetExport::isCellOutputUnsigned src/Export/DeepNetExport.cpp:370-388
+//
+// Differences that follow from the integer representation: weights and stimuli are 8-bit integers
+// (the reference holds the same integers in float tensors), activations live on the GPU as NHWC,
+// and errors of the C ABI surface as std::runtime_error like the reference's own.
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/n2d2b.h"
+
+namespace N2D2 {
+
+typedef float Float_T;
+
+enum class ScalingMode { NONE, FLOAT_MULT, FIXED_MULT16, FIXED_MULT32, SINGLE_SHIFT, DOUBLE_SHIFT };
+
+// Value type holding the per-output rescale of an activation (include/Scaling.hpp:45-427).
+class Scaling {
+public:
+    Scaling() : mMode(ScalingMode::NONE), mNbFractionalBits(0), mIsClipped(false) {}
+
+    static Scaling floatingPointScaling(std::vector<Float_T> scalingPerOutput, bool isClipped,
+                                        std::vector<Float_T> clippingPerOutput)
+    {
+        Scaling s;
+        s.mMode = ScalingMode::FLOAT_MULT;
+        s.mFloat = std::move(scalingPerOutput);
+        s.mIsClipped = isClipped;
+        s.mClipping = std::move(clippingPerOutput);
+        return s;
+    }
+    static Scaling fixedPointScaling(ScalingMode mode, std::size_t nbFractionalBits,
+                                     std::vector<std::int32_t> scalingPerOutput, bool isClipped,
+                                     std::vector<Float_T> clippingPerOutput)
+    {
+        if (mode != ScalingMode::FIXED_MULT16 && mode != ScalingMode::FIXED_MULT32)
+            throw std::runtime_error("Scaling::fixedPointScaling(): mode must be FIXED_MULT16 or FIXED_MULT32");
+        Scaling s;
+        s.mMode = mode;
+        s.mNbFractionalBits = nbFractionalBits;
+        s.mFixed = std::move(scalingPerOutput);
+        s.mIsClipped = isClipped;
+        s.mClipping = std::move(clippingPerOutput);
+        return s;
+    }
+    static Scaling singleShiftScaling(std::vector<unsigned char> scalingPerOutput, bool isClipped,
+                                      std::vector<Float_T> clippingPerOutput)
+    {
+        Scaling s;
+        s.mMode = ScalingMode::SINGLE_SHIFT;
+        s.mShift0 = std::move(scalingPerOutput);
+        s.mIsClipped = isClipped;
+        s.mClipping = std::move(clippingPerOutput);
+        return s;
+    }
+    static Scaling doubleShiftScaling(std::vector<std::pair<unsigned char, unsigned char> > scalingPerOutput,
+                                      bool isClipped,
+                                      std::vector<std::pair<unsigned char, unsigned char> > /*clippingPerOutput*/)
+    {
+        Scaling s;
+        s.mMode = ScalingMode::DOUBLE_SHIFT;
+        for (const auto& p : scalingPerOutput) {
+            s.mShift0.push_back(p.first);
+            s.mShift1.push_back(p.second);
+        }
+        s.mIsClipped = isClipped;  // ignored by the shift modes, as on the reference's CPU path
+        return s;
+    }
+
+    ScalingMode getMode() const { return mMode; }
+    std::size_t getFractionalBits() const { return mNbFractionalBits; }
+    bool getIsClipped() const { return mIsClipped; }
+
+    // Fills the C-ABI view (pointers stay valid as long as this object lives).
+    void describe(n2d2b_scaling& d, int nbOutputs) const
+    {
+        d = n2d2b_scaling();
+        d.mode = (int32_t)mMode;
+        d.nb_channels = nbOutputs;
+        d.fscale = mFloat.empty() ? nullptr : mFloat.data();
+        d.mult = mFixed.empty() ? nullptr : mFixed.data();
+        d.frac_bits = (int32_t)mNbFractionalBits;
+        d.shift0 = mShift0.empty() ? nullptr : mShift0.data();
+        d.shift1 = mShift1.empty() ? nullptr : mShift1.data();
+        d.is_clipped = (mIsClipped && !mClipping.empty()) ? 1 : 0;
+        d.clip = mClipping.empty() ? nullptr : mClipping.data();
+    }
+
+private:
+    ScalingMode mMode;
+    std::size_t mNbFractionalBits;
+    bool mIsClipped;
+    std::vector<Float_T> mFloat, mClipping;
+    std::vector<std::int32_t> mFixed;
+    std::vector<unsigned char> mShift0, mShift1;
+};
+
+// Activation: owns the Scaling (include/Activation/Activation.hpp:70-99).
+class Activation {
+public:
+    virtual ~Activation() {}
+    virtual const char* getType() const = 0;
+    virtual int kind() const = 0;
+    void setActivationScaling(Scaling scaling) { mScaling = std::move(scaling); }
+    const Scaling& getActivationScaling() const { return mScaling; }
+    void setQuantized(std::size_t nbBits) { mQuantizedNbBits = nbBits; }
+    std::size_t getQuantizedNbBits() const { return mQuantizedNbBits; }
+
+protected:
+    Scaling mScaling;
+    std::size_t mQuantizedNbBits = 0;
+};
+class LinearActivation : public Activation {
+public:
+    const char* getType() const override { return "Linear"; }
+    int kind() const override { return N2D2B_ACT_LINEAR; }
+};
+class RectifierActivation : public Activation {
+public:
+    const char* getType() const override { return "Rectifier"; }
+    int kind() const override { return N2D2B_ACT_RECTIFIER; }
+};
+class SaturationActivation : public Activation {
+public:
+    explicit SaturationActivation(int threshold = 0) : mThreshold(threshold) {}
+    const char* getType() const override { return "Saturation"; }
+    int kind() const override { return N2D2B_ACT_SATURATION; }
+    int mThreshold;
+};
+
+// Process-wide export switches the reference keeps as statics (src/Export/DeepNetExport.cpp:33-34)
+struct DeepNetExport {
+    static bool& mUnsignedData() { static bool v = true; return v; }
+    static bool& mEnvDataUnsigned() { static bool v = true; return v; }
+};
+
+class DeepNet;
+
+class Cell {
+public:
+    Cell(const std::string& name, unsigned int nbOutputs) : mName(name), mNbOutputs(nbOutputs) {}
+    virtual ~Cell() {}
+    virtual const char* getType() const = 0;
+    const std::string& getName() const { return mName; }
+    unsigned int getNbOutputs() const { return mNbOutputs; }
+    bool isQuantized() const { return mQuantizedNbBits > 0; }
+    void setQuantized(std::size_t nbBits) { mQuantizedNbBits = nbBits; }
+    std::size_t getQuantizedNbBits() const { return mQuantizedNbBits; }
+    const std::shared_ptr<Activation>& getActivation() const { return mActivation; }
+    void setActivation(const std::shared_ptr<Activation>& activation) { mActivation = activation; }
+    unsigned int getOutputsWidth() const { return mOutputsWidth; }
+    unsigned int getOutputsHeight() const { return mOutputsHeight; }
+
+    // Signedness of the cell's output as DeepNetExport::isCellOutputUnsigned derives it: unsigned only
+    // when unsigned data is allowed and the output range starts at 0 (a Rectifier); may be overridden.
+    bool isOutputUnsigned() const
+    {
+        if (mForcedSign >= 0) return mForcedSign != 0;
+        return DeepNetExport::mUnsignedData() && mActivation && mActivation->kind() == N2D2B_ACT_RECTIFIER;
+    }
+    void setOutputUnsigned(bool u) { mForcedSign = u ? 1 : 0; }
+
+protected:
+    friend class DeepNet;
+    // what the activation does on the way out, as the C ABI wants it
+    void describeQuant(n2d2b_quant& q) const
+    {
+        q = n2d2b_quant();
+        static const Scaling none;
+        const Scaling& s = mActivation ? mActivation->getActivationScaling() : none;
+        s.describe(q.scaling, (int)mNbOutputs);
+        q.activation = mActivation ? mActivation->kind() : N2D2B_ACT_LINEAR;
+        const std::size_t actBits = mActivation ? mActivation->getQuantizedNbBits() : 0;
+        q.out_bits = (int32_t)(actBits > 0 ? actBits : (mQuantizedNbBits > 0 ? mQuantizedNbBits : 8));
+        q.out_unsigned = isOutputUnsigned() ? 1 : 0;
+        if (auto* sat = dynamic_cast<const SaturationActivation*>(mActivation.get())) q.saturation_threshold = sat->mThreshold;
+    }
+    std::string mName;
+    unsigned int mNbOutputs;
+    std::size_t mQuantizedNbBits = 0;
+    std::shared_ptr<Activation> mActivation;
+    unsigned int mOutputsWidth = 0, mOutputsHeight = 0;
+    int mForcedSign = -1;
+    int mTensorId = -1;
+};
+
+class ConvCell : public Cell {
+public:
+    // kernelDims / strideDims / dilationDims are {x, y}; paddingDims {x, y} or {left, top, right, bottom}
+    ConvCell(const std::string& name, const std::vector<unsigned int>& kernelDims, unsigned int nbOutputs,
+             const std::vector<unsigned int>& subSampleDims = {1, 1}, const std::vector<unsigned int>& strideDims = {1, 1},
+             const std::vector<int>& paddingDims = {0, 0}, const std::vector<unsigned int>& dilationDims = {1, 1},
+             const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
+        : Cell(name, nbOutputs), mKernelDims(kernelDims), mStrideDims(strideDims), mPaddingDims(paddingDims),
+          mDilationDims(dilationDims)
+    {
+        for (unsigned int s : subSampleDims)
+            if (s != 1) throw std::domain_error("ConvCell: sub-sampling is not supported (the reference's CUDA cell rejects it too)");
+        if (mPaddingDims.size() == 2) { mPaddingDims.push_back(mPaddingDims[0]); mPaddingDims.push_back(mPaddingDims[1]); }
+        mActivation = activation;
+    }
+    const char* getType() const override { return "Conv"; }
+    void setNbGroups(unsigned int groups) { mGroups = groups; }
+    // weights in the reference's memory order: [output][channel][ky][kx] (kx fastest)
+    void setWeights(const std::vector<std::int8_t>& oihw) { mWeights = oihw; }
+    void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
+    std::int8_t getWeight(unsigned int output, unsigned int channel, unsigned int sx, unsigned int sy) const
+    {
+        const std::size_t cg = mWeights.size() / ((std::size_t)mNbOutputs * mKernelDims[0] * mKernelDims[1]);
+        return mWeights[(((std::size_t)output * cg + channel) * mKernelDims[1] + sy) * mKernelDims[0] + sx];
+    }
+
+private:
+    friend class DeepNet;
+    std::vector<unsigned int> mKernelDims, mStrideDims;
+    std::vector<int> mPaddingDims;
+    std::vector<unsigned int> mDilationDims;
+    unsigned int mGroups = 1;
+    std::vector<std::int8_t> mWeights;
+    std::vector<std::int32_t> mBiases;
+};
+
+class FcCell : public Cell {
+public:
+    FcCell(const std::string& name, unsigned int nbOutputs,
+           const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
+        : Cell(name, nbOutputs)
+    {
+        mActivation = activation;
+    }
+    const char* getType() const override { return "Fc"; }
+    // weights in the reference's order: [output][channel][y][x] over the input tensor
+    void setWeights(const std::vector<std::int8_t>& w) { mWeights = w; }
+    void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
+
+private:
+    friend class DeepNet;
+    std::vector<std::int8_t> mWeights;
+    std::vector<std::int32_t> mBiases;
+};
+
+class PoolCell : public Cell {
+public:
+    enum Pooling { Max, Average };
+    PoolCell(const std::string& name, const std::vector<unsigned int>& poolDims, unsigned int nbOutputs,
+             const std::vector<unsigned int>& strideDims = {1, 1}, const std::vector<unsigned int>& paddingDims = {0, 0},
+             Pooling pooling = Max)
+        : Cell(name, nbOutputs), mPoolDims(poolDims), mStrideDims(strideDims), mPaddingDims(paddingDims), mPooling(pooling)
+    {
+    }
+    const char* getType() const override { return "Pool"; }
+
+private:
+    friend class DeepNet;
+    std::vector<unsigned int> mPoolDims, mStrideDims, mPaddingDims;
+    Pooling mPooling;
+};
+
+class ElemWiseCell : public Cell {
+public:
+    enum Operation { Sum };
+    ElemWiseCell(const std::string& name, unsigned int nbOutputs, Operation operation = Sum,
+                 const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
+        : Cell(name, nbOutputs)
+    {
+        if (operation != Sum) throw std::runtime_error("ElemWiseCell: only Sum exists on the quantized path");
+        mActivation = activation;
+    }
+    const char* getType() const override { return "ElemWise"; }
+};
+
+class ScalingCell : public Cell {
+public:
+    ScalingCell(const std::string& name, unsigned int nbOutputs, Scaling scaling) : Cell(name, nbOutputs)
+    {
+        // a ScalingCell applies its Scaling with its own quantized bit count and no non-linearity
+        mActivation = std::make_shared<LinearActivation>();
+        mActivation->setActivationScaling(std::move(scaling));
+    }
+    const char* getType() const override { return "Scaling"; }
+};
+
+// Graph container + executor: cells run in insertion order like DeepNet::propagate.
+class DeepNet {
+public:
+    DeepNet(unsigned int stimuliChannels, unsigned int stimuliHeight, unsigned int stimuliWidth, int device = 0)
+    {
+        check(n2d2b_net_create(device, &mNet));
+        int id = 0;
+        check(n2d2b_net_set_input(mNet, (int)stimuliChannels, (int)stimuliHeight, (int)stimuliWidth,
+                                  DeepNetExport::mEnvDataUnsigned() ? 1 : 0, &id));
+        mShapes[id] = {stimuliChannels, stimuliHeight, stimuliWidth};
+    }
+    ~DeepNet() { n2d2b_net_destroy(mNet); }
+    DeepNet(const DeepNet&) = delete;
+    DeepNet& operator=(const DeepNet&) = delete;
+
+    // parents: empty = the stimuli (the reference passes a null parent for the environment)
+    void addCell(const std::shared_ptr<Cell>& cell, const std::vector<std::shared_ptr<Cell> >& parents)
+    {
+        if (mCells.count(cell->getName())) throw std::runtime_error("DeepNet::addCell(): cell " + cell->getName() + " already exists");
+        std::vector<int> ins;
+        for (const auto& p : parents) ins.push_back(p ? p->mTensorId : 0);
+        if (ins.empty()) ins.push_back(0);
+        const Shape in = mShapes.at(ins[0]);
+        n2d2b_quant q;
+        cell->describeQuant(q);
+        int id = -1;
+        if (auto* conv = dynamic_cast<ConvCell*>(cell.get())) {
+            n2d2b_conv_desc d = n2d2b_conv_desc();
+            d.input = ins[0];
+            d.nb_outputs = (int)conv->getNbOutputs();
+            d.kernel_w = (int)conv->mKernelDims[0]; d.kernel_h = (int)conv->mKernelDims[1];
+            d.stride_x = (int)conv->mStrideDims[0]; d.stride_y = (int)conv->mStrideDims[1];
+            d.pad_left = conv->mPaddingDims[0]; d.pad_top = conv->mPaddingDims[1];
+            d.pad_right = conv->mPaddingDims[2]; d.pad_bottom = conv->mPaddingDims[3];
+            d.dilation_x = (int)conv->mDilationDims[0]; d.dilation_y = (int)conv->mDilationDims[1];
+            d.groups = (int)conv->mGroups;
+            d.weight_bits = 8;
+            // OIHW (reference memory order) -> OHWI (kernel order)
+            const std::size_t cg = in.c / conv->mGroups, kh = d.kernel_h, kw = d.kernel_w, O = d.nb_outputs;
+            if (conv->mWeights.size() != O * cg * kh * kw) throw std::runtime_error("ConvCell " + cell->getName() + ": wrong number of weights");
+            std::vector<std::int8_t> ohwi(conv->mWeights.size());
+            for (std::size_t o = 0; o < O; ++o)
+                for (std::size_t c = 0; c < cg; ++c)
+                    for (std::size_t y = 0; y < kh; ++y)
+                        for (std::size_t x = 0; x < kw; ++x)
+                            ohwi[((o * kh + y) * kw + x) * cg + c] = conv->mWeights[((o * cg + c) * kh + y) * kw + x];
+            check(n2d2b_net_add_conv(mNet, &d, ohwi.data(), conv->mBiases.empty() ? nullptr : conv->mBiases.data(), &q, &id));
+        } else if (auto* fc = dynamic_cast<FcCell*>(cell.get())) {
+            const std::size_t K = (std::size_t)in.c * in.h * in.w, O = fc->getNbOutputs();
+            if (fc->mWeights.size() != O * K) throw std::runtime_error("FcCell " + cell->getName() + ": wrong number of weights");
+            // the reference flattens the input as (channel, y, x); the device tensor is (y, x, channel)
+            std::vector<std::int8_t> w(fc->mWeights.size());
+            for (std::size_t o = 0; o < O; ++o)
+                for (std::size_t c = 0; c < in.c; ++c)
+                    for (std::size_t y = 0; y < in.h; ++y)
+                        for (std::size_t x = 0; x < in.w; ++x)
+                            w[o * K + (y * in.w + x) * in.c + c] = fc->mWeights[o * K + (c * in.h + y) * in.w + x];
+            check(n2d2b_net_add_fc(mNet, ins[0], (int)O, 8, w.data(), fc->mBiases.empty() ? nullptr : fc->mBiases.data(), &q, &id));
+        } else if (auto* pool = dynamic_cast<PoolCell*>(cell.get())) {
+            n2d2b_pool_desc d = n2d2b_pool_desc();
+            d.input = ins[0];
+            d.pooling = pool->mPooling == PoolCell::Max ? N2D2B_POOL_MAX : N2D2B_POOL_AVERAGE;
+            d.pool_w = (int)pool->mPoolDims[0]; d.pool_h = (int)pool->mPoolDims[1];
+            d.stride_x = (int)pool->mStrideDims[0]; d.stride_y = (int)pool->mStrideDims[1];
+            d.pad_x = (int)pool->mPaddingDims[0]; d.pad_y = (int)pool->mPaddingDims[1];
+            check(n2d2b_net_add_pool(mNet, &d, &id));
+        } else if (dynamic_cast<ElemWiseCell*>(cell.get())) {
+            check(n2d2b_net_add_elemwise_sum(mNet, ins.data(), (int)ins.size(), &q, &id));
+        } else if (dynamic_cast<ScalingCell*>(cell.get())) {
+            check(n2d2b_net_add_scaling(mNet, ins[0], &q, &id));
+        } else {
+            throw std::runtime_error("DeepNet::addCell(): cell type " + std::string(cell->getType()) + " is not on the quantized path");
+        }
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, id, &info));
+        cell->mTensorId = id;
+        cell->mOutputsWidth = (unsigned)info.width;
+        cell->mOutputsHeight = (unsigned)info.height;
+        mShapes[id] = {(unsigned)info.channels, (unsigned)info.height, (unsigned)info.width};
+        mCells[cell->getName()] = cell;
+        mLayers.push_back({cell->getName()});
+        mLast = cell;
+    }
+
+    template <class T> std::shared_ptr<T> getCell(const std::string& name) const
+    {
+        auto it = mCells.find(name);
+        if (it == mCells.end()) throw std::runtime_error("DeepNet::getCell(): layer " + name + " does not exist");
+        auto p = std::dynamic_pointer_cast<T>(it->second);
+        if (!p) throw std::runtime_error("DeepNet::getCell(): wrong type for layer " + name);
+        return p;
+    }
+    const std::vector<std::vector<std::string> >& getLayers() const { return mLayers; }
+
+    // Cell::initialize() of every cell: allocates activations for up to maxBatch stimuli.
+    void initialize(unsigned int maxBatch, bool keepAllOutputs = false)
+    {
+        check(n2d2b_net_finalize(mNet, (int)maxBatch, keepAllOutputs ? (N2D2B_KEEP_ALL_OUTPUTS | N2D2B_NO_FUSION) : 0u));
+    }
+
+    // DeepNet::test on a batch of stimuli (8-bit, [batch][height][width][channels]); returns the last
+    // cell's outputs as integers, [batch][outputs].
+    std::vector<int> test(const std::vector<std::uint8_t>& stimuli, unsigned int batch)
+    {
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, mLast->mTensorId, &info));
+        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
+        std::vector<int> out(n);
+        if (info.dtype == N2D2B_I32) {
+            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, out.data(), nullptr));
+        } else {
+            std::vector<std::uint8_t> raw(n);
+            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, raw.data(), nullptr));
+            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
+        }
+        return out;
+    }
+
+    // Outputs of one cell after test() (needs initialize(..., keepAllOutputs = true)), NHWC.
+    std::vector<int> getOutputs(const std::string& name, unsigned int batch)
+    {
+        const auto cell = getCell<Cell>(name);
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, cell->mTensorId, &info));
+        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
+        std::vector<int> out(n);
+        if (info.dtype == N2D2B_I32) {
+            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, out.data(), n * 4));
+        } else {
+            std::vector<std::uint8_t> raw(n);
+            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, raw.data(), n));
+            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
+        }
+        return out;
+    }
+
+private:
+    struct Shape { unsigned int c, h, w; };
+    static void check(int rc)
+    {
+        if (rc < 0) throw std::runtime_error(n2d2b_last_error());
+    }
+    n2d2b_net* mNet = nullptr;
+    std::map<std::string, std::shared_ptr<Cell> > mCells;
+    std::map<int, Shape> mShapes;
+    std::vector<std::vector<std::string> > mLayers;
+    std::shared_ptr<Cell> mLast;
+};
+
+}  // namespace N2D2
