@@ -50,6 +50,7 @@ struct IgemmArgs {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
                         const IgemmArgs a)
 {
     constexpr bool FAST = MODE != 0;
@@ -62,14 +63,17 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int b_stage_bytes = a.BN * a.BK;
     const int stage_bytes = a_stage_bytes + b_stage_bytes;
     unsigned char* tiles = smem;
-    unsigned long long* bars = (unsigned long long*)(smem + (size_t)a.stages * stage_bytes);
-    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2]
+    // output staging: one 4 KiB region per epilogue warp (32 rows x up to 128 bytes, swizzled for TMA)
+    unsigned char* stage_out = smem + (size_t)a.stages * stage_bytes;
+    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * 4096);
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[NUM_EPI_WARPS]
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
     const unsigned tfull0 = empty0 + 8u * a.stages;
     const unsigned tempty0 = tfull0 + 16u;
     const unsigned pready0 = tempty0 + 16u;
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6);
+    const unsigned rbar0 = pready0 + 16u;
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + NUM_EPI_WARPS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -87,6 +91,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
             mbar_init(pready0 + 8u * s, 32 * NUM_EPI_WARPS);
         }
+        for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -183,6 +188,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int cols_per_warp = a.BN / 2;
         unsigned acc_it = 0;
         unsigned stage_it = 0;
+        unsigned res_it = 0;
         int staged_n_tile = -1;
         int* par = epi_params;
         bool ok = true;
@@ -216,42 +222,68 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int nchunks = cols_per_warp / 32;
             const int cbase = half * cols_per_warp;
             if (FAST) {
-                // the residual operand does not depend on the accumulator: fetch it while the MMAs run
-                uint4 rres[8];
-                if (RES) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        rres[2 * i] = make_uint4(0, 0, 0, 0);
-                        rres[2 * i + 1] = rres[2 * i];
-                        const int nb = n0 + cbase + 32 * i;
-                        if (i < nchunks && m_ok && nb < a.N) {
-                            const uint4* rp = (const uint4*)((const uint8_t*)a.r.ptr + (size_t)m * a.N + nb);
-                            rres[2 * i] = rp[0];
-                            rres[2 * i + 1] = rp[1];
-                        }
+                // Fragment-layout epilogue: every thread owns a few column pairs of 4 rows, so the
+                // per-channel constants are loaded once per 8 values; results are staged in a swizzled
+                // shared-memory region (32 rows x wb bytes per warp) and leave through one TMA store;
+                // the residual operand arrives in the same region through one TMA load and is replaced
+                // in place.
+                const int wb = cols_per_warp;
+                const int ew = warp - EPI_WARP0;
+                unsigned char* region = stage_out + (size_t)ew * 4096;
+                const unsigned region_s = smem_u32(region);
+                const unsigned rb = rbar0 + 8u * ew;
+                const int gx = n0 + cbase, gy = m0 + quad * 32;
+                const bool active = gx < a.N && gy < a.M;
+                if (lane == 0) {
+                    bulk_wait_read_all();   // the previous tile's store has finished reading the region
+                    if (RES && active) {
+                        mbar_expect_tx(rb, (unsigned)(32 * wb));
+                        tma_load_2d(region_s, &tmR, rb, gx, gy);
                     }
                 }
+                __syncwarp();
                 if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
+                if (RES && active) {
+                    if (!mbar_wait(rb, res_it & 1u, abort_flag, a.status, 7)) { ok = false; break; }
+                    ++res_it;
+                }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)cbase;
                 const bool res_unsigned = a.r.is_unsigned != 0;
                 const bool out_unsigned = a.out_unsigned != 0;
-                uint8_t* orow = (uint8_t*)a.out + (size_t)m * a.N + n0 + cbase;
-                // The asynchronous TMEM load is waited for at once: its destination registers must not
-                // stay live across other code (a compiler-inserted move or spill between the load and
-                // the wait would capture stale values).  The second warp on each scheduler hides the
-                // load latency instead.
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (i < nchunks) {
-                        unsigned v[32];
-                        tc_ld32(tbase + 32u * i, v);
-                        tc_wait_ld_into(v);
-                        if (m_ok && n0 + cbase + 32 * i < a.N)
-                            fast_chunk<RES, CLAMP>(v, par, cbase + 32 * i, rres[2 * i], rres[2 * i + 1], res_unsigned,
-                                                   out_unsigned, a.t_lo, a.t_hi, orow + 32 * i);
+                if (wb >= 64) {
+                    for (int cb = 0; cb < wb; cb += 64) {
+                        unsigned vA[32], vB[32];
+                        tc_ld_16x256b_x8(tbase + (unsigned)cb, vA);
+                        tc_ld_16x256b_x8(tbase + (16u << 16) + (unsigned)cb, vB);
+                        tc_wait_ld_into(vA);
+                        tc_wait_ld_into(vB);
+                        if (active)
+                            frag_block<8, RES, CLAMP>(vA, vB, par, cbase + cb, region_s, wb, cb, lane, res_unsigned,
+                                                      out_unsigned, a.t_lo, a.t_hi);
                     }
+                } else {
+                    unsigned vA[16], vB[16];
+                    tc_ld_16x256b_x4(tbase, vA);
+                    tc_ld_16x256b_x4(tbase + (16u << 16), vB);
+                    tc_wait_ld();
+                    reg_fence16(vA);
+                    reg_fence16(vB);
+                    if (active)
+                        frag_block<4, RES, CLAMP>(vA, vB, par, cbase, region_s, wb, 0, lane, res_unsigned, out_unsigned,
+                                                  a.t_lo, a.t_hi);
                 }
+                // the accumulator is drained: hand it back before the store goes out
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8u * as);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0 && active) {
+                    tma_store_2d(&tmO, region_s, gx, gy);
+                    bulk_commit();
+                }
+                continue;
             } else {
                 if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
                 tc_fence_after();
@@ -303,6 +335,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8u * as);
         }
+        // no bulk store may still be reading this CTA's shared memory when it exits
+        if (FAST && lane == 0) bulk_wait_all();
     }
 
     tc_fence_before();
@@ -352,11 +386,12 @@ static CUtensorMapSwizzle swizzle_for(int bk)
 
 static size_t igemm_smem_bytes(int stages, int BK, int BN)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + (2 * stages + 6) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * 4096
+         + (2 * stages + 6 + NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
-int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned,
-                    int force_im2col, int force_bn, int num_sms, const char** why)
+int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
+                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why)
 {
     static const char* kWhy = "";
     *why = kWhy;
@@ -436,6 +471,27 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const Conv
             if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
         }
     }
+    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 32 rows x BN/2 columns
+    plan->has_out_maps = 0;
+    if (out && g.O % 16 == 0 && !((uintptr_t)out & 15) && !((uintptr_t)res & 15)) {
+        const int wb = plan->BN / 2;
+        const cuuint64_t dims[2] = {(cuuint64_t)g.O, (cuuint64_t)plan->M};
+        const cuuint64_t strides[1] = {(cuuint64_t)g.O};
+        const cuuint32_t box[2] = {(cuuint32_t)wb, 32};
+        const cuuint32_t estr[2] = {1, 1};
+        rc = g_encode_tiled(&plan->tmO, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)out, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(wb), CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the output matrix"; return -1; }
+        plan->tmR = plan->tmO;
+        if (res) {
+            rc = g_encode_tiled(&plan->tmR, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)res, dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(wb), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the residual matrix"; return -1; }
+        }
+        plan->has_out_maps = 1;
+    }
     return 0;
 }
 
@@ -465,7 +521,8 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.r = r;
     a.fq = fast.fq; a.fq2 = fast.fq2; a.cpad = fast.cpad; a.t_lo = fast.t_lo; a.t_hi = fast.t_hi;
     a.out_unsigned = fast.out_unsigned;
-    const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2);
+    const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
+                          && plan.has_out_maps;
     const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : 4) : (fast.need_clamp ? 1 : 3));
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -486,11 +543,11 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     // so its per-channel constants are staged once
     if (tiles > grid && a.num_n_tiles > 1 && grid > a.num_n_tiles) grid -= grid % a.num_n_tiles;
     switch (mode) {
-    case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
-    case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
-    case 3: igemm_i8_tcgen05_kernel<3><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
-    case 4: igemm_i8_tcgen05_kernel<4><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
-    default: igemm_i8_tcgen05_kernel<0><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a); break;
+    case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
+    case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
+    case 3: igemm_i8_tcgen05_kernel<3><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
+    case 4: igemm_i8_tcgen05_kernel<4><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
+    default: igemm_i8_tcgen05_kernel<0><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     }
     return cudaGetLastError();
 }

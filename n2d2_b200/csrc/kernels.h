@@ -65,6 +65,9 @@ struct FastQuant {
 struct IgemmPlan {
     CUtensorMap tmA;      // activations: 2-D tiled [M][K] or 4-D im2col NHWC
     CUtensorMap tmB;      // weights [N][Ktot], K-major
+    CUtensorMap tmO;      // output [M][N] bytes, box = 32 rows x BN/2 (TMA store of the epilogue)
+    CUtensorMap tmR;      // residual operand, same geometry (TMA load of the epilogue)
+    int has_out_maps;
     int a_im2col;         // 0: 2-D tiled, 1: im2col
     int M, N;             // GEMM extents (output pixels, output channels)
     int Cin, taps;        // K = taps * Cin, walked tap by tap
@@ -78,8 +81,8 @@ struct IgemmPlan {
     size_t smem_bytes;
 };
 // Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
-int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const ConvGeom& g,
-                    int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
+int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
+                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,
                          void* out, int out_dtype, int* status_word, cudaStream_t s);
 

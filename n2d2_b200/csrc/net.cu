@@ -775,7 +775,9 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             // that is re-encoded on first use
             static char placeholder[16] __attribute__((aligned(16)));
             const void* enc_ptr = in_ptr ? in_ptr : (const void*)placeholder;
-            if (igemm_make_plan(&c.plan, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
+            const void* out_ptr = net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
+            const void* res_ptr = c.residual >= 0 ? tensor_ptr(net, c.residual, nullptr) : nullptr;
+            if (igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
                                 (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why) == 0) {
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
@@ -812,7 +814,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
             ConvGeom gb = c.geom;
             gb.B = net->max_batch;
             const char* why = "";
-            if (igemm_make_plan(&c.plan, in0, c.d_weights, gb, tin.is_unsigned,
+            if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? out : nullptr, r.ptr, gb, tin.is_unsigned,
                                 (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
             c.plan_input = in0;

@@ -220,4 +220,150 @@ __device__ __forceinline__ void fast_chunk(const unsigned* v, const int* par, in
 }
 
 
+
+// ---- TMA store / bulk-group helpers ----
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, unsigned src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tm), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the bulk stores of this thread have finished *reading* shared memory
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// tcgen05.ld 16 lanes x 256 bits, repeated over 8 (x8: 64 columns) or 4 (x4: 32 columns) column groups.
+// Thread t receives, for group i: regs 4i+{0,1} = row (lane0 + t/4), columns 8i + 2(t%4) + {0,1};
+// regs 4i+{2,3} = the same columns of row (lane0 + t/4 + 8).
+__device__ __forceinline__ void tc_ld_16x256b_x8(unsigned taddr, unsigned* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_16x256b_x4(unsigned taddr, unsigned* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void reg_fence16(unsigned* v)
+{
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                      "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :: "memory");
+}
+
+// Byte offset of (row r, byte column c) inside a staging region whose rows are `wb` bytes (32, 64 or
+// 128) and which TMA reads / writes with the swizzle of that width: address bits [4,7) are XORed with
+// bits [7,10) (masked to the swizzle width).  The region base must be 1024-byte aligned.
+__device__ __forceinline__ unsigned swz_off(int r, int c, int wb)
+{
+    const unsigned a = (unsigned)(r * wb + c);
+    return a ^ (((a >> 7) & (unsigned)(wb / 16 - 1)) << 4);
+}
+
+__device__ __forceinline__ void sts_u16(unsigned addr, unsigned v)
+{
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+}
+__device__ __forceinline__ unsigned lds_u16(unsigned addr)
+{
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+    return (unsigned)v;
+}
+
+// NG 8-column groups (NG = 8: 64 columns, NG = 4: 32 columns) of all 32 accumulator rows of a warp in
+// the fragment layout above (vA: rows 0-15, vB: rows 16-31 of the quadrant), through the 32-bit
+// epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  Every thread
+// owns column pair 8i + 2(t%4) of rows t/4 + {0, 8, 16, 24}, so one load of the per-channel constants
+// serves eight values.  `region_s` = shared address of the region (1024-byte aligned), `col0` = first
+// column of the block within the warp's columns (0 or 64), `pcol0` = the same within the tile.
+//
+// Addressing: the byte at (row r, column c) of a region with wb-byte rows sits at
+// r*wb + (c ^ x(r)), x(r) = the swizzle term of row r (address bits [7,10) folded into bits [4,7)).
+// c = col0 | 8i | 2(t%4) has disjoint bit fields, so the address of group i is base(r) ^ 8i.
+template <int NG, bool RES, bool CLAMP>
+__device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, const int* par, int pcol0,
+                                           unsigned region_s, int wb, int col0, int lane, bool res_unsigned,
+                                           bool out_unsigned, int t_lo, int t_hi)
+{
+    const int tr = lane >> 2, tc = (lane & 3) * 2;
+    unsigned base[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const unsigned ro = (unsigned)((tr + 8 * k) * wb);
+        const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
+        base[k] = region_s + ro + ((unsigned)(col0 | tc) ^ xm);
+    }
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+        const int pc = pcol0 + 8 * i + tc;   // column pair within the tile
+        const int2 mu = *(const int2*)&par[2 * 256 + pc];
+        const int2 ad = *(const int2*)&par[3 * 256 + pc];
+        const int2 sh = *(const int2*)&par[4 * 256 + pc];
+        int2 lo = make_int2(0, 0), hi = make_int2(0, 0);
+        if (CLAMP) {
+            lo = *(const int2*)&par[0 * 256 + pc];
+            hi = *(const int2*)&par[1 * 256 + pc];
+        }
+        int2 mu2 = make_int2(0, 0), ad2 = mu2, sh2 = mu2, lo2 = mu2, hi2 = mu2;
+        if (RES) {
+            mu2 = *(const int2*)&par[(FAST_NP + 2) * 256 + pc];
+            ad2 = *(const int2*)&par[(FAST_NP + 3) * 256 + pc];
+            sh2 = *(const int2*)&par[(FAST_NP + 4) * 256 + pc];
+            if (CLAMP) {
+                lo2 = *(const int2*)&par[(FAST_NP + 0) * 256 + pc];
+                hi2 = *(const int2*)&par[(FAST_NP + 1) * 256 + pc];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // rows tr + 8k
+            const unsigned* v = (k < 2) ? vA : vB;
+            int x0 = (int)v[4 * i + 2 * (k & 1)], x1 = (int)v[4 * i + 2 * (k & 1) + 1];
+            if (CLAMP) {
+                x0 = min(max(x0, lo.x), hi.x);
+                x1 = min(max(x1, lo.y), hi.y);
+            }
+            int y0 = (x0 * mu.x + ad.x) >> sh.x;
+            int y1 = (x1 * mu.y + ad.y) >> sh.y;
+            const unsigned addr = base[k] ^ (unsigned)(8 * i);
+            if (RES) {
+                const unsigned rw = lds_u16(addr);   // two residual bytes, replaced below
+                int r0, r1;
+                if (res_unsigned) {
+                    r0 = (int)(rw & 0xffu);
+                    r1 = (int)(rw >> 8);
+                } else {
+                    r0 = byte_extend(rw, 0, false);
+                    r1 = byte_extend(rw, 1, false);
+                }
+                int u0 = min(max(y0, t_lo), t_hi) + r0;
+                int u1 = min(max(y1, t_lo), t_hi) + r1;
+                if (CLAMP) {
+                    u0 = min(max(u0, lo2.x), hi2.x);
+                    u1 = min(max(u1, lo2.y), hi2.y);
+                }
+                y0 = (u0 * mu2.x + ad2.x) >> sh2.x;
+                y1 = (u1 * mu2.y + ad2.y) >> sh2.y;
+            }
+            unsigned d;
+            if (out_unsigned) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
+            else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
+            sts_u16(addr, d);
+        }
+    }
+}
+
 }  // namespace n2d2b
