@@ -24,7 +24,9 @@ namespace n2d2b {
 
 static constexpr int BM = 128;
 static constexpr int EPI_WARP0 = 2;
-static constexpr int NUM_EPI_WARPS = 8;       // two per TMEM lane quadrant, each takes half of the tile's columns
+static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant, each takes a quarter of the tile's columns
+static constexpr int EPI_PARTS = NUM_EPI_WARPS / 4;
+static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 32 rows x up to 64 bytes
 static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
@@ -63,9 +65,9 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int b_stage_bytes = a.BN * a.BK;
     const int stage_bytes = a_stage_bytes + b_stage_bytes;
     unsigned char* tiles = smem;
-    // output staging: one 4 KiB region per epilogue warp (32 rows x up to 128 bytes, swizzled for TMA)
+    // output staging: one region per epilogue warp (32 rows x up to 64 bytes, swizzled for TMA)
     unsigned char* stage_out = smem + (size_t)a.stages * stage_bytes;
-    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * 4096);
+    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[NUM_EPI_WARPS]
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
@@ -182,10 +184,12 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int half = (warp - EPI_WARP0) >> 2;        // which half of the tile's columns
+        const int part = (warp - EPI_WARP0) >> 2;        // which slice of the tile's columns
         const int row = quad * 32 + lane;
         const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
-        const int cols_per_warp = a.BN / 2;
+        // the 32-bit epilogue splits the columns over all warps of a quadrant; the exact 64-bit one works
+        // in 32-column chunks and uses the first two warps of each quadrant
+        const int cols_per_warp = FAST ? a.BN / EPI_PARTS : a.BN / 2;
         unsigned acc_it = 0;
         unsigned stage_it = 0;
         unsigned res_it = 0;
@@ -220,7 +224,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int m = m0 + row;
             const bool m_ok = m < a.M;
             const int nchunks = cols_per_warp / 32;
-            const int cbase = half * cols_per_warp;
+            const int cbase = part * cols_per_warp;
             if (FAST) {
                 // Fragment-layout epilogue: every thread owns a few column pairs of 4 rows, so the
                 // per-channel constants are loaded once per 8 values; results are staged in a swizzled
@@ -229,7 +233,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 // in place.
                 const int wb = cols_per_warp;
                 const int ew = warp - EPI_WARP0;
-                unsigned char* region = stage_out + (size_t)ew * 4096;
+                unsigned char* region = stage_out + (size_t)ew * REGION_BYTES;
                 const unsigned region_s = smem_u32(region);
                 const unsigned rb = rbar0 + 8u * ew;
                 const int gx = n0 + cbase, gy = m0 + quad * 32;
@@ -251,26 +255,27 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)cbase;
                 const bool res_unsigned = a.r.is_unsigned != 0;
                 const bool out_unsigned = a.out_unsigned != 0;
-                if (wb >= 64) {
-                    for (int cb = 0; cb < wb; cb += 64) {
-                        unsigned vA[32], vB[32];
-                        tc_ld_16x256b_x8(tbase + (unsigned)cb, vA);
-                        tc_ld_16x256b_x8(tbase + (16u << 16) + (unsigned)cb, vB);
-                        tc_wait_ld_into(vA);
-                        tc_wait_ld_into(vB);
+                if (wb >= 32) {
+                    for (int cb = 0; cb < wb; cb += 32) {
+                        unsigned vA[16], vB[16];
+                        tc_ld_16x256b_x4(tbase + (unsigned)cb, vA);
+                        tc_ld_16x256b_x4(tbase + (16u << 16) + (unsigned)cb, vB);
+                        tc_wait_ld();
+                        reg_fence16(vA);
+                        reg_fence16(vB);
                         if (active)
-                            frag_block<8, RES, CLAMP>(vA, vB, par, cbase + cb, region_s, wb, cb, lane, res_unsigned,
+                            frag_block<4, RES, CLAMP>(vA, vB, par, cbase + cb, region_s, wb, cb, lane, res_unsigned,
                                                       out_unsigned, a.t_lo, a.t_hi);
                     }
                 } else {
-                    unsigned vA[16], vB[16];
-                    tc_ld_16x256b_x4(tbase, vA);
-                    tc_ld_16x256b_x4(tbase + (16u << 16), vB);
+                    unsigned vA[8], vB[8];
+                    tc_ld_16x256b_x2(tbase, vA);
+                    tc_ld_16x256b_x2(tbase + (16u << 16), vB);
                     tc_wait_ld();
-                    reg_fence16(vA);
-                    reg_fence16(vB);
+                    reg_fence8(vA);
+                    reg_fence8(vB);
                     if (active)
-                        frag_block<4, RES, CLAMP>(vA, vB, par, cbase, region_s, wb, 0, lane, res_unsigned, out_unsigned,
+                        frag_block<2, RES, CLAMP>(vA, vB, par, cbase, region_s, wb, 0, lane, res_unsigned, out_unsigned,
                                                   a.t_lo, a.t_hi);
                 }
                 // the accumulator is drained: hand it back before the store goes out
@@ -287,7 +292,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             } else {
                 if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
                 tc_fence_after();
-                for (int cc = 0; cc < cols_per_warp; cc += 32) {
+                for (int cc = 0; cc < cols_per_warp && part < 2; cc += 32) {
                     const int c0 = cbase + cc;
                     unsigned v[32];
                     const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)c0;
@@ -381,12 +386,13 @@ static int load_driver_entry_points(const char** why)
 
 static CUtensorMapSwizzle swizzle_for(int bk)
 {
-    return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+         : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
 }
 
 static size_t igemm_smem_bytes(int stages, int BK, int BN)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * 4096
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * REGION_BYTES
          + (2 * stages + 6 + NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
@@ -471,10 +477,10 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
             if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
         }
     }
-    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 32 rows x BN/2 columns
+    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 32 rows x BN/4 columns
     plan->has_out_maps = 0;
     if (out && g.O % 16 == 0 && !((uintptr_t)out & 15) && !((uintptr_t)res & 15)) {
-        const int wb = plan->BN / 2;
+        const int wb = plan->BN / EPI_PARTS;
         const cuuint64_t dims[2] = {(cuuint64_t)g.O, (cuuint64_t)plan->M};
         const cuuint64_t strides[1] = {(cuuint64_t)g.O};
         const cuuint32_t box[2] = {(cuuint32_t)wb, 32};

@@ -157,21 +157,29 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const StemArgs
             }
             const int ix0 = ox * a.sX - a.pL, iy0 = oy * a.sY - a.pT;
             unsigned char* stage = smA + (size_t)s * a_stage_bytes;
-            for (int ky = 0; ky < a.nkb * 4; ++ky) {
-                uint32_t w[8];
-                const int iy = iy0 + ky;
-                const bool row_ok = m_ok && ky < a.kH && iy >= 0 && iy < a.H;
-                const uint32_t* rowp = in4 + ((size_t)n * a.H + (row_ok ? iy : 0)) * a.W;
+            // one 128-byte K block (four kernel rows) at a time: all 32 loads are issued before the first
+            // store so that a tile costs one memory latency per K block, not one per kernel row
+            for (int kb = 0; kb < a.nkb; ++kb) {
+                uint32_t w[4][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int ix = ix0 + j;
-                    w[j] = (row_ok && j < a.kW && ix >= 0 && ix < a.W) ? rowp[ix] : 0u;
+                for (int q = 0; q < 4; ++q) {
+                    const int ky = kb * 4 + q;
+                    const int iy = iy0 + ky;
+                    const bool row_ok = m_ok && ky < a.kH && iy >= 0 && iy < a.H;
+                    const uint32_t* rowp = in4 + ((size_t)n * a.H + (row_ok ? iy : 0)) * a.W;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int ix = ix0 + j;
+                        w[q][j] = (row_ok && j < a.kW && ix >= 0 && ix < a.W) ? __ldg(rowp + ix) : 0u;
+                    }
                 }
-                const int kb = ky >> 2;
-                const int c = (ky & 3) * 2;   // 16-byte chunk index of this kernel row within the 128-byte row
                 unsigned char* rowbase = stage + (size_t)kb * SBM * 128 + (size_t)r * 128;
-                *(uint4*)(rowbase + (((c + 0) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                *(uint4*)(rowbase + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    // kernel row q of the block occupies 16-byte chunks 2q and 2q+1 of the 128-byte row
+                    *(uint4*)(rowbase + (((2 * q + 0) ^ (r & 7)) << 4)) = make_uint4(w[q][0], w[q][1], w[q][2], w[q][3]);
+                    *(uint4*)(rowbase + (((2 * q + 1) ^ (r & 7)) << 4)) = make_uint4(w[q][4], w[q][5], w[q][6], w[q][7]);
+                }
             }
             // make the generic-proxy stores visible to the tensor core (async proxy), then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -257,6 +257,18 @@ __device__ __forceinline__ void tc_ld_16x256b_x4(unsigned taddr, unsigned* v)
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld_16x256b_x2(unsigned taddr, unsigned* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void reg_fence8(unsigned* v)
+{
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+                 :: "memory");
+}
 __device__ __forceinline__ void reg_fence16(unsigned* v)
 {
     asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
@@ -289,7 +301,7 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 // epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  Every thread
 // owns column pair 8i + 2(t%4) of rows t/4 + {0, 8, 16, 24}, so one load of the per-channel constants
 // serves eight values.  `region_s` = shared address of the region (1024-byte aligned), `col0` = first
-// column of the block within the warp's columns (0 or 64), `pcol0` = the same within the tile.
+// column of the block within the warp's columns (a multiple of 8*NG), `pcol0` = the same within the tile.
 //
 // Addressing: the byte at (row r, column c) of a region with wb-byte rows sits at
 // r*wb + (c ^ x(r)), x(r) = the swizzle term of row r (address bits [7,10) folded into bits [4,7)).
