@@ -107,6 +107,12 @@ struct n2d2b_net {
     const void* last_input = nullptr;
     void* d_stage_in = nullptr;   // device staging of the host-buffer entry point
     void* d_stage_out = nullptr;
+    // host-buffer entry point: the upload is cut into slices on its own stream so that the leading
+    // cells (which need no tensor map and work slice by slice) run while later slices still arrive
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t slice_ready[8] = {nullptr};
+    cudaEvent_t stage_free = nullptr;
+    int head_cells = 0;
 };
 
 static int validate_quant(const n2d2b_quant* qu, int channels, bool accumulators_have_bias, QuantHost& q,
@@ -423,6 +429,10 @@ void n2d2b_net_destroy(n2d2b_net* net)
     cudaFree(net->d_status);
     cudaFree(net->d_stage_in);
     cudaFree(net->d_stage_out);
+    if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    for (cudaEvent_t e : net->slice_ready)
+        if (e) cudaEventDestroy(e);
+    if (net->stage_free) cudaEventDestroy(net->stage_free);
     delete net;
 }
 
@@ -790,18 +800,40 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     CUDA_TRY(cudaMalloc(&net->d_stage_in, net->tensors[0].bytes_per_image() * (size_t)max_batch + 256));
     CUDA_TRY(cudaMalloc(&net->d_stage_out,
                         net->tensors[final_tensor_of(net)].bytes_per_image() * (size_t)max_batch + 256));
+    CUDA_TRY(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+    for (cudaEvent_t& e : net->slice_ready) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&net->stage_free, cudaEventDisableTiming));
+    // leading cells that take plain pointers (no tensor map over the whole batch) and read only the
+    // stimuli or the previous cell: they can run on a slice of the batch
+    net->head_cells = 0;
+    for (size_t ci = 0; ci < net->cells.size(); ++ci) {
+        const CellRec& c = net->cells[ci];
+        const bool sliceable = !c.skipped && c.residual < 0 && c.inputs.size() == 1
+                               && c.inputs[0] == (ci == 0 ? 0 : net->cells[ci - 1].output) && c.type != CELL_FC
+                               && (c.engine == ENG_STEM || c.engine == ENG_POOL || c.engine == ENG_DEPTHWISE
+                                   || c.engine == ENG_SIMT);
+        if (!sliceable) break;
+        net->head_cells = (int)ci + 1;
+    }
     net->finalized = true;
     return 0;
 }
 
 // ---- forward --------------------------------------------------------------------------------
-static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, cudaStream_t s)
+// Runs one cell on images [img0, img0 + batch) of the batch (img0 != 0 only for cells without tensor maps).
+static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, cudaStream_t s, int img0 = 0)
 {
     const void* in0 = tensor_ptr(net, c.inputs[0], d_input);
     void* out = tensor_ptr(net, c.output, d_input);
     const TensorRec& tin = net->tensors[c.inputs[0]];
     const TensorRec& tout = net->tensors[c.output];
     if (!in0 || !out) return fail(N2D2B_ERR_STATE, "internal: tensor without a buffer");
+    if (img0) {
+        if (c.engine == ENG_TCGEN05 || c.engine == ENG_SUM || c.residual >= 0)
+            return fail(N2D2B_ERR_STATE, "internal: this cell cannot run on a slice");
+        in0 = (const uint8_t*)in0 + (size_t)img0 * tin.bytes_per_image();
+        out = (uint8_t*)out + (size_t)img0 * tout.bytes_per_image();
+    }
     Residual r{};
     if (c.residual >= 0) {
         r.ptr = tensor_ptr(net, c.residual, d_input);
@@ -829,8 +861,9 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         g.B = batch;
         const void* in4 = in0;
         if (c.d_pad4) {
-            CUDA_TRY(launch_pad_channels(in0, g.C, (size_t)batch * g.H * g.W, c.d_pad4, s));
-            in4 = c.d_pad4;
+            void* pad = (uint8_t*)c.d_pad4 + (size_t)img0 * g.H * g.W * 4;
+            CUDA_TRY(launch_pad_channels(in0, g.C, (size_t)batch * g.H * g.W, pad, s));
+            in4 = pad;
         }
         CUDA_TRY(launch_stem(c.stem, in4, g, c.fast, out, net->d_status, s));
         break;
@@ -875,7 +908,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
 }
 
 static int forward_impl(n2d2b_net* net, const void* d_input, int batch, void* d_output, cudaStream_t s, float* ms,
-                        int nb_cells)
+                        int nb_cells, int first_cell = 0)
 {
     if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
     if (!net->finalized) return fail(N2D2B_ERR_STATE, "forward before finalize");
@@ -892,7 +925,7 @@ static int forward_impl(n2d2b_net* net, const void* d_input, int batch, void* d_
         for (auto& e : ev) CUDA_TRY(cudaEventCreate(&e));
         CUDA_TRY(cudaEventRecord(ev[0], s));
     }
-    for (size_t ci = 0; ci < net->cells.size(); ++ci) {
+    for (size_t ci = (size_t)first_cell; ci < net->cells.size(); ++ci) {
         CellRec& c = net->cells[ci];
         if (!c.skipped)
             if (int rc = run_cell(net, c, d_input, batch, s)) return rc;
@@ -952,8 +985,26 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
     const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
     void* d_in = net->d_stage_in;
     void* d_out = net->d_stage_out;
-    CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
-    if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0)) return rc;
+    const int nslices = (net->head_cells > 0 && batch >= 256) ? 8 : 1;
+    if (nslices == 1) {
+        CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
+        if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0)) return rc;
+    } else {
+        // the staging buffer may still be read by work queued on `s` by an earlier call
+        CUDA_TRY(cudaEventRecord(net->stage_free, s));
+        CUDA_TRY(cudaStreamWaitEvent(net->copy_stream, net->stage_free, 0));
+        const size_t img_bytes = net->tensors[0].bytes_per_image();
+        for (int k = 0; k < nslices; ++k) {
+            const int b0 = (int)((long long)batch * k / nslices), b1 = (int)((long long)batch * (k + 1) / nslices);
+            CUDA_TRY(cudaMemcpyAsync((uint8_t*)d_in + (size_t)b0 * img_bytes, (const uint8_t*)h_input + (size_t)b0 * img_bytes,
+                                     (size_t)(b1 - b0) * img_bytes, cudaMemcpyHostToDevice, net->copy_stream));
+            CUDA_TRY(cudaEventRecord(net->slice_ready[k], net->copy_stream));
+            CUDA_TRY(cudaStreamWaitEvent(s, net->slice_ready[k], 0));
+            for (int ci = 0; ci < net->head_cells; ++ci)
+                if (int rc = run_cell(net, net->cells[ci], d_in, b1 - b0, s, b0)) return rc;
+        }
+        if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0, net->head_cells)) return rc;
+    }
     CUDA_TRY(cudaMemcpyAsync(h_output, d_out, out_bytes, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaStreamSynchronize(s));
     return check_status(net);
