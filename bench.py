@@ -119,7 +119,7 @@ def cpu_baseline(net, seconds_budget=20.0):
     from oracle import oracle, refshim
     use_ref = refshim.available()
     run = (lambda x: refshim.run_net(net, x)) if use_ref else (lambda x: oracle.run_net(net, x, 'f32'))
-    cores = oracle.num_threads()
+    cores = oracle.use_all_cores()
     x1 = netdesc.make_input(net, 1, seed=99)
     t = time.perf_counter(); run(x1); dt1 = time.perf_counter() - t
     n = int(max(1, min(64, seconds_budget / max(dt1, 1e-3) / 2)))
@@ -139,6 +139,7 @@ def run_reference(args):
     from oracle import oracle, refshim
     net = build_net(args)
     use_ref = refshim.available()
+    cores = oracle.use_all_cores()
     run = (lambda x: refshim.run_net(net, x)) if use_ref else (lambda x: oracle.run_net(net, x, 'f32'))
     n = args.ref_images
     x = netdesc.make_input(net, n, seed=100)
@@ -154,7 +155,7 @@ def run_reference(args):
             'warmup': args.warmup, 'ms_per_step': dt / args.steps * 1e3, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': None, 'dtype': 'f32 holding integers (reference CPU path)', 'data': 'synthetic',
             'config': dict(workload_config(args, net, world), sample_images_per_step=n),
-            'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': oracle.num_threads(),
+            'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': cores,
                              'kind': 'reference' if use_ref else 'port',
                              'sample': f'{n} images per step x {args.steps} steps'},
             'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},

@@ -63,6 +63,17 @@ static inline float n2d2o_clipf(float v, float clip)
 #undef FN
 #undef IS_FLOAT
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline wants every host core. */
+void n2d2o_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int n2d2o_num_threads(void)
 {
 #ifdef _OPENMP

@@ -10,6 +10,7 @@ extern "C" {
 int n2d2o_conv_out_dim(int in, int k, int stride, int pad0, int pad1, int dil);
 int n2d2o_pool_out_dim(int in, int pool, int stride, int pad);
 int n2d2o_num_threads(void);
+void n2d2o_set_num_threads(int n);
 
 #define N2D2O_DECLARE(T, S)                                                                        \
     void n2d2o_conv_##S(const T* in, int inW, int inH, int inC, int B, const T* w, int kW, int kH, \

@@ -46,6 +46,17 @@ def num_threads():
     return lib().n2d2o_num_threads()
 
 
+def use_all_cores():
+    """Makes the OpenMP runtime (shared with the reference shim) use every core this process may run on,
+    whatever OMP_NUM_THREADS the launcher exported. Returns the thread count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().n2d2o_set_num_threads(n)
+    return num_threads()
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
