@@ -24,9 +24,8 @@ namespace n2d2b {
 
 static constexpr int BM = 128;
 static constexpr int EPI_WARP0 = 2;
-static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant, each takes a quarter of the tile's columns
-static constexpr int EPI_PARTS = NUM_EPI_WARPS / 4;
-static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 32 rows x up to 64 bytes
+static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant: 2 halves of its 32 rows x up to 2 column halves
+static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 16 rows x up to 128 bytes
 static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
@@ -46,6 +45,8 @@ struct IgemmArgs {
     int cpad;
     int t_lo, t_hi;     // saturation range of the cell's own output (before the residual add)
     int out_unsigned;   // final 8-bit range: 1 = [0,255], 0 = [-128,127]
+    unsigned dp_xor;    // dot-product form of the residual stage: byte flips and operand signedness
+    int dp_a_signed;
 };
 
 // ----------------------------------------------------------------------------- the kernel
@@ -56,8 +57,9 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         const IgemmArgs a)
 {
     constexpr bool FAST = MODE != 0;
-    constexpr bool RES = (MODE == 2 || MODE == 4);
+    constexpr bool RES = (MODE == 2 || MODE == 4 || MODE == 5);
     constexpr bool CLAMP = (MODE == 1 || MODE == 2);
+    constexpr bool DP = (MODE == 5);
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment of the tile ring (required by the 128-byte swizzle)
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -67,15 +69,17 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     unsigned char* tiles = smem;
     // output staging: one region per epilogue warp (32 rows x up to 64 bytes, swizzled for TMA)
     unsigned char* stage_out = smem + (size_t)a.stages * stage_bytes;
-    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES);
-    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[NUM_EPI_WARPS]
+    // cells with a fused residual keep two regions per warp so that the next tile's residual can arrive early
+    const int regions_per_warp = RES ? 2 : 1;
+    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES * regions_per_warp);
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[2 * NUM_EPI_WARPS]
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
     const unsigned tfull0 = empty0 + 8u * a.stages;
     const unsigned tempty0 = tfull0 + 16u;
     const unsigned pready0 = tempty0 + 16u;
     const unsigned rbar0 = pready0 + 16u;
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + NUM_EPI_WARPS);
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 2 * NUM_EPI_WARPS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -93,7 +97,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
             mbar_init(pready0 + 8u * s, 32 * NUM_EPI_WARPS);
         }
-        for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
+        for (int w = 0; w < 2 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -184,15 +188,17 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int part = (warp - EPI_WARP0) >> 2;        // which slice of the tile's columns
+        const int part = (warp - EPI_WARP0) >> 2;        // 0..3 within the quadrant
+        const int rh = part & 1;                         // which 16 of the quadrant's 32 rows (32-bit epilogue)
+        const int col_parts = a.BN > 128 ? 2 : 1;        // column halves (32-bit epilogue): rows stay <= 128 bytes
         const int row = quad * 32 + lane;
         const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
         // the 32-bit epilogue splits the columns over all warps of a quadrant; the exact 64-bit one works
         // in 32-column chunks and uses the first two warps of each quadrant
-        const int cols_per_warp = FAST ? a.BN / EPI_PARTS : a.BN / 2;
+        const int cols_per_warp = FAST ? a.BN / col_parts : a.BN / 2;
         unsigned acc_it = 0;
         unsigned stage_it = 0;
-        unsigned res_it = 0;
+        EpiState est;
         int staged_n_tile = -1;
         int* par = epi_params;
         bool ok = true;
@@ -224,70 +230,27 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int m = m0 + row;
             const bool m_ok = m < a.M;
             const int nchunks = cols_per_warp / 32;
-            const int cbase = part * cols_per_warp;
+            const int cbase = FAST ? (part >> 1) * cols_per_warp : part * cols_per_warp;
             if (FAST) {
-                // Fragment-layout epilogue: every thread owns a few column pairs of 4 rows, so the
-                // per-channel constants are loaded once per 8 values; results are staged in a swizzled
-                // shared-memory region (32 rows x wb bytes per warp) and leave through one TMA store;
-                // the residual operand arrives in the same region through one TMA load and is replaced
-                // in place.
-                const int wb = cols_per_warp;
+                // fragment-layout epilogue with swizzled staging, TMA store and TMA residual load
                 const int ew = warp - EPI_WARP0;
-                unsigned char* region = stage_out + (size_t)ew * REGION_BYTES;
-                const unsigned region_s = smem_u32(region);
-                const unsigned rb = rbar0 + 8u * ew;
-                const int gx = n0 + cbase, gy = m0 + quad * 32;
-                const bool active = gx < a.N && gy < a.M;
-                if (lane == 0) {
-                    bulk_wait_read_all();   // the previous tile's store has finished reading the region
-                    if (RES && active) {
-                        mbar_expect_tx(rb, (unsigned)(32 * wb));
-                        tma_load_2d(region_s, &tmR, rb, gx, gy);
-                    }
+                EpiTile e;
+                e.tmem_acc = tmem_base + as * (unsigned)a.BN;
+                e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = m0; e.n0 = n0;
+                e.par = par;
+                e.region_p = stage_out + (size_t)ew * REGION_BYTES * regions_per_warp;
+                e.region_stride = RES ? REGION_BYTES : 0;
+                e.rbar = rbar0 + 16u * ew;
+                {
+                    const int nt = tile + (int)gridDim.x;
+                    e.next_m0 = nt < num_tiles ? (nt / a.num_n_tiles) * BM : -1;
+                    e.next_n0 = nt < num_tiles ? (nt % a.num_n_tiles) * a.BN : 0;
                 }
-                __syncwarp();
-                if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
-                if (RES && active) {
-                    if (!mbar_wait(rb, res_it & 1u, abort_flag, a.status, 7)) { ok = false; break; }
-                    ++res_it;
-                }
-                tc_fence_after();
-                const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.BN + (unsigned)cbase;
-                const bool res_unsigned = a.r.is_unsigned != 0;
-                const bool out_unsigned = a.out_unsigned != 0;
-                if (wb >= 32) {
-                    for (int cb = 0; cb < wb; cb += 32) {
-                        unsigned vA[16], vB[16];
-                        tc_ld_16x256b_x4(tbase + (unsigned)cb, vA);
-                        tc_ld_16x256b_x4(tbase + (16u << 16) + (unsigned)cb, vB);
-                        tc_wait_ld();
-                        reg_fence16(vA);
-                        reg_fence16(vB);
-                        if (active)
-                            frag_block<4, RES, CLAMP>(vA, vB, par, cbase + cb, region_s, wb, cb, lane, res_unsigned,
-                                                      out_unsigned, a.t_lo, a.t_hi);
-                    }
-                } else {
-                    unsigned vA[8], vB[8];
-                    tc_ld_16x256b_x2(tbase, vA);
-                    tc_ld_16x256b_x2(tbase + (16u << 16), vB);
-                    tc_wait_ld();
-                    reg_fence8(vA);
-                    reg_fence8(vB);
-                    if (active)
-                        frag_block<2, RES, CLAMP>(vA, vB, par, cbase, region_s, wb, 0, lane, res_unsigned, out_unsigned,
-                                                  a.t_lo, a.t_hi);
-                }
-                // the accumulator is drained: hand it back before the store goes out
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8u * as);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0 && active) {
-                    tma_store_2d(&tmO, region_s, gx, gy);
-                    bulk_commit();
-                }
+                e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
+                e.abort_flag = abort_flag; e.status = a.status;
+                e.res_unsigned = a.r.is_unsigned != 0; e.out_unsigned = a.out_unsigned != 0;
+                e.dp_a_signed = a.dp_a_signed != 0; e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
+                if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, rh, part >> 1, lane, est)) { ok = false; break; }
                 continue;
             } else {
                 if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
@@ -390,10 +353,10 @@ static CUtensorMapSwizzle swizzle_for(int bk)
          : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
 }
 
-static size_t igemm_smem_bytes(int stages, int BK, int BN)
+static size_t igemm_smem_bytes(int stages, int BK, int BN, int with_res)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * REGION_BYTES
-         + (2 * stages + 6 + NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * REGION_BYTES * (with_res ? 2 : 1)
+         + (2 * stages + 6 + 2 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
@@ -424,9 +387,10 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     plan->sX = g.sX; plan->sY = g.sY; plan->pL = g.pL; plan->pT = g.pT; plan->dX = g.dX; plan->dY = g.dY;
     // pipeline depth: fill up to ~200 KB of shared memory, at most 8 stages
     int stages = 8;
-    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN) > 224 * 1024) --stages;
+    const int with_res = res ? 1 : 0;
+    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res) > 226 * 1024) --stages;
     plan->stages = stages;
-    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN);
+    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, with_res);
     const int num_m_tiles = (plan->M + BM - 1) / BM;
     const int num_n_tiles = (plan->N + plan->BN - 1) / plan->BN;
     const long long tiles = (long long)num_m_tiles * num_n_tiles;
@@ -477,13 +441,13 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
             if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
         }
     }
-    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 32 rows x BN/4 columns
+    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 16 rows x up to 128 columns
     plan->has_out_maps = 0;
     if (out && g.O % 16 == 0 && !((uintptr_t)out & 15) && !((uintptr_t)res & 15)) {
-        const int wb = plan->BN / EPI_PARTS;
+        const int wb = plan->BN > 128 ? plan->BN / 2 : plan->BN;
         const cuuint64_t dims[2] = {(cuuint64_t)g.O, (cuuint64_t)plan->M};
         const cuuint64_t strides[1] = {(cuuint64_t)g.O};
-        const cuuint32_t box[2] = {(cuuint32_t)wb, 32};
+        const cuuint32_t box[2] = {(cuuint32_t)wb, 16};
         const cuuint32_t estr[2] = {1, 1};
         rc = g_encode_tiled(&plan->tmO, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)out, dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(wb), CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -527,16 +491,18 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.r = r;
     a.fq = fast.fq; a.fq2 = fast.fq2; a.cpad = fast.cpad; a.t_lo = fast.t_lo; a.t_hi = fast.t_hi;
     a.out_unsigned = fast.out_unsigned;
+    a.dp_xor = fast.dp_xor;
+    a.dp_a_signed = fast.dp_a_signed;
     const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
                           && plan.has_out_maps;
-    const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : 4) : (fast.need_clamp ? 1 : 3));
+    const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : (fast.dp4a ? 5 : 4)) : (fast.need_clamp ? 1 : 3));
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        const void* variants[5] = {(const void*)igemm_i8_tcgen05_kernel<0>, (const void*)igemm_i8_tcgen05_kernel<1>,
+        const void* variants[6] = {(const void*)igemm_i8_tcgen05_kernel<0>, (const void*)igemm_i8_tcgen05_kernel<1>,
                                    (const void*)igemm_i8_tcgen05_kernel<2>, (const void*)igemm_i8_tcgen05_kernel<3>,
-                                   (const void*)igemm_i8_tcgen05_kernel<4>};
+                                   (const void*)igemm_i8_tcgen05_kernel<4>, (const void*)igemm_i8_tcgen05_kernel<5>};
         for (const void* fn : variants) {
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return e;
@@ -553,6 +519,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     case 3: igemm_i8_tcgen05_kernel<3><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     case 4: igemm_i8_tcgen05_kernel<4><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
+    case 5: igemm_i8_tcgen05_kernel<5><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     default: igemm_i8_tcgen05_kernel<0><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     }
     return cudaGetLastError();

@@ -308,7 +308,7 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
     return true;
 }
 
-static int upload_fast(CellRec& c, const TensorRec& tout)
+static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8 = false, int residual_unsigned = 0)
 {
     c.fast = FastQuant{};
     if (tout.dtype != DT_I8) return 0;
@@ -323,6 +323,30 @@ static int upload_fast(CellRec& c, const TensorRec& tout)
     if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) return 0;
     bool with_res = c.residual >= 0;
     if (with_res && !build_fast_quant(c.q2, cpad, 512, f2, &lo2, &hi2, &need_clamp)) return 0;
+    // Dot-product form of the residual stage (see frag_block): every multiplier of the sum's scaling fits
+    // a byte, both operands have a native 8-bit range and no clamp is needed.
+    bool dp4a = false;
+    unsigned dp_xor = 0;
+    int dp_a_signed = 1;
+    if (with_res && !need_clamp && residual_dtype_i8) {
+        const bool t_uns = (lo1 == 0 && hi1 == 255), t_sig = (lo1 == -128 && hi1 == 127);
+        bool small = true;
+        for (int ch = 0; ch < C; ++ch) small = small && f2[(size_t)2 * cpad + ch] >= 0 && f2[(size_t)2 * cpad + ch] <= 255;
+        if ((t_uns || t_sig) && small) {
+            dp4a = true;
+            const bool flip = (t_uns != (residual_unsigned != 0));
+            dp_a_signed = (t_uns && residual_unsigned) ? 0 : 1;
+            // the byte vector is [t0, t1, r0, r1]: flip the unsigned pair when the two differ
+            if (flip) dp_xor = t_uns ? 0x00008080u : 0x80800000u;
+            for (int ch = 0; ch < cpad; ++ch) {
+                const long long m2 = f2[(size_t)2 * cpad + ch];
+                // row 0 of the residual set: the multiplier in the byte lanes of this column (even column:
+                // lanes 0 and 2 = t0 and r0; odd column: lanes 1 and 3)
+                f2[(size_t)0 * cpad + ch] = (int32_t)((ch & 1) ? (m2 << 8 | m2 << 24) : (m2 | m2 << 16));
+                if (flip) f2[(size_t)3 * cpad + ch] += (int32_t)(128 * m2);
+            }
+        }
+    }
     const size_t words = f1.size() + f2.size();
     CUDA_TRY(cudaMalloc((void**)&c.d_fast, words * 4 + 16));
     CUDA_TRY(cudaMemcpy(c.d_fast, f1.data(), f1.size() * 4, cudaMemcpyHostToDevice));
@@ -334,6 +358,9 @@ static int upload_fast(CellRec& c, const TensorRec& tout)
     c.fast.t_hi = hi1;
     c.fast.out_unsigned = with_res ? c.q2.out_unsigned : c.q.out_unsigned;
     c.fast.need_clamp = need_clamp;
+    c.fast.dp4a = dp4a;
+    c.fast.dp_xor = dp_xor;
+    c.fast.dp_a_signed = dp_a_signed;
     c.fast.enabled = true;
     return 0;
 }
@@ -792,8 +819,12 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
                 c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
-                if (!(flags & N2D2B_EXACT64_EPILOGUE))
-                    if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+                if (!(flags & N2D2B_EXACT64_EPILOGUE)) {
+                    const bool res_i8 = c.residual >= 0 && net->tensors[c.residual].dtype == DT_I8;
+                    if (int rc = upload_fast(c, net->tensors[c.output], res_i8,
+                                             c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0))
+                        return rc;
+                }
             }
         }
     }

@@ -296,8 +296,8 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
     return (unsigned)v;
 }
 
-// NG 8-column groups (NG = 8: 64 columns, NG = 4: 32 columns) of all 32 accumulator rows of a warp in
-// the fragment layout above (vA: rows 0-15, vB: rows 16-31 of the quadrant), through the 32-bit
+// NG 8-column groups (NG = 8: 64 columns, NG = 4: 32 columns) of 16 (NK = 2, vA only) or 32 (NK = 4)
+// accumulator rows in the fragment layout above (vA: rows 0-15, vB: rows 16-31 of the region), through the 32-bit
 // epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  Every thread
 // owns column pair 8i + 2(t%4) of rows t/4 + {0, 8, 16, 24}, so one load of the per-channel constants
 // serves eight values.  `region_s` = shared address of the region (1024-byte aligned), `col0` = first
@@ -306,18 +306,32 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 // Addressing: the byte at (row r, column c) of a region with wb-byte rows sits at
 // r*wb + (c ^ x(r)), x(r) = the swizzle term of row r (address bits [7,10) folded into bits [4,7)).
 // c = col0 | 8i | 2(t%4) has disjoint bit fields, so the address of group i is base(r) ^ 8i.
-template <int NG, bool RES, bool CLAMP>
+// DP (with RES, without CLAMP): the second requantisation of a shift scaling, (t + r) * m2 + add2, is one
+// four-way byte dot product per value: the saturating pack that clamps t also places the two residual
+// bytes beside it, a = [t0, t1, r0, r1], and b = [m2, 0, m2, 0] (resp. [0, m2, 0, m2]) selects one
+// column.  When t and r differ in signedness the unsigned pair is flipped to signed by xor 0x80 and the
+// host adds 128 * m2 to add2.  dp_xor / dp_a_signed / t_unsigned describe that choice.
+template <int NG, bool RES, bool CLAMP, bool DP, int NK = 4>
 __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, const int* par, int pcol0,
-                                           unsigned region_s, int wb, int col0, int lane, bool res_unsigned,
-                                           bool out_unsigned, int t_lo, int t_hi)
+                                           unsigned char* region, int wb, int col0, int lane, bool res_unsigned,
+                                           bool out_unsigned, int t_lo, int t_hi, unsigned dp_xor = 0,
+                                           bool dp_a_signed = true, bool t_unsigned = false)
 {
     const int tr = lane >> 2, tc = (lane & 3) * 2;
-    unsigned base[4];
+    unsigned base[NK];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < NK; ++k) {
         const unsigned ro = (unsigned)((tr + 8 * k) * wb);
         const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
-        base[k] = region_s + ro + ((unsigned)(col0 | tc) ^ xm);
+        base[k] = ro + ((unsigned)(col0 | tc) ^ xm);
+    }
+    // the residual bytes of the whole block first: plain loads the compiler can keep in flight together
+    unsigned rres[NG][NK];
+    if (RES) {
+#pragma unroll
+        for (int i = 0; i < NG; ++i)
+#pragma unroll
+            for (int k = 0; k < NK; ++k) rres[i][k] = *(const unsigned short*)(region + (base[k] ^ (unsigned)(8 * i)));
     }
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
@@ -339,9 +353,10 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
                 lo2 = *(const int2*)&par[(FAST_NP + 0) * 256 + pc];
                 hi2 = *(const int2*)&par[(FAST_NP + 1) * 256 + pc];
             }
+            if (DP) lo2 = *(const int2*)&par[(FAST_NP + 0) * 256 + pc];
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {   // rows tr + 8k
+        for (int k = 0; k < NK; ++k) {   // rows tr + 8k
             const unsigned* v = (k < 2) ? vA : vB;
             int x0 = (int)v[4 * i + 2 * (k & 1)], x1 = (int)v[4 * i + 2 * (k & 1) + 1];
             if (CLAMP) {
@@ -351,8 +366,25 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
             int y0 = (x0 * mu.x + ad.x) >> sh.x;
             int y1 = (x1 * mu.y + ad.y) >> sh.y;
             const unsigned addr = base[k] ^ (unsigned)(8 * i);
-            if (RES) {
-                const unsigned rw = lds_u16(addr);   // two residual bytes, replaced below
+            if (RES && DP) {
+                const unsigned rw = rres[i][k];   // two residual bytes, replaced below
+                unsigned a4;
+                if (t_unsigned) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(a4) : "r"(y1), "r"(y0), "r"(rw));
+                else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(a4) : "r"(y1), "r"(y0), "r"(rw));
+                a4 ^= dp_xor;
+                // lo2 row holds the column-selecting multiplier words, ad2 the (compensated) addends
+                int d0, d1;
+                if (dp_a_signed) {
+                    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d0) : "r"(a4), "r"(lo2.x), "r"(ad2.x));
+                    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d1) : "r"(a4), "r"(lo2.y), "r"(ad2.y));
+                } else {
+                    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d0) : "r"(a4), "r"(lo2.x), "r"(ad2.x));
+                    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d1) : "r"(a4), "r"(lo2.y), "r"(ad2.y));
+                }
+                y0 = d0 >> sh2.x;
+                y1 = d1 >> sh2.y;
+            } else if (RES) {
+                const unsigned rw = rres[i][k];   // two residual bytes, replaced below
                 int r0, r1;
                 if (res_unsigned) {
                     r0 = (int)(rw & 0xffu);
@@ -373,9 +405,112 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
             unsigned d;
             if (out_unsigned) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
             else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
-            sts_u16(addr, d);
+            *(unsigned short*)(region + addr) = (unsigned short)d;
         }
     }
+}
+
+
+// The 32-bit epilogue of one 128 x BN accumulator tile, as executed by one epilogue warp.  The warp owns
+// 16 of the tile's rows (lane quadrant `quad` of TMEM, half `rh`) and the column half `cp` (tiles wider
+// than 128 columns are split in two so that a staged row stays within 128 bytes): it waits for the
+// accumulator (and for its slice of the residual, which it fetched itself by TMA into its staging
+// region), requantises in the fragment layout, hands the accumulator back, and stores its region with one
+// TMA store.  Returns false when a bounded wait gave up.
+struct EpiTile {
+    unsigned tmem_acc;      // TMEM address of the accumulator stage (lane 0, first column)
+    int BN, N, M, m0, n0;
+    int next_m0, next_n0;   // the tile this warp handles next (next_m0 < 0: none): its residual is prefetched
+    const int* par;         // staged per-channel constants of this column block
+    unsigned char* region_p; // this warp's staging region(s) (1024-byte aligned)
+    unsigned region_stride; // distance to the second region (residual cells double-buffer), 0 = one region
+    unsigned rbar;          // this warp's residual-arrival mbarriers (two, 8 bytes apart)
+    unsigned tfull, tfull_parity, tempty;
+    volatile int* abort_flag;
+    int* status;
+    bool res_unsigned, out_unsigned, dp_a_signed;
+    int t_lo, t_hi;
+    unsigned dp_xor;
+};
+
+// Per-warp state carried from tile to tile.
+struct EpiState {
+    unsigned t = 0;          // tiles handled so far (selects the staging region of a residual cell)
+    unsigned used0 = 0, used1 = 0;   // completed waits per residual barrier (its parity)
+    bool prefetched = false; // the current tile's residual load was issued during the previous tile
+};
+
+template <bool RES, bool CLAMP, bool DP>
+__device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
+                                                   int rh, int cp, int lane, EpiState& st)
+{
+    const int col_parts = e.BN > 128 ? 2 : 1;
+    const int wb = e.BN / col_parts;
+    const int cbase = cp * wb;
+    const int gx = e.n0 + cbase, gy = e.m0 + quad * 32 + rh * 16;
+    const bool owns = cp < col_parts;
+    const bool active = owns && gx < e.N && gy < e.M;
+    const unsigned b = (RES && e.region_stride) ? (st.t & 1u) : 0u;
+    unsigned char* region_p = e.region_p + b * e.region_stride;
+    const unsigned region = smem_u32(region_p);
+    if (lane == 0) {
+        bulk_wait_read_all();   // earlier stores have finished reading both regions
+        if (RES) {
+            if (active && !st.prefetched) {
+                mbar_expect_tx(e.rbar + 8u * b, (unsigned)(16 * wb));
+                tma_load_2d(region, tmR, e.rbar + 8u * b, gx, gy);
+            }
+            // the next tile's slice of the residual travels while this tile is computed
+            if (e.region_stride && e.next_m0 >= 0) {
+                const int nx = e.next_n0 + cbase, ny = e.next_m0 + quad * 32 + rh * 16;
+                if (owns && nx < e.N && ny < e.M) {
+                    const unsigned nb = b ^ 1u;
+                    mbar_expect_tx(e.rbar + 8u * nb, (unsigned)(16 * wb));
+                    tma_load_2d(smem_u32(e.region_p + nb * e.region_stride), tmR, e.rbar + 8u * nb, nx, ny);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    if (RES) {
+        // same decision on every lane: was the next tile's load issued?
+        bool next_issued = false;
+        if (e.region_stride && e.next_m0 >= 0) {
+            const int nx = e.next_n0 + cbase, ny = e.next_m0 + quad * 32 + rh * 16;
+            next_issued = owns && nx < e.N && ny < e.M;
+        }
+        st.prefetched = next_issued;
+    }
+    if (!mbar_wait(e.tfull, e.tfull_parity, e.abort_flag, e.status, 4)) return false;
+    if (RES && active) {
+        if (!mbar_wait(e.rbar + 8u * b, (b ? st.used1 : st.used0) & 1u, e.abort_flag, e.status, 7)) return false;
+        if (b) ++st.used1; else ++st.used0;
+    }
+    tc_fence_after();
+    if (owns) {
+        const unsigned tbase = e.tmem_acc + ((unsigned)(quad * 32 + rh * 16) << 16) + (unsigned)cbase;
+        for (int cb = 0; cb < wb; cb += 32) {
+            unsigned v[16];
+            tc_ld_16x256b_x4(tbase + (unsigned)cb, v);
+            tc_wait_ld();
+            reg_fence16(v);
+            if (active)
+                frag_block<4, RES, CLAMP, DP, 2>(v, v, e.par, cbase + cb, region_p, wb, cb, lane, e.res_unsigned,
+                                                 e.out_unsigned, e.t_lo, e.t_hi, e.dp_xor, e.dp_a_signed, e.t_lo == 0);
+        }
+    }
+    // the accumulator is drained: hand it back before the store goes out
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(e.tempty);
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0 && active) {
+        tma_store_2d(tmO, region, gx, gy);
+        bulk_commit();
+    }
+    ++st.t;
+    return true;
 }
 
 }  // namespace n2d2b

@@ -70,6 +70,22 @@ def test_tensor_core_convolutions(case):
     compare_net(net, 3, flags=KEEP | flags, want_engine='tcgen05')
 
 
+@pytest.mark.parametrize('mode', ['double', 'single', 'fixed'])
+@pytest.mark.parametrize('t_act', ['linear', 'relu'])
+@pytest.mark.parametrize('r_act', ['linear', 'relu'])
+def test_fused_residual_sum_all_sign_combinations(mode, t_act, r_act):
+    # conv (signed or unsigned output) + residual operand (signed or unsigned) -> second requantisation,
+    # folded into the convolution's epilogue; several widths so that every column slice size occurs
+    for O in (64, 128, 256):
+        b = netdesc.NetBuilder('res', 64, 9, 9, 5, mode, weight_dist=('normal', 30))
+        r = b.conv(-1, O, 1, act=r_act)
+        t = b.conv(r, O, 3, pad=1, act=t_act)
+        b.sum([t, r], act='relu')
+        n, eng = compare_net(b.net, 3, flags=0)
+        assert 'fused' in eng
+        compare_net(b.net, 3)     # and cell by cell, unfused
+
+
 def test_exact64_epilogue_matches_too():
     # the tensor-core cells default to the 32-bit epilogue wherever it is provably exact; the 64-bit
     # form must give the same integers
