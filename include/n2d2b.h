@@ -200,7 +200,8 @@ int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t
  * For callers that cannot call cudaMalloc where they need the result: plugins inside a host
  * framework that owns the device heap, latency-bound loops that cannot afford an allocation's
  * device-wide synchronisation, processes at their memory budget.  The scratch the kernel needs
- * (the input re-laid with 4 bytes per pixel, the re-ordered weights, the per-channel constants)
+ * (the input re-laid with 4 bytes per pixel and its zero padding written out, the re-ordered weights,
+ * the per-channel constants)
  * lives in a fixed array inside the library's device image instead of in allocated memory.
  *
  *   d_input / d_output  device buffers: batch x height x width x channels 8-bit values in, batch x
@@ -208,11 +209,13 @@ int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t
  *                       cell added with n2d2b_net_add_conv)
  *   desc, weights, bias, quant   host data, as for n2d2b_net_add_conv (desc->input is ignored);
  *                       8-bit weights; <= 4 channels, kernel <= 8x8, no dilation or groups, nb_outputs
- *                       a multiple of 32 and <= 256; a shift or fixed-point scaling whose products
+ *                       a multiple of 32 and <= 128, output at least 2 wide; a shift or fixed-point scaling whose products
  *                       fit 32 bits, 8-bit output
  *
  * Limits and sharing
- *   - batch x height x width must not exceed N2D2B_NOALLOC_MAX_PIXELS (else N2D2B_ERR_TOO_LARGE).
+ *   - batch x padded height x padded width must not exceed N2D2B_NOALLOC_MAX_PIXELS (else
+ *     N2D2B_ERR_TOO_LARGE); the padded image is the input plus its top / left padding, extended to the
+ *     last pixel any output reads and to a multiple of four pixels per row.
  *   - Every GPU that loads the library holds N2D2B_NOALLOC_SCRATCH_BYTES for this array until the
  *     process exits, whether or not this function is ever called.
  *   - All calls on a device share the one array: calls whose GPU work overlaps (different streams,

@@ -30,6 +30,7 @@ static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
+    int b_resident;     // the CTA's whole weight block stays in shared memory (its column block never changes)
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
     int num_m_tiles, num_n_tiles;
     unsigned idesc;
@@ -65,21 +66,27 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int a_stage_bytes = BM * a.BK;
     const int b_stage_bytes = a.BN * a.BK;
-    const int stage_bytes = a_stage_bytes + b_stage_bytes;
-    unsigned char* tiles = smem;
+    const int stage_bytes = a_stage_bytes + (a.b_resident ? 0 : b_stage_bytes);
+    const int kchunks = (a.Cin + a.BK - 1) / a.BK;
+    const int num_kb = a.taps * kchunks;
+    // resident weights first (one BN x BK block per K block), then the ring of activation (and weight) stages
+    unsigned char* res_b = smem;
+    unsigned char* tiles = smem + (a.b_resident ? (size_t)num_kb * b_stage_bytes : 0);
+    unsigned char* stage_out = tiles + (size_t)a.stages * stage_bytes;
     // output staging: one region per epilogue warp (32 rows x up to 64 bytes, swizzled for TMA)
-    unsigned char* stage_out = smem + (size_t)a.stages * stage_bytes;
     // cells with a fused residual keep two regions per warp so that the next tile's residual can arrive early
     const int regions_per_warp = RES ? 2 : 1;
     unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES * regions_per_warp);
-    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[2 * NUM_EPI_WARPS]
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[2 * NUM_EPI_WARPS],
+    //       resident weights
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
     const unsigned tfull0 = empty0 + 8u * a.stages;
     const unsigned tempty0 = tfull0 + 16u;
     const unsigned pready0 = tempty0 + 16u;
     const unsigned rbar0 = pready0 + 16u;
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 2 * NUM_EPI_WARPS);
+    const unsigned bfull = rbar0 + 8u * (2 * NUM_EPI_WARPS);
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 2 * NUM_EPI_WARPS + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -95,9 +102,10 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         for (int s = 0; s < 2; ++s) {
             mbar_init(tfull0 + 8u * s, 1);
             mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
-            mbar_init(pready0 + 8u * s, 32 * NUM_EPI_WARPS);
+            mbar_init(pready0 + 8u * s, NUM_EPI_WARPS);
         }
         for (int w = 0; w < 2 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
+        mbar_init(bfull, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -110,16 +118,30 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    const unsigned tiles_s = smem_u32(tiles), res_b_s = smem_u32(res_b);
 
     const int num_tiles = a.num_m_tiles * a.num_n_tiles;
-    const int kchunks = (a.Cin + a.BK - 1) / a.BK;
-    const int num_kb = a.taps * kchunks;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             unsigned it = 0;
             bool ok = true;
+            if (a.b_resident && (int)blockIdx.x < num_tiles) {
+                // the launch keeps every CTA on one column block: its weights are fetched once
+                const int n0 = ((int)blockIdx.x % a.num_n_tiles) * a.BN;
+                mbar_expect_tx(bfull, (unsigned)(num_kb * b_stage_bytes));
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int tap = kb / kchunks;
+                    const int kc = kb - tap * kchunks;
+                    tma_load_2d(smem_u32(res_b + (size_t)kb * b_stage_bytes), &tmB, bfull, tap * a.Cin + kc * a.BK, n0);
+                }
+            }
+            // The loops below keep ring slot, phase, tap and channel-chunk as running counters: a single
+            // thread pays the full latency of every dependent instruction, so an integer division per K
+            // block costs more than the load it prepares.
+            int s = 0;
+            unsigned ph = 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int n_tile = tile % a.num_n_tiles;
                 const int m_tile = tile / a.num_n_tiles;
@@ -133,24 +155,27 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     iw0 = ox * a.sX - a.pL;
                     ih0 = oy * a.sY - a.pT;
                 }
+                int kx = 0, ky = 0, kc = 0, kcoord = 0;   // kcoord = tap * Cin + kc * BK
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % a.stages;
-                    const unsigned ph = (it / a.stages) & 1u;
                     if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
-                    const int tap = kb / kchunks;
-                    const int kc = kb - tap * kchunks;
                     const unsigned bar = full0 + 8u * s;
-                    const unsigned dstA = smem_u32(tiles + (size_t)s * stage_bytes);
-                    const unsigned dstB = dstA + a_stage_bytes;
+                    const unsigned dstA = tiles_s + (unsigned)(s * stage_bytes);
                     mbar_expect_tx(bar, (unsigned)stage_bytes);
                     if (a.a_im2col) {
-                        const int ky = tap / a.kW, kx = tap - ky * a.kW;
                         tma_load_im2col_4d(dstA, &tmA, bar, kc * a.BK, iw0, ih0, in0,
                                            (unsigned short)(kx * a.dX), (unsigned short)(ky * a.dY));
                     } else {
-                        tma_load_2d(dstA, &tmA, bar, tap * a.Cin + kc * a.BK, m0);
+                        tma_load_2d(dstA, &tmA, bar, kcoord, m0);
                     }
-                    tma_load_2d(dstB, &tmB, bar, tap * a.Cin + kc * a.BK, n0);
+                    if (!a.b_resident) tma_load_2d(dstA + a_stage_bytes, &tmB, bar, kcoord, n0);
+                    if (++s == a.stages) { s = 0; ph ^= 1u; }
+                    if (++kc == kchunks) {
+                        kc = 0;
+                        kcoord += a.Cin - (kchunks - 1) * a.BK;
+                        if (++kx == a.kW) { kx = 0; ++ky; }
+                    } else {
+                        kcoord += a.BK;
+                    }
                 }
             }
         }
@@ -161,6 +186,11 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             unsigned acc_it = 0;
             bool ok = true;
             const int ksteps = a.BK / 32;
+            if (a.b_resident && (int)blockIdx.x < num_tiles) ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
+            int s = 0;
+            unsigned ph = 0;
+            // descriptor bits that do not depend on the address (stride between 8-row groups, version, swizzle)
+            const unsigned long long desc_hi = make_smem_desc(0u, a.BK);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
                 const unsigned as = acc_it & 1u;
                 const unsigned aph = (acc_it >> 1) & 1u;
@@ -168,19 +198,19 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % a.stages;
-                    const unsigned ph = (it / a.stages) & 1u;
                     if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
                     tc_fence_after();
-                    const unsigned sa = smem_u32(tiles + (size_t)s * stage_bytes);
-                    const unsigned long long adesc = make_smem_desc(sa, a.BK);
-                    const unsigned long long bdesc = make_smem_desc(sa + a_stage_bytes, a.BK);
+                    const unsigned long long adesc = desc_hi | (unsigned long long)(((tiles_s + (unsigned)(s * stage_bytes)) & 0x3ffffu) >> 4);
+                    const unsigned long long bdesc = a.b_resident
+                        ? (desc_hi | (unsigned long long)(((res_b_s + (unsigned)(kb * b_stage_bytes)) & 0x3ffffu) >> 4))
+                        : adesc + (unsigned long long)(a_stage_bytes >> 4);
                     for (int k = 0; k < ksteps; ++k) {
                         // advancing K by 32 bytes inside the swizzle span = +2 in the 16-byte address field
                         tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k),
                                   a.idesc, (kb | k) ? 1u : 0u);
                     }
                     tc_commit(empty0 + 8u * s);  // frees the stage once these MMAs have read it
+                    if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) tc_commit(tfull0 + 8u * as);
             }
@@ -222,8 +252,9 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     par[(set * FAST_NP + prm) * 256 + c] = __ldg(src + (size_t)prm * a.cpad + n0 + c);
                 }
                 const unsigned pb = pready0 + 8u * (stage_it & 1u);
-                mbar_arrive(pb);
-                if (!mbar_wait(pb, (stage_it >> 1) & 1u, abort_flag, a.status, 5)) { ok = false; break; }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pb);
+                if (!mbar_wait_warp(pb, (stage_it >> 1) & 1u, abort_flag, a.status, 5, lane)) { ok = false; break; }
                 staged_n_tile = n_tile;
                 ++stage_it;
             }
@@ -253,7 +284,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, rh, part >> 1, lane, est)) { ok = false; break; }
                 continue;
             } else {
-                if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
+                if (!mbar_wait_warp(tfull0 + 8u * as, aph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 for (int cc = 0; cc < cols_per_warp && part < 2; cc += 32) {
                     const int c0 = cbase + cc;
@@ -353,10 +384,12 @@ static CUtensorMapSwizzle swizzle_for(int bk)
          : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
 }
 
-static size_t igemm_smem_bytes(int stages, int BK, int BN, int with_res)
+// resident_b = bytes of the weight block kept in shared memory for the whole launch (0: weights ride the ring)
+static size_t igemm_smem_bytes(int stages, int BK, int BN, int with_res, size_t resident_b)
 {
-    return 1024 /*alignment slack*/ + (size_t)stages * (BM + BN) * BK + NUM_EPI_WARPS * REGION_BYTES * (with_res ? 2 : 1)
-         + (2 * stages + 6 + 2 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+    return 1024 /*alignment slack*/ + resident_b + (size_t)stages * (BM + (resident_b ? 0 : BN)) * BK
+         + NUM_EPI_WARPS * REGION_BYTES * (with_res ? 2 : 1)
+         + (2 * stages + 8 + 2 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
@@ -386,16 +419,26 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     plan->oW = g.oW; plan->oH = g.oH; plan->kW = g.kW;
     plan->sX = g.sX; plan->sY = g.sY; plan->pL = g.pL; plan->pT = g.pT; plan->dX = g.dX; plan->dY = g.dY;
     // pipeline depth: fill up to ~200 KB of shared memory, at most 8 stages
-    int stages = 8;
     const int with_res = res ? 1 : 0;
-    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res) > 226 * 1024) --stages;
-    plan->stages = stages;
-    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, with_res);
     const int num_m_tiles = (plan->M + BM - 1) / BM;
     const int num_n_tiles = (plan->N + plan->BN - 1) / plan->BN;
     const long long tiles = (long long)num_m_tiles * num_n_tiles;
     plan->grid = (int)(tiles < num_sms ? tiles : num_sms);
     if (plan->grid < 1) plan->grid = 1;
+    // A CTA whose column block never changes keeps that block's weights in shared memory: the loads of
+    // a small-K layer are then activations only.
+    const size_t wblock = (size_t)plan->taps * ((g.C + plan->BK - 1) / plan->BK) * plan->BK * plan->BN;
+    plan->b_resident = (wblock <= 96 * 1024 && (num_n_tiles == 1 || num_sms > num_n_tiles)) ? 1 : 0;
+    int stages = 8;
+    const size_t resident = plan->b_resident ? wblock : 0;
+    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, resident) > 226 * 1024) --stages;
+    if (plan->b_resident && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, resident) > 226 * 1024) {
+        plan->b_resident = 0;
+        stages = 8;
+        while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, 0) > 226 * 1024) --stages;
+    }
+    plan->stages = stages;
+    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, plan->b_resident ? wblock : 0);
 
     const CUtensorMapSwizzle swz = swizzle_for(plan->BK);
     CUresult rc;
@@ -472,6 +515,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     IgemmArgs a;
     memset(&a, 0, sizeof(a));
     a.M = plan.M; a.N = plan.N; a.Cin = plan.Cin; a.taps = plan.taps; a.BK = plan.BK; a.BN = plan.BN;
+    a.b_resident = plan.b_resident;
     a.stages = plan.stages; a.a_im2col = plan.a_im2col;
     a.oW = plan.oW; a.oH = plan.oH; a.kW = plan.kW; a.sX = plan.sX; a.sY = plan.sY;
     a.pL = plan.pL; a.pT = plan.pT; a.dX = plan.dX; a.dY = plan.dY;
@@ -514,6 +558,8 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     // a grid that is a multiple of the number of column blocks keeps every CTA on one column block,
     // so its per-channel constants are staged once
     if (tiles > grid && a.num_n_tiles > 1 && grid > a.num_n_tiles) grid -= grid % a.num_n_tiles;
+    // resident weights rely on exactly that (or on one tile per CTA)
+    if (a.b_resident && tiles > grid && a.num_n_tiles > 1 && grid % a.num_n_tiles != 0) return cudaErrorInvalidConfiguration;
     switch (mode) {
     case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;

@@ -77,6 +77,7 @@ struct IgemmPlan {
     int BK;               // bytes of K per pipeline stage: 32, 64 or 128 (also the swizzle width)
     int BN;               // tile N: 64, 128 or 256
     int stages;
+    int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
     int a_unsigned;
     // im2col geometry
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
@@ -92,7 +93,9 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
 // ---- first-layer convolution (<= 4 input channels) on the tensor cores ----
 struct StemPlan {
     CUtensorMap tmB;      // arranged weights [O][nkb*128]
+    void* encode;         // cuTensorMapEncodeTiled (the output map is encoded per launch)
     int nkb;
+    int BN;
     int stages;
     int in_unsigned;
     int num_sms;
@@ -104,7 +107,9 @@ void stem_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* dst);
 int stem_make_plan(StemPlan* plan, const int8_t* d_w_arranged, const ConvGeom& g, int in_unsigned, int num_sms,
                    const char** why);
 // Re-lays [pixels][C] (C <= 4) as [pixels][4] with zero fill.
-cudaError_t launch_pad_channels(const void* in, int C, size_t pixels, void* out, cudaStream_t s);
+// [batch][H][W][C] -> [batch][Hp][Wp][4] with the zero padding written out (dimensions from stem_padded_dims)
+void stem_padded_dims(const ConvGeom& g, int* Hp, int* Wp);
+cudaError_t launch_pad_image(const void* in, const ConvGeom& g, int batch, void* out, cudaStream_t s);
 cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g, const FastQuant& fast, void* out,
                         int* status_word, cudaStream_t s);
 

@@ -85,7 +85,7 @@ struct CellRec {
     int* d_fast = nullptr;
     // first-layer tensor-core kernel
     StemPlan stem{};
-    void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel
+    void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel and its zero padding written out
     // tensor-core plan
     IgemmPlan plan{};
     bool has_plan = false;
@@ -777,10 +777,10 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
                 const char* why = "";
                 if (stem_make_plan(&c.stem, c.d_weights, g, net->tensors[c.inputs[0]].is_unsigned, net->num_sms, &why) == 0) {
-                    if (g.C != 4) {
-                        CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * g.H * g.W * 4 + 256));
-                        net->launches++;
-                    }
+                    int Hp = 0, Wp = 0;
+                    stem_padded_dims(g, &Hp, &Wp);
+                    CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * Hp * Wp * 4 + 256));
+                    net->launches++;
                     c.engine = ENG_STEM;
                     continue;
                 }
@@ -890,12 +890,10 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
     case ENG_STEM: {
         ConvGeom g = c.geom;
         g.B = batch;
-        const void* in4 = in0;
-        if (c.d_pad4) {
-            void* pad = (uint8_t*)c.d_pad4 + (size_t)img0 * g.H * g.W * 4;
-            CUDA_TRY(launch_pad_channels(in0, g.C, (size_t)batch * g.H * g.W, pad, s));
-            in4 = pad;
-        }
+        int Hp = 0, Wp = 0;
+        stem_padded_dims(g, &Hp, &Wp);
+        void* in4 = (uint8_t*)c.d_pad4 + (size_t)img0 * Hp * Wp * 4;
+        CUDA_TRY(launch_pad_image(in0, g, batch, in4, s));
         CUDA_TRY(launch_stem(c.stem, in4, g, c.fast, out, net->d_status, s));
         break;
     }

@@ -3,13 +3,17 @@
 //
 // With 3 channels a pixel is 3 bytes, far below the 16-byte granule of a TMA load, so this layer
 // cannot use the tensor-map path of the main kernel.  Instead the input is first re-laid with 4
-// bytes per pixel (pad_channels_kernel, one pass over ~150 KB per image), and four producer warps
-// gather, for every output pixel and kernel row ky, the 32 contiguous bytes
-// [kx = 0..7][c = 0..3] starting at input pixel (oy*s - pad + ky, ox*s - pad) straight into the
-// 128-byte-swizzled K-major layout the MMA expects (one 32-byte K step per kernel row, four kernel
-// rows per 128-byte row).  The weights (Cout x K, a few KB) are loaded once per CTA by TMA and stay
-// resident.  One thread issues tcgen05.mma kind::i8 into a double-buffered TMEM accumulator; four
-// epilogue warps run the fused 32-bit requantisation.  Every wait is bounded.
+// bytes per pixel and its zero padding written out (pad_image_kernel, one pass over ~200 KB per
+// image), so that the gather needs no bounds checks: eight producer warps (two threads per output
+// pixel) read, for every kernel row ky, the 32 contiguous bytes [kx = 0..7][c = 0..3] starting at
+// padded pixel (oy*s + ky, ox*s) and store them straight into the 128-byte-swizzled K-major layout
+// the MMA expects (one 32-byte K step per kernel row, four kernel rows per 128-byte row).  Taps beyond
+// the kernel width meet zero weights.  The weights (Cout x K, a few KB) are loaded once per CTA by TMA
+// and stay resident.  One thread issues tcgen05.mma kind::i8 into a double-buffered TMEM accumulator;
+// eight epilogue warps run the fused 32-bit requantisation and store through TMA.  Every wait is
+// bounded.  A producer is a long chain of dependent instructions on few warps, so its instruction
+// count per tile, not memory, sets the pace: hence the padded image, 8-byte loads where the stride
+// allows, and multiplications by reciprocals instead of divisions.
 #include <cstring>
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -18,54 +22,84 @@
 namespace n2d2b {
 
 static constexpr int SBM = 128;
-static constexpr int S_PROD_WARPS = 4;
-static constexpr int S_EPI_WARPS = 4;
+static constexpr int S_PROD_WARPS = 8;     // two threads per tile row
+static constexpr int S_EPI_WARPS = 8;      // 4 TMEM lane quadrants x 2 row halves
 static constexpr int S_THREADS = 32 * (1 + S_PROD_WARPS + S_EPI_WARPS);   // warp 0: weights + MMA
 
 struct StemArgs {
-    const uint8_t* in4;   // [B][H][W][4]
-    int B, H, W, oH, oW, N, M;
-    int kH, kW, sY, sX, pT, pL;
+    const uint8_t* in4;   // zero-padded input [B][Hp][Wp][4]
+    int B, Hp, Wp, oH, oW, N, M, BN;
+    unsigned rcp_oW;            // ceil(2^32 / oW): exact quotients for the image sizes accepted
+    unsigned step_n, step_rem;  // (gridDim.x * 128) / (oH*oW) and the remainder: a tile step in (image, pixel) terms
+    int kH, sY, sX;
     int nkb;              // 128-byte K blocks = ceil(kH / 4)
     int stages;
     unsigned idesc, tmem_cols;
-    void* out;
     int* status;
     const int* fq;
     int cpad;
     int out_unsigned;
-    int need_clamp;
 };
 
-__global__ void pad_channels_kernel(const uint8_t* __restrict__ in, int C, size_t pixels, uint32_t* __restrict__ out)
+// [B][H][W][C] (C <= 4) -> [B][Hp][Wp][4] with the image at (pT, pL) and zeros elsewhere
+__global__ void pad_image_kernel(const uint8_t* __restrict__ in, int C, int H, int W, int Hp, int Wp, int pT, int pL,
+                                 size_t out_pixels, uint32_t* __restrict__ out)
 {
-    for (size_t p = blockIdx.x * (size_t)blockDim.x + threadIdx.x; p < pixels; p += (size_t)gridDim.x * blockDim.x) {
+    for (size_t p = blockIdx.x * (size_t)blockDim.x + threadIdx.x; p < out_pixels; p += (size_t)gridDim.x * blockDim.x) {
+        const int xp = (int)(p % (size_t)Wp);
+        const size_t t = p / (size_t)Wp;
+        const int yp = (int)(t % (size_t)Hp);
+        const size_t n = t / (size_t)Hp;
+        const int x = xp - pL, y = yp - pT;
         uint32_t v = 0;
-        for (int c = 0; c < C; ++c) v |= (uint32_t)in[p * C + c] << (8 * c);
+        if (x >= 0 && x < W && y >= 0 && y < H) {
+            const uint8_t* src = in + ((n * H + y) * (size_t)W + x) * C;
+            if (C == 4) {
+                v = *(const uint32_t*)src;
+            } else {
+                for (int c = 0; c < C; ++c) v |= (uint32_t)src[c] << (8 * c);
+            }
+        }
         out[p] = v;
     }
 }
 
-cudaError_t launch_pad_channels(const void* in, int C, size_t pixels, void* out, cudaStream_t s)
+void stem_padded_dims(const ConvGeom& g, int* Hp, int* Wp)
 {
+    *Hp = (g.oH - 1) * g.sY + ((g.kH + 3) / 4) * 4;   // every K block reads four kernel rows
+    if (*Hp < g.H + g.pT) *Hp = g.H + g.pT;
+    int w = (g.oW - 1) * g.sX + 8;                    // every kernel row reads eight pixels
+    if (w < g.W + g.pL) w = g.W + g.pL;
+    *Wp = (w + 3) & ~3;                               // rows stay 16-byte multiples
+}
+
+cudaError_t launch_pad_image(const void* in, const ConvGeom& g, int batch, void* out, cudaStream_t s)
+{
+    int Hp, Wp;
+    stem_padded_dims(g, &Hp, &Wp);
+    const size_t pixels = (size_t)batch * Hp * Wp;
     if (pixels == 0) return cudaSuccess;
-    size_t g = (pixels + 255) / 256;
-    if (g > 148u * 64u) g = 148u * 64u;
-    pad_channels_kernel<<<(unsigned)g, 256, 0, s>>>((const uint8_t*)in, C, pixels, (uint32_t*)out);
+    size_t grid = (pixels + 255) / 256;
+    if (grid > 148u * 64u) grid = 148u * 64u;
+    pad_image_kernel<<<(unsigned)grid, 256, 0, s>>>((const uint8_t*)in, g.C, g.H, g.W, Hp, Wp, g.pT, g.pL, pixels,
+                                                   (uint32_t*)out);
     return cudaGetLastError();
 }
 
-template <bool CLAMP>
+// VEC8: the first pixel of every row read is 8-byte aligned (even stride), so a row is four 8-byte loads
+template <bool CLAMP, bool VEC8>
 __global__ void __launch_bounds__(S_THREADS, 1)
-stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const StemArgs a)
+stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmO, const StemArgs a)
 {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int b_bytes = a.nkb * a.N * 128;                 // resident weights: [nkb][N][128]
+    const int b_bytes = a.nkb * a.BN * 128;                // resident weights: [nkb][BN][128]
     const int a_stage_bytes = a.nkb * SBM * 128;           // one tile of gathered activations
     unsigned char* smB = smem;
     unsigned char* smA = smem + ((b_bytes + 1023) & ~1023);
-    unsigned long long* bars = (unsigned long long*)(smA + (size_t)a.stages * a_stage_bytes);
+    unsigned char* stage_out = smA + (size_t)a.stages * a_stage_bytes;
+    const int region_bytes = 16 * a.BN;                    // staging of one epilogue warp: 16 rows x BN bytes
+    unsigned long long* bars = (unsigned long long*)(stage_out + S_EPI_WARPS * region_bytes);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], weights
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
@@ -81,7 +115,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const StemArgs
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
-            mbar_init(full0 + 8u * s, 32 * S_PROD_WARPS);
+            mbar_init(full0 + 8u * s, S_PROD_WARPS);
             mbar_init(empty0 + 8u * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -113,104 +147,130 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const StemArgs
         if (lane == 0) {
             mbar_expect_tx(wbar, (unsigned)b_bytes);
             for (int kb = 0; kb < a.nkb; ++kb)
-                tma_load_2d(smem_u32(smB + (size_t)kb * a.N * 128), &tmB, wbar, kb * 128, 0);
+                tma_load_2d(smem_u32(smB + (size_t)kb * a.BN * 128), &tmB, wbar, kb * 128, 0);
             bool ok = mbar_wait(wbar, 0, abort_flag, a.status, 6);
-            unsigned it = 0, acc_it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it, ++acc_it) {
+            const unsigned long long desc_hi = make_smem_desc(0u, 128);
+            const unsigned smA_s = smem_u32(smA), smB_s = smem_u32(smB);
+            int s = 0;
+            unsigned ph = 0, acc_it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
                 const unsigned as = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-                const int s = it % a.stages;
-                const unsigned ph = (it / a.stages) & 1u;
                 if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                 if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
                 tc_fence_after();
-                const unsigned d_tmem = tmem_base + as * (unsigned)a.N;
+                const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
                 for (int kb = 0; kb < a.nkb; ++kb) {
                     const unsigned long long adesc =
-                        make_smem_desc(smem_u32(smA + (size_t)s * a_stage_bytes + (size_t)kb * SBM * 128), 128);
-                    const unsigned long long bdesc = make_smem_desc(smem_u32(smB + (size_t)kb * a.N * 128), 128);
-                    for (int k = 0; k < 4; ++k)
+                        desc_hi | (unsigned long long)(((smA_s + (unsigned)(s * a_stage_bytes + kb * SBM * 128)) & 0x3ffffu) >> 4);
+                    const unsigned long long bdesc =
+                        desc_hi | (unsigned long long)(((smB_s + (unsigned)(kb * a.BN * 128)) & 0x3ffffu) >> 4);
+                    const int ksteps = min(4, a.kH - kb * 4);   // one 32-byte K step per kernel row
+                    for (int k = 0; k < ksteps; ++k)
                         tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k), a.idesc,
                                   (kb | k) ? 1u : 0u);
                 }
                 tc_commit(empty0 + 8u * s);
                 tc_commit(tfull0 + 8u * as);
+                if (++s == a.stages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp <= S_PROD_WARPS) {
         // ------------------------------------------------------------------ gather producers
-        const int r = (warp - 1) * 32 + lane;   // tile row = output pixel
-        unsigned it = 0;
+        const int pt = (warp - 1) * 32 + lane;  // 0..255
+        const int r = pt & 127;                 // tile row = output pixel
+        const int h = pt >> 7;                  // kernel rows 2h and 2h+1 of every K block
+        int s = 0;
+        unsigned ph = 0;
         bool ok = true;
-        const uint32_t* in4 = (const uint32_t*)a.in4;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-            const int s = it % a.stages;
-            const unsigned ph = (it / a.stages) & 1u;
-            if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
-            const int m = tile * SBM + r;
-            const bool m_ok = m < a.M;
-            int ox = 0, oy = 0, n = 0;
-            if (m_ok) {
-                ox = m % a.oW;
-                const int t = m / a.oW;
-                oy = t % a.oH;
-                n = t / a.oH;
-            }
-            const int ix0 = ox * a.sX - a.pL, iy0 = oy * a.sY - a.pT;
-            unsigned char* stage = smA + (size_t)s * a_stage_bytes;
-            // one 128-byte K block (four kernel rows) at a time: all 32 loads are issued before the first
-            // store so that a tile costs one memory latency per K block, not one per kernel row
-            for (int kb = 0; kb < a.nkb; ++kb) {
-                uint32_t w[4][8];
+        const size_t row_bytes = (size_t)a.Wp * 4;
+        // this thread's part of a stage: 16-byte chunks 4h .. 4h+3 of row r in every K block
+        const unsigned sw = (unsigned)(r & 7);
+        unsigned char* const my_row = smA + (size_t)r * 128;
+        // (image, pixel within the image) of this thread's row, advanced tile by tile without a division
+        const unsigned oHW = (unsigned)(a.oH * a.oW);
+        unsigned m = blockIdx.x * SBM + r;
+        unsigned n = m / oHW;
+        unsigned rem = m - n * oHW;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            if (!mbar_wait_warp(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1, lane)) { ok = false; break; }
+            // rows past the end repeat the last pixel; they are never stored
+            const unsigned nn = m < (unsigned)a.M ? n : (unsigned)a.B - 1u;
+            const unsigned rr = m < (unsigned)a.M ? rem : oHW - 1u;
+            const unsigned oy = __umulhi(rr, a.rcp_oW);
+            const unsigned ox = rr - oy * (unsigned)a.oW;
+            const unsigned char* src = a.in4 + ((size_t)nn * a.Hp + (size_t)oy * a.sY + 2 * h) * row_bytes + (size_t)ox * a.sX * 4;
+            unsigned char* dst = my_row + (size_t)s * a_stage_bytes;
+            // all loads of the tile are issued before the first store: one memory latency per tile
+            uint32_t w[2][2][8];   // [K block][kernel row of this thread][pixel]
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int ky = kb * 4 + q;
-                    const int iy = iy0 + ky;
-                    const bool row_ok = m_ok && ky < a.kH && iy >= 0 && iy < a.H;
-                    const uint32_t* rowp = in4 + ((size_t)n * a.H + (row_ok ? iy : 0)) * a.W;
+            for (int kb = 0; kb < 2; ++kb) {
+                if (kb < a.nkb) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int ix = ix0 + j;
-                        w[q][j] = (row_ok && j < a.kW && ix >= 0 && ix < a.W) ? __ldg(rowp + ix) : 0u;
+                    for (int q = 0; q < 2; ++q) {
+                        const unsigned char* rp = src + (size_t)(kb * 4 + q) * row_bytes;
+                        if (VEC8) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint2 v = __ldg((const uint2*)rp + j);
+                                w[kb][q][2 * j] = v.x;
+                                w[kb][q][2 * j + 1] = v.y;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) w[kb][q][j] = __ldg((const uint32_t*)rp + j);
+                        }
                     }
                 }
-                unsigned char* rowbase = stage + (size_t)kb * SBM * 128 + (size_t)r * 128;
+            }
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    // kernel row q of the block occupies 16-byte chunks 2q and 2q+1 of the 128-byte row
-                    *(uint4*)(rowbase + (((2 * q + 0) ^ (r & 7)) << 4)) = make_uint4(w[q][0], w[q][1], w[q][2], w[q][3]);
-                    *(uint4*)(rowbase + (((2 * q + 1) ^ (r & 7)) << 4)) = make_uint4(w[q][4], w[q][5], w[q][6], w[q][7]);
+            for (int kb = 0; kb < 2; ++kb) {
+                if (kb < a.nkb) {
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        // kernel row c of the block occupies 16-byte chunks 2c and 2c+1 of the 128-byte row
+                        const unsigned c = (unsigned)(2 * h + q);
+                        unsigned char* rowbase = dst + (size_t)kb * SBM * 128;
+                        *(uint4*)(rowbase + (((2 * c + 0) ^ sw) << 4)) =
+                            make_uint4(w[kb][q][0], w[kb][q][1], w[kb][q][2], w[kb][q][3]);
+                        *(uint4*)(rowbase + (((2 * c + 1) ^ sw) << 4)) =
+                            make_uint4(w[kb][q][4], w[kb][q][5], w[kb][q][6], w[kb][q][7]);
+                    }
                 }
             }
             // make the generic-proxy stores visible to the tensor core (async proxy), then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(full0 + 8u * s);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8u * s);
+            if (++s == a.stages) { s = 0; ph ^= 1u; }
+            m += gridDim.x * SBM;
+            n += a.step_n;
+            rem += a.step_rem;
+            if (rem >= oHW) { rem -= oHW; ++n; }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        const int ew = warp - (1 + S_PROD_WARPS);
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;
+        const int rh = (ew >> 2) & 1;
         unsigned acc_it = 0;
-        bool ok = true;
-        const bool out_unsigned = a.out_unsigned != 0;
-        const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
+        EpiState est;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
             const unsigned as = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-            if (!mbar_wait(tfull0 + 8u * as, aph, abort_flag, a.status, 4)) { ok = false; break; }
-            tc_fence_after();
-            const int m = tile * SBM + row;
-            const bool m_ok = m < a.M;
-            const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + as * (unsigned)a.N;
-            uint8_t* orow = (uint8_t*)a.out + (size_t)m * a.N;
-            for (int c0 = 0; c0 < a.N; c0 += 32) {
-                unsigned v[32];
-                tc_ld32(tbase + (unsigned)c0, v);
-                tc_wait_ld_into(v);
-                if (m_ok) fast_chunk<false, CLAMP>(v, par, c0, zero4, zero4, false, out_unsigned, 0, 0, orow + c0);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8u * as);
+            EpiTile e;
+            e.tmem_acc = tmem_base + as * (unsigned)a.BN;
+            e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = tile * SBM; e.n0 = 0;
+            e.next_m0 = -1; e.next_n0 = 0;
+            e.par = par;
+            e.region_p = stage_out + (size_t)ew * region_bytes;
+            e.region_stride = 0;
+            e.rbar = 0;
+            e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
+            e.abort_flag = abort_flag; e.status = a.status;
+            e.res_unsigned = false; e.out_unsigned = a.out_unsigned != 0;
+            e.dp_a_signed = true; e.t_lo = 0; e.t_hi = 0; e.dp_xor = 0;
+            if (!fast_epilogue_tile<false, CLAMP, false>(&tmO, &tmO, e, quad, rh, 0, lane, est)) break;
         }
+        if (lane == 0) bulk_wait_all();
     }
 
     tc_fence_before();
@@ -229,7 +289,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 bool stem_eligible(const ConvGeom& g)
 {
-    return g.groups == 1 && g.C <= 4 && g.kW <= 8 && g.kH <= 8 && g.dX == 1 && g.dY == 1 && g.O % 32 == 0 && g.O <= 256;
+    // the pixel decomposition multiplies by ceil(2^32 / oW): exact while oH * oW * oW < 2^32
+    return g.groups == 1 && g.C <= 4 && g.kW <= 8 && g.kH <= 8 && g.dX == 1 && g.dY == 1 && g.O % 32 == 0 && g.O <= 128
+           && g.oW >= 2 && (long long)g.oH * g.oW * g.oW < (1ll << 32);
 }
 
 size_t stem_weight_bytes(const ConvGeom& g)
@@ -267,16 +329,20 @@ int stem_make_plan(StemPlan* plan, const int8_t* d_w_arranged, const ConvGeom& g
     plan->in_unsigned = in_unsigned;
     const cuuint64_t dims[2] = {(cuuint64_t)plan->nkb * 128, (cuuint64_t)g.O};
     const cuuint64_t strides[1] = {(cuuint64_t)plan->nkb * 128};
-    const cuuint32_t box[2] = {128, (cuuint32_t)g.O};
+    plan->BN = g.O <= 64 ? 64 : 128;
+    const cuuint32_t box[2] = {128, (cuuint32_t)plan->BN};   // rows beyond the outputs read as zero
     const cuuint32_t estr[2] = {1, 1};
     CUresult rc = ((EncodeTiledFn)fn)(&plan->tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d_w_arranged, dims, strides, box,
                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the stem weights"; return -1; }
-    const size_t b_bytes = (((size_t)plan->nkb * g.O * 128) + 1023) & ~(size_t)1023;
+    plan->encode = fn;
+    const size_t b_bytes = (((size_t)plan->nkb * plan->BN * 128) + 1023) & ~(size_t)1023;
     const size_t a_stage = (size_t)plan->nkb * SBM * 128;
     int stages = 4;
-    auto smem_for = [&](int st) { return 1024 + b_bytes + st * a_stage + (2 * st + 5) * 8 + 32 + FAST_NP * 256 * 4 + 64; };
+    auto smem_for = [&](int st) {
+        return 1024 + b_bytes + st * a_stage + S_EPI_WARPS * 16 * plan->BN + (2 * st + 5) * 8 + 32 + FAST_NP * 256 * 4 + 64;
+    };
     while (stages > 2 && smem_for(stages) > 200 * 1024) --stages;
     plan->stages = stages;
     plan->smem_bytes = smem_for(stages);
@@ -290,40 +356,58 @@ cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g
     StemArgs a;
     memset(&a, 0, sizeof(a));
     a.in4 = (const uint8_t*)in4;
-    a.B = g.B; a.H = g.H; a.W = g.W; a.oH = g.oH; a.oW = g.oW; a.N = g.O;
+    a.B = g.B; a.oH = g.oH; a.oW = g.oW; a.N = g.O;
+    stem_padded_dims(g, &a.Hp, &a.Wp);
     a.M = g.B * g.oH * g.oW;
     if (a.M == 0) return cudaSuccess;
-    a.kH = g.kH; a.kW = g.kW; a.sY = g.sY; a.sX = g.sX; a.pT = g.pT; a.pL = g.pL;
+    // The output map is encoded per launch (a host-side fill of 128 bytes): its row extent is this call's
+    // pixel count, so the stores of a partial last tile are clipped exactly at the end of the batch slice.
+    CUtensorMap tmO;
+    {
+        const cuuint64_t odims[2] = {(cuuint64_t)g.O, (cuuint64_t)a.M};
+        const cuuint64_t ostrides[1] = {(cuuint64_t)g.O};
+        const cuuint32_t obox[2] = {(cuuint32_t)plan.BN, 16};   // an epilogue warp's 16 rows x BN columns (clipped to N)
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult rc = ((EncodeTiledFn)plan.encode)(
+            &tmO, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, out, odims, ostrides, obox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            plan.BN == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    a.kH = g.kH; a.sY = g.sY; a.sX = g.sX;
+    a.rcp_oW = (unsigned)(((1ull << 32) + (unsigned)g.oW - 1) / (unsigned)g.oW);
     a.nkb = plan.nkb;
     a.stages = plan.stages;
-    a.idesc = (2u << 4) | ((plan.in_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(g.O >> 3) << 17)
+    a.BN = plan.BN;
+    a.idesc = (2u << 4) | ((plan.in_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
             | ((unsigned)(SBM >> 4) << 24);
-    unsigned cols = 2u * g.O, p2 = 32;
+    unsigned cols = 2u * plan.BN, p2 = 32;
     while (p2 < cols) p2 <<= 1;
     a.tmem_cols = p2;
-    a.out = out;
     a.status = status_word;
     a.fq = fast.fq;
     a.cpad = fast.cpad;
     a.out_unsigned = fast.out_unsigned;
-    a.need_clamp = fast.need_clamp ? 1 : 0;
+    typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
+    static const StemKernel variants[4] = {stem_conv_tcgen05_kernel<false, false>, stem_conv_tcgen05_kernel<false, true>,
+                                           stem_conv_tcgen05_kernel<true, false>, stem_conv_tcgen05_kernel<true, true>};
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(stem_conv_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(stem_conv_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return e;
+        for (StemKernel k : variants) {
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return e;
+        }
         attr_set[dev] = true;
     }
     const int tiles = (a.M + SBM - 1) / SBM;
     const int grid = tiles < plan.num_sms ? tiles : plan.num_sms;
-    if (fast.need_clamp)
-        stem_conv_tcgen05_kernel<true><<<grid, S_THREADS, plan.smem_bytes, s>>>(plan.tmB, a);
-    else
-        stem_conv_tcgen05_kernel<false><<<grid, S_THREADS, plan.smem_bytes, s>>>(plan.tmB, a);
+    const unsigned step = (unsigned)grid * SBM, oHW = (unsigned)(g.oH * g.oW);
+    a.step_n = step / oHW;
+    a.step_rem = step % oHW;
+    const bool vec8 = (g.sX % 2 == 0) && ((uintptr_t)in4 % 8 == 0);
+    variants[(fast.need_clamp ? 2 : 0) + (vec8 ? 1 : 0)]<<<grid, S_THREADS, plan.smem_bytes, s>>>(plan.tmB, tmO, a);
     return cudaGetLastError();
 }
 
@@ -396,11 +480,14 @@ extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int bat
     if (!stem_eligible(g))
         return set_error(N2D2B_ERR_INVALID,
                          "outside the first-layer kernel: needs <= 4 channels, kernel <= 8x8, no dilation or groups, "
-                         "outputs a multiple of 32 and <= 256");
-    const size_t pixels = (size_t)batch * height * width;
+                         "outputs a multiple of 32 and <= 128, output at least 2 wide");
+    int Hp = 0, Wp = 0;
+    stem_padded_dims(g, &Hp, &Wp);
+    const size_t pixels = (size_t)batch * Hp * Wp;
     if (pixels > (size_t)N2D2B_NOALLOC_MAX_PIXELS)
-        return set_error(N2D2B_ERR_TOO_LARGE, "batch x height x width = %zu input pixels exceeds the fixed scratch of %u pixels",
-                         pixels, (unsigned)N2D2B_NOALLOC_MAX_PIXELS);
+        return set_error(N2D2B_ERR_TOO_LARGE,
+                         "batch x padded height x padded width = %zu pixels exceeds the fixed scratch of %u pixels", pixels,
+                         (unsigned)N2D2B_NOALLOC_MAX_PIXELS);
     if (stem_weight_bytes(g) > NA_WEIGHT_BYTES)
         return set_error(N2D2B_ERR_TOO_LARGE, "arranged weights exceed the fixed scratch");
     cudaError_t e = cudaSetDevice(device);
@@ -436,13 +523,10 @@ extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int bat
     const char* why = "";
     if (stem_make_plan(&plan, (const int8_t*)scratch, g, in_unsigned ? 1 : 0, sms, &why))
         return set_error(N2D2B_ERR_INVALID, "first-layer plan failed: %s", why);
-    const void* in4 = d_input;
-    if (channels != 4) {
-        // every pixel of the region is rewritten in full, so nothing of an earlier call survives
-        e = launch_pad_channels(d_input, channels, pixels, scratch + NA_PAD_OFFSET, s);
-        if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "re-layout launch failed: %s", cudaGetErrorString(e));
-        in4 = scratch + NA_PAD_OFFSET;
-    }
+    // every pixel of the padded image is rewritten in full, so nothing of an earlier call survives
+    e = launch_pad_image(d_input, g, batch, scratch + NA_PAD_OFFSET, s);
+    if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "re-layout launch failed: %s", cudaGetErrorString(e));
+    const void* in4 = scratch + NA_PAD_OFFSET;
     FastQuant fq;
     fq.fq = (const int*)(scratch + NA_CONST_OFFSET);
     fq.cpad = cpad;

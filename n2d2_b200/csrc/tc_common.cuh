@@ -36,6 +36,16 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity)
+{
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -48,6 +58,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
                                           int* status, int code)
 {
     if (mbar_try_wait(bar, parity)) return true;
+    // try_wait suspends the thread in hardware until the phase completes or a time limit passes, so a
+    // waiting warp leaves the issue slots to the warps that work
     const unsigned long long t0 = globaltimer_ns();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -58,6 +70,19 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
             return false;
         }
     }
+}
+
+// Warp-wide bounded wait: one lane polls (32 lanes polling one word, times many warps, crowd out the
+// arrivals and the shared-memory traffic of the working warps), then every lane observes the completed
+// phase itself, which costs one successful try_wait and gives each lane its own acquire.
+__device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, volatile int* abort_flag,
+                                               int* status, int code, int lane)
+{
+    unsigned ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+    return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* tm, unsigned bar, int x, int y)
@@ -481,9 +506,9 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
         }
         st.prefetched = next_issued;
     }
-    if (!mbar_wait(e.tfull, e.tfull_parity, e.abort_flag, e.status, 4)) return false;
+    if (!mbar_wait_warp(e.tfull, e.tfull_parity, e.abort_flag, e.status, 4, lane)) return false;
     if (RES && active) {
-        if (!mbar_wait(e.rbar + 8u * b, (b ? st.used1 : st.used0) & 1u, e.abort_flag, e.status, 7)) return false;
+        if (!mbar_wait_warp(e.rbar + 8u * b, (b ? st.used1 : st.used0) & 1u, e.abort_flag, e.status, 7, lane)) return false;
         if (b) ++st.used1; else ++st.used0;
     }
     tc_fence_after();

@@ -106,7 +106,7 @@ def test_wide_shifts_fall_back_to_the_exact_epilogue():
 # (C, H, W, O, k, stride, pad, input unsigned)
 STEM_CASES = [(3, 32, 32, 64, 7, 2, 3, True), (3, 224, 224, 64, 7, 2, 3, True), (3, 33, 29, 32, 3, 2, 1, True),
               (1, 24, 24, 32, 4, 2, 0, True), (4, 17, 19, 64, 5, 1, 2, False), (2, 16, 16, 96, 8, 3, 0, True),
-              (3, 20, 20, 256, 3, 1, 1, True)]
+              (3, 20, 20, 128, 3, 1, 1, True)]
 
 
 @pytest.mark.parametrize('case', STEM_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_s%d_p%d' % c[:7])
