@@ -33,6 +33,8 @@ struct IgemmArgs {
     int b_resident;     // the CTA's whole weight block stays in shared memory (its column block never changes)
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
     int num_m_tiles, num_n_tiles;
+    int step_m, step_n;   // gridDim.x / num_n_tiles and gridDim.x % num_n_tiles: one persistent-loop step in tile coordinates
+    int ef;               // EF_* switches of the 32-bit epilogue
     unsigned idesc;
     unsigned tmem_cols;
     int out_dtype;
@@ -142,10 +144,12 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             // block costs more than the load it prepares.
             int s = 0;
             unsigned ph = 0;
+            int m_tile = (int)blockIdx.x / a.num_n_tiles, n_tile = (int)blockIdx.x % a.num_n_tiles;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int n_tile = tile % a.num_n_tiles;
-                const int m_tile = tile / a.num_n_tiles;
                 const int m0 = m_tile * BM, n0 = n_tile * a.BN;
+                m_tile += a.step_m;
+                n_tile += a.step_n;
+                if (n_tile >= a.num_n_tiles) { n_tile -= a.num_n_tiles; ++m_tile; }
                 int iw0 = 0, ih0 = 0, in0 = 0;
                 if (a.a_im2col) {
                     const int ox = m0 % a.oW;
@@ -232,9 +236,12 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         int staged_n_tile = -1;
         int* par = epi_params;
         bool ok = true;
+        int m_next = (int)blockIdx.x / a.num_n_tiles, n_next = (int)blockIdx.x % a.num_n_tiles;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
-            const int n_tile = tile % a.num_n_tiles;
-            const int m_tile = tile / a.num_n_tiles;
+            const int n_tile = n_next, m_tile = m_next;
+            m_next += a.step_m;
+            n_next += a.step_n;
+            if (n_next >= a.num_n_tiles) { n_next -= a.num_n_tiles; ++m_next; }
             const int m0 = m_tile * BM, n0 = n_tile * a.BN;
             const unsigned as = acc_it & 1u;
             const unsigned aph = (acc_it >> 1) & 1u;
@@ -268,19 +275,19 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 EpiTile e;
                 e.tmem_acc = tmem_base + as * (unsigned)a.BN;
                 e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = m0; e.n0 = n0;
-                e.par = par;
-                e.region_p = stage_out + (size_t)ew * REGION_BYTES * regions_per_warp;
+                e.par_off = (unsigned)((unsigned char*)par - smem_raw);
+                e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * REGION_BYTES * regions_per_warp);
                 e.region_stride = RES ? REGION_BYTES : 0;
                 e.rbar = rbar0 + 16u * ew;
                 {
                     const int nt = tile + (int)gridDim.x;
-                    e.next_m0 = nt < num_tiles ? (nt / a.num_n_tiles) * BM : -1;
-                    e.next_n0 = nt < num_tiles ? (nt % a.num_n_tiles) * a.BN : 0;
+                    e.next_m0 = nt < num_tiles ? m_next * BM : -1;
+                    e.next_n0 = nt < num_tiles ? n_next * a.BN : 0;
                 }
                 e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
                 e.abort_flag = abort_flag; e.status = a.status;
-                e.res_unsigned = a.r.is_unsigned != 0; e.out_unsigned = a.out_unsigned != 0;
-                e.dp_a_signed = a.dp_a_signed != 0; e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
+                e.ef = a.ef;
+                e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
                 if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, rh, part >> 1, lane, est)) { ok = false; break; }
                 continue;
             } else {
@@ -537,6 +544,8 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.out_unsigned = fast.out_unsigned;
     a.dp_xor = fast.dp_xor;
     a.dp_a_signed = fast.dp_a_signed;
+    a.ef = (fast.out_unsigned ? EF_OUT_UNSIGNED : 0) | (r.is_unsigned ? EF_RES_UNSIGNED : 0)
+         | (fast.t_lo == 0 ? EF_T_UNSIGNED : 0) | (fast.dp_a_signed ? EF_DP_A_SIGNED : 0);
     const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
                           && plan.has_out_maps;
     const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : (fast.dp4a ? 5 : 4)) : (fast.need_clamp ? 1 : 3));
@@ -560,6 +569,8 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     if (tiles > grid && a.num_n_tiles > 1 && grid > a.num_n_tiles) grid -= grid % a.num_n_tiles;
     // resident weights rely on exactly that (or on one tile per CTA)
     if (a.b_resident && tiles > grid && a.num_n_tiles > 1 && grid % a.num_n_tiles != 0) return cudaErrorInvalidConfiguration;
+    a.step_m = grid / a.num_n_tiles;
+    a.step_n = grid % a.num_n_tiles;
     switch (mode) {
     case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
     case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;

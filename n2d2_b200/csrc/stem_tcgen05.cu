@@ -260,14 +260,14 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             e.tmem_acc = tmem_base + as * (unsigned)a.BN;
             e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = tile * SBM; e.n0 = 0;
             e.next_m0 = -1; e.next_n0 = 0;
-            e.par = par;
-            e.region_p = stage_out + (size_t)ew * region_bytes;
+            e.par_off = (unsigned)((unsigned char*)par - smem_raw);
+            e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
             e.region_stride = 0;
             e.rbar = 0;
             e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
             e.abort_flag = abort_flag; e.status = a.status;
-            e.res_unsigned = false; e.out_unsigned = a.out_unsigned != 0;
-            e.dp_a_signed = true; e.t_lo = 0; e.t_hi = 0; e.dp_xor = 0;
+            e.ef = a.out_unsigned ? EF_OUT_UNSIGNED : 0;
+            e.t_lo = 0; e.t_hi = 0; e.dp_xor = 0;
             if (!fast_epilogue_tile<false, CLAMP, false>(&tmO, &tmO, e, quad, rh, 0, lane, est)) break;
         }
         if (lane == 0) bulk_wait_all();

@@ -158,20 +158,6 @@ __device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr,
     return d;
 }
 
-// Packs four 32-bit values into four bytes with saturation to the unsigned or signed 8-bit range
-// (y0 in the low byte).
-__device__ __forceinline__ unsigned pack4_sat(int y0, int y1, int y2, int y3, bool is_unsigned)
-{
-    unsigned t, d;
-    if (is_unsigned) {
-        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
-        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
-    } else {
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(y3), "r"(y2), "r"(0));
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(t));
-    }
-    return d;
-}
 // Byte j of w, zero- or sign-extended, in one permute: a selector nibble with its top bit set
 // replicates the sign of the selected byte (the __byte_perm intrinsic only honours 3 bits per nibble,
 // hence the PTX form).
@@ -182,70 +168,6 @@ __device__ __forceinline__ int byte_extend(unsigned w, int j, bool is_unsigned)
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(sel));
     return (int)d;
 }
-__device__ __forceinline__ int byte_of(unsigned w, int j, bool is_unsigned)
-{
-    return is_unsigned ? (int)((w >> (8 * j)) & 0xffu) : ((int)(w << (24 - 8 * j)) >> 24);
-}
-// One 32-column chunk of one accumulator row through the 32-bit epilogue.
-//   RES   : add the residual operand and requantise a second time
-//   CLAMP : keep the overflow / ReLU clamps (the host drops them when every product provably fits)
-// par points at the staged constants: rows of 256 words: lo, hi, mult, add, shift (+ the same five
-// of the residual stage).
-template <bool RES, bool CLAMP>
-__device__ __forceinline__ void fast_chunk(const unsigned* v, const int* par, int c0, const uint4& rv0, const uint4& rv1,
-                                           bool res_unsigned, bool out_unsigned, int t_lo, int t_hi, uint8_t* op)
-{
-    const unsigned rw[8] = {rv0.x, rv0.y, rv0.z, rv0.w, rv1.x, rv1.y, rv1.z, rv1.w};
-    unsigned wds[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        const int4 mu4 = *(const int4*)&par[2 * 256 + c0 + 4 * g];
-        const int4 ad4 = *(const int4*)&par[3 * 256 + c0 + 4 * g];
-        const int4 sh4 = *(const int4*)&par[4 * 256 + c0 + 4 * g];
-        const int mu[4] = {mu4.x, mu4.y, mu4.z, mu4.w}, ad[4] = {ad4.x, ad4.y, ad4.z, ad4.w};
-        const int sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
-        int y[4];
-        if (CLAMP) {
-            const int4 lo4 = *(const int4*)&par[0 * 256 + c0 + 4 * g];
-            const int4 hi4 = *(const int4*)&par[1 * 256 + c0 + 4 * g];
-            const int lo[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] = (min(max((int)v[4 * g + j], lo[j]), hi[j]) * mu[j] + ad[j]) >> sh[j];
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] = ((int)v[4 * g + j] * mu[j] + ad[j]) >> sh[j];
-        }
-        if (RES) {
-            const int4 mu2 = *(const int4*)&par[(FAST_NP + 2) * 256 + c0 + 4 * g];
-            const int4 ad2 = *(const int4*)&par[(FAST_NP + 3) * 256 + c0 + 4 * g];
-            const int4 sh2 = *(const int4*)&par[(FAST_NP + 4) * 256 + c0 + 4 * g];
-            const int m2[4] = {mu2.x, mu2.y, mu2.z, mu2.w}, a2[4] = {ad2.x, ad2.y, ad2.z, ad2.w};
-            const int s2[4] = {sh2.x, sh2.y, sh2.z, sh2.w};
-            int l2[4] = {0, 0, 0, 0}, h2[4] = {0, 0, 0, 0};
-            if (CLAMP) {
-                const int4 lo2 = *(const int4*)&par[(FAST_NP + 0) * 256 + c0 + 4 * g];
-                const int4 hi2 = *(const int4*)&par[(FAST_NP + 1) * 256 + c0 + 4 * g];
-                l2[0] = lo2.x; l2[1] = lo2.y; l2[2] = lo2.z; l2[3] = lo2.w;
-                h2[0] = hi2.x; h2[1] = hi2.y; h2[2] = hi2.z; h2[3] = hi2.w;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int t = min(max(y[j], t_lo), t_hi);
-                // one byte of the residual word, zero- or sign-extended by a single byte permute
-                const int r = byte_extend(rw[g], j, res_unsigned);
-                int u = t + r;
-                if (CLAMP) u = min(max(u, l2[j]), h2[j]);
-                y[j] = (u * m2[j] + a2[j]) >> s2[j];
-            }
-        }
-        wds[g] = pack4_sat(y[0], y[1], y[2], y[3], out_unsigned);
-    }
-    ((uint4*)op)[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-    ((uint4*)op)[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
-}
-
-
-
 // ---- TMA store / bulk-group helpers ----
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, unsigned src, int x, int y)
 {
@@ -321,12 +243,27 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
     return (unsigned)v;
 }
 
-// NG 8-column groups (NG = 8: 64 columns, NG = 4: 32 columns) of 16 (NK = 2, vA only) or 32 (NK = 4)
-// accumulator rows in the fragment layout above (vA: rows 0-15, vB: rows 16-31 of the region), through the 32-bit
-// epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  Every thread
-// owns column pair 8i + 2(t%4) of rows t/4 + {0, 8, 16, 24}, so one load of the per-channel constants
-// serves eight values.  `region_s` = shared address of the region (1024-byte aligned), `col0` = first
-// column of the block within the warp's columns (a multiple of 8*NG), `pcol0` = the same within the tile.
+// The kernel's dynamic shared memory, named so that the compiler sees shared-space accesses (32-bit
+// addresses, LDS/STS) in the epilogue instead of generic ones with 64-bit address arithmetic.
+__device__ __forceinline__ unsigned char* dyn_smem()
+{
+    extern __shared__ unsigned char smem_raw[];
+    return smem_raw;
+}
+
+// Compile-time switches of the epilogue arithmetic (a bit mask, so that no per-value branch remains)
+static constexpr int EF_OUT_UNSIGNED = 1;   // final range [0,255] instead of [-128,127]
+static constexpr int EF_RES_UNSIGNED = 2;   // residual operand is unsigned
+static constexpr int EF_T_UNSIGNED = 4;     // DP: the cell's own output saturates to [0,255]
+static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are read as signed
+
+// NG 8-column groups (NG = 4: 32 columns) of 16 (NK = 2) accumulator rows in the fragment layout of the
+// 16x256b TMEM load (thread t: rows t/4 and t/4 + 8, column pair 8i + 2(t%4) of group i), through the
+// 32-bit epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  One load of
+// the per-channel constants serves the thread's rows.  `region_off` / `par_off` = byte offsets of the
+// region (1024-byte aligned in shared memory) and of the staged constants from the start of the dynamic
+// shared memory; `col0` = first column of the block within the warp's columns (a multiple of 8*NG),
+// `pcol0` = the same within the tile.
 //
 // Addressing: the byte at (row r, column c) of a region with wb-byte rows sits at
 // r*wb + (c ^ x(r)), x(r) = the swizzle term of row r (address bits [7,10) folded into bits [4,7)).
@@ -335,71 +272,69 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 // four-way byte dot product per value: the saturating pack that clamps t also places the two residual
 // bytes beside it, a = [t0, t1, r0, r1], and b = [m2, 0, m2, 0] (resp. [0, m2, 0, m2]) selects one
 // column.  When t and r differ in signedness the unsigned pair is flipped to signed by xor 0x80 and the
-// host adds 128 * m2 to add2.  dp_xor / dp_a_signed / t_unsigned describe that choice.
-template <int NG, bool RES, bool CLAMP, bool DP, int NK = 4>
-__device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, const int* par, int pcol0,
-                                           unsigned char* region, int wb, int col0, int lane, bool res_unsigned,
-                                           bool out_unsigned, int t_lo, int t_hi, unsigned dp_xor = 0,
-                                           bool dp_a_signed = true, bool t_unsigned = false)
+// host adds 128 * m2 to add2.
+template <int NG, bool RES, bool CLAMP, bool DP, int NK, int EF>
+__device__ __forceinline__ void frag_block(const unsigned* v, unsigned par_off, int pcol0, unsigned region_off, int wb,
+                                           int col0, int lane, int t_lo, int t_hi, unsigned dp_xor)
 {
+    unsigned char* const sm = dyn_smem();
     const int tr = lane >> 2, tc = (lane & 3) * 2;
     unsigned base[NK];
 #pragma unroll
     for (int k = 0; k < NK; ++k) {
         const unsigned ro = (unsigned)((tr + 8 * k) * wb);
         const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
-        base[k] = ro + ((unsigned)(col0 | tc) ^ xm);
+        base[k] = region_off + ro + ((unsigned)(col0 | tc) ^ xm);
     }
-    // the residual bytes of the whole block first: plain loads the compiler can keep in flight together
+    // the residual bytes of the whole block first: loads the compiler can keep in flight together
     unsigned rres[NG][NK];
     if (RES) {
 #pragma unroll
         for (int i = 0; i < NG; ++i)
 #pragma unroll
-            for (int k = 0; k < NK; ++k) rres[i][k] = *(const unsigned short*)(region + (base[k] ^ (unsigned)(8 * i)));
+            for (int k = 0; k < NK; ++k) rres[i][k] = *(const unsigned short*)(sm + (base[k] ^ (unsigned)(8 * i)));
     }
+    const unsigned pbase = par_off + (unsigned)(pcol0 + tc) * 4u;
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
-        const int pc = pcol0 + 8 * i + tc;   // column pair within the tile
-        const int2 mu = *(const int2*)&par[2 * 256 + pc];
-        const int2 ad = *(const int2*)&par[3 * 256 + pc];
-        const int2 sh = *(const int2*)&par[4 * 256 + pc];
+        const unsigned pp = pbase + 32u * i;   // column pair 8i + tc within the tile
+        const int2 mu = *(const int2*)(sm + pp + 2 * 1024);
+        const int2 ad = *(const int2*)(sm + pp + 3 * 1024);
+        const int2 sh = *(const int2*)(sm + pp + 4 * 1024);
         int2 lo = make_int2(0, 0), hi = make_int2(0, 0);
         if (CLAMP) {
-            lo = *(const int2*)&par[0 * 256 + pc];
-            hi = *(const int2*)&par[1 * 256 + pc];
+            lo = *(const int2*)(sm + pp + 0 * 1024);
+            hi = *(const int2*)(sm + pp + 1 * 1024);
         }
         int2 mu2 = make_int2(0, 0), ad2 = mu2, sh2 = mu2, lo2 = mu2, hi2 = mu2;
         if (RES) {
-            mu2 = *(const int2*)&par[(FAST_NP + 2) * 256 + pc];
-            ad2 = *(const int2*)&par[(FAST_NP + 3) * 256 + pc];
-            sh2 = *(const int2*)&par[(FAST_NP + 4) * 256 + pc];
+            mu2 = *(const int2*)(sm + pp + (FAST_NP + 2) * 1024);
+            ad2 = *(const int2*)(sm + pp + (FAST_NP + 3) * 1024);
+            sh2 = *(const int2*)(sm + pp + (FAST_NP + 4) * 1024);
             if (CLAMP) {
-                lo2 = *(const int2*)&par[(FAST_NP + 0) * 256 + pc];
-                hi2 = *(const int2*)&par[(FAST_NP + 1) * 256 + pc];
+                lo2 = *(const int2*)(sm + pp + (FAST_NP + 0) * 1024);
+                hi2 = *(const int2*)(sm + pp + (FAST_NP + 1) * 1024);
             }
-            if (DP) lo2 = *(const int2*)&par[(FAST_NP + 0) * 256 + pc];
+            if (DP) lo2 = *(const int2*)(sm + pp + (FAST_NP + 0) * 1024);
         }
 #pragma unroll
         for (int k = 0; k < NK; ++k) {   // rows tr + 8k
-            const unsigned* v = (k < 2) ? vA : vB;
-            int x0 = (int)v[4 * i + 2 * (k & 1)], x1 = (int)v[4 * i + 2 * (k & 1) + 1];
+            int x0 = (int)v[4 * i + 2 * k], x1 = (int)v[4 * i + 2 * k + 1];
             if (CLAMP) {
                 x0 = min(max(x0, lo.x), hi.x);
                 x1 = min(max(x1, lo.y), hi.y);
             }
             int y0 = (x0 * mu.x + ad.x) >> sh.x;
             int y1 = (x1 * mu.y + ad.y) >> sh.y;
-            const unsigned addr = base[k] ^ (unsigned)(8 * i);
             if (RES && DP) {
                 const unsigned rw = rres[i][k];   // two residual bytes, replaced below
                 unsigned a4;
-                if (t_unsigned) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(a4) : "r"(y1), "r"(y0), "r"(rw));
+                if (EF & EF_T_UNSIGNED) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(a4) : "r"(y1), "r"(y0), "r"(rw));
                 else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(a4) : "r"(y1), "r"(y0), "r"(rw));
                 a4 ^= dp_xor;
                 // lo2 row holds the column-selecting multiplier words, ad2 the (compensated) addends
                 int d0, d1;
-                if (dp_a_signed) {
+                if (EF & EF_DP_A_SIGNED) {
                     asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d0) : "r"(a4), "r"(lo2.x), "r"(ad2.x));
                     asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d1) : "r"(a4), "r"(lo2.y), "r"(ad2.y));
                 } else {
@@ -411,7 +346,7 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
             } else if (RES) {
                 const unsigned rw = rres[i][k];   // two residual bytes, replaced below
                 int r0, r1;
-                if (res_unsigned) {
+                if (EF & EF_RES_UNSIGNED) {
                     r0 = (int)(rw & 0xffu);
                     r1 = (int)(rw >> 8);
                 } else {
@@ -428,32 +363,29 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
                 y1 = (u1 * mu2.y + ad2.y) >> sh2.y;
             }
             unsigned d;
-            if (out_unsigned) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
+            if (EF & EF_OUT_UNSIGNED) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
             else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
-            *(unsigned short*)(region + addr) = (unsigned short)d;
+            *(unsigned short*)(sm + (base[k] ^ (unsigned)(8 * i))) = (unsigned short)d;
         }
     }
 }
 
-
-// The 32-bit epilogue of one 128 x BN accumulator tile, as executed by one epilogue warp.  The warp owns
-// 16 of the tile's rows (lane quadrant `quad` of TMEM, half `rh`) and the column half `cp` (tiles wider
-// than 128 columns are split in two so that a staged row stays within 128 bytes): it waits for the
-// accumulator (and for its slice of the residual, which it fetched itself by TMA into its staging
-// region), requantises in the fragment layout, hands the accumulator back, and stores its region with one
-// TMA store.  Returns false when a bounded wait gave up.
+// One accumulator tile through the fragment-layout epilogue: residual slice in by TMA (issued one tile
+// ahead when the warp has two staging regions), accumulator slice out of TMEM, requantisation into the
+// swizzled staging region, TMA store.  A warp owns 16 rows (quadrant `quad`, half `rh`) and the column
+// part `cp` of the tile; tiles up to 128 columns have a single part, so `cp` != 0 idles there.
 struct EpiTile {
     unsigned tmem_acc;      // TMEM address of the accumulator stage (lane 0, first column)
     int BN, N, M, m0, n0;
     int next_m0, next_n0;   // the tile this warp handles next (next_m0 < 0: none): its residual is prefetched
-    const int* par;         // staged per-channel constants of this column block
-    unsigned char* region_p; // this warp's staging region(s) (1024-byte aligned)
+    unsigned par_off;       // staged per-channel constants of this column block (byte offset in dynamic shared memory)
+    unsigned region_off;    // this warp's staging region(s) (1024-byte aligned; byte offset in dynamic shared memory)
     unsigned region_stride; // distance to the second region (residual cells double-buffer), 0 = one region
     unsigned rbar;          // this warp's residual-arrival mbarriers (two, 8 bytes apart)
     unsigned tfull, tfull_parity, tempty;
     volatile int* abort_flag;
     int* status;
-    bool res_unsigned, out_unsigned, dp_a_signed;
+    int ef;                 // EF_* switches of this cell
     int t_lo, t_hi;
     unsigned dp_xor;
 };
@@ -464,6 +396,20 @@ struct EpiState {
     unsigned used0 = 0, used1 = 0;   // completed waits per residual barrier (its parity)
     bool prefetched = false; // the current tile's residual load was issued during the previous tile
 };
+
+// The accumulator slice of one warp: wb columns in blocks of 32, 16 rows
+template <bool RES, bool CLAMP, bool DP, int EF>
+__device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, int wb, int lane)
+{
+#pragma unroll 1
+    for (int cb = 0; cb < wb; cb += 32) {
+        unsigned v[16];
+        tc_ld_16x256b_x4(tbase + (unsigned)cb, v);
+        tc_wait_ld();
+        reg_fence16(v);
+        frag_block<4, RES, CLAMP, DP, 2, EF>(v, e.par_off, cbase + cb, region_off, wb, cb, lane, e.t_lo, e.t_hi, e.dp_xor);
+    }
+}
 
 template <bool RES, bool CLAMP, bool DP>
 __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
@@ -476,8 +422,8 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
     const bool owns = cp < col_parts;
     const bool active = owns && gx < e.N && gy < e.M;
     const unsigned b = (RES && e.region_stride) ? (st.t & 1u) : 0u;
-    unsigned char* region_p = e.region_p + b * e.region_stride;
-    const unsigned region = smem_u32(region_p);
+    const unsigned region_off = e.region_off + b * e.region_stride;
+    const unsigned region = smem_u32(dyn_smem() + region_off);
     if (lane == 0) {
         bulk_wait_read_all();   // earlier stores have finished reading both regions
         if (RES) {
@@ -491,7 +437,7 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
                 if (owns && nx < e.N && ny < e.M) {
                     const unsigned nb = b ^ 1u;
                     mbar_expect_tx(e.rbar + 8u * nb, (unsigned)(16 * wb));
-                    tma_load_2d(smem_u32(e.region_p + nb * e.region_stride), tmR, e.rbar + 8u * nb, nx, ny);
+                    tma_load_2d(smem_u32(dyn_smem() + e.region_off + nb * e.region_stride), tmR, e.rbar + 8u * nb, nx, ny);
                 }
             }
         }
@@ -512,16 +458,30 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
         if (b) ++st.used1; else ++st.used0;
     }
     tc_fence_after();
-    if (owns) {
+    if (active) {
         const unsigned tbase = e.tmem_acc + ((unsigned)(quad * 32 + rh * 16) << 16) + (unsigned)cbase;
-        for (int cb = 0; cb < wb; cb += 32) {
-            unsigned v[16];
-            tc_ld_16x256b_x4(tbase + (unsigned)cb, v);
-            tc_wait_ld();
-            reg_fence16(v);
-            if (active)
-                frag_block<4, RES, CLAMP, DP, 2>(v, v, e.par, cbase + cb, region_p, wb, cb, lane, e.res_unsigned,
-                                                 e.out_unsigned, e.t_lo, e.t_hi, e.dp_xor, e.dp_a_signed, e.t_lo == 0);
+        // one branch per tile selects the arithmetic variant; inside, nothing depends on a run-time flag
+        if (!RES) {
+            if (e.ef & EF_OUT_UNSIGNED) epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, wb, lane);
+            else epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane);
+        } else if (!DP) {
+            switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED)) {
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, wb, lane); break;
+            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, wb, lane); break;
+            default: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, wb, lane); break;
+            }
+        } else {
+            switch (e.ef & (EF_OUT_UNSIGNED | EF_T_UNSIGNED | EF_DP_A_SIGNED)) {
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, wb, lane); break;
+            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, wb, lane); break;
+            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, wb, lane); break;
+            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, wb, lane); break;
+            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, wb, lane); break;
+            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, wb, lane); break;
+            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, wb, lane); break;
+            }
         }
     }
     // the accumulator is drained: hand it back before the store goes out
