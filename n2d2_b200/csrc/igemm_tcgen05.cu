@@ -222,14 +222,11 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int part = (warp - EPI_WARP0) >> 2;        // 0..3 within the quadrant
-        const int rh = part & 1;                         // which 16 of the quadrant's 32 rows (32-bit epilogue)
-        const int col_parts = a.BN > 128 ? 2 : 1;        // column halves (32-bit epilogue): rows stay <= 128 bytes
+        const int part = (warp - EPI_WARP0) >> 2;        // 0..3 within the quadrant: a quarter of the columns (32-bit epilogue)
         const int row = quad * 32 + lane;
         const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
-        // the 32-bit epilogue splits the columns over all warps of a quadrant; the exact 64-bit one works
-        // in 32-column chunks and uses the first two warps of each quadrant
-        const int cols_per_warp = FAST ? a.BN / col_parts : a.BN / 2;
+        // the exact 64-bit epilogue works in 32-column chunks on the first two warps of each quadrant
+        const int cols_per_warp = a.BN / 2;
         unsigned acc_it = 0;
         unsigned stage_it = 0;
         EpiState est;
@@ -268,13 +265,14 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int m = m0 + row;
             const bool m_ok = m < a.M;
             const int nchunks = cols_per_warp / 32;
-            const int cbase = FAST ? (part >> 1) * cols_per_warp : part * cols_per_warp;
+            const int cbase = part * cols_per_warp;
             if (FAST) {
                 // fragment-layout epilogue with swizzled staging, TMA store and TMA residual load
                 const int ew = warp - EPI_WARP0;
                 EpiTile e;
                 e.tmem_acc = tmem_base + as * (unsigned)a.BN;
                 e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = m0; e.n0 = n0;
+                e.wp = a.BN >> 2;
                 e.par_off = (unsigned)((unsigned char*)par - smem_raw);
                 e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * REGION_BYTES * regions_per_warp);
                 e.region_stride = RES ? REGION_BYTES : 0;
@@ -288,7 +286,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 e.abort_flag = abort_flag; e.status = a.status;
                 e.ef = a.ef;
                 e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
-                if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, rh, part >> 1, lane, est)) { ok = false; break; }
+                if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, part, lane, est)) { ok = false; break; }
                 continue;
             } else {
                 if (!mbar_wait_warp(tfull0 + 8u * as, aph, abort_flag, a.status, 4, lane)) { ok = false; break; }
@@ -491,13 +489,13 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
             if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
         }
     }
-    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 16 rows x up to 128 columns
+    // output (and residual) as [M][N] bytes, one box = an epilogue warp's 32 rows x BN/4 columns
     plan->has_out_maps = 0;
     if (out && g.O % 16 == 0 && !((uintptr_t)out & 15) && !((uintptr_t)res & 15)) {
-        const int wb = plan->BN > 128 ? plan->BN / 2 : plan->BN;
+        const int wb = plan->BN / 4;   // an epilogue warp's columns: 64, 32 or 16
         const cuuint64_t dims[2] = {(cuuint64_t)g.O, (cuuint64_t)plan->M};
         const cuuint64_t strides[1] = {(cuuint64_t)g.O};
-        const cuuint32_t box[2] = {(cuuint32_t)wb, 16};
+        const cuuint32_t box[2] = {(cuuint32_t)wb, 32};
         const cuuint32_t estr[2] = {1, 1};
         rc = g_encode_tiled(&plan->tmO, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)out, dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(wb), CU_TENSOR_MAP_L2_PROMOTION_NONE,

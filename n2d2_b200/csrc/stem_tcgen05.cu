@@ -98,7 +98,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     unsigned char* smB = smem;
     unsigned char* smA = smem + ((b_bytes + 1023) & ~1023);
     unsigned char* stage_out = smA + (size_t)a.stages * a_stage_bytes;
-    const int region_bytes = 16 * a.BN;                    // staging of one epilogue warp: 16 rows x BN bytes
+    const int region_bytes = 16 * a.BN;                    // staging of one epilogue warp: 32 rows x BN/2 bytes
     unsigned long long* bars = (unsigned long long*)(stage_out + S_EPI_WARPS * region_bytes);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], weights
     const unsigned full0 = smem_u32(bars);
@@ -251,7 +251,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         // ------------------------------------------------------------------ epilogue warps
         const int ew = warp - (1 + S_PROD_WARPS);
         const int quad = warp & 3;
-        const int rh = (ew >> 2) & 1;
+        const int cp = (ew >> 2) & 1;           // column half of the tile
         unsigned acc_it = 0;
         EpiState est;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
@@ -259,6 +259,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             EpiTile e;
             e.tmem_acc = tmem_base + as * (unsigned)a.BN;
             e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = tile * SBM; e.n0 = 0;
+            e.wp = a.BN >> 1;
             e.next_m0 = -1; e.next_n0 = 0;
             e.par_off = (unsigned)((unsigned char*)par - smem_raw);
             e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
@@ -268,7 +269,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             e.abort_flag = abort_flag; e.status = a.status;
             e.ef = a.out_unsigned ? EF_OUT_UNSIGNED : 0;
             e.t_lo = 0; e.t_hi = 0; e.dp_xor = 0;
-            if (!fast_epilogue_tile<false, CLAMP, false>(&tmO, &tmO, e, quad, rh, 0, lane, est)) break;
+            if (!fast_epilogue_tile<false, CLAMP, false>(&tmO, &tmO, e, quad, cp, lane, est)) break;
         }
         if (lane == 0) bulk_wait_all();
     }
@@ -366,11 +367,11 @@ cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g
     {
         const cuuint64_t odims[2] = {(cuuint64_t)g.O, (cuuint64_t)a.M};
         const cuuint64_t ostrides[1] = {(cuuint64_t)g.O};
-        const cuuint32_t obox[2] = {(cuuint32_t)plan.BN, 16};   // an epilogue warp's 16 rows x BN columns (clipped to N)
+        const cuuint32_t obox[2] = {(cuuint32_t)(plan.BN / 2), 32};   // an epilogue warp's 32 rows x BN/2 columns (clipped to N)
         const cuuint32_t estr[2] = {1, 1};
         const CUresult rc = ((EncodeTiledFn)plan.encode)(
             &tmO, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, out, odims, ostrides, obox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            plan.BN == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            plan.BN == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rc != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }

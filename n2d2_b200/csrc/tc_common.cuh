@@ -180,49 +180,45 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// tcgen05.ld 16 lanes x 256 bits, repeated over 8 (x8: 64 columns) or 4 (x4: 32 columns) column groups.
+// tcgen05.ld 16 lanes x 256 bits, repeated over 4 (x4: 32 columns) or 2 (x2: 16 columns) column groups.
 // Thread t receives, for group i: regs 4i+{0,1} = row (lane0 + t/4), columns 8i + 2(t%4) + {0,1};
 // regs 4i+{2,3} = the same columns of row (lane0 + t/4 + 8).
-__device__ __forceinline__ void tc_ld_16x256b_x8(unsigned taddr, unsigned* v)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_16x256b_x4(unsigned taddr, unsigned* v)
+// The load and its wait form one statement, so every use of the registers follows the wait.
+__device__ __forceinline__ void tc_ld_16x256b_x4_wait(unsigned taddr, unsigned* v)
 {
     asm volatile(
         "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tc_ld_16x256b_x2(unsigned taddr, unsigned* v)
+// Two 16-lane halves of a warp's 32 TMEM lanes, one wait for both
+__device__ __forceinline__ void tc_ld_2x16x256b_x4_wait(unsigned taddr, unsigned* va, unsigned* vb)
 {
     asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-        : "r"(taddr) : "memory");
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%32];\n\t"
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%33];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(va[0]), "=r"(va[1]), "=r"(va[2]), "=r"(va[3]), "=r"(va[4]), "=r"(va[5]), "=r"(va[6]), "=r"(va[7]),
+          "=r"(va[8]), "=r"(va[9]), "=r"(va[10]), "=r"(va[11]), "=r"(va[12]), "=r"(va[13]), "=r"(va[14]), "=r"(va[15]),
+          "=r"(vb[0]), "=r"(vb[1]), "=r"(vb[2]), "=r"(vb[3]), "=r"(vb[4]), "=r"(vb[5]), "=r"(vb[6]), "=r"(vb[7]),
+          "=r"(vb[8]), "=r"(vb[9]), "=r"(vb[10]), "=r"(vb[11]), "=r"(vb[12]), "=r"(vb[13]), "=r"(vb[14]), "=r"(vb[15])
+        : "r"(taddr), "r"(taddr + (16u << 16)) : "memory");
 }
-__device__ __forceinline__ void reg_fence8(unsigned* v)
+__device__ __forceinline__ void tc_ld_2x16x256b_x2_wait(unsigned taddr, unsigned* va, unsigned* vb)
 {
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
-                 :: "memory");
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%16];\n\t"
+        "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%8, %9, %10, %11, %12, %13, %14, %15}, [%17];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(va[0]), "=r"(va[1]), "=r"(va[2]), "=r"(va[3]), "=r"(va[4]), "=r"(va[5]), "=r"(va[6]), "=r"(va[7]),
+          "=r"(vb[0]), "=r"(vb[1]), "=r"(vb[2]), "=r"(vb[3]), "=r"(vb[4]), "=r"(vb[5]), "=r"(vb[6]), "=r"(vb[7])
+        : "r"(taddr), "r"(taddr + (16u << 16)) : "memory");
 }
-__device__ __forceinline__ void reg_fence16(unsigned* v)
-{
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                      "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
-                 :: "memory");
-}
-
 // Byte offset of (row r, byte column c) inside a staging region whose rows are `wb` bytes (32, 64 or
 // 128) and which TMA reads / writes with the swizzle of that width: address bits [4,7) are XORed with
 // bits [7,10) (masked to the swizzle width).  The region base must be 1024-byte aligned.
@@ -257,10 +253,11 @@ static constexpr int EF_RES_UNSIGNED = 2;   // residual operand is unsigned
 static constexpr int EF_T_UNSIGNED = 4;     // DP: the cell's own output saturates to [0,255]
 static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are read as signed
 
-// NG 8-column groups (NG = 4: 32 columns) of 16 (NK = 2) accumulator rows in the fragment layout of the
-// 16x256b TMEM load (thread t: rows t/4 and t/4 + 8, column pair 8i + 2(t%4) of group i), through the
+// NG 8-column groups (NG = 4: 32 columns, NG = 2: 16) of a warp's 32 accumulator rows in the fragment layout
+// of the 16x256b TMEM load (thread t: rows t/4 + {0, 8, 16, 24}, column pair 8i + 2(t%4) of group i), through the
 // 32-bit epilogue, into (and, for the residual, out of) the warp's swizzled staging region.  One load of
-// the per-channel constants serves the thread's rows.  `region_off` / `par_off` = byte offsets of the
+// the per-channel constants serves the thread's four rows: shared-memory bandwidth, not arithmetic, is
+// what this epilogue runs out of first, and a 64-bit load costs two wavefronts however many lanes share it.  `region_off` / `par_off` = byte offsets of the
 // region (1024-byte aligned in shared memory) and of the staged constants from the start of the dynamic
 // shared memory; `col0` = first column of the block within the warp's columns (a multiple of 8*NG),
 // `pcol0` = the same within the tile.
@@ -273,11 +270,12 @@ static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are r
 // bytes beside it, a = [t0, t1, r0, r1], and b = [m2, 0, m2, 0] (resp. [0, m2, 0, m2]) selects one
 // column.  When t and r differ in signedness the unsigned pair is flipped to signed by xor 0x80 and the
 // host adds 128 * m2 to add2.
-template <int NG, bool RES, bool CLAMP, bool DP, int NK, int EF>
-__device__ __forceinline__ void frag_block(const unsigned* v, unsigned par_off, int pcol0, unsigned region_off, int wb,
+template <int NG, bool RES, bool CLAMP, bool DP, int EF>
+__device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, unsigned par_off, int pcol0, unsigned region_off, int wb,
                                            int col0, int lane, int t_lo, int t_hi, unsigned dp_xor)
 {
     unsigned char* const sm = dyn_smem();
+    constexpr int NK = 4;   // rows tr + 8k: k = 0, 1 from vA (TMEM lanes 0-15), k = 2, 3 from vB (lanes 16-31)
     const int tr = lane >> 2, tc = (lane & 3) * 2;
     unsigned base[NK];
 #pragma unroll
@@ -319,7 +317,8 @@ __device__ __forceinline__ void frag_block(const unsigned* v, unsigned par_off, 
         }
 #pragma unroll
         for (int k = 0; k < NK; ++k) {   // rows tr + 8k
-            int x0 = (int)v[4 * i + 2 * k], x1 = (int)v[4 * i + 2 * k + 1];
+            const unsigned* v = (k < 2) ? vA : vB;
+            int x0 = (int)v[4 * i + 2 * (k & 1)], x1 = (int)v[4 * i + 2 * (k & 1) + 1];
             if (CLAMP) {
                 x0 = min(max(x0, lo.x), hi.x);
                 x1 = min(max(x1, lo.y), hi.y);
@@ -372,11 +371,12 @@ __device__ __forceinline__ void frag_block(const unsigned* v, unsigned par_off, 
 
 // One accumulator tile through the fragment-layout epilogue: residual slice in by TMA (issued one tile
 // ahead when the warp has two staging regions), accumulator slice out of TMEM, requantisation into the
-// swizzled staging region, TMA store.  A warp owns 16 rows (quadrant `quad`, half `rh`) and the column
-// part `cp` of the tile; tiles up to 128 columns have a single part, so `cp` != 0 idles there.
+// swizzled staging region, TMA store.  A warp owns the 32 rows of its TMEM quadrant `quad` and the column
+// part `cp` (wp columns) of the tile.
 struct EpiTile {
     unsigned tmem_acc;      // TMEM address of the accumulator stage (lane 0, first column)
     int BN, N, M, m0, n0;
+    int wp;                 // columns per warp: BN / (epilogue warps per TMEM quadrant); 64, 32 or 16
     int next_m0, next_n0;   // the tile this warp handles next (next_m0 < 0: none): its residual is prefetched
     unsigned par_off;       // staged per-channel constants of this column block (byte offset in dynamic shared memory)
     unsigned region_off;    // this warp's staging region(s) (1024-byte aligned; byte offset in dynamic shared memory)
@@ -397,61 +397,57 @@ struct EpiState {
     bool prefetched = false; // the current tile's residual load was issued during the previous tile
 };
 
-// The accumulator slice of one warp: wb columns in blocks of 32, 16 rows
+// The accumulator slice of one warp: 32 rows, wp columns in blocks of 32 (or one block of 16)
 template <bool RES, bool CLAMP, bool DP, int EF>
-__device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, int wb, int lane)
+__device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, int lane)
 {
+    if (e.wp >= 32) {
 #pragma unroll 1
-    for (int cb = 0; cb < wb; cb += 32) {
-        unsigned v[16];
-        tc_ld_16x256b_x4(tbase + (unsigned)cb, v);
-        tc_wait_ld();
-        reg_fence16(v);
-        frag_block<4, RES, CLAMP, DP, 2, EF>(v, e.par_off, cbase + cb, region_off, wb, cb, lane, e.t_lo, e.t_hi, e.dp_xor);
+        for (int cb = 0; cb < e.wp; cb += 32) {
+            unsigned va[16], vb[16];
+            tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
+            frag_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, e.wp, cb, lane, e.t_lo, e.t_hi,
+                                              e.dp_xor);
+        }
+    } else {
+        unsigned va[8], vb[8];
+        tc_ld_2x16x256b_x2_wait(tbase, va, vb);
+        frag_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, e.wp, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
     }
 }
 
 template <bool RES, bool CLAMP, bool DP>
 __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
-                                                   int rh, int cp, int lane, EpiState& st)
+                                                   int cp, int lane, EpiState& st)
 {
-    const int col_parts = e.BN > 128 ? 2 : 1;
-    const int wb = e.BN / col_parts;
-    const int cbase = cp * wb;
-    const int gx = e.n0 + cbase, gy = e.m0 + quad * 32 + rh * 16;
-    const bool owns = cp < col_parts;
-    const bool active = owns && gx < e.N && gy < e.M;
+    const int wp = e.wp;
+    const int cbase = cp * wp;
+    const int gx = e.n0 + cbase, gy = e.m0 + quad * 32;
+    const bool active = gx < e.N && gy < e.M;
     const unsigned b = (RES && e.region_stride) ? (st.t & 1u) : 0u;
     const unsigned region_off = e.region_off + b * e.region_stride;
     const unsigned region = smem_u32(dyn_smem() + region_off);
+    bool next_issued = false;   // same decision on every lane: does the next tile's residual travel early?
+    if (RES && e.region_stride && e.next_m0 >= 0)
+        next_issued = e.next_n0 + cbase < e.N && e.next_m0 + quad * 32 < e.M;
     if (lane == 0) {
         bulk_wait_read_all();   // earlier stores have finished reading both regions
         if (RES) {
             if (active && !st.prefetched) {
-                mbar_expect_tx(e.rbar + 8u * b, (unsigned)(16 * wb));
+                mbar_expect_tx(e.rbar + 8u * b, (unsigned)(32 * wp));
                 tma_load_2d(region, tmR, e.rbar + 8u * b, gx, gy);
             }
             // the next tile's slice of the residual travels while this tile is computed
-            if (e.region_stride && e.next_m0 >= 0) {
-                const int nx = e.next_n0 + cbase, ny = e.next_m0 + quad * 32 + rh * 16;
-                if (owns && nx < e.N && ny < e.M) {
-                    const unsigned nb = b ^ 1u;
-                    mbar_expect_tx(e.rbar + 8u * nb, (unsigned)(16 * wb));
-                    tma_load_2d(smem_u32(dyn_smem() + e.region_off + nb * e.region_stride), tmR, e.rbar + 8u * nb, nx, ny);
-                }
+            if (next_issued) {
+                const unsigned nb = b ^ 1u;
+                mbar_expect_tx(e.rbar + 8u * nb, (unsigned)(32 * wp));
+                tma_load_2d(smem_u32(dyn_smem() + e.region_off + nb * e.region_stride), tmR, e.rbar + 8u * nb,
+                            e.next_n0 + cbase, e.next_m0 + quad * 32);
             }
         }
     }
     __syncwarp();
-    if (RES) {
-        // same decision on every lane: was the next tile's load issued?
-        bool next_issued = false;
-        if (e.region_stride && e.next_m0 >= 0) {
-            const int nx = e.next_n0 + cbase, ny = e.next_m0 + quad * 32 + rh * 16;
-            next_issued = owns && nx < e.N && ny < e.M;
-        }
-        st.prefetched = next_issued;
-    }
+    if (RES) st.prefetched = next_issued;
     if (!mbar_wait_warp(e.tfull, e.tfull_parity, e.abort_flag, e.status, 4, lane)) return false;
     if (RES && active) {
         if (!mbar_wait_warp(e.rbar + 8u * b, (b ? st.used1 : st.used0) & 1u, e.abort_flag, e.status, 7, lane)) return false;
@@ -459,28 +455,28 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
     }
     tc_fence_after();
     if (active) {
-        const unsigned tbase = e.tmem_acc + ((unsigned)(quad * 32 + rh * 16) << 16) + (unsigned)cbase;
+        const unsigned tbase = e.tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)cbase;
         // one branch per tile selects the arithmetic variant; inside, nothing depends on a run-time flag
         if (!RES) {
-            if (e.ef & EF_OUT_UNSIGNED) epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, wb, lane);
-            else epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane);
+            if (e.ef & EF_OUT_UNSIGNED) epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane);
+            else epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane);
         } else if (!DP) {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, wb, lane); break;
-            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, wb, lane); break;
-            default: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, wb, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, lane); break;
+            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, lane); break;
+            default: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, lane); break;
             }
         } else {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_T_UNSIGNED | EF_DP_A_SIGNED)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, wb, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, wb, lane); break;
-            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, wb, lane); break;
-            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, wb, lane); break;
-            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, wb, lane); break;
-            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, wb, lane); break;
-            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, wb, lane); break;
-            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, wb, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, lane); break;
+            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, lane); break;
+            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, lane); break;
+            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, lane); break;
+            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, lane); break;
+            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, lane); break;
+            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, lane); break;
             }
         }
     }
