@@ -64,6 +64,25 @@ struct FastQuant {
     bool enabled = false;
 };
 
+// ---- stride-1 convolution from a shared-memory input patch (tcgen05 kind::i8) ----
+struct PatchPlan {
+    CUtensorMap tmA;      // NHWC activations, box = one patch: C x Wp x (R + halo rows) x 1 image
+    CUtensorMap tmB;      // weights [O][taps*C], box = one tap of all outputs
+    int BN;               // accumulator columns: 64 or 128
+    int Wp;               // patch width in pixels: oW + (kW-1)*dX
+    int R, bands;         // output rows per band, bands per image
+    int patch_bytes;      // bytes of one patch load
+    int patch_alloc;      // bytes reserved per patch buffer
+    int in_unsigned;
+    int num_sms;
+    size_t smem_bytes;
+};
+bool patch_eligible(const ConvGeom& g);
+int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
+                    const char** why);
+cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQuant& fast, void* out, int* status_word,
+                         cudaStream_t s);
+
 // ---- tensor-core implicit GEMM (tcgen05 kind::i8) ----
 struct IgemmPlan {
     CUtensorMap tmA;      // activations: 2-D tiled [M][K] or 4-D im2col NHWC

@@ -38,7 +38,7 @@ static int fail(int code, const char* fmt, ...)
 
 // ------------------------------------------------------------------------------------ model
 enum CellType { CELL_CONV, CELL_FC, CELL_POOL, CELL_SUM, CELL_SCALING };
-enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED, ENG_STEM };
+enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED, ENG_STEM, ENG_PATCH };
 
 struct TensorRec {
     int C = 0, H = 0, W = 0;
@@ -86,6 +86,8 @@ struct CellRec {
     // first-layer tensor-core kernel
     StemPlan stem{};
     void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel and its zero padding written out
+    // stride-1 convolution from a shared-memory patch
+    PatchPlan patch{};
     // tensor-core plan
     IgemmPlan plan{};
     bool has_plan = false;
@@ -825,6 +827,12 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                                              c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0))
                         return rc;
                 }
+                // small-channel stride-1 layers read their input once, from a shared-memory patch
+                if (c.fast.enabled && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
+                    && !(flags & (N2D2B_FORCE_IM2COL | N2D2B_EXACT64_EPILOGUE)) && patch_eligible(gb)
+                    && patch_make_plan(&c.patch, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
+                                       net->num_sms, &why) == 0)
+                    c.engine = ENG_PATCH;
             }
         }
     }
@@ -860,7 +868,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
     const TensorRec& tout = net->tensors[c.output];
     if (!in0 || !out) return fail(N2D2B_ERR_STATE, "internal: tensor without a buffer");
     if (img0) {
-        if (c.engine == ENG_TCGEN05 || c.engine == ENG_SUM || c.residual >= 0)
+        if (c.engine == ENG_TCGEN05 || c.engine == ENG_PATCH || c.engine == ENG_SUM || c.residual >= 0)
             return fail(N2D2B_ERR_STATE, "internal: this cell cannot run on a slice");
         in0 = (const uint8_t*)in0 + (size_t)img0 * tin.bytes_per_image();
         out = (uint8_t*)out + (size_t)img0 * tout.bytes_per_image();
@@ -885,6 +893,20 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         IgemmPlan p = c.plan;
         p.M = batch * c.geom.oH * c.geom.oW;
         CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, net->d_status, s));
+        break;
+    }
+    case ENG_PATCH: {
+        if (c.plan_input != in0) {
+            ConvGeom gb = c.geom;
+            gb.B = net->max_batch;
+            const char* why = "";
+            if (patch_make_plan(&c.patch, in0, c.d_weights, gb, tin.is_unsigned, net->num_sms, &why))
+                return fail(N2D2B_ERR_INVALID, "patch plan failed: %s", why);
+            c.plan_input = in0;
+        }
+        ConvGeom g = c.geom;
+        g.B = batch;
+        CUDA_TRY(launch_patch(c.patch, g, c.fast, out, net->d_status, s));
         break;
     }
     case ENG_STEM: {
@@ -1086,6 +1108,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
     case ENG_SUM: return "sum";
     case ENG_FUSED: return "fused";
     case ENG_STEM: return "stem-tcgen05";
+    case ENG_PATCH: return "patch-tcgen05";
     }
     return "";
 }

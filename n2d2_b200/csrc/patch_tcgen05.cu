@@ -1,0 +1,377 @@
+// Stride-1 convolution with a small channel count (32, 64 or 128) on the tensor cores, fed from an input
+// patch that is loaded once: the 3x3 layers of the first ResNet stage, where the implicit-GEMM kernel
+// would fetch every input pixel nine times through im2col loads and wait on a barrier per filter tap.
+//
+// A CTA works on a band of R output rows of one image.  One TMA load brings the (R + halo) x (oW + halo)
+// x C input patch, zero-filled outside the image, into shared memory as rows of one pixel each (C bytes,
+// swizzled by C).  Seen as a list of pixels p = y * Wp + x, the patch is its own im2col matrix: the operand
+// of filter tap (ky, kx) for the 128 consecutive positions p0 .. p0+127 is the 128 patch rows that start
+// at p0 + ky*dY*Wp + kx*dX.  So every tap is one shared-memory descriptor with a different start row,
+// no data moves, and the MMAs of a tile (taps x C/32 of them) are issued back to back.  Positions in the
+// halo columns (x >= oW) compute values nobody stores.  The weights of all taps stay resident.
+//
+// Warp 0 loads (weights once, patches double-buffered), warp 1 issues tcgen05.mma kind::i8 into a ring of
+// four TMEM accumulators, and four groups of four epilogue warps (one warp per TMEM lane quadrant) each
+// drain every fourth tile: 32-bit requantisation in the fragment layout into a swizzled staging region,
+// then one 16-byte-vector copy per pixel row to the NHWC output.  Every wait is bounded.
+#include <cstring>
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace n2d2b {
+
+static constexpr int PBM = 128;
+static constexpr int P_EPI_WARPS = 16;
+static constexpr int P_SLOTS = 4;            // TMEM accumulators = epilogue groups
+static constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
+
+struct PatchArgs {
+    int B, oH, oW, N, BN, C;
+    int taps_y, taps_x, dY, dX, pT, pL;
+    int Wp;                 // patch width in pixels: oW + (kW-1)*dX
+    int R;                  // output rows per band
+    int bands;              // bands per image
+    int patch_bytes;        // bytes one patch load delivers (the full TMA box)
+    int patch_alloc;        // bytes reserved per patch buffer (box + the rows a last tile may read past it)
+    unsigned rcp_Wp;        // ceil(2^32 / Wp)
+    unsigned idesc, tmem_cols;
+    void* out;
+    int* status;
+    const int* fq;
+    int cpad;
+    int out_unsigned;
+};
+
+template <bool CLAMP, int EF>
+__device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int BN, int lane)
+{
+#pragma unroll 1
+    for (int cb = 0; cb < BN; cb += 32) {
+        unsigned va[16], vb[16];
+        tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
+        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, cb, region_off, BN, cb, lane, 0, 0, 0u);
+    }
+}
+
+template <bool CLAMP>
+__global__ void __launch_bounds__(P_THREADS, 1)
+patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PatchArgs a)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int taps = a.taps_y * a.taps_x;
+    const int b_tap_bytes = a.BN * a.C;
+    unsigned char* res_b = smem;                                              // [taps][BN][C]
+    unsigned char* patch0 = smem + (((size_t)taps * b_tap_bytes + 1023) & ~(size_t)1023);
+    unsigned char* stage_out = patch0 + 2 * (size_t)a.patch_alloc;             // [16 warps][32 rows][BN]
+    const int region_bytes = 32 * a.BN;
+    unsigned long long* bars = (unsigned long long*)(stage_out + (size_t)P_EPI_WARPS * region_bytes);
+    // bars: patch_full[2], patch_empty[2], tmem_full[4], tmem_empty[4], weights
+    const unsigned pfull0 = smem_u32(bars);
+    const unsigned pempty0 = pfull0 + 16u;
+    const unsigned tfull0 = pempty0 + 16u;
+    const unsigned tempty0 = tfull0 + 8u * P_SLOTS;
+    const unsigned bfull = tempty0 + 8u * P_SLOTS;
+    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * P_SLOTS + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(pfull0 + 8u * s, 1);
+            mbar_init(pempty0 + 8u * s, 1);
+        }
+        for (int s = 0; s < P_SLOTS; ++s) {
+            mbar_init(tfull0 + 8u * s, 1);
+            mbar_init(tempty0 + 8u * s, 4);
+        }
+        mbar_init(bfull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < FAST_NP * 256; i += P_THREADS) {
+        const int prm = i >> 8, c = i & 255;
+        par[i] = (c < a.cpad) ? __ldg(a.fq + (size_t)prm * a.cpad + c) : 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    const int items = a.B * a.bands;
+    // rows and 128-position tiles of band `band` (the last band of an image may be shorter)
+    auto band_rows = [&](int band) { const int r = a.oH - band * a.R; return r < a.R ? r : a.R; };
+    auto band_tiles = [&](int band) { return (band_rows(band) * a.Wp + PBM - 1) / PBM; };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && (int)blockIdx.x < items) {
+            mbar_expect_tx(bfull, (unsigned)(taps * b_tap_bytes));
+            for (int t = 0; t < taps; ++t)
+                tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, 0);
+            unsigned it = 0;
+            int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
+            const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
+            for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
+                const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
+                if (!mbar_wait(pempty0 + 8u * pb, ph ^ 1u, abort_flag, a.status, 1)) break;
+                mbar_expect_tx(pfull0 + 8u * pb, (unsigned)a.patch_bytes);
+                tma_load_4d(smem_u32(patch0 + (size_t)pb * a.patch_alloc), &tmA, pfull0 + 8u * pb, 0, -a.pL,
+                            band * a.R - a.pT, n);
+                n += step_n;
+                band += step_b;
+                if (band >= a.bands) { band -= a.bands; ++n; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && (int)blockIdx.x < items) {
+            bool ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
+            const unsigned long long desc_hi = make_smem_desc(0u, a.C);
+            const unsigned res_b_s = smem_u32(res_b), patch_s = smem_u32(patch0);
+            const int ksteps = a.C / 32;
+            unsigned it = 0, seq = 0;
+            int band = (int)blockIdx.x % a.bands;
+            const int step_b = (int)gridDim.x % a.bands;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
+                const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
+                const int T = band_tiles(band);
+                if (!mbar_wait(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned pbase = patch_s + pb * (unsigned)a.patch_alloc;
+                for (int t = 0; t < T && ok; ++t, ++seq) {
+                    const unsigned slot = seq & (P_SLOTS - 1), sph = (seq / P_SLOTS) & 1u;
+                    if (!mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned d_tmem = tmem_base + slot * (unsigned)a.BN;
+                    unsigned row_y = pbase + (unsigned)(t * PBM * a.C);    // first patch row of tap (ky, 0)
+                    unsigned bt = res_b_s;
+                    unsigned first = 0;
+                    for (int ky = 0; ky < a.taps_y; ++ky) {
+                        unsigned row = row_y;
+                        for (int kx = 0; kx < a.taps_x; ++kx) {
+                            // the operand starts at an arbitrary pixel row; the swizzle is a function of the
+                            // absolute shared-memory address, so the descriptor needs nothing but that address
+                            // (measured: with the base-offset field left 0 every start row gives exact results)
+                            const unsigned long long adesc = desc_hi | (unsigned long long)((row & 0x3ffffu) >> 4);
+                            const unsigned long long bdesc = desc_hi | (unsigned long long)((bt & 0x3ffffu) >> 4);
+                            for (int k = 0; k < ksteps; ++k) {
+                                tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k),
+                                          a.idesc, first);
+                                first = 1u;
+                            }
+                            row += (unsigned)(a.dX * a.C);
+                            bt += (unsigned)b_tap_bytes;
+                        }
+                        row_y += (unsigned)(a.dY * a.Wp * a.C);
+                    }
+                    tc_commit(tfull0 + 8u * slot);
+                }
+                if (ok) tc_commit(pempty0 + 8u * pb);   // the patch is free once the item's MMAs have read it
+                band += step_b;
+                if (band >= a.bands) band -= a.bands;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int ew = warp - 2;
+        const int quad = warp & 3;          // TMEM lane quadrant this warp may read
+        const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
+        const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
+        const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
+        const unsigned swz_mask = (unsigned)(a.BN / 16 - 1);
+        unsigned seq = 0;
+        int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
+        const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
+        bool ok = true;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const int rows = band_rows(band);
+            const int T = band_tiles(band);
+            for (int t = 0; t < T; ++t, ++seq) {
+                if ((int)(seq & (P_SLOTS - 1)) != group) continue;
+                const unsigned sph = (seq / P_SLOTS) & 1u;
+                if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
+                if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
+                else patch_drain<CLAMP, 0>(tbase, par_off, region_off, a.BN, lane);
+                // the accumulator is drained: hand it back, then copy this warp's 32 rows out
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8u * group);
+                const unsigned p = (unsigned)(t * PBM + quad * 32 + lane);   // position within the band
+                const unsigned yy = __umulhi(p, a.rcp_Wp);
+                const unsigned x = p - yy * (unsigned)a.Wp;
+                if (x < (unsigned)a.oW && yy < (unsigned)rows) {
+                    uint8_t* dst = (uint8_t*)a.out + (((size_t)n * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N;
+                    const unsigned ro = (unsigned)(lane * a.BN);
+                    const unsigned xm = (ro >> 7) & swz_mask;
+                    for (int c = 0; c * 16 < a.N; ++c)
+                        *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
+                }
+                __syncwarp();   // the region is rewritten by the next tile of this group
+            }
+            n += step_n;
+            band += step_b;
+            if (band >= a.bands) { band -= a.bands; ++n; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static size_t patch_smem_bytes(int taps, int C, int BN, int patch_alloc)
+{
+    const size_t b = (((size_t)taps * BN * C) + 1023) & ~(size_t)1023;
+    return 1024 + b + 2 * (size_t)patch_alloc + (size_t)P_EPI_WARPS * 32 * BN + (4 + 2 * P_SLOTS + 2) * 8 + 32
+         + FAST_NP * 256 * 4 + 64;
+}
+
+// bytes a patch buffer must hold for bands of R rows: the tiles of a band read 128-row operands that start
+// up to (kH-1)*dY*Wp + (kW-1)*dX rows after the tile's first position
+static int patch_alloc_bytes(const ConvGeom& g, int Wp, int R)
+{
+    const int tiles = (R * Wp + PBM - 1) / PBM;
+    const int reach = tiles * PBM + (g.kH - 1) * g.dY * Wp + (g.kW - 1) * g.dX;
+    const int box = (R + (g.kH - 1) * g.dY) * Wp;
+    const int rows = reach > box ? reach : box;
+    return (rows * g.C + 1023) & ~1023;
+}
+
+bool patch_eligible(const ConvGeom& g)
+{
+    if (g.groups != 1 || g.sX != 1 || g.sY != 1) return false;
+    if (g.C != 32 && g.C != 64 && g.C != 128) return false;
+    if (g.O % 32 != 0 || g.O > 128) return false;
+    if (g.kH * g.kW < 2) return false;   // a 1x1 layer gains nothing from a patch
+    const int BN = g.O <= 64 ? 64 : 128;
+    if ((size_t)g.kH * g.kW * g.C * BN > 96 * 1024) return false;
+    const int Wp = g.oW + (g.kW - 1) * g.dX;
+    if (Wp > 256 || Wp < 2 || g.oH < 1) return false;
+    if ((g.kH - 1) * g.dY + 1 > 256) return false;
+    // at least one output row per band must fit
+    return patch_smem_bytes(g.kH * g.kW, g.C, BN, patch_alloc_bytes(g, Wp, 1)) <= 226 * 1024;
+}
+
+int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
+                    const char** why)
+{
+    static const char* kWhy = "";
+    *why = kWhy;
+    if (!patch_eligible(g)) { *why = "geometry outside the patch kernel"; return -1; }
+    if (((uintptr_t)in & 15) || ((uintptr_t)w & 15)) { *why = "operands must be 16-byte aligned"; return -1; }
+    cudaDriverEntryPointQueryResult qr;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn) {
+        *why = "cuTensorMapEncodeTiled is not available from the CUDA driver";
+        return -1;
+    }
+    memset(plan, 0, sizeof(*plan));
+    const int taps = g.kH * g.kW;
+    plan->BN = g.O <= 64 ? 64 : 128;
+    plan->Wp = g.oW + (g.kW - 1) * g.dX;
+    plan->in_unsigned = in_unsigned;
+    plan->num_sms = num_sms;
+    // rows per band: among the heights that fit shared memory (and the 256-row TMA box), the one that
+    // wastes the fewest 128-position tiles per image; ties go to the taller band (fewer halo rows re-read)
+    int best_R = 0;
+    long long best_tiles = 0;
+    for (int R = 1; R <= g.oH; ++R) {
+        if (R + (g.kH - 1) * g.dY > 256) break;
+        if (patch_smem_bytes(taps, g.C, plan->BN, patch_alloc_bytes(g, plan->Wp, R)) > 226 * 1024) break;
+        const int full = g.oH / R, rest = g.oH % R;
+        const long long tiles = (long long)full * ((R * plan->Wp + PBM - 1) / PBM)
+                              + (rest ? (rest * plan->Wp + PBM - 1) / PBM : 0);
+        if (best_R == 0 || tiles <= best_tiles) { best_R = R; best_tiles = tiles; }
+    }
+    if (best_R == 0) { *why = "no band height fits shared memory"; return -1; }
+    plan->R = best_R;
+    plan->bands = (g.oH + best_R - 1) / best_R;
+    const int box_rows = best_R + (g.kH - 1) * g.dY;
+    plan->patch_bytes = box_rows * plan->Wp * g.C;
+    plan->patch_alloc = patch_alloc_bytes(g, plan->Wp, best_R);
+    plan->smem_bytes = patch_smem_bytes(taps, g.C, plan->BN, plan->patch_alloc);
+    const CUtensorMapSwizzle swz = g.C == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                              : (g.C == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    CUresult rc;
+    {   // weights [O][taps*C], one box = one tap of all outputs (rows beyond O read as zero)
+        const cuuint64_t dims[2] = {(cuuint64_t)taps * g.C, (cuuint64_t)g.O};
+        const cuuint64_t strides[1] = {(cuuint64_t)taps * g.C};
+        const cuuint32_t box[2] = {(cuuint32_t)g.C, (cuuint32_t)plan->BN};
+        const cuuint32_t estr[2] = {1, 1};
+        rc = ((EncodeTiledFn)fn)(&plan->tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w, dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the weights"; return -1; }
+    }
+    {   // NHWC activations as (C, W, H, B); one box = a whole patch, zero-filled outside the image
+        const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)g.C, (cuuint64_t)g.C * g.W, (cuuint64_t)g.C * g.W * g.H};
+        const cuuint32_t box[4] = {(cuuint32_t)g.C, (cuuint32_t)plan->Wp, (cuuint32_t)box_rows, 1};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        rc = ((EncodeTiledFn)fn)(&plan->tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)in, dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the activation patch"; return -1; }
+    }
+    return 0;
+}
+
+cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQuant& fast, void* out, int* status_word,
+                         cudaStream_t s)
+{
+    PatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.B = g.B; a.oH = g.oH; a.oW = g.oW; a.N = g.O; a.BN = plan.BN; a.C = g.C;
+    if (a.B == 0) return cudaSuccess;
+    a.taps_y = g.kH; a.taps_x = g.kW; a.dY = g.dY; a.dX = g.dX; a.pT = g.pT; a.pL = g.pL;
+    a.Wp = plan.Wp; a.R = plan.R; a.bands = plan.bands;
+    a.patch_bytes = plan.patch_bytes; a.patch_alloc = plan.patch_alloc;
+    a.rcp_Wp = (unsigned)(((1ull << 32) + (unsigned)plan.Wp - 1) / (unsigned)plan.Wp);
+    a.idesc = (2u << 4) | ((plan.in_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
+            | ((unsigned)(PBM >> 4) << 24);
+    a.tmem_cols = (unsigned)(P_SLOTS * plan.BN);   // 256 or 512: a power of two
+    a.out = out;
+    a.status = status_word;
+    a.fq = fast.fq;
+    a.cpad = fast.cpad;
+    a.out_unsigned = fast.out_unsigned;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(patch_conv_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(patch_conv_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const long long items = (long long)a.B * a.bands;
+    const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
+    if (fast.need_clamp)
+        patch_conv_tcgen05_kernel<true><<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
+    else
+        patch_conv_tcgen05_kernel<false><<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
+    return cudaGetLastError();
+}
+
+}  // namespace n2d2b

@@ -224,6 +224,47 @@ __global__ void pool_vec_kernel(const uint8_t* __restrict__ in, int in_unsigned,
     }
 }
 
+// Max pooling, 16 channels per thread, one block per output row: the window bounds of the row are
+// computed once, the maximum runs on four bytes at a time, and no thread divides 64-bit indices.
+template <bool UNSIGNED>
+__global__ void pool_max_row_kernel(const uint8_t* __restrict__ in, PoolGeom g, uint8_t* __restrict__ out)
+{
+    const int cv = g.C / 16;
+    for (int row = blockIdx.x; row < g.B * g.oH; row += gridDim.x) {
+        const int b = row / g.oH, oy = row - b * g.oH;
+        const int iy0 = oy * g.sY - g.padY;
+        const int ky_lo = iy0 < 0 ? -iy0 : 0;
+        const int ky_hi = (g.H - iy0) < g.pH ? (g.H - iy0) : g.pH;
+        const uint8_t* img = in + (size_t)b * g.H * g.W * g.C;
+        uint8_t* orow = out + (size_t)row * g.oW * g.C;
+        for (int t = threadIdx.x; t < g.oW * cv; t += blockDim.x) {
+            const int ox = t / cv, c16 = t - ox * cv;
+            const int ix0 = ox * g.sX - g.padX;
+            const int kx_lo = ix0 < 0 ? -ix0 : 0;
+            const int kx_hi = (g.W - ix0) < g.pW ? (g.W - ix0) : g.pW;
+            uint4 m = make_uint4(0u, 0u, 0u, 0u);
+            bool first = true;
+            for (int ky = ky_lo; ky < ky_hi; ++ky) {
+                const uint8_t* p = img + ((size_t)(iy0 + ky) * g.W + ix0) * g.C + c16 * 16;
+                for (int kx = kx_lo; kx < kx_hi; ++kx) {
+                    const uint4 xv = __ldg((const uint4*)(p + (size_t)kx * g.C));
+                    if (first) {
+                        m = xv;
+                        first = false;
+                    } else if (UNSIGNED) {
+                        m.x = __vmaxu4(m.x, xv.x); m.y = __vmaxu4(m.y, xv.y);
+                        m.z = __vmaxu4(m.z, xv.z); m.w = __vmaxu4(m.w, xv.w);
+                    } else {
+                        m.x = __vmaxs4(m.x, xv.x); m.y = __vmaxs4(m.y, xv.y);
+                        m.z = __vmaxs4(m.z, xv.z); m.w = __vmaxs4(m.w, xv.w);
+                    }
+                }
+            }
+            *(uint4*)(orow + (size_t)t * 16) = m;   // an all-padding window stays 0
+        }
+    }
+}
+
 template <typename ElemT>
 __global__ void pool_scalar_kernel(const void* __restrict__ in, int in_unsigned, PoolGeom g,
                                    void* __restrict__ out, size_t total)
@@ -263,7 +304,15 @@ cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void
 {
     // int8 tensors; int32 tensors go through launch_pool_i32
     const int block = 256;
-    if (g.C % 16 == 0) {
+    if (g.C % 16 == 0 && g.is_max) {
+        const long long rows = (long long)g.B * g.oH;
+        if (rows == 0 || g.oW == 0) return cudaSuccess;
+        const int items = g.oW * (g.C / 16);
+        const int threads = items >= 256 ? 256 : ((items + 31) / 32) * 32;
+        const unsigned grid = (unsigned)(rows < (1ll << 20) ? rows : (1ll << 20));
+        if (in_unsigned) pool_max_row_kernel<true><<<grid, threads, 0, s>>>((const uint8_t*)in, g, (uint8_t*)out);
+        else pool_max_row_kernel<false><<<grid, threads, 0, s>>>((const uint8_t*)in, g, (uint8_t*)out);
+    } else if (g.C % 16 == 0) {
         const size_t total = (size_t)g.B * g.oH * g.oW * (g.C / 16);
         if (total == 0) return cudaSuccess;
         pool_vec_kernel<<<grid_for(total, block), block, 0, s>>>((const uint8_t*)in, in_unsigned, g, (uint8_t*)out, total);

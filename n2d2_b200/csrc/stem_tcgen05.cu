@@ -41,26 +41,31 @@ struct StemArgs {
     int out_unsigned;
 };
 
-// [B][H][W][C] (C <= 4) -> [B][Hp][Wp][4] with the image at (pT, pL) and zeros elsewhere
+// [B][H][W][C] (C <= 4) -> [B][Hp][Wp][4] with the image at (pT, pL) and zeros elsewhere.
+// One block per padded row: the row's image coordinates are computed once.
 __global__ void pad_image_kernel(const uint8_t* __restrict__ in, int C, int H, int W, int Hp, int Wp, int pT, int pL,
-                                 size_t out_pixels, uint32_t* __restrict__ out)
+                                 int rows, uint32_t* __restrict__ out)
 {
-    for (size_t p = blockIdx.x * (size_t)blockDim.x + threadIdx.x; p < out_pixels; p += (size_t)gridDim.x * blockDim.x) {
-        const int xp = (int)(p % (size_t)Wp);
-        const size_t t = p / (size_t)Wp;
-        const int yp = (int)(t % (size_t)Hp);
-        const size_t n = t / (size_t)Hp;
-        const int x = xp - pL, y = yp - pT;
-        uint32_t v = 0;
-        if (x >= 0 && x < W && y >= 0 && y < H) {
-            const uint8_t* src = in + ((n * H + y) * (size_t)W + x) * C;
-            if (C == 4) {
-                v = *(const uint32_t*)src;
-            } else {
-                for (int c = 0; c < C; ++c) v |= (uint32_t)src[c] << (8 * c);
-            }
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int n = row / Hp, yp = row - n * Hp;
+        const int y = yp - pT;
+        uint32_t* orow = out + (size_t)row * Wp;
+        if (y < 0 || y >= H) {
+            for (int xp = threadIdx.x; xp < Wp; xp += blockDim.x) orow[xp] = 0u;
+            continue;
         }
-        out[p] = v;
+        const uint8_t* irow = in + ((size_t)n * H + y) * (size_t)W * C;
+        for (int xp = threadIdx.x; xp < Wp; xp += blockDim.x) {
+            const int x = xp - pL;
+            uint32_t v = 0;
+            if (x >= 0 && x < W) {
+                if (C == 4) v = *(const uint32_t*)(irow + (size_t)x * 4);
+                else if (C == 3) v = irow[3 * x] | ((uint32_t)irow[3 * x + 1] << 8) | ((uint32_t)irow[3 * x + 2] << 16);
+                else if (C == 2) v = irow[2 * x] | ((uint32_t)irow[2 * x + 1] << 8);
+                else v = irow[x];
+            }
+            orow[xp] = v;
+        }
     }
 }
 
@@ -77,12 +82,12 @@ cudaError_t launch_pad_image(const void* in, const ConvGeom& g, int batch, void*
 {
     int Hp, Wp;
     stem_padded_dims(g, &Hp, &Wp);
-    const size_t pixels = (size_t)batch * Hp * Wp;
-    if (pixels == 0) return cudaSuccess;
-    size_t grid = (pixels + 255) / 256;
-    if (grid > 148u * 64u) grid = 148u * 64u;
-    pad_image_kernel<<<(unsigned)grid, 256, 0, s>>>((const uint8_t*)in, g.C, g.H, g.W, Hp, Wp, g.pT, g.pL, pixels,
-                                                   (uint32_t*)out);
+    const long long rows = (long long)batch * Hp;
+    if (rows == 0) return cudaSuccess;
+    const unsigned grid = (unsigned)(rows < (1ll << 20) ? rows : (1ll << 20));
+    const int threads = Wp >= 256 ? 256 : ((Wp + 31) / 32) * 32;
+    pad_image_kernel<<<grid, threads, 0, s>>>((const uint8_t*)in, g.C, g.H, g.W, Hp, Wp, g.pT, g.pL, (int)rows,
+                                             (uint32_t*)out);
     return cudaGetLastError();
 }
 
@@ -181,7 +186,6 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         const int h = pt >> 7;                  // kernel rows 2h and 2h+1 of every K block
         int s = 0;
         unsigned ph = 0;
-        bool ok = true;
         const size_t row_bytes = (size_t)a.Wp * 4;
         // this thread's part of a stage: 16-byte chunks 4h .. 4h+3 of row r in every K block
         const unsigned sw = (unsigned)(r & 7);
@@ -191,17 +195,15 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         unsigned m = blockIdx.x * SBM + r;
         unsigned n = m / oHW;
         unsigned rem = m - n * oHW;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            if (!mbar_wait_warp(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1, lane)) { ok = false; break; }
+        // The loads of a tile are issued one tile ahead of its stores (two register sets, ping-pong), so the
+        // global-memory latency of tile t+1 overlaps the stores of tile t instead of adding to them.
+        auto issue = [&](uint32_t (&w)[2][2][8]) {
             // rows past the end repeat the last pixel; they are never stored
             const unsigned nn = m < (unsigned)a.M ? n : (unsigned)a.B - 1u;
             const unsigned rr = m < (unsigned)a.M ? rem : oHW - 1u;
             const unsigned oy = __umulhi(rr, a.rcp_oW);
             const unsigned ox = rr - oy * (unsigned)a.oW;
             const unsigned char* src = a.in4 + ((size_t)nn * a.Hp + (size_t)oy * a.sY + 2 * h) * row_bytes + (size_t)ox * a.sX * 4;
-            unsigned char* dst = my_row + (size_t)s * a_stage_bytes;
-            // all loads of the tile are issued before the first store: one memory latency per tile
-            uint32_t w[2][2][8];   // [K block][kernel row of this thread][pixel]
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) {
                 if (kb < a.nkb) {
@@ -222,6 +224,15 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     }
                 }
             }
+            // next tile of this CTA
+            m += gridDim.x * SBM;
+            n += a.step_n;
+            rem += a.step_rem;
+            if (rem >= oHW) { rem -= oHW; ++n; }
+        };
+        auto flush = [&](const uint32_t (&w)[2][2][8]) -> bool {
+            if (!mbar_wait_warp(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1, lane)) return false;
+            unsigned char* dst = my_row + (size_t)s * a_stage_bytes;
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) {
                 if (kb < a.nkb) {
@@ -242,10 +253,19 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8u * s);
             if (++s == a.stages) { s = 0; ph ^= 1u; }
-            m += gridDim.x * SBM;
-            n += a.step_n;
-            rem += a.step_rem;
-            if (rem >= oHW) { rem -= oHW; ++n; }
+            return true;
+        };
+        uint32_t wa[2][2][8], wb[2][2][8];
+        int tile = blockIdx.x;
+        if (tile < num_tiles) issue(wa);
+        while (tile < num_tiles) {
+            if (tile + (int)gridDim.x < num_tiles) issue(wb);
+            if (!flush(wa)) break;
+            tile += gridDim.x;
+            if (tile >= num_tiles) break;
+            if (tile + (int)gridDim.x < num_tiles) issue(wa);
+            if (!flush(wb)) break;
+            tile += gridDim.x;
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps

@@ -9,6 +9,32 @@ from oracle import oracle
 
 from gpu_common import KEEP, compare_net, single_conv_net
 
+# (C, H, W, O, k, pad, dilation, input unsigned): stride-1 layers small enough for resident weights
+PATCH_CASES = [(64, 56, 56, 64, 3, 1, 1, True), (64, 20, 17, 64, 3, 1, 1, True), (32, 9, 9, 32, 3, 1, 1, False),
+               (128, 12, 12, 64, 3, 1, 1, True), (32, 15, 15, 64, 5, 2, 1, True), (64, 20, 20, 64, 3, 2, 2, True),
+               (64, 10, 10, 32, 3, 0, 1, True), (64, 6, 250, 64, 3, 1, 1, True), (64, 33, 29, 128, 2, 1, 1, False),
+               (32, 40, 40, 96, 3, 1, 1, True)]
+
+
+@pytest.mark.parametrize('case', PATCH_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_p%d_d%d' % c[:7])
+@pytest.mark.parametrize('mode', ['double', 'fixed'])
+def test_stride1_patch_kernel(case, mode):
+    C, H, W, O, k, p, d, uns = case
+    net = single_conv_net(C, H, W, O, k, 1, p, in_unsigned=uns, mode=mode, dil=d)
+    compare_net(net, 3, want_engine=None if mode == 'fixed' else 'patch-tcgen05')
+
+
+def test_stride1_patch_kernel_many_bands_and_images():
+    # more (image, band) items than SMs, a last band shorter than the others, linear activation (signed output)
+    net = single_conv_net(64, 56, 56, 64, 3, 1, 1, in_unsigned=True, mode='single', act='linear')
+    compare_net(net, 40, want_engine='patch-tcgen05')
+
+
+def test_forced_im2col_keeps_the_implicit_gemm_kernel():
+    net = single_conv_net(64, 20, 17, 64, 3, 1, 1, mode='double')
+    compare_net(net, 2, flags=runtime.KEEP_ALL_OUTPUTS | runtime.FORCE_IM2COL, want_engine='tcgen05')
+
+
 pytestmark = pytest.mark.gpu
 R = runtime
 
@@ -67,7 +93,11 @@ TC_CASES = [
 def test_tensor_core_convolutions(case):
     C, H, O, k, s, p, uns, flags = case
     net = single_conv_net(C, H, H, O, k, s, p, in_unsigned=uns)
-    compare_net(net, 3, flags=KEEP | flags, want_engine='tcgen05')
+    # stride-1 layers with few channels and resident weights take the patch kernel unless im2col is forced
+    patch = (s == 1 and k > 1 and C in (32, 64, 128) and O % 32 == 0 and O <= 128 and not flags & R.FORCE_IM2COL)
+    compare_net(net, 3, flags=KEEP | flags, want_engine='patch-tcgen05' if patch else 'tcgen05')
+    if patch:
+        compare_net(net, 3, flags=KEEP | R.FORCE_IM2COL, want_engine='tcgen05')
 
 
 @pytest.mark.parametrize('mode', ['double', 'single', 'fixed'])
@@ -120,7 +150,8 @@ def test_first_layer_tensor_core_kernel(case, mode):
 
 def test_tensor_core_dilated_convolution():
     net = single_conv_net(64, 15, 15, 64, 3, 1, 2, dil=2)
-    compare_net(net, 2, want_engine='tcgen05')
+    compare_net(net, 2, flags=KEEP | R.FORCE_IM2COL, want_engine='tcgen05')
+    compare_net(net, 2, want_engine='patch-tcgen05')
 
 
 @pytest.mark.parametrize('mode', ['single', 'double', 'fixed', 'float'])
