@@ -185,36 +185,48 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        // The issuing thread pays the latency of every instruction it executes, so what surrounds a short
+        // MMA is kept to 32-bit adds on running descriptor words and an unrolled K loop.
         if (lane == 0) {
-            unsigned it = 0;
             unsigned acc_it = 0;
             bool ok = true;
-            const int ksteps = a.BK / 32;
             if (a.b_resident && (int)blockIdx.x < num_tiles) ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
             int s = 0;
             unsigned ph = 0;
-            // descriptor bits that do not depend on the address (stride between 8-row groups, version, swizzle)
-            const unsigned long long desc_hi = make_smem_desc(0u, a.BK);
+            // upper descriptor word: stride between 8-row groups, version, swizzle; lower word: address / 16
+            const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.BK) >> 32);
+            const unsigned a_lo0 = (tiles_s & 0x3ffffu) >> 4, b_res0 = (res_b_s & 0x3ffffu) >> 4;
+            const unsigned stage16 = (unsigned)(stage_bytes >> 4), a16 = (unsigned)(a_stage_bytes >> 4);
+            const unsigned b16 = (unsigned)(b_stage_bytes >> 4);
+            unsigned a_lo = a_lo0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
                 const unsigned as = acc_it & 1u;
                 const unsigned aph = (acc_it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                unsigned b_res = b_res0;
+                for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
                     tc_fence_after();
-                    const unsigned long long adesc = desc_hi | (unsigned long long)(((tiles_s + (unsigned)(s * stage_bytes)) & 0x3ffffu) >> 4);
-                    const unsigned long long bdesc = a.b_resident
-                        ? (desc_hi | (unsigned long long)(((res_b_s + (unsigned)(kb * b_stage_bytes)) & 0x3ffffu) >> 4))
-                        : adesc + (unsigned long long)(a_stage_bytes >> 4);
-                    for (int k = 0; k < ksteps; ++k) {
-                        // advancing K by 32 bytes inside the swizzle span = +2 in the 16-byte address field
-                        tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k),
-                                  a.idesc, (kb | k) ? 1u : 0u);
+                    const unsigned b_lo = a.b_resident ? b_res : a_lo + a16;
+                    const unsigned acc = kb ? 1u : 0u;
+                    // advancing K by 32 bytes inside the swizzle span = +2 in the 16-byte address field
+                    if (a.BK == 128) {
+                        tc_mma_i8_lohi(d_tmem, a_lo, b_lo, desc_hi, a.idesc, acc);
+                        tc_mma_i8_lohi(d_tmem, a_lo + 2u, b_lo + 2u, desc_hi, a.idesc, 1u);
+                        tc_mma_i8_lohi(d_tmem, a_lo + 4u, b_lo + 4u, desc_hi, a.idesc, 1u);
+                        tc_mma_i8_lohi(d_tmem, a_lo + 6u, b_lo + 6u, desc_hi, a.idesc, 1u);
+                    } else if (a.BK == 64) {
+                        tc_mma_i8_lohi(d_tmem, a_lo, b_lo, desc_hi, a.idesc, acc);
+                        tc_mma_i8_lohi(d_tmem, a_lo + 2u, b_lo + 2u, desc_hi, a.idesc, 1u);
+                    } else {
+                        tc_mma_i8_lohi(d_tmem, a_lo, b_lo, desc_hi, a.idesc, acc);
                     }
                     tc_commit(empty0 + 8u * s);  // frees the stage once these MMAs have read it
-                    if (++s == a.stages) { s = 0; ph ^= 1u; }
+                    a_lo += stage16;
+                    b_res += b16;
+                    if (++s == a.stages) { s = 0; ph ^= 1u; a_lo = a_lo0; }
                 }
                 if (ok) tc_commit(tfull0 + 8u * as);
             }

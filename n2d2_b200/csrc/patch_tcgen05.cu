@@ -53,7 +53,25 @@ __device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, un
     }
 }
 
-template <bool CLAMP>
+// The MMAs of one tile with compile-time tap counts: a straight run of address adds and MMAs.  The issuing
+// thread pays the latency of every instruction it executes, so loop control and address arithmetic around a
+// short MMA (one of 128 x 64 x 32 takes about 60 cycles of the tensor pipe) would cost more than the MMA.
+template <int KH, int KW, int KS>
+__device__ __forceinline__ void issue_tile(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
+                                           unsigned row_step, unsigned col_step, unsigned btap)
+{
+#pragma unroll
+    for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+        for (int kx = 0; kx < KW; ++kx)
+#pragma unroll
+            for (int k = 0; k < KS; ++k)
+                tc_mma_i8_lohi(d_tmem, a_lo + ky * row_step + kx * col_step + 2u * k, b_lo + (ky * KW + kx) * btap + 2u * k,
+                               desc_hi, idesc, (ky | kx | k) ? 1u : 0u);
+}
+
+// SHAPE: 0 = any filter (loops), 1 / 2 / 3 = 3x3 filter with 32 / 64 / 128 channels (unrolled issue)
+template <bool CLAMP, int SHAPE>
 __global__ void __launch_bounds__(P_THREADS, 1)
 patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PatchArgs a)
 {
@@ -134,43 +152,42 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && (int)blockIdx.x < items) {
             bool ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
-            const unsigned long long desc_hi = make_smem_desc(0u, a.C);
-            const unsigned res_b_s = smem_u32(res_b), patch_s = smem_u32(patch0);
+            const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.C) >> 32);
+            const unsigned res_b_lo = (smem_u32(res_b) & 0x3ffffu) >> 4, patch_lo = (smem_u32(patch0) & 0x3ffffu) >> 4;
             const int ksteps = a.C / 32;
+            const unsigned row_step = (unsigned)((a.dY * a.Wp * a.C) >> 4), col_step = (unsigned)((a.dX * a.C) >> 4);
+            const unsigned btap = (unsigned)(b_tap_bytes >> 4);
             unsigned it = 0, seq = 0;
             int band = (int)blockIdx.x % a.bands;
             const int step_b = (int)gridDim.x % a.bands;
+            const unsigned tile_step = (unsigned)((PBM * a.C) >> 4);
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 const int T = band_tiles(band);
                 if (!mbar_wait(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
                 tc_fence_after();
-                const unsigned pbase = patch_s + pb * (unsigned)a.patch_alloc;
-                for (int t = 0; t < T && ok; ++t, ++seq) {
+                unsigned a_lo = patch_lo + pb * (unsigned)(a.patch_alloc >> 4);
+                for (int t = 0; t < T; ++t, ++seq, a_lo += tile_step) {
                     const unsigned slot = seq & (P_SLOTS - 1), sph = (seq / P_SLOTS) & 1u;
                     if (!mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
                     const unsigned d_tmem = tmem_base + slot * (unsigned)a.BN;
-                    unsigned row_y = pbase + (unsigned)(t * PBM * a.C);    // first patch row of tap (ky, 0)
-                    unsigned bt = res_b_s;
-                    unsigned first = 0;
-                    for (int ky = 0; ky < a.taps_y; ++ky) {
-                        unsigned row = row_y;
-                        for (int kx = 0; kx < a.taps_x; ++kx) {
-                            // the operand starts at an arbitrary pixel row; the swizzle is a function of the
-                            // absolute shared-memory address, so the descriptor needs nothing but that address
-                            // (measured: with the base-offset field left 0 every start row gives exact results)
-                            const unsigned long long adesc = desc_hi | (unsigned long long)((row & 0x3ffffu) >> 4);
-                            const unsigned long long bdesc = desc_hi | (unsigned long long)((bt & 0x3ffffu) >> 4);
-                            for (int k = 0; k < ksteps; ++k) {
-                                tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k),
-                                          a.idesc, first);
-                                first = 1u;
-                            }
-                            row += (unsigned)(a.dX * a.C);
-                            bt += (unsigned)b_tap_bytes;
+                    // The operand of a tap starts at an arbitrary pixel row.  The swizzle is a function of the
+                    // absolute shared-memory address, so the descriptor needs nothing but that address
+                    // (measured: with the base-offset field left 0 every start row gives exact results).
+                    if (SHAPE == 1) issue_tile<3, 3, 1>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
+                    else if (SHAPE == 2) issue_tile<3, 3, 2>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
+                    else if (SHAPE == 3) issue_tile<3, 3, 4>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
+                    else {
+                        unsigned ar = a_lo, bt = res_b_lo, first = 0;
+                        for (int ky = 0; ky < a.taps_y; ++ky, ar += row_step) {
+                            unsigned ac = ar;
+                            for (int kx = 0; kx < a.taps_x; ++kx, ac += col_step, bt += btap)
+                                for (int k = 0; k < ksteps; ++k) {
+                                    tc_mma_i8_lohi(d_tmem, ac + 2u * k, bt + 2u * k, desc_hi, a.idesc, first);
+                                    first = 1u;
+                                }
                         }
-                        row_y += (unsigned)(a.dY * a.Wp * a.C);
                     }
                     tc_commit(tfull0 + 8u * slot);
                 }
@@ -354,23 +371,25 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQua
     a.fq = fast.fq;
     a.cpad = fast.cpad;
     a.out_unsigned = fast.out_unsigned;
+    typedef void (*PatchKernel)(const CUtensorMap, const CUtensorMap, const PatchArgs);
+    static const PatchKernel variants[8] = {
+        patch_conv_tcgen05_kernel<false, 0>, patch_conv_tcgen05_kernel<false, 1>, patch_conv_tcgen05_kernel<false, 2>,
+        patch_conv_tcgen05_kernel<false, 3>, patch_conv_tcgen05_kernel<true, 0>,  patch_conv_tcgen05_kernel<true, 1>,
+        patch_conv_tcgen05_kernel<true, 2>,  patch_conv_tcgen05_kernel<true, 3>};
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(patch_conv_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(patch_conv_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return e;
+        for (PatchKernel k : variants) {
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return e;
+        }
         attr_set[dev] = true;
     }
     const long long items = (long long)a.B * a.bands;
     const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
-    if (fast.need_clamp)
-        patch_conv_tcgen05_kernel<true><<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
-    else
-        patch_conv_tcgen05_kernel<false><<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
+    const int shape = (g.kH == 3 && g.kW == 3) ? (g.C == 32 ? 1 : (g.C == 64 ? 2 : 3)) : 0;
+    variants[(fast.need_clamp ? 4 : 0) + shape]<<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
     return cudaGetLastError();
 }
 

@@ -154,29 +154,31 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             for (int kb = 0; kb < a.nkb; ++kb)
                 tma_load_2d(smem_u32(smB + (size_t)kb * a.BN * 128), &tmB, wbar, kb * 128, 0);
             bool ok = mbar_wait(wbar, 0, abort_flag, a.status, 6);
-            const unsigned long long desc_hi = make_smem_desc(0u, 128);
-            const unsigned smA_s = smem_u32(smA), smB_s = smem_u32(smB);
+            const unsigned desc_hi = (unsigned)(make_smem_desc(0u, 128) >> 32);
+            const unsigned a_lo0 = (smem_u32(smA) & 0x3ffffu) >> 4, b_lo = (smem_u32(smB) & 0x3ffffu) >> 4;
+            const unsigned stage16 = (unsigned)(a_stage_bytes >> 4), kb16 = (unsigned)((SBM * 128) >> 4);
+            const unsigned bkb16 = (unsigned)((a.BN * 128) >> 4);
+            const int k1 = a.nkb > 1 ? a.kH - 4 : 0;   // kernel rows (32-byte K steps) in the second K block
+            const int k0 = a.nkb > 1 ? 4 : a.kH;       // and in the first
             int s = 0;
-            unsigned ph = 0, acc_it = 0;
+            unsigned ph = 0, acc_it = 0, a_lo = a_lo0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
                 const unsigned as = acc_it & 1u, aph = (acc_it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                 if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
-                for (int kb = 0; kb < a.nkb; ++kb) {
-                    const unsigned long long adesc =
-                        desc_hi | (unsigned long long)(((smA_s + (unsigned)(s * a_stage_bytes + kb * SBM * 128)) & 0x3ffffu) >> 4);
-                    const unsigned long long bdesc =
-                        desc_hi | (unsigned long long)(((smB_s + (unsigned)(kb * a.BN * 128)) & 0x3ffffu) >> 4);
-                    const int ksteps = min(4, a.kH - kb * 4);   // one 32-byte K step per kernel row
-                    for (int k = 0; k < ksteps; ++k)
-                        tc_mma_i8(d_tmem, adesc + (unsigned long long)(2 * k), bdesc + (unsigned long long)(2 * k), a.idesc,
-                                  (kb | k) ? 1u : 0u);
-                }
+                // one 32-byte K step per kernel row; unrolled with compile-time offsets and a bound check
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < k0) tc_mma_i8_lohi(d_tmem, a_lo + 2u * k, b_lo + 2u * k, desc_hi, a.idesc, k ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < k1) tc_mma_i8_lohi(d_tmem, a_lo + kb16 + 2u * k, b_lo + bkb16 + 2u * k, desc_hi, a.idesc, 1u);
                 tc_commit(empty0 + 8u * s);
                 tc_commit(tfull0 + 8u * as);
-                if (++s == a.stages) { s = 0; ph ^= 1u; }
+                a_lo += stage16;
+                if (++s == a.stages) { s = 0; ph ^= 1u; a_lo = a_lo0; }
             }
         }
     } else if (warp <= S_PROD_WARPS) {

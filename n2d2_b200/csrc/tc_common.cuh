@@ -36,16 +36,6 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity)
-{
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -118,6 +108,21 @@ __device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long ad
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Descriptors as halves: both operands of a K-major int8 MMA share the upper word (stride between 8-row
+// groups, version, swizzle mode), and the lower word is the 16-byte-granular shared-memory address, so a
+// loop over filter taps or K steps advances a 32-bit integer.  The issuing thread pays the latency of every
+// instruction it executes, which makes this arithmetic the cost of a short MMA, not the MMA.
+__device__ __forceinline__ void tc_mma_i8_lohi(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
+                                               unsigned accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_commit(unsigned bar)
 {
