@@ -430,7 +430,13 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     // multiple of 16 uses 32-byte slabs whose tail the TMA unit zero-fills
     plan->BK = (g.C % 128 == 0) ? 128 : (g.C % 64 == 0 ? 64 : 32);
     int bn = force_bn;
-    if (bn == 0) bn = (g.O >= 256) ? 256 : (g.O > 64 ? 128 : 64);
+    if (bn == 0) {
+        bn = (g.O >= 256) ? 256 : (g.O > 64 ? 128 : 64);
+        // a layer with few output pixels (the classifier, late stages at small batch) would leave most
+        // SMs without a tile: narrower column blocks give more tiles
+        const long long m_tiles = ((long long)g.B * g.oH * g.oW + BM - 1) / BM;
+        while (bn > 64 && m_tiles * ((g.O + bn - 1) / bn) < num_sms) bn >>= 1;
+    }
     plan->BN = bn;
     plan->a_unsigned = in_unsigned;
     plan->oW = g.oW; plan->oH = g.oH; plan->kW = g.kW;

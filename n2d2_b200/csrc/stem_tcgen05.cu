@@ -42,29 +42,38 @@ struct StemArgs {
 };
 
 // [B][H][W][C] (C <= 4) -> [B][Hp][Wp][4] with the image at (pT, pL) and zeros elsewhere.
-// One block per padded row: the row's image coordinates are computed once.
+// A block takes PAD_ROWS padded rows at a time, every thread one pixel column of each: the loads of the
+// rows are independent, so several are in flight per thread.
+static constexpr int PAD_ROWS = 4;
 __global__ void pad_image_kernel(const uint8_t* __restrict__ in, int C, int H, int W, int Hp, int Wp, int pT, int pL,
                                  int rows, uint32_t* __restrict__ out)
 {
-    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-        const int n = row / Hp, yp = row - n * Hp;
-        const int y = yp - pT;
-        uint32_t* orow = out + (size_t)row * Wp;
-        if (y < 0 || y >= H) {
-            for (int xp = threadIdx.x; xp < Wp; xp += blockDim.x) orow[xp] = 0u;
-            continue;
+    for (int row0 = blockIdx.x * PAD_ROWS; row0 < rows; row0 += gridDim.x * PAD_ROWS) {
+        const uint8_t* irow[PAD_ROWS];
+#pragma unroll
+        for (int j = 0; j < PAD_ROWS; ++j) {
+            const int row = row0 + j;
+            const int n = row / Hp, y = row - n * Hp - pT;
+            irow[j] = (row < rows && y >= 0 && y < H) ? in + ((size_t)n * H + y) * (size_t)W * C : nullptr;
         }
-        const uint8_t* irow = in + ((size_t)n * H + y) * (size_t)W * C;
         for (int xp = threadIdx.x; xp < Wp; xp += blockDim.x) {
             const int x = xp - pL;
-            uint32_t v = 0;
-            if (x >= 0 && x < W) {
-                if (C == 4) v = *(const uint32_t*)(irow + (size_t)x * 4);
-                else if (C == 3) v = irow[3 * x] | ((uint32_t)irow[3 * x + 1] << 8) | ((uint32_t)irow[3 * x + 2] << 16);
-                else if (C == 2) v = irow[2 * x] | ((uint32_t)irow[2 * x + 1] << 8);
-                else v = irow[x];
+            const bool inside = x >= 0 && x < W;
+            uint32_t v[PAD_ROWS];
+#pragma unroll
+            for (int j = 0; j < PAD_ROWS; ++j) {
+                v[j] = 0u;
+                if (inside && irow[j]) {
+                    const uint8_t* p = irow[j] + (size_t)x * C;
+                    if (C == 4) v[j] = __ldg((const uint32_t*)p);
+                    else if (C == 3) v[j] = __ldg(p) | ((uint32_t)__ldg(p + 1) << 8) | ((uint32_t)__ldg(p + 2) << 16);
+                    else if (C == 2) v[j] = __ldg(p) | ((uint32_t)__ldg(p + 1) << 8);
+                    else v[j] = __ldg(p);
+                }
             }
-            orow[xp] = v;
+#pragma unroll
+            for (int j = 0; j < PAD_ROWS; ++j)
+                if (row0 + j < rows) out[(size_t)(row0 + j) * Wp + xp] = v[j];
         }
     }
 }
@@ -84,7 +93,8 @@ cudaError_t launch_pad_image(const void* in, const ConvGeom& g, int batch, void*
     stem_padded_dims(g, &Hp, &Wp);
     const long long rows = (long long)batch * Hp;
     if (rows == 0) return cudaSuccess;
-    const unsigned grid = (unsigned)(rows < (1ll << 20) ? rows : (1ll << 20));
+    const long long blocks = (rows + PAD_ROWS - 1) / PAD_ROWS;
+    const unsigned grid = (unsigned)(blocks < (1ll << 20) ? blocks : (1ll << 20));
     const int threads = Wp >= 256 ? 256 : ((Wp + 31) / 32) * 32;
     pad_image_kernel<<<grid, threads, 0, s>>>((const uint8_t*)in, g.C, g.H, g.W, Hp, Wp, g.pT, g.pL, (int)rows,
                                              (uint32_t*)out);
@@ -166,6 +176,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 const unsigned as = acc_it & 1u, aph = (acc_it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                 if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
+
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
                 // one 32-byte K step per kernel row; unrolled with compile-time offsets and a bound check
