@@ -64,6 +64,27 @@ struct FastQuant {
     bool enabled = false;
 };
 
+// ---- stride-2 first layer through space-to-depth (tcgen05 kind::i8, no gather) ----
+struct StemS2dPlan {
+    CUtensorMap tmA;      // re-laid image [B][Hs][Ws][16] as (8-byte words, rows, images); box = one band
+    const int8_t* w;      // weights in the canonical unswizzled K-major layout (device)
+    int BN, KH, KWp, Wp;
+    int R, bands;
+    int band_bytes, band_alloc, w_bytes;
+    int in_unsigned;
+    int num_sms;
+    size_t smem_bytes;
+};
+bool stem_s2d_eligible(const ConvGeom& g);
+void stem_s2d_dims(const ConvGeom& g, int* Hs, int* Ws);
+size_t stem_s2d_weight_bytes(const ConvGeom& g);
+void stem_s2d_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* dst);
+cudaError_t launch_s2d_image(const void* in, const ConvGeom& g, int batch, void* out, cudaStream_t s);
+int stem_s2d_make_plan(StemS2dPlan* plan, const void* d_s2d, const int8_t* d_w_arranged, const ConvGeom& g, int max_batch,
+                       int in_unsigned, int num_sms, const char** why);
+cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_base, const FastQuant& fast, void* out,
+                            int* status_word, cudaStream_t s);
+
 // ---- stride-1 convolution from a shared-memory input patch (tcgen05 kind::i8) ----
 struct PatchPlan {
     CUtensorMap tmA;      // NHWC activations, box = one patch: C x Wp x (R + halo rows) x 1 image

@@ -38,7 +38,7 @@ static int fail(int code, const char* fmt, ...)
 
 // ------------------------------------------------------------------------------------ model
 enum CellType { CELL_CONV, CELL_FC, CELL_POOL, CELL_SUM, CELL_SCALING };
-enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED, ENG_STEM, ENG_PATCH };
+enum Engine { ENG_TCGEN05, ENG_SIMT, ENG_DEPTHWISE, ENG_POOL, ENG_SUM, ENG_FUSED, ENG_STEM, ENG_PATCH, ENG_STEM_S2D };
 
 struct TensorRec {
     int C = 0, H = 0, W = 0;
@@ -83,8 +83,9 @@ struct CellRec {
     // 32-bit epilogue constants (tensor-core cells)
     FastQuant fast{};
     int* d_fast = nullptr;
-    // first-layer tensor-core kernel
+    // first-layer tensor-core kernels
     StemPlan stem{};
+    StemS2dPlan stem2{};
     void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel and its zero padding written out
     // stride-1 convolution from a shared-memory patch
     PatchPlan patch{};
@@ -772,6 +773,27 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                           && stem_eligible(g) && net->tensors[c.output].dtype == DT_I8 && !(flags & N2D2B_EXACT64_EPILOGUE);
         if (stem) {
             if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+            if (c.fast.enabled && stem_s2d_eligible(g)) {
+                // stride 2: space-to-depth image, no gather
+                std::vector<int8_t> arranged(stem_s2d_weight_bytes(g));
+                stem_s2d_arrange_weights(g, c.weights.data(), arranged.data());
+                CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
+                CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
+                int Hs = 0, Ws = 0;
+                stem_s2d_dims(g, &Hs, &Ws);
+                CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * Hs * Ws * 16 + 256));
+                const char* why = "";
+                if (stem_s2d_make_plan(&c.stem2, c.d_pad4, c.d_weights, g, max_batch, net->tensors[c.inputs[0]].is_unsigned,
+                                       net->num_sms, &why) == 0) {
+                    net->launches++;
+                    c.engine = ENG_STEM_S2D;
+                    continue;
+                }
+                cudaFree(c.d_weights);
+                c.d_weights = nullptr;
+                cudaFree(c.d_pad4);
+                c.d_pad4 = nullptr;
+            }
             if (c.fast.enabled) {
                 std::vector<int8_t> arranged(stem_weight_bytes(g));
                 stem_arrange_weights(g, c.weights.data(), arranged.data());
@@ -849,7 +871,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
         const CellRec& c = net->cells[ci];
         const bool sliceable = !c.skipped && c.residual < 0 && c.inputs.size() == 1
                                && c.inputs[0] == (ci == 0 ? 0 : net->cells[ci - 1].output) && c.type != CELL_FC
-                               && (c.engine == ENG_STEM || c.engine == ENG_POOL || c.engine == ENG_DEPTHWISE
+                               && (c.engine == ENG_STEM || c.engine == ENG_STEM_S2D || c.engine == ENG_POOL || c.engine == ENG_DEPTHWISE
                                    || c.engine == ENG_SIMT);
         if (!sliceable) break;
         net->head_cells = (int)ci + 1;
@@ -907,6 +929,15 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         ConvGeom g = c.geom;
         g.B = batch;
         CUDA_TRY(launch_patch(c.patch, g, c.fast, out, net->d_status, s));
+        break;
+    }
+    case ENG_STEM_S2D: {
+        ConvGeom g = c.geom;
+        g.B = batch;
+        int Hs = 0, Ws = 0;
+        stem_s2d_dims(g, &Hs, &Ws);
+        CUDA_TRY(launch_s2d_image(in0, g, batch, (uint8_t*)c.d_pad4 + (size_t)img0 * Hs * Ws * 16, s));
+        CUDA_TRY(launch_stem_s2d(c.stem2, g, img0, c.fast, out, net->d_status, s));
         break;
     }
     case ENG_STEM: {
@@ -1108,6 +1139,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
     case ENG_SUM: return "sum";
     case ENG_FUSED: return "fused";
     case ENG_STEM: return "stem-tcgen05";
+    case ENG_STEM_S2D: return "stem-tcgen05";
     case ENG_PATCH: return "patch-tcgen05";
     }
     return "";

@@ -81,6 +81,12 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* tm,
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* tm, unsigned bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* tm, unsigned bar, int c0, int c1, int c2, int c3)
 {
     asm volatile(
