@@ -10,8 +10,8 @@
 // no data moves, and the MMAs of a tile (taps x C/32 of them) are issued back to back.  Positions in the
 // halo columns (x >= oW) compute values nobody stores.  The weights of all taps stay resident.
 //
-// Warp 0 loads (weights once, patches double-buffered), warp 1 issues tcgen05.mma kind::i8 into a ring of
-// four TMEM accumulators, and four groups of four epilogue warps (one warp per TMEM lane quadrant) each
+// Warp 0 loads (weights once, patches double-buffered), warps 1-2 issue tcgen05.mma kind::i8 for alternate
+// tiles into a ring of four TMEM accumulators, and four groups of four epilogue warps (one warp per TMEM lane quadrant) each
 // drain every fourth tile: 32-bit requantisation in the fragment layout into a swizzled staging region,
 // then one 16-byte-vector copy per pixel row to the NHWC output.  Every wait is bounded.
 #include <cstring>
@@ -23,7 +23,9 @@ namespace n2d2b {
 static constexpr int PBM = 128;
 static constexpr int P_EPI_WARPS = 16;
 static constexpr int P_SLOTS = 4;            // TMEM accumulators = epilogue groups
-static constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
+static constexpr int P_ISSUERS = 2;           // MMA-issuing warps: tiles alternate between them
+static constexpr int P_EPI_WARP0 = 1 + P_ISSUERS;
+static constexpr int P_THREADS = 32 * (P_EPI_WARP0 + P_EPI_WARPS);
 
 struct PatchArgs {
     int B, oH, oW, N, BN, C;
@@ -100,7 +102,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(pfull0 + 8u * s, 1);
-            mbar_init(pempty0 + 8u * s, 1);
+            mbar_init(pempty0 + 8u * s, P_ISSUERS);
         }
         for (int s = 0; s < P_SLOTS; ++s) {
             mbar_init(tfull0 + 8u * s, 1);
@@ -148,8 +150,11 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 if (band >= a.bands) { band -= a.bands; ++n; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp < P_EPI_WARP0) {
+        // ------------------------------------------------------------------ MMA issuers
+        // Issuing a tile costs one thread about 100 cycles per MMA, the tensor pipe about 60: two threads take
+        // alternate tiles (each tile has its own accumulator, so their MMAs are independent).
+        const unsigned me = (unsigned)(warp - 1);
         if (lane == 0 && (int)blockIdx.x < items) {
             bool ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
             const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.C) >> 32);
@@ -168,6 +173,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 tc_fence_after();
                 unsigned a_lo = patch_lo + pb * (unsigned)(a.patch_alloc >> 4);
                 for (int t = 0; t < T; ++t, ++seq, a_lo += tile_step) {
+                    if ((seq & (P_ISSUERS - 1)) != me) continue;
                     const unsigned slot = seq & (P_SLOTS - 1), sph = (seq / P_SLOTS) & 1u;
                     if (!mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
@@ -191,14 +197,14 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                     }
                     tc_commit(tfull0 + 8u * slot);
                 }
-                if (ok) tc_commit(pempty0 + 8u * pb);   // the patch is free once the item's MMAs have read it
+                if (ok) tc_commit(pempty0 + 8u * pb);   // the patch is free once both issuers' MMAs have read it
                 band += step_b;
                 if (band >= a.bands) band -= a.bands;
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        const int ew = warp - 2;
+        const int ew = warp - P_EPI_WARP0;
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);

@@ -13,9 +13,9 @@
 // pixel on), the next 8 rows 128 bytes further.  So no thread touches the activations between the TMA copy
 // and the tensor core; the weights sit resident in the canonical unswizzled layout.
 //
-// Roles as in the patch kernel: warp 0 loads (weights once, bands double-buffered), warp 1 issues
-// tcgen05.mma kind::i8 into a ring of four TMEM accumulators, four groups of four epilogue warps each drain
-// every fourth 128-position tile (32-bit requantisation in the fragment layout, swizzled staging, one
+// Roles as in the patch kernel: warp 0 loads (weights once, bands double-buffered), warps 1-2 issue
+// tcgen05.mma kind::i8 for alternate tiles into a ring of four TMEM accumulators, four groups of four
+// epilogue warps each drain every fourth 128-position tile (32-bit requantisation in the fragment layout, swizzled staging, one
 // 16-byte-vector copy per pixel row to the NHWC output).  Positions in the halo columns (x >= oW) compute
 // values nobody stores.  Every wait is bounded.
 #include <cstring>
@@ -28,7 +28,9 @@ namespace n2d2b {
 static constexpr int ZBM = 128;
 static constexpr int Z_EPI_WARPS = 16;
 static constexpr int Z_SLOTS = 4;
-static constexpr int Z_THREADS = 32 * (2 + Z_EPI_WARPS);
+static constexpr int Z_ISSUERS = 2;           // MMA-issuing warps: tiles alternate between them
+static constexpr int Z_EPI_WARP0 = 1 + Z_ISSUERS;
+static constexpr int Z_THREADS = 32 * (Z_EPI_WARP0 + Z_EPI_WARPS);
 
 struct S2dArgs {
     int B, oH, oW, N, BN;
@@ -154,7 +156,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(pfull0 + 8u * s, 1);
-            mbar_init(pempty0 + 8u * s, 1);
+            mbar_init(pempty0 + 8u * s, Z_ISSUERS);
         }
         for (int s = 0; s < Z_SLOTS; ++s) {
             mbar_init(tfull0 + 8u * s, 1);
@@ -199,8 +201,9 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
                 if (band >= a.bands) { band -= a.bands; ++n; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp < Z_EPI_WARP0) {
+        // ------------------------------------------------------------------ MMA issuers (alternate tiles)
+        const unsigned me = (unsigned)(warp - 1);
         if (lane == 0 && (int)blockIdx.x < items) {
             bool ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
             // activations: rows of 16 bytes, next K chunk = next pixel (16 bytes), next 8 rows 128 bytes on
@@ -222,6 +225,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
                 tc_fence_after();
                 unsigned a_lo = band_lo + pb * (unsigned)(a.band_alloc >> 4);
                 for (int t = 0; t < T; ++t, ++seq, a_lo += tile_step) {
+                    if ((seq & (Z_ISSUERS - 1)) != me) continue;
                     const unsigned slot = seq & (Z_SLOTS - 1), sph = (seq / Z_SLOTS) & 1u;
                     if (!mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
@@ -245,7 +249,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        const int ew = warp - 2;
+        const int ew = warp - Z_EPI_WARP0;
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
