@@ -94,6 +94,7 @@ struct PatchPlan {
     int R, bands;         // output rows per band, bands per image
     int patch_bytes;      // bytes of one patch load
     int patch_alloc;      // bytes reserved per patch buffer
+    int b_stream;         // weights stream through a ring (too large to stay resident)
     int in_unsigned;
     int num_sms;
     size_t smem_bytes;

@@ -26,6 +26,7 @@ static constexpr int P_SLOTS = 4;            // TMEM accumulators = epilogue gro
 static constexpr int P_ISSUERS = 2;           // MMA-issuing warps: tiles alternate between them
 static constexpr int P_EPI_WARP0 = 1 + P_ISSUERS;
 static constexpr int P_THREADS = 32 * (P_EPI_WARP0 + P_EPI_WARPS);
+static constexpr int P_BRING = 4;             // weight ring slots (one filter tap each) when the weights stream
 
 struct PatchArgs {
     int B, oH, oW, N, BN, C;
@@ -35,6 +36,7 @@ struct PatchArgs {
     int bands;              // bands per image
     int patch_bytes;        // bytes one patch load delivers (the full TMA box)
     int patch_alloc;        // bytes reserved per patch buffer (box + the rows a last tile may read past it)
+    int b_stream;           // weights too large to stay resident: their tap blocks stream through a ring
     unsigned rcp_Wp;        // ceil(2^32 / Wp)
     unsigned idesc, tmem_cols;
     void* out;
@@ -81,18 +83,20 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int taps = a.taps_y * a.taps_x;
     const int b_tap_bytes = a.BN * a.C;
-    unsigned char* res_b = smem;                                              // [taps][BN][C]
-    unsigned char* patch0 = smem + (((size_t)taps * b_tap_bytes + 1023) & ~(size_t)1023);
+    unsigned char* res_b = smem;                                              // [taps][BN][C], or a ring of P_BRING taps
+    unsigned char* patch0 = smem + (((size_t)(a.b_stream ? P_BRING : taps) * b_tap_bytes + 1023) & ~(size_t)1023);
     unsigned char* stage_out = patch0 + 2 * (size_t)a.patch_alloc;             // [16 warps][32 rows][BN]
     const int region_bytes = 32 * a.BN;
     unsigned long long* bars = (unsigned long long*)(stage_out + (size_t)P_EPI_WARPS * region_bytes);
-    // bars: patch_full[2], patch_empty[2], tmem_full[4], tmem_empty[4], weights
+    // bars: patch_full[2], patch_empty[2], tmem_full[4], tmem_empty[4], weights, (spare), ring_full[4], ring_empty[4]
     const unsigned pfull0 = smem_u32(bars);
     const unsigned pempty0 = pfull0 + 16u;
     const unsigned tfull0 = pempty0 + 16u;
     const unsigned tempty0 = tfull0 + 8u * P_SLOTS;
     const unsigned bfull = tempty0 + 8u * P_SLOTS;
-    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * P_SLOTS + 2);
+    const unsigned rfull0 = bfull + 16u;
+    const unsigned rempty0 = rfull0 + 8u * P_BRING;
+    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * P_SLOTS + 2 + 2 * P_BRING);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256]
 
@@ -109,6 +113,10 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             mbar_init(tempty0 + 8u * s, 4);
         }
         mbar_init(bfull, 1);
+        for (int r = 0; r < P_BRING; ++r) {
+            mbar_init(rfull0 + 8u * r, 1);
+            mbar_init(rempty0 + 8u * r, P_ISSUERS);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -133,10 +141,15 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && (int)blockIdx.x < items) {
-            mbar_expect_tx(bfull, (unsigned)(taps * b_tap_bytes));
-            for (int t = 0; t < taps; ++t)
-                tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, 0);
+            if (!a.b_stream) {
+                mbar_expect_tx(bfull, (unsigned)(taps * b_tap_bytes));
+                for (int t = 0; t < taps; ++t)
+                    tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, 0);
+            }
             unsigned it = 0;
+            int rs = 0;              // weight ring slot and its phase
+            unsigned rph = 0;
+            bool ok = true;
             int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
             const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
             for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
@@ -145,6 +158,16 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 mbar_expect_tx(pfull0 + 8u * pb, (unsigned)a.patch_bytes);
                 tma_load_4d(smem_u32(patch0 + (size_t)pb * a.patch_alloc), &tmA, pfull0 + 8u * pb, 0, -a.pL,
                             band * a.R - a.pT, n);
+                if (a.b_stream) {
+                    // every item walks all taps once: its weights follow the patch through the ring
+                    for (int t = 0; t < taps && ok; ++t) {
+                        if (!mbar_wait(rempty0 + 8u * rs, rph ^ 1u, abort_flag, a.status, 5)) { ok = false; break; }
+                        mbar_expect_tx(rfull0 + 8u * rs, (unsigned)b_tap_bytes);
+                        tma_load_2d(smem_u32(res_b + (size_t)rs * b_tap_bytes), &tmB, rfull0 + 8u * rs, t * a.C, 0);
+                        if (++rs == P_BRING) { rs = 0; rph ^= 1u; }
+                    }
+                    if (!ok) break;
+                }
                 n += step_n;
                 band += step_b;
                 if (band >= a.bands) { band -= a.bands; ++n; }
@@ -156,7 +179,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         // alternate tiles (each tile has its own accumulator, so their MMAs are independent).
         const unsigned me = (unsigned)(warp - 1);
         if (lane == 0 && (int)blockIdx.x < items) {
-            bool ok = mbar_wait(bfull, 0, abort_flag, a.status, 8);
+            bool ok = a.b_stream ? true : mbar_wait(bfull, 0, abort_flag, a.status, 8);
             const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.C) >> 32);
             const unsigned res_b_lo = (smem_u32(res_b) & 0x3ffffu) >> 4, patch_lo = (smem_u32(patch0) & 0x3ffffu) >> 4;
             const int ksteps = a.C / 32;
@@ -166,12 +189,48 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             int band = (int)blockIdx.x % a.bands;
             const int step_b = (int)gridDim.x % a.bands;
             const unsigned tile_step = (unsigned)((PBM * a.C) >> 4);
+            int rs = 0;              // weight ring slot and its phase (streamed weights)
+            unsigned rph = 0;
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 const int T = band_tiles(band);
                 if (!mbar_wait(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
                 tc_fence_after();
                 unsigned a_lo = patch_lo + pb * (unsigned)(a.patch_alloc >> 4);
+                if (a.b_stream) {
+                    // At most P_ISSUERS tiles per item: this thread owns tile `me` and walks the taps as their
+                    // weights arrive; a thread without a tile still releases every ring slot.
+                    const bool mine = (int)me < T;
+                    const unsigned myseq = seq + me;
+                    const unsigned slot = myseq & (P_SLOTS - 1), sph = (myseq / P_SLOTS) & 1u;
+                    if (mine && !mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned d_tmem = tmem_base + slot * (unsigned)a.BN;
+                    unsigned ar = a_lo + me * tile_step, first = 0;
+                    for (int ky = 0; ky < a.taps_y && ok; ++ky, ar += row_step) {
+                        unsigned ac = ar;
+                        for (int kx = 0; kx < a.taps_x; ++kx, ac += col_step) {
+                            if (!mbar_wait(rfull0 + 8u * rs, rph, abort_flag, a.status, 6)) { ok = false; break; }
+                            tc_fence_after();
+                            if (mine) {
+                                const unsigned bt = res_b_lo + (unsigned)rs * btap;
+                                for (int k = 0; k < ksteps; ++k) {
+                                    tc_mma_i8_lohi(d_tmem, ac + 2u * k, bt + 2u * k, desc_hi, a.idesc, first);
+                                    first = 1u;
+                                }
+                            }
+                            tc_commit(rempty0 + 8u * rs);
+                            if (++rs == P_BRING) { rs = 0; rph ^= 1u; }
+                        }
+                    }
+                    if (!ok) break;
+                    if (mine) tc_commit(tfull0 + 8u * slot);
+                    seq += (unsigned)T;
+                    tc_commit(pempty0 + 8u * pb);
+                    band += step_b;
+                    if (band >= a.bands) band -= a.bands;
+                    continue;
+                }
                 for (int t = 0; t < T; ++t, ++seq, a_lo += tile_step) {
                     if ((seq & (P_ISSUERS - 1)) != me) continue;
                     const unsigned slot = seq & (P_SLOTS - 1), sph = (seq / P_SLOTS) & 1u;
@@ -261,10 +320,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// weights of up to this size stay resident; larger ones stream tap by tap through a ring of P_BRING blocks
+static constexpr size_t P_RESIDENT_MAX = 96 * 1024;
+static bool patch_streams(int taps, int C, int BN) { return (size_t)taps * BN * C > P_RESIDENT_MAX; }
+
 static size_t patch_smem_bytes(int taps, int C, int BN, int patch_alloc)
 {
-    const size_t b = (((size_t)taps * BN * C) + 1023) & ~(size_t)1023;
-    return 1024 + b + 2 * (size_t)patch_alloc + (size_t)P_EPI_WARPS * 32 * BN + (4 + 2 * P_SLOTS + 2) * 8 + 32
+    const int blocks = patch_streams(taps, C, BN) ? P_BRING : taps;
+    const size_t b = (((size_t)blocks * BN * C) + 1023) & ~(size_t)1023;
+    return 1024 + b + 2 * (size_t)patch_alloc + (size_t)P_EPI_WARPS * 32 * BN + (4 + 2 * P_SLOTS + 2 + 2 * P_BRING) * 8 + 32
          + FAST_NP * 256 * 4 + 64;
 }
 
@@ -286,7 +350,6 @@ bool patch_eligible(const ConvGeom& g)
     if (g.O % 32 != 0 || g.O > 128) return false;
     if (g.kH * g.kW < 2) return false;   // a 1x1 layer gains nothing from a patch
     const int BN = g.O <= 64 ? 64 : 128;
-    if ((size_t)g.kH * g.kW * g.C * BN > 96 * 1024) return false;
     const int Wp = g.oW + (g.kW - 1) * g.dX;
     if (Wp > 256 || Wp < 2 || g.oH < 1) return false;
     if ((g.kH - 1) * g.dY + 1 > 256) return false;
@@ -317,9 +380,12 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     // wastes the fewest 128-position tiles per image; ties go to the taller band (fewer halo rows re-read)
     int best_R = 0;
     long long best_tiles = 0;
+    plan->b_stream = patch_streams(taps, g.C, plan->BN) ? 1 : 0;
     for (int R = 1; R <= g.oH; ++R) {
         if (R + (g.kH - 1) * g.dY > 256) break;
         if (patch_smem_bytes(taps, g.C, plan->BN, patch_alloc_bytes(g, plan->Wp, R)) > 226 * 1024) break;
+        // streamed weights: every tile of a band accumulates while the taps pass, one tile per issuing warp
+        if (plan->b_stream && (R * plan->Wp + PBM - 1) / PBM > P_ISSUERS) break;
         const int full = g.oH / R, rest = g.oH % R;
         const long long tiles = (long long)full * ((R * plan->Wp + PBM - 1) / PBM)
                               + (rest ? (rest * plan->Wp + PBM - 1) / PBM : 0);
@@ -368,6 +434,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQua
     a.taps_y = g.kH; a.taps_x = g.kW; a.dY = g.dY; a.dX = g.dX; a.pT = g.pT; a.pL = g.pL;
     a.Wp = plan.Wp; a.R = plan.R; a.bands = plan.bands;
     a.patch_bytes = plan.patch_bytes; a.patch_alloc = plan.patch_alloc;
+    a.b_stream = plan.b_stream;
     a.rcp_Wp = (unsigned)(((1ull << 32) + (unsigned)plan.Wp - 1) / (unsigned)plan.Wp);
     a.idesc = (2u << 4) | ((plan.in_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
             | ((unsigned)(PBM >> 4) << 24);
@@ -394,7 +461,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQua
     }
     const long long items = (long long)a.B * a.bands;
     const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
-    const int shape = (g.kH == 3 && g.kW == 3) ? (g.C == 32 ? 1 : (g.C == 64 ? 2 : 3)) : 0;
+    const int shape = (g.kH == 3 && g.kW == 3 && !plan.b_stream) ? (g.C == 32 ? 1 : (g.C == 64 ? 2 : 3)) : 0;
     variants[(fast.need_clamp ? 4 : 0) + shape]<<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
     return cudaGetLastError();
 }

@@ -294,12 +294,15 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
     unsigned char* const sm = dyn_smem();
     constexpr int NK = 4;   // rows tr + 8k: k = 0, 1 from vA (TMEM lanes 0-15), k = 2, 3 from vB (lanes 16-31)
     const int tr = lane >> 2, tc = (lane & 3) * 2;
-    unsigned base[NK];
+    unsigned base[NK], base16[NK];
 #pragma unroll
     for (int k = 0; k < NK; ++k) {
         const unsigned ro = (unsigned)((tr + 8 * k) * wb);
         const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
         base[k] = region_off + ro + ((unsigned)(col0 | tc) ^ xm);
+        // group i sits at base ^ 8i: bit 3 of base is clear (tc <= 6, col0 a multiple of 16, the swizzle term
+        // touches bits 4-6 only), so odd groups are +8 (an immediate offset) and groups 2-3 one xor away
+        base16[k] = base[k] ^ 16u;
     }
     // the residual bytes of the whole block first: loads the compiler can keep in flight together
     unsigned rres[NG][NK];
@@ -307,7 +310,7 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
 #pragma unroll
         for (int i = 0; i < NG; ++i)
 #pragma unroll
-            for (int k = 0; k < NK; ++k) rres[i][k] = *(const unsigned short*)(sm + (base[k] ^ (unsigned)(8 * i)));
+            for (int k = 0; k < NK; ++k) rres[i][k] = *(const unsigned short*)(sm + ((i & 2) ? base16[k] : base[k]) + 8 * (i & 1));
     }
     const unsigned pbase = par_off + (unsigned)(pcol0 + tc) * 4u;
 #pragma unroll
@@ -381,7 +384,7 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
             unsigned d;
             if (EF & EF_OUT_UNSIGNED) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
             else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
-            *(unsigned short*)(sm + (base[k] ^ (unsigned)(8 * i))) = (unsigned short)d;
+            *(unsigned short*)(sm + ((i & 2) ? base16[k] : base[k]) + 8 * (i & 1)) = (unsigned short)d;
         }
     }
 }

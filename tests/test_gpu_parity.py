@@ -13,7 +13,10 @@ from gpu_common import KEEP, compare_net, single_conv_net
 PATCH_CASES = [(64, 56, 56, 64, 3, 1, 1, True), (64, 20, 17, 64, 3, 1, 1, True), (32, 9, 9, 32, 3, 1, 1, False),
                (128, 12, 12, 64, 3, 1, 1, True), (32, 15, 15, 64, 5, 2, 1, True), (64, 20, 20, 64, 3, 2, 2, True),
                (64, 10, 10, 32, 3, 0, 1, True), (64, 6, 250, 64, 3, 1, 1, True), (64, 33, 29, 128, 2, 1, 1, False),
-               (32, 40, 40, 96, 3, 1, 1, True)]
+               (32, 40, 40, 96, 3, 1, 1, True),
+               # weights beyond the resident limit: the tap blocks stream through a ring
+               (128, 28, 28, 128, 3, 1, 1, True), (64, 14, 14, 128, 5, 2, 1, True), (128, 9, 33, 96, 3, 1, 1, False),
+               (128, 5, 100, 96, 3, 1, 1, True)]
 
 
 @pytest.mark.parametrize('case', PATCH_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_p%d_d%d' % c[:7])
