@@ -95,6 +95,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -139,6 +140,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     tma_load_2d(smem_u32(res_b + (size_t)kb * b_stage_bytes), &tmB, bfull, tap * a.Cin + kc * a.BK, n0);
                 }
             }
+            pdl_wait();   // weights are constants; the activations are the previous kernel's output
             // The loops below keep ring slot, phase, tap and channel-chunk as running counters: a single
             // thread pays the full latency of every dependent instruction, so an integer division per K
             // block costs more than the load it prepares.
@@ -233,6 +235,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        pdl_wait();   // residual loads and output stores touch tensors the previous kernel reads or writes
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
         const int part = (warp - EPI_WARP0) >> 2;        // 0..3 within the quadrant: a quarter of the columns (32-bit epilogue)
         const int row = quad * 32 + lane;
@@ -587,15 +590,10 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     if (a.b_resident && tiles > grid && a.num_n_tiles > 1 && grid % a.num_n_tiles != 0) return cudaErrorInvalidConfiguration;
     a.step_m = grid / a.num_n_tiles;
     a.step_n = grid % a.num_n_tiles;
-    switch (mode) {
-    case 1: igemm_i8_tcgen05_kernel<1><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    case 2: igemm_i8_tcgen05_kernel<2><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    case 3: igemm_i8_tcgen05_kernel<3><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    case 4: igemm_i8_tcgen05_kernel<4><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    case 5: igemm_i8_tcgen05_kernel<5><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    default: igemm_i8_tcgen05_kernel<0><<<grid, NUM_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, plan.tmO, plan.tmR, a); break;
-    }
-    return cudaGetLastError();
+    typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
+    static const Kernel kernels[6] = {igemm_i8_tcgen05_kernel<0>, igemm_i8_tcgen05_kernel<1>, igemm_i8_tcgen05_kernel<2>,
+                                      igemm_i8_tcgen05_kernel<3>, igemm_i8_tcgen05_kernel<4>, igemm_i8_tcgen05_kernel<5>};
+    return launch_pdl(kernels[mode], grid, NUM_THREADS, plan.smem_bytes, s, plan.tmA, plan.tmB, plan.tmO, plan.tmR, a);
 }
 
 }  // namespace n2d2b

@@ -102,6 +102,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
@@ -146,6 +147,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 for (int t = 0; t < taps; ++t)
                     tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, 0);
             }
+            pdl_wait();   // weights are constants; the activations are the previous kernel's output
             unsigned it = 0;
             int rs = 0;              // weight ring slot and its phase
             unsigned rph = 0;
@@ -263,6 +265,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        pdl_wait();   // the output buffer may still be read by the previous kernel
         const int ew = warp - P_EPI_WARP0;
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
@@ -462,8 +465,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQua
     const long long items = (long long)a.B * a.bands;
     const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
     const int shape = (g.kH == 3 && g.kW == 3 && !plan.b_stream) ? (g.C == 32 ? 1 : (g.C == 64 ? 2 : 3)) : 0;
-    variants[(fast.need_clamp ? 4 : 0) + shape]<<<grid, P_THREADS, plan.smem_bytes, s>>>(plan.tmA, plan.tmB, a);
-    return cudaGetLastError();
+    return launch_pdl(variants[(fast.need_clamp ? 4 : 0) + shape], grid, P_THREADS, plan.smem_bytes, s, plan.tmA, plan.tmB, a);
 }
 
 }  // namespace n2d2b

@@ -152,6 +152,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
@@ -188,6 +189,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         if (lane == 0 && (int)blockIdx.x < items) {
             mbar_expect_tx(bfull, (unsigned)a.w_bytes);
             bulk_load(smem_u32(res_b), a.w, (unsigned)a.w_bytes, bfull);
+            pdl_wait();   // weights are constants; the re-laid image is the previous kernel's output
             unsigned it = 0;
             int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
             const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
@@ -249,6 +251,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        pdl_wait();   // the output buffer may still be read by the previous kernel
         const int ew = warp - Z_EPI_WARP0;
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
@@ -489,8 +492,7 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     const long long items = (long long)a.B * a.bands;
     const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
     const int shape = (plan.KH == 4 && plan.KWp == 4) ? 1 : ((plan.KH == 2 && plan.KWp == 2) ? 2 : 0);
-    variants[(fast.need_clamp ? 3 : 0) + shape]<<<grid, Z_THREADS, plan.smem_bytes, s>>>(plan.tmA, a);
-    return cudaGetLastError();
+    return launch_pdl(variants[(fast.need_clamp ? 3 : 0) + shape], grid, Z_THREADS, plan.smem_bytes, s, plan.tmA, a);
 }
 
 }  // namespace n2d2b

@@ -11,6 +11,31 @@ namespace n2d2b {
 static constexpr unsigned long long WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
 static constexpr int FAST_NP = 5;             // words per channel of a fast requantisation: lo, hi, mult, add, shift
 
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with launch_pdl may start while the kernel before it on the stream still runs: its CTAs
+// take the SMs the earlier kernel's CTAs leave, set up barriers, TMEM, constants and weights, and only then
+// wait (pdl_wait) for the earlier kernel to complete and its memory to be visible.  Everything that reads
+// activations or writes outputs sits behind that wait, directly or through the kernel's own barriers.
+// pdl_launch_dependents, at the start of a kernel, lets the next one begin that early.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... P, typename... A>
+static inline cudaError_t launch_pdl(void (*kernel)(P...), int grid, int threads, size_t smem, cudaStream_t s, A... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
+
 // ----------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
