@@ -6,12 +6,18 @@
 // One persistent CTA per SM loops over 128 x BN output tiles.  Warp 0 issues TMA loads into a
 // multi-stage shared-memory ring (A tile through a 2-D tiled map for a plain GEMM, or through an
 // im2col map that applies stride / padding / dilation and zero-fills the halo; B tile through a 2-D
-// map), warp 1 issues tcgen05.mma kind::i8 into one of two TMEM accumulators, warps 2-5 drain the
-// other accumulator with tcgen05.ld and run the fused epilogue (bias, per-channel rescale, rounding,
-// saturation, ReLU, optional residual add + second rescale) straight to int8 NHWC.  This replaces
-// the reference's cudnnConvolutionForward + cudnnAddTensor + Scaling kernel + cudnnActivationForward
-// sequence (src/Cell/ConvCell_Frame_CUDA.cpp:1169-1270) and its cublasGemm FC
+// map, or once into a resident block when the layer's weights are small), warp 1 issues
+// tcgen05.mma kind::i8 into one of two TMEM accumulators, warps 2-17 drain the other accumulator with
+// tcgen05.ld and run the fused epilogue (bias, per-channel rescale, rounding, saturation, ReLU,
+// optional residual add + second rescale) straight to int8 NHWC: every warp owns the 32 rows of its
+// TMEM lane quadrant and a quarter of the tile's columns.  This replaces the reference's
+// cudnnConvolutionForward + cudnnAddTensor + Scaling kernel + cudnnActivationForward sequence
+// (src/Cell/ConvCell_Frame_CUDA.cpp:1169-1270) and its cublasGemm FC
 // (src/Cell/FcCell_Frame_CUDA.cpp:308-427).
+//
+// The kernel is launched with programmatic stream serialization: barriers, TMEM, constants and
+// resident weights are set up while the previous kernel drains; activations are touched only after
+// griddepcontrol.wait.
 //
 // Every wait on an mbarrier is bounded: a wait that does not complete within about a second sets
 // *status_word and makes the whole CTA drain and exit, so a wrong descriptor cannot hang the GPU.
@@ -24,8 +30,8 @@ namespace n2d2b {
 
 static constexpr int BM = 128;
 static constexpr int EPI_WARP0 = 2;
-static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant: 2 halves of its 32 rows x up to 2 column halves
-static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 16 rows x up to 128 bytes
+static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant, a quarter of the columns each
+static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 32 rows x up to 64 bytes
 static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
