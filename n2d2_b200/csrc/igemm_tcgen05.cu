@@ -36,6 +36,7 @@ static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
+    int m_base;         // first output row of this call within the tensors (a batch slice starts at image img0)
     int b_resident;     // the CTA's whole weight block stays in shared memory (its column block never changes)
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
     int num_m_tiles, num_n_tiles;
@@ -154,7 +155,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             unsigned ph = 0;
             int m_tile = (int)blockIdx.x / a.num_n_tiles, n_tile = (int)blockIdx.x % a.num_n_tiles;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = m_tile * BM, n0 = n_tile * a.BN;
+                const int m0 = a.m_base + m_tile * BM, n0 = n_tile * a.BN;
                 m_tile += a.step_m;
                 n_tile += a.step_n;
                 if (n_tile >= a.num_n_tiles) { n_tile -= a.num_n_tiles; ++m_tile; }
@@ -260,7 +261,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             m_next += a.step_m;
             n_next += a.step_n;
             if (n_next >= a.num_n_tiles) { n_next -= a.num_n_tiles; ++m_next; }
-            const int m0 = m_tile * BM, n0 = n_tile * a.BN;
+            const int m0 = a.m_base + m_tile * BM, n0 = n_tile * a.BN;
             const unsigned as = acc_it & 1u;
             const unsigned aph = (acc_it >> 1) & 1u;
             if (FAST && n_tile != staged_n_tile) {
@@ -284,7 +285,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 ++stage_it;
             }
             const int m = m0 + row;
-            const bool m_ok = m < a.M;
+            const bool m_ok = m < a.m_base + a.M;
             const int nchunks = cols_per_warp / 32;
             const int cbase = part * cols_per_warp;
             if (FAST) {
@@ -292,7 +293,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 const int ew = warp - EPI_WARP0;
                 EpiTile e;
                 e.tmem_acc = tmem_base + as * (unsigned)a.BN;
-                e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = m0; e.n0 = n0;
+                e.BN = a.BN; e.N = a.N; e.M = a.m_base + a.M; e.m0 = m0; e.n0 = n0;
                 e.wp = a.BN >> 2;
                 e.par_off = (unsigned)((unsigned char*)par - smem_raw);
                 e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * REGION_BYTES * regions_per_warp);
@@ -300,7 +301,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 e.rbar = rbar0 + 16u * ew;
                 {
                     const int nt = tile + (int)gridDim.x;
-                    e.next_m0 = nt < num_tiles ? m_next * BM : -1;
+                    e.next_m0 = nt < num_tiles ? a.m_base + m_next * BM : -1;
                     e.next_n0 = nt < num_tiles ? n_next * a.BN : 0;
                 }
                 e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
@@ -541,11 +542,12 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
 }
 
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast, void* out,
-                         int out_dtype, int* status_word, cudaStream_t s)
+                         int out_dtype, int m_base, int* status_word, cudaStream_t s)
 {
     if (plan.M == 0 || plan.N == 0) return cudaSuccess;
     IgemmArgs a;
     memset(&a, 0, sizeof(a));
+    a.m_base = m_base;
     a.M = plan.M; a.N = plan.N; a.Cin = plan.Cin; a.taps = plan.taps; a.BK = plan.BK; a.BN = plan.BN;
     a.b_resident = plan.b_resident;
     a.stages = plan.stages; a.a_im2col = plan.a_im2col;

@@ -102,8 +102,9 @@ struct PatchPlan {
 bool patch_eligible(const ConvGeom& g);
 int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
                     const char** why);
-cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQuant& fast, void* out, int* status_word,
-                         cudaStream_t s);
+// n_base: first image of this call within the tensors the plan was encoded for (`out` = the tensor's base)
+cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, const FastQuant& fast, void* out,
+                         int* status_word, cudaStream_t s);
 
 // ---- tensor-core implicit GEMM (tcgen05 kind::i8) ----
 struct IgemmPlan {
@@ -128,8 +129,10 @@ struct IgemmPlan {
 // Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
                     const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
+// m_base: first output row (pixel) of this call within the tensors the plan was encoded for; `out` and the
+// residual stay the tensors' base pointers
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,
-                         void* out, int out_dtype, int* status_word, cudaStream_t s);
+                         void* out, int out_dtype, int m_base, int* status_word, cudaStream_t s);
 
 // ---- first-layer convolution (<= 4 input channels) on the tensor cores ----
 struct StemPlan {

@@ -864,15 +864,24 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     CUDA_TRY(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
     for (cudaEvent_t& e : net->slice_ready) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     CUDA_TRY(cudaEventCreateWithFlags(&net->stage_free, cudaEventDisableTiming));
-    // leading cells that take plain pointers (no tensor map over the whole batch) and read only the
-    // stimuli or the previous cell: they can run on a slice of the batch
+    // Leading cells that the host-buffer entry point runs slice by slice while later slices of the batch
+    // are still being uploaded: every cell works image by image, so a slice is an offset (in images for the
+    // pointer-based kernels, in rows of the tensor maps for the tensor-core ones).  The head ends where the
+    // per-image tensors get small (after the first stage of a ResNet): from there on a launch per slice would
+    // cost more in fixed launch time than the overlap gains.
     net->head_cells = 0;
     for (size_t ci = 0; ci < net->cells.size(); ++ci) {
         const CellRec& c = net->cells[ci];
-        const bool sliceable = !c.skipped && c.residual < 0 && c.inputs.size() == 1
-                               && c.inputs[0] == (ci == 0 ? 0 : net->cells[ci - 1].output) && c.type != CELL_FC
-                               && (c.engine == ENG_STEM || c.engine == ENG_STEM_S2D || c.engine == ENG_POOL || c.engine == ENG_DEPTHWISE
-                                   || c.engine == ENG_SIMT);
+        bool sliceable = true;
+        if (!c.skipped) {
+            const bool mapped = c.engine == ENG_TCGEN05 || c.engine == ENG_PATCH;
+            const bool pointer_based = (c.engine == ENG_STEM || c.engine == ENG_STEM_S2D || c.engine == ENG_POOL
+                                        || c.engine == ENG_DEPTHWISE || c.engine == ENG_SIMT)
+                                       && c.residual < 0 && c.inputs.size() == 1;
+            sliceable = c.type != CELL_FC && (mapped || pointer_based);
+            const TensorRec& t = net->tensors[c.output];
+            if ((long long)t.H * t.W < 2048) sliceable = false;
+        }
         if (!sliceable) break;
         net->head_cells = (int)ci + 1;
     }
@@ -889,8 +898,11 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
     const TensorRec& tin = net->tensors[c.inputs[0]];
     const TensorRec& tout = net->tensors[c.output];
     if (!in0 || !out) return fail(N2D2B_ERR_STATE, "internal: tensor without a buffer");
-    if (img0) {
-        if (c.engine == ENG_TCGEN05 || c.engine == ENG_PATCH || c.engine == ENG_SUM || c.residual >= 0)
+    // the tensor-core cells address their tensors through maps encoded over the whole buffers: a batch slice
+    // is an offset in rows / images there; every other cell takes offset pointers
+    const bool mapped = c.engine == ENG_TCGEN05 || c.engine == ENG_PATCH;
+    if (img0 && !mapped) {
+        if (c.engine == ENG_SUM || c.residual >= 0)
             return fail(N2D2B_ERR_STATE, "internal: this cell cannot run on a slice");
         in0 = (const uint8_t*)in0 + (size_t)img0 * tin.bytes_per_image();
         out = (uint8_t*)out + (size_t)img0 * tout.bytes_per_image();
@@ -914,7 +926,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         }
         IgemmPlan p = c.plan;
         p.M = batch * c.geom.oH * c.geom.oW;
-        CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, net->d_status, s));
+        CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, img0 * c.geom.oH * c.geom.oW, net->d_status, s));
         break;
     }
     case ENG_PATCH: {
@@ -928,7 +940,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         }
         ConvGeom g = c.geom;
         g.B = batch;
-        CUDA_TRY(launch_patch(c.patch, g, c.fast, out, net->d_status, s));
+        CUDA_TRY(launch_patch(c.patch, g, img0, c.fast, out, net->d_status, s));
         break;
     }
     case ENG_STEM_S2D: {
@@ -1067,7 +1079,9 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
     const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
     void* d_in = net->d_stage_in;
     void* d_out = net->d_stage_out;
-    const int nslices = (net->head_cells > 0 && batch >= 256) ? 8 : 1;
+    // slices of about 256 images: large enough to fill the GPU, small enough that the first one arrives early
+    int nslices = (net->head_cells > 0 && batch >= 256) ? (batch / 256 < 2 ? 2 : (batch / 256 > 8 ? 8 : batch / 256)) : 1;
+    if (const char* e = getenv("N2D2B_SLICES")) nslices = atoi(e) > 0 && atoi(e) <= 8 ? atoi(e) : nslices;
     if (nslices == 1) {
         CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
         if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0)) return rc;
@@ -1083,7 +1097,8 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
             CUDA_TRY(cudaEventRecord(net->slice_ready[k], net->copy_stream));
             CUDA_TRY(cudaStreamWaitEvent(s, net->slice_ready[k], 0));
             for (int ci = 0; ci < net->head_cells; ++ci)
-                if (int rc = run_cell(net, net->cells[ci], d_in, b1 - b0, s, b0)) return rc;
+                if (!net->cells[ci].skipped)
+                    if (int rc = run_cell(net, net->cells[ci], d_in, b1 - b0, s, b0)) return rc;
         }
         if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0, net->head_cells)) return rc;
     }

@@ -34,6 +34,7 @@ struct PatchArgs {
     int Wp;                 // patch width in pixels: oW + (kW-1)*dX
     int R;                  // output rows per band
     int bands;              // bands per image
+    int n_base;             // first image of this call within the tensors (batch slices)
     int patch_bytes;        // bytes one patch load delivers (the full TMA box)
     int patch_alloc;        // bytes reserved per patch buffer (box + the rows a last tile may read past it)
     int b_stream;           // weights too large to stay resident: their tap blocks stream through a ring
@@ -159,7 +160,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 if (!mbar_wait(pempty0 + 8u * pb, ph ^ 1u, abort_flag, a.status, 1)) break;
                 mbar_expect_tx(pfull0 + 8u * pb, (unsigned)a.patch_bytes);
                 tma_load_4d(smem_u32(patch0 + (size_t)pb * a.patch_alloc), &tmA, pfull0 + 8u * pb, 0, -a.pL,
-                            band * a.R - a.pT, n);
+                            band * a.R - a.pT, a.n_base + n);
                 if (a.b_stream) {
                     // every item walks all taps once: its weights follow the patch through the ring
                     for (int t = 0; t < taps && ok; ++t) {
@@ -295,7 +296,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 const unsigned yy = __umulhi(p, a.rcp_Wp);
                 const unsigned x = p - yy * (unsigned)a.Wp;
                 if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                    uint8_t* dst = (uint8_t*)a.out + (((size_t)n * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N;
+                    uint8_t* dst = (uint8_t*)a.out + (((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N;
                     const unsigned ro = (unsigned)(lane * a.BN);
                     const unsigned xm = (ro >> 7) & swz_mask;
                     for (int c = 0; c * 16 < a.N; ++c)
@@ -427,8 +428,8 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     return 0;
 }
 
-cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQuant& fast, void* out, int* status_word,
-                         cudaStream_t s)
+cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, const FastQuant& fast, void* out,
+                         int* status_word, cudaStream_t s)
 {
     PatchArgs a;
     memset(&a, 0, sizeof(a));
@@ -436,6 +437,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, const FastQua
     if (a.B == 0) return cudaSuccess;
     a.taps_y = g.kH; a.taps_x = g.kW; a.dY = g.dY; a.dX = g.dX; a.pT = g.pT; a.pL = g.pL;
     a.Wp = plan.Wp; a.R = plan.R; a.bands = plan.bands;
+    a.n_base = n_base;
     a.patch_bytes = plan.patch_bytes; a.patch_alloc = plan.patch_alloc;
     a.b_stream = plan.b_stream;
     a.rcp_Wp = (unsigned)(((1ull << 32) + (unsigned)plan.Wp - 1) / (unsigned)plan.Wp);

@@ -38,6 +38,24 @@ def test_forced_im2col_keeps_the_implicit_gemm_kernel():
     compare_net(net, 2, flags=runtime.KEEP_ALL_OUTPUTS | runtime.FORCE_IM2COL, want_engine='tcgen05')
 
 
+@pytest.mark.parametrize('slices', ['2', '3', '5'])
+def test_host_entry_point_runs_the_leading_cells_slice_by_slice(slices, monkeypatch):
+    # at batch >= 256 the host-buffer entry point uploads the batch in slices and runs the leading cells
+    # (here: all of them - im2col and 1x1 implicit GEMM, patch kernel, fused residual sum, pooling) per slice;
+    # uneven slice sizes, every layer compared with the oracle
+    monkeypatch.setenv('N2D2B_SLICES', slices)
+    b = netdesc.NetBuilder('sliced', 16, 48, 48, 11, 'double', weight_dist=('normal', 30))
+    c0 = b.conv(-1, 64, 3, pad=1, name='c0')
+    c1 = b.conv(c0, 64, 3, pad=1, name='c1')
+    x4 = b.conv(c1, 128, 1, act='linear', name='x4')
+    pj = b.conv(c0, 128, 1, act='linear', name='proj')
+    sm = b.sum([x4, pj], act='relu', name='sum')
+    b.pool(sm, 'max', 2, 2, name='pool')
+    n, eng = compare_net(b.net, 261, flags=0)
+    assert 'fused' in eng and 'patch-tcgen05' in eng and 'tcgen05' in eng
+    compare_net(b.net, 261)     # and with every cell's output kept and compared
+
+
 pytestmark = pytest.mark.gpu
 R = runtime
 
