@@ -572,7 +572,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.dp_xor = fast.dp_xor;
     a.dp_a_signed = fast.dp_a_signed;
     a.ef = (fast.out_unsigned ? EF_OUT_UNSIGNED : 0) | (r.is_unsigned ? EF_RES_UNSIGNED : 0)
-         | (fast.t_lo == 0 ? EF_T_UNSIGNED : 0) | (fast.dp_a_signed ? EF_DP_A_SIGNED : 0);
+         | (fast.t_lo == 0 ? EF_T_UNSIGNED : 0) | (fast.dp_a_signed ? EF_DP_A_SIGNED : 0) | (fast.wide ? EF_WIDE : 0);
     const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
                           && plan.has_out_maps;
     const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : (fast.dp4a ? 5 : 4)) : (fast.need_clamp ? 1 : 3));

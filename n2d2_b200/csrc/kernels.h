@@ -58,6 +58,7 @@ struct FastQuant {
     int t_lo = 0, t_hi = 0;     // range the cell's own output saturates to
     int out_unsigned = 0;       // final 8-bit range
     bool need_clamp = true;     // false: no product can leave 32 bits and saturation is the final pack's
+    bool wide = false;          // first rescale in 64 bits: row 0 of fq holds the upper words of the addends (no clamps)
     bool dp4a = false;          // residual stage as a byte dot product (multipliers <= 255, native 8-bit ranges)
     unsigned dp_xor = 0;        //   bytes to flip from unsigned to signed (0x80 per byte)
     int dp_a_signed = 1;        //   signedness of the (t, r) byte vector

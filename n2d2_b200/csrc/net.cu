@@ -258,6 +258,33 @@ static long long ceil_div(long long a, long long b)  // b > 0
     return (a >= 0) ? (a + b - 1) / b : -((-a) / b);
 }
 
+// 64-bit form of the same rescale, for fixed-point scalings whose products leave 32 bits: no clamps (the final
+// pack saturates), so it applies when none is needed for other reasons; the shifted result must fit 32 bits.
+static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out)
+{
+    if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned)) return false;
+    const int C = q.nb_channels;
+    out.assign((size_t)5 * cpad, 0);
+    for (int c = 0; c < C; ++c) {
+        long long m, s;
+        if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
+        else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
+        else { m = q.p0[c]; s = q.p1[c]; }
+        if (m < 0 || m > (1ll << 30) || s > 31) return false;
+        const long long half = s > 0 ? (1ll << (s - 1)) : 0;
+        const long long b = q.has_bias ? q.bias[c] : 0;
+        if (std::llabs(b) > (1ll << 30)) return false;   // keeps every 64-bit intermediate below 2^61
+        const long long add = b * m + half;                                   // < 2^62
+        const long long worst = x_bound * m + std::llabs(add);               // < 2^62 for x_bound < 2^30
+        if ((worst >> s) > (1ll << 31) - 2) return false;
+        out[(size_t)0 * cpad + c] = (int32_t)(add >> 32);
+        out[(size_t)2 * cpad + c] = (int32_t)m;
+        out[(size_t)3 * cpad + c] = (int32_t)(uint32_t)(add & 0xffffffffll);
+        out[(size_t)4 * cpad + c] = (int32_t)s;
+    }
+    return true;
+}
+
 static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int* eff_lo,
                              int* eff_hi, bool* need_clamp)
 {
@@ -322,16 +349,29 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     // |accumulator| <= K * 255 * 128; the residual stage adds two 8-bit values
     const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * 128ll;
     if (acc_bound > (1ll << 30)) return 0;
-    bool need_clamp = false;
-    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) return 0;
+    bool need_clamp = false, wide = false;
+    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) {
+        // eff range etc. were set before the failing channel; retry in 64 bits
+        need_clamp = false;
+        if (c.q.out_bits != 8 || c.q.act == ACT_SATURATION
+            || (c.q.mode != SC_SINGLE_SHIFT && c.q.mode != SC_DOUBLE_SHIFT && c.q.mode != SC_FIXED_MULT16
+                && c.q.mode != SC_FIXED_MULT32)
+            || !build_wide_quant(c.q, cpad, acc_bound, f1))
+            return 0;
+        wide = true;
+        lo1 = c.q.out_unsigned ? 0 : -128;
+        hi1 = c.q.out_unsigned ? 255 : 127;
+        if (c.q.act == ACT_RECTIFIER && lo1 < 0) lo1 = 0;
+    }
     bool with_res = c.residual >= 0;
     if (with_res && !build_fast_quant(c.q2, cpad, 512, f2, &lo2, &hi2, &need_clamp)) return 0;
+    if (wide && need_clamp) return 0;   // the 64-bit form has no clamps
     // Dot-product form of the residual stage (see frag_block): every multiplier of the sum's scaling fits
     // a byte, both operands have a native 8-bit range and no clamp is needed.
     bool dp4a = false;
     unsigned dp_xor = 0;
     int dp_a_signed = 1;
-    if (with_res && !need_clamp && residual_dtype_i8) {
+    if (with_res && !need_clamp && !wide && residual_dtype_i8) {
         const bool t_uns = (lo1 == 0 && hi1 == 255), t_sig = (lo1 == -128 && hi1 == 127);
         bool small = true;
         for (int ch = 0; ch < C; ++ch) small = small && f2[(size_t)2 * cpad + ch] >= 0 && f2[(size_t)2 * cpad + ch] <= 255;
@@ -361,6 +401,7 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     c.fast.t_hi = hi1;
     c.fast.out_unsigned = with_res ? c.q2.out_unsigned : c.q.out_unsigned;
     c.fast.need_clamp = need_clamp;
+    c.fast.wide = wide;
     c.fast.dp4a = dp4a;
     c.fast.dp_xor = dp_xor;
     c.fast.dp_a_signed = dp_a_signed;

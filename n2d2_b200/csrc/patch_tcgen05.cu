@@ -45,6 +45,7 @@ struct PatchArgs {
     const int* fq;
     int cpad;
     int out_unsigned;
+    int wide;               // 64-bit first rescale (see EF_WIDE)
 };
 
 template <bool CLAMP, int EF>
@@ -286,7 +287,10 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
-                if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
+                if (a.wide) {
+                    if (a.out_unsigned) patch_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
+                    else patch_drain<false, EF_WIDE>(tbase, par_off, region_off, a.BN, lane);
+                } else if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
                 else patch_drain<CLAMP, 0>(tbase, par_off, region_off, a.BN, lane);
                 // the accumulator is drained: hand it back, then copy this warp's 32 rows out
                 tc_fence_before();
@@ -449,6 +453,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, c
     a.fq = fast.fq;
     a.cpad = fast.cpad;
     a.out_unsigned = fast.out_unsigned;
+    a.wide = fast.wide ? 1 : 0;
     typedef void (*PatchKernel)(const CUtensorMap, const CUtensorMap, const PatchArgs);
     static const PatchKernel variants[8] = {
         patch_conv_tcgen05_kernel<false, 0>, patch_conv_tcgen05_kernel<false, 1>, patch_conv_tcgen05_kernel<false, 2>,

@@ -49,6 +49,7 @@ struct S2dArgs {
     const int* fq;
     int cpad;
     int out_unsigned;
+    int wide;               // 64-bit first rescale (see EF_WIDE)
 };
 
 // [B][H][W][C] (C <= 4) -> [B][Hs][Ws][2][2][4]: block (dy, dx) of pixel (Y, X) = input pixel
@@ -271,7 +272,10 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
                 if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
-                if (a.out_unsigned) s2d_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
+                if (a.wide) {
+                    if (a.out_unsigned) s2d_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
+                    else s2d_drain<false, EF_WIDE>(tbase, par_off, region_off, a.BN, lane);
+                } else if (a.out_unsigned) s2d_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
                 else s2d_drain<CLAMP, 0>(tbase, par_off, region_off, a.BN, lane);
                 // the accumulator is drained: hand it back, then copy this warp's 32 rows out
                 tc_fence_before();
@@ -475,6 +479,7 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     a.fq = fast.fq;
     a.cpad = fast.cpad;
     a.out_unsigned = fast.out_unsigned;
+    a.wide = fast.wide ? 1 : 0;
     typedef void (*Kernel)(const CUtensorMap, const S2dArgs);
     static const Kernel variants[6] = {stem_s2d_tcgen05_kernel<false, 0>, stem_s2d_tcgen05_kernel<false, 1>,
                                        stem_s2d_tcgen05_kernel<false, 2>, stem_s2d_tcgen05_kernel<true, 0>,

@@ -39,6 +39,7 @@ struct StemArgs {
     const int* fq;
     int cpad;
     int out_unsigned;
+    int wide;
 };
 
 // [B][H][W][C] (C <= 4) -> [B][Hp][Wp][4] with the image at (pT, pL) and zeros elsewhere.
@@ -300,7 +301,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             e.rbar = 0;
             e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
             e.abort_flag = abort_flag; e.status = a.status;
-            e.ef = a.out_unsigned ? EF_OUT_UNSIGNED : 0;
+            e.ef = (a.out_unsigned ? EF_OUT_UNSIGNED : 0) | (a.wide ? EF_WIDE : 0);
             e.t_lo = 0; e.t_hi = 0; e.dp_xor = 0;
             if (!fast_epilogue_tile<false, CLAMP, false>(&tmO, &tmO, e, quad, cp, lane, est)) break;
         }
@@ -422,6 +423,7 @@ cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g
     a.fq = fast.fq;
     a.cpad = fast.cpad;
     a.out_unsigned = fast.out_unsigned;
+    a.wide = fast.wide ? 1 : 0;
     typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
     static const StemKernel variants[4] = {stem_conv_tcgen05_kernel<false, false>, stem_conv_tcgen05_kernel<false, true>,
                                            stem_conv_tcgen05_kernel<true, false>, stem_conv_tcgen05_kernel<true, true>};

@@ -294,6 +294,7 @@ static constexpr int EF_OUT_UNSIGNED = 1;   // final range [0,255] instead of [-
 static constexpr int EF_RES_UNSIGNED = 2;   // residual operand is unsigned
 static constexpr int EF_T_UNSIGNED = 4;     // DP: the cell's own output saturates to [0,255]
 static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are read as signed
+static constexpr int EF_WIDE = 16;          // first rescale in 64 bits: x * mult + (row 0 : row 3 as a 64-bit addend) >> shift
 
 // NG 8-column groups (NG = 4: 32 columns, NG = 2: 16) of a warp's 32 accumulator rows in the fragment layout
 // of the 16x256b TMEM load (thread t: rows t/4 + {0, 8, 16, 24}, column pair 8i + 2(t%4) of group i), through the
@@ -348,6 +349,8 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
         if (CLAMP) {
             lo = *(const int2*)(sm + pp + 0 * 1024);
             hi = *(const int2*)(sm + pp + 1 * 1024);
+        } else if (EF & EF_WIDE) {
+            lo = *(const int2*)(sm + pp + 0 * 1024);   // upper words of the 64-bit addends
         }
         int2 mu2 = make_int2(0, 0), ad2 = mu2, sh2 = mu2, lo2 = mu2, hi2 = mu2;
         if (RES) {
@@ -368,8 +371,18 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
                 x0 = min(max(x0, lo.x), hi.x);
                 x1 = min(max(x1, lo.y), hi.y);
             }
-            int y0 = (x0 * mu.x + ad.x) >> sh.x;
-            int y1 = (x1 * mu.y + ad.y) >> sh.y;
+            int y0, y1;
+            if (EF & EF_WIDE) {
+                // fixed-point scalings with many fractional bits: the product needs more than 32 bits, the
+                // shifted result does not (proved on the host); no clamps in this form, the pack saturates
+                const long long p0 = (long long)x0 * mu.x + (long long)(((unsigned long long)(unsigned)lo.x << 32) | (unsigned)ad.x);
+                const long long p1 = (long long)x1 * mu.y + (long long)(((unsigned long long)(unsigned)lo.y << 32) | (unsigned)ad.y);
+                y0 = (int)(p0 >> sh.x);
+                y1 = (int)(p1 >> sh.y);
+            } else {
+                y0 = (x0 * mu.x + ad.x) >> sh.x;
+                y1 = (x1 * mu.y + ad.y) >> sh.y;
+            }
             if (RES && DP) {
                 const unsigned rw = rres[i][k];   // two residual bytes, replaced below
                 unsigned a4;
@@ -503,14 +516,22 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
         const unsigned tbase = e.tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)cbase;
         // one branch per tile selects the arithmetic variant; inside, nothing depends on a run-time flag
         if (!RES) {
-            if (e.ef & EF_OUT_UNSIGNED) epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane);
-            else epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane);
+            switch (e.ef & (EF_OUT_UNSIGNED | EF_WIDE)) {
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
+            case EF_OUT_UNSIGNED: epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane); break;
+            case EF_WIDE: epi_drain<RES, false, DP, EF_WIDE>(e, tbase, cbase, region_off, lane); break;
+            default: epi_drain<RES, false, DP, EF_WIDE | EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane); break;
+            }
         } else if (!DP) {
-            switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED)) {
+            switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED | EF_WIDE)) {
             case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
             case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, lane); break;
             case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, lane); break;
-            default: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, lane); break;
+            case 3: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, lane); break;
+            case EF_WIDE | 0: epi_drain<RES, false, DP, EF_WIDE | 0>(e, tbase, cbase, region_off, lane); break;
+            case EF_WIDE | 1: epi_drain<RES, false, DP, EF_WIDE | 1>(e, tbase, cbase, region_off, lane); break;
+            case EF_WIDE | 2: epi_drain<RES, false, DP, EF_WIDE | 2>(e, tbase, cbase, region_off, lane); break;
+            default: epi_drain<RES, false, DP, EF_WIDE | 3>(e, tbase, cbase, region_off, lane); break;
             }
         } else {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_T_UNSIGNED | EF_DP_A_SIGNED)) {
