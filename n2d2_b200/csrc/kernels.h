@@ -39,8 +39,10 @@ cudaError_t launch_conv_direct(const void* in, int in_unsigned, const int8_t* w,
                                const QuantDev& q, const Residual& r, void* out, int out_dtype,
                                cudaStream_t s);
 // Depthwise convolution, C % 16 == 0; weights re-laid as [kH][kW][C].
-cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc,
-                                  const ConvGeom& g, const QuantDev& q, void* out, cudaStream_t s);
+struct FastQuant;
+// `fast` (when enabled): the proved 32-bit rescale; 3x3 filters then take the dot-product kernel
+cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc, const ConvGeom& g,
+                                  const QuantDev& q, const FastQuant& fast, void* out, cudaStream_t s);
 cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void* out, cudaStream_t s);
 cudaError_t launch_pool_i32(const void* in, const PoolGeom& g, void* out, cudaStream_t s);
 cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, const QuantDev& q,

@@ -858,6 +858,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
         }
         if (depthwise) {
             c.engine = ENG_DEPTHWISE;
+            if (!(flags & N2D2B_EXACT64_EPILOGUE))
+                if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
             // [C][kH][kW] -> [kH][kW][C] so that 16 channels of a tap are one 128-bit load
             const int taps = g.kH * g.kW;
             for (int ch = 0; ch < g.C; ++ch)
@@ -1015,7 +1017,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
     case ENG_DEPTHWISE: {
         ConvGeom g = c.geom;
         g.B = batch;
-        CUDA_TRY(launch_conv_depthwise(in0, tin.is_unsigned, c.d_weights, g, c.q.dev, out, s));
+        CUDA_TRY(launch_conv_depthwise(in0, tin.is_unsigned, c.d_weights, g, c.q.dev, c.fast, out, s));
         break;
     }
     case ENG_POOL: {

@@ -164,9 +164,124 @@ __global__ void conv_depthwise_kernel(const uint8_t* __restrict__ in, int in_uns
     }
 }
 
-cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc,
-                                  const ConvGeom& g, const QuantDev& q, void* out, cudaStream_t s)
+// Depthwise 3x3 convolution with the 32-bit epilogue.  A thread owns four channels (one 32-bit word per pixel) of
+// four horizontally adjacent output pixels.  Its weights are kept as one word per (tap, channel) with the other three
+// bytes cleared, so a channel's product is a single four-way byte dot product on the packed input word, without
+// unpacking anything: 144 dp4a for 16 outputs.  One block per output row, no 64-bit index arithmetic.
+// fq = [5][cpad] constants of the 32-bit rescale (lo, hi, mult, add, shift), proved exact on the host.
+template <bool IN_UNSIGNED, bool CLAMP, bool OUT_UNSIGNED>
+__global__ void __launch_bounds__(256)
+conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __restrict__ w_hwc, ConvGeom g,
+                              const int* __restrict__ fq, int cpad, uint8_t* __restrict__ out)
 {
+    const int cw = g.C / 4;                        // channel words per pixel
+    // blockDim.x is a multiple of cw: a thread keeps its channel word over the whole launch.  A thread's four
+    // pixels are adjacent, so most of its 36 input words are shared between them and hit in L1 (spreading a
+    // thread's pixels for fully coalesced warp loads measured slower).
+    const int c4 = threadIdx.x % cw;
+    const int xi = threadIdx.x / cw;
+    const int xthreads = blockDim.x / cw;
+    unsigned wm[9][4];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+        const unsigned wv = __ldg((const unsigned*)(w_hwc + (size_t)t * g.C) + c4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wm[t][j] = wv & (0xffu << (8 * j));
+    }
+    int lo[4], hi[4], mu[4], ad[4], sh[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int ch = c4 * 4 + j;
+        lo[j] = __ldg(fq + 0 * cpad + ch); hi[j] = __ldg(fq + 1 * cpad + ch);
+        mu[j] = __ldg(fq + 2 * cpad + ch); ad[j] = __ldg(fq + 3 * cpad + ch); sh[j] = __ldg(fq + 4 * cpad + ch);
+    }
+    const unsigned* in_w = (const unsigned*)in;
+    unsigned* out_w = (unsigned*)out;
+    for (int row = blockIdx.x; row < g.B * g.oH; row += gridDim.x) {
+        const int b = row / g.oH, oy = row - b * g.oH;
+        const int iy0 = oy * g.sY - g.pT;
+        for (int chunk0 = 0; chunk0 < g.oW; chunk0 += 4 * xthreads) {
+            const int ox0 = chunk0 + 4 * xi;       // pixels ox0 .. ox0 + 3
+            int acc[4][4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[p][j] = 0;
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                const int iy = iy0 + ky * g.dY;
+                const bool row_ok = iy >= 0 && iy < g.H;
+                const unsigned* rowp = in_w + ((size_t)b * g.H + (row_ok ? iy : 0)) * g.W * cw + c4;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+#pragma unroll
+                    for (int kx = 0; kx < 3; ++kx) {
+                        const int ix = (ox0 + p) * g.sX - g.pL + kx * g.dX;
+                        const unsigned xv = (row_ok && ix >= 0 && ix < g.W) ? __ldg(rowp + (size_t)ix * cw) : 0u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (IN_UNSIGNED) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(acc[p][j]) : "r"(xv), "r"(wm[ky * 3 + kx][j]), "r"(acc[p][j]));
+                            else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(acc[p][j]) : "r"(xv), "r"(wm[ky * 3 + kx][j]), "r"(acc[p][j]));
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                if (ox0 + p >= g.oW) break;
+                int y[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int x = acc[p][j];
+                    if (CLAMP) x = min(max(x, lo[j]), hi[j]);
+                    y[j] = (x * mu[j] + ad[j]) >> sh[j];
+                }
+                unsigned tmp, d;
+                if (OUT_UNSIGNED) {
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(0));
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y[1]), "r"(y[0]), "r"(tmp));
+                } else {
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(0));
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y[1]), "r"(y[0]), "r"(tmp));
+                }
+                out_w[((size_t)row * g.oW + ox0 + p) * cw + c4] = d;
+            }
+        }
+    }
+}
+
+cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t* w_hwc,
+                                  const ConvGeom& g, const QuantDev& q, const FastQuant& fast, void* out, cudaStream_t s)
+{
+    // 3x3 filters whose rescale has the proved 32-bit form take the dot-product kernel
+    const int cw = g.C / 4;
+    if (fast.enabled && !fast.wide && g.kH == 3 && g.kW == 3 && 256 % cw == 0) {
+        const long long rows = (long long)g.B * g.oH;
+        if (rows == 0 || g.oW == 0) return cudaSuccess;
+        // few, long-lived blocks: a thread's weights and constants (29 loads) are fetched once and serve many rows
+        const long long max_blocks = 148ll * 6;
+        const unsigned grid = (unsigned)(rows < max_blocks ? rows : max_blocks);
+        // a block's threads cover 4 * (threads / cw) pixels of a row per pass
+        int threads = 256;
+        while (threads > 32 && (threads / 2) % cw == 0 && 4 * (threads / 2 / cw) >= g.oW) threads /= 2;
+        const uint8_t* ip = (const uint8_t*)in;
+        uint8_t* op = (uint8_t*)out;
+#define N2D2B_DW(U, C, O) conv_depthwise3x3_dp4a_kernel<U, C, O><<<grid, threads, 0, s>>>(ip, w_hwc, g, fast.fq, fast.cpad, op)
+        const int v = (in_unsigned ? 4 : 0) | (fast.need_clamp ? 2 : 0) | (fast.out_unsigned ? 1 : 0);
+        switch (v) {
+        case 0: N2D2B_DW(false, false, false); break;
+        case 1: N2D2B_DW(false, false, true); break;
+        case 2: N2D2B_DW(false, true, false); break;
+        case 3: N2D2B_DW(false, true, true); break;
+        case 4: N2D2B_DW(true, false, false); break;
+        case 5: N2D2B_DW(true, false, true); break;
+        case 6: N2D2B_DW(true, true, false); break;
+        default: N2D2B_DW(true, true, true); break;
+        }
+#undef N2D2B_DW
+        return cudaGetLastError();
+    }
+
     const size_t total = (size_t)g.B * g.oH * g.oW * (g.C / 16);
     if (total == 0) return cudaSuccess;
     const int block = 256;

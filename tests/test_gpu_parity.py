@@ -56,6 +56,22 @@ def test_host_entry_point_runs_the_leading_cells_slice_by_slice(slices, monkeypa
     compare_net(b.net, 261)     # and with every cell's output kept and compared
 
 
+# (C, H, W, stride, pad, dilation, input unsigned, activation)
+DW_CASES = [(32, 20, 20, 1, 1, 1, True, 'relu'), (64, 21, 19, 2, 1, 1, True, 'relu'), (16, 9, 9, 1, 0, 1, False, 'linear'),
+            (128, 14, 14, 1, 1, 1, True, 'relu'), (512, 7, 9, 2, 1, 1, True, 'relu'), (1024, 7, 7, 1, 1, 1, True, 'linear'),
+            (48, 13, 13, 1, 2, 2, True, 'relu'), (32, 5, 3, 1, 1, 1, False, 'relu')]
+
+
+@pytest.mark.parametrize('case', DW_CASES, ids=lambda c: 'C%d_%dx%d_s%d_p%d_d%d' % c[:6])
+@pytest.mark.parametrize('mode', ['single', 'double', 'fixed'])
+def test_depthwise_3x3(case, mode):
+    # the dot-product kernel (32-bit epilogue) and, with the exact-epilogue flag, the 64-bit kernel
+    C, H, W, s, p, d, uns, act = case
+    net = single_conv_net(C, H, W, C, 3, s, p, in_unsigned=uns, act=act, mode=mode, dil=d, groups=C)
+    compare_net(net, 3, want_engine='depthwise')
+    compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='depthwise')
+
+
 pytestmark = pytest.mark.gpu
 R = runtime
 
