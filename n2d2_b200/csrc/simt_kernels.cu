@@ -169,15 +169,26 @@ __global__ void conv_depthwise_kernel(const uint8_t* __restrict__ in, int in_uns
 // bytes cleared, so a channel's product is a single four-way byte dot product on the packed input word, without
 // unpacking anything: 144 dp4a for 16 outputs.  One block per output row, no 64-bit index arithmetic.
 // fq = [5][cpad] constants of the 32-bit rescale (lo, hi, mult, add, shift), proved exact on the host.
-template <bool IN_UNSIGNED, bool CLAMP, bool OUT_UNSIGNED>
+template <bool IN_UNSIGNED>
+__device__ __forceinline__ void dw_mac4(int (&acc)[4], unsigned xv, const unsigned (&w)[4])
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (IN_UNSIGNED) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(acc[j]) : "r"(xv), "r"(w[j]), "r"(acc[j]));
+        else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(acc[j]) : "r"(xv), "r"(w[j]), "r"(acc[j]));
+    }
+}
+
+// S1: stride 1 and dilation 1 - the four pixels of a thread read six input columns per row instead of twelve
+template <bool IN_UNSIGNED, bool CLAMP, bool OUT_UNSIGNED, bool S1>
 __global__ void __launch_bounds__(256)
 conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __restrict__ w_hwc, ConvGeom g,
                               const int* __restrict__ fq, int cpad, uint8_t* __restrict__ out)
 {
     const int cw = g.C / 4;                        // channel words per pixel
     // blockDim.x is a multiple of cw: a thread keeps its channel word over the whole launch.  A thread's four
-    // pixels are adjacent, so most of its 36 input words are shared between them and hit in L1 (spreading a
-    // thread's pixels for fully coalesced warp loads measured slower).
+    // pixels are adjacent, so most of its input words are shared between them (spreading a thread's pixels for
+    // fully coalesced warp loads measured slower).  All offsets are 32-bit word indices (checked by the host).
     const int c4 = threadIdx.x % cw;
     const int xi = threadIdx.x / cw;
     const int xthreads = blockDim.x / cw;
@@ -195,11 +206,20 @@ conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __re
         lo[j] = __ldg(fq + 0 * cpad + ch); hi[j] = __ldg(fq + 1 * cpad + ch);
         mu[j] = __ldg(fq + 2 * cpad + ch); ad[j] = __ldg(fq + 3 * cpad + ch); sh[j] = __ldg(fq + 4 * cpad + ch);
     }
-    const unsigned* in_w = (const unsigned*)in;
-    unsigned* out_w = (unsigned*)out;
+    const unsigned* in_w = (const unsigned*)in + c4;
+    unsigned* out_w = (unsigned*)out + c4;
     for (int row = blockIdx.x; row < g.B * g.oH; row += gridDim.x) {
         const int b = row / g.oH, oy = row - b * g.oH;
         const int iy0 = oy * g.sY - g.pT;
+        unsigned rbase[3];
+        bool rok[3];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            const int iy = iy0 + ky * g.dY;
+            rok[ky] = iy >= 0 && iy < g.H;
+            rbase[ky] = (unsigned)((b * g.H + (rok[ky] ? iy : 0)) * g.W * cw);
+        }
+        const unsigned obase = (unsigned)(row * g.oW * cw);
         for (int chunk0 = 0; chunk0 < g.oW; chunk0 += 4 * xthreads) {
             const int ox0 = chunk0 + 4 * xi;       // pixels ox0 .. ox0 + 3
             int acc[4][4];
@@ -207,24 +227,46 @@ conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __re
             for (int p = 0; p < 4; ++p)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[p][j] = 0;
+            if (S1) {
+                // columns ox0 - pL .. ox0 - pL + 5; pixel p, tap kx reads column p + kx
+                unsigned coff[6];
+                bool cok[6];
 #pragma unroll
-            for (int ky = 0; ky < 3; ++ky) {
-                const int iy = iy0 + ky * g.dY;
-                const bool row_ok = iy >= 0 && iy < g.H;
-                const unsigned* rowp = in_w + ((size_t)b * g.H + (row_ok ? iy : 0)) * g.W * cw + c4;
+                for (int q = 0; q < 6; ++q) {
+                    const int ix = ox0 - g.pL + q;
+                    cok[q] = ix >= 0 && ix < g.W;
+                    coff[q] = (unsigned)((cok[q] ? ix : 0) * cw);
+                }
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {
+                for (int ky = 0; ky < 3; ++ky) {
+                    unsigned xv[6];
+#pragma unroll
+                    for (int q = 0; q < 6; ++q) xv[q] = (rok[ky] && cok[q]) ? __ldg(in_w + rbase[ky] + coff[q]) : 0u;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p)
+#pragma unroll
+                        for (int kx = 0; kx < 3; ++kx) dw_mac4<IN_UNSIGNED>(acc[p], xv[p + kx], wm[ky * 3 + kx]);
+                }
+            } else {
+                unsigned coff[4][3];
+                bool cok[4][3];
+#pragma unroll
+                for (int p = 0; p < 4; ++p)
 #pragma unroll
                     for (int kx = 0; kx < 3; ++kx) {
                         const int ix = (ox0 + p) * g.sX - g.pL + kx * g.dX;
-                        const unsigned xv = (row_ok && ix >= 0 && ix < g.W) ? __ldg(rowp + (size_t)ix * cw) : 0u;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (IN_UNSIGNED) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(acc[p][j]) : "r"(xv), "r"(wm[ky * 3 + kx][j]), "r"(acc[p][j]));
-                            else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(acc[p][j]) : "r"(xv), "r"(wm[ky * 3 + kx][j]), "r"(acc[p][j]));
-                        }
+                        cok[p][kx] = ix >= 0 && ix < g.W;
+                        coff[p][kx] = (unsigned)((cok[p][kx] ? ix : 0) * cw);
                     }
-                }
+#pragma unroll
+                for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+                    for (int p = 0; p < 4; ++p)
+#pragma unroll
+                        for (int kx = 0; kx < 3; ++kx) {
+                            const unsigned xv = (rok[ky] && cok[p][kx]) ? __ldg(in_w + rbase[ky] + coff[p][kx]) : 0u;
+                            dw_mac4<IN_UNSIGNED>(acc[p], xv, wm[ky * 3 + kx]);
+                        }
             }
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
@@ -244,7 +286,7 @@ conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __re
                     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(0));
                     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y[1]), "r"(y[0]), "r"(tmp));
                 }
-                out_w[((size_t)row * g.oW + ox0 + p) * cw + c4] = d;
+                out_w[obase + (unsigned)((ox0 + p) * cw)] = d;
             }
         }
     }
@@ -255,7 +297,8 @@ cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t*
 {
     // 3x3 filters whose rescale has the proved 32-bit form take the dot-product kernel
     const int cw = g.C / 4;
-    if (fast.enabled && !fast.wide && g.kH == 3 && g.kW == 3 && 256 % cw == 0) {
+    const bool idx32 = (long long)g.B * g.H * g.W * cw < (1ll << 31) && (long long)g.B * g.oH * g.oW * cw < (1ll << 31);
+    if (fast.enabled && !fast.wide && g.kH == 3 && g.kW == 3 && 256 % cw == 0 && idx32) {
         const long long rows = (long long)g.B * g.oH;
         if (rows == 0 || g.oW == 0) return cudaSuccess;
         // few, long-lived blocks: a thread's weights and constants (29 loads) are fetched once and serve many rows
@@ -266,7 +309,12 @@ cudaError_t launch_conv_depthwise(const void* in, int in_unsigned, const int8_t*
         while (threads > 32 && (threads / 2) % cw == 0 && 4 * (threads / 2 / cw) >= g.oW) threads /= 2;
         const uint8_t* ip = (const uint8_t*)in;
         uint8_t* op = (uint8_t*)out;
-#define N2D2B_DW(U, C, O) conv_depthwise3x3_dp4a_kernel<U, C, O><<<grid, threads, 0, s>>>(ip, w_hwc, g, fast.fq, fast.cpad, op)
+        const bool s1 = g.sX == 1 && g.dX == 1;
+#define N2D2B_DW(U, C, O)                                                                                         \
+    do {                                                                                                          \
+        if (s1) conv_depthwise3x3_dp4a_kernel<U, C, O, true><<<grid, threads, 0, s>>>(ip, w_hwc, g, fast.fq, fast.cpad, op); \
+        else conv_depthwise3x3_dp4a_kernel<U, C, O, false><<<grid, threads, 0, s>>>(ip, w_hwc, g, fast.fq, fast.cpad, op);   \
+    } while (0)
         const int v = (in_unsigned ? 4 : 0) | (fast.need_clamp ? 2 : 0) | (fast.out_unsigned ? 1 : 0);
         switch (v) {
         case 0: N2D2B_DW(false, false, false); break;
