@@ -280,10 +280,10 @@ conv_depthwise3x3_dp4a_kernel(const uint8_t* __restrict__ in, const int8_t* __re
                 }
                 unsigned tmp, d;
                 if (OUT_UNSIGNED) {
-                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(0));
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(y[2]));   // upper half shifted out below
                     asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y[1]), "r"(y[0]), "r"(tmp));
                 } else {
-                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(0));
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(tmp) : "r"(y[3]), "r"(y[2]), "r"(y[2]));   // upper half shifted out below
                     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y[1]), "r"(y[0]), "r"(tmp));
                 }
                 out_w[obase + (unsigned)((ox0 + p) * cw)] = d;

@@ -420,8 +420,10 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
                 y1 = (u1 * mu2.y + ad2.y) >> sh2.y;
             }
             unsigned d;
-            if (EF & EF_OUT_UNSIGNED) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
-            else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(0));
+            // the third operand fills the upper half of d, which the 16-bit store drops: any live register will do
+            // (a literal 0 would cost a register move per pack)
+            if (EF & EF_OUT_UNSIGNED) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(y0));
+            else asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(y1), "r"(y0), "r"(y0));
             *(unsigned short*)(sm + ((i & 2) ? base16[k] : base[k]) + 8 * (i & 1)) = (unsigned short)d;
         }
     }
