@@ -296,15 +296,35 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8u * group);
-                const unsigned p = (unsigned)(t * PBM + quad * 32 + lane);   // position within the band
-                const unsigned yy = __umulhi(p, a.rcp_Wp);
-                const unsigned x = p - yy * (unsigned)a.Wp;
-                if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                    uint8_t* dst = (uint8_t*)a.out + (((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N;
-                    const unsigned ro = (unsigned)(lane * a.BN);
-                    const unsigned xm = (ro >> 7) & swz_mask;
-                    for (int c = 0; c * 16 < a.N; ++c)
-                        *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
+                // Copy the warp's 32 rows out in 16-byte units, consecutive lanes on consecutive units of a pixel and
+                // then on the next pixel: a store instruction covers whole contiguous runs of the NHWC output.
+                const int nch = a.N >> 4;                       // 16-byte units per pixel
+                const unsigned pix0 = (unsigned)(t * PBM + quad * 32);
+                if ((nch & (nch - 1)) == 0) {
+                    const int lg = 31 - __clz(nch);
+                    for (int u = lane; u < 32 * nch; u += 32) {
+                        const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
+                        const unsigned p = pix0 + r;            // position within the band
+                        const unsigned yy = __umulhi(p, a.rcp_Wp);
+                        const unsigned x = p - yy * (unsigned)a.Wp;
+                        if (x < (unsigned)a.oW && yy < (unsigned)rows) {
+                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
+                            const unsigned ro = r * (unsigned)a.BN;
+                            const unsigned xm = (ro >> 7) & swz_mask;
+                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
+                        }
+                    }
+                } else {
+                    const unsigned p = pix0 + (unsigned)lane;
+                    const unsigned yy = __umulhi(p, a.rcp_Wp);
+                    const unsigned x = p - yy * (unsigned)a.Wp;
+                    if (x < (unsigned)a.oW && yy < (unsigned)rows) {
+                        uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
+                        const unsigned ro = (unsigned)(lane * a.BN);
+                        const unsigned xm = (ro >> 7) & swz_mask;
+                        for (int c = 0; c < nch; ++c)
+                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
+                    }
                 }
                 __syncwarp();   // the region is rewritten by the next tile of this group
             }
