@@ -133,6 +133,7 @@ typedef struct n2d2b_tensor_info {
 #define N2D2B_FORCE_SIMT 4u       /* CUDA-core kernels everywhere (cross-check of the tensor-core path) */
 #define N2D2B_FORCE_IM2COL 8u     /* tensor-core convolutions always load activations through the im2col map */
 #define N2D2B_EXACT64_EPILOGUE 16u /* tensor-core cells always use the 64-bit requantisation (cross-check of the 32-bit form) */
+#define N2D2B_FORCE_PAIR 32u      /* 256-row tiles wherever their structure allows, whatever the layer's size (tests) */
 
 const char* n2d2b_last_error(void);
 int n2d2b_version(void);

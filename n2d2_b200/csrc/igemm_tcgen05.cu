@@ -374,6 +374,235 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
 }
 
+// ----------------------------------------------------------------------------- 256-row tiles
+// Large-K layers with 256 output channels per tile are bound by L2-to-shared bandwidth at 128 x 256 tiles
+// (48 KB per K slab for 512 cycles of MMA).  This variant gives a CTA two 128-row tiles that share every
+// weight slab: 64 KB per slab for 1024 cycles of MMA.  Both TMEM accumulators belong to the pair, so the
+// epilogue of a pair does not overlap the MMAs of the next one - affordable when K is large.  No residual, the
+// 32-bit epilogue only; the staging regions are 1 KB (32 rows x 32 columns, two passes per warp) to make
+// room for three 64 KB stages.
+static constexpr int PAIR_STAGES = 3;
+static constexpr int PAIR_REGION = 1024;
+
+template <bool CLAMP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+igemm_pair_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                             const __grid_constant__ CUtensorMap tmO32, const IgemmArgs a)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = BM * 128, B_BYTES = 256 * 128, STAGE_BYTES = 2 * A_BYTES + B_BYTES;
+    unsigned char* tiles = smem;
+    unsigned char* stage_out = tiles + (size_t)PAIR_STAGES * STAGE_BYTES;
+    unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * PAIR_REGION);
+    // bars: full[3], empty[3], tmem_full[2], tmem_empty[2], params_ready
+    const unsigned full0 = smem_u32(bars);
+    const unsigned empty0 = full0 + 8u * PAIR_STAGES;
+    const unsigned tfull0 = empty0 + 8u * PAIR_STAGES;
+    const unsigned tempty0 = tfull0 + 16u;
+    const unsigned pready = tempty0 + 16u;
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * PAIR_STAGES + 6);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull0 + 8u * s, 1);
+            mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
+        }
+        mbar_init(pready, NUM_EPI_WARPS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    const int num_pairs = (a.num_m_tiles + 1) / 2;
+    const int num_pt = num_pairs * a.num_n_tiles;          // pair tiles, column block fastest
+    const int kchunks = a.Cin / 128;
+    const int num_kb = a.taps * kchunks;
+    const int m_end = a.m_base + a.M;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            pdl_wait();
+            int s = 0;
+            unsigned ph = 0;
+            bool ok = true;
+            int m_pair = (int)blockIdx.x / a.num_n_tiles, n_tile = (int)blockIdx.x % a.num_n_tiles;
+            for (int pt = blockIdx.x; pt < num_pt && ok; pt += gridDim.x) {
+                const int n0 = n_tile * 256;
+                int m0[2], iw0[2] = {0, 0}, ih0[2] = {0, 0}, in0[2] = {0, 0};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    m0[h] = a.m_base + (2 * m_pair + h) * BM;
+                    if (a.a_im2col) {
+                        const int ox = m0[h] % a.oW;
+                        const int t = m0[h] / a.oW;
+                        const int oy = t % a.oH;
+                        in0[h] = t / a.oH;
+                        iw0[h] = ox * a.sX - a.pL;
+                        ih0[h] = oy * a.sY - a.pT;
+                    }
+                }
+                m_pair += a.step_m;
+                n_tile += a.step_n;
+                if (n_tile >= a.num_n_tiles) { n_tile -= a.num_n_tiles; ++m_pair; }
+                int kx = 0, ky = 0, kc = 0, kcoord = 0;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+                    const unsigned bar = full0 + 8u * s;
+                    const unsigned dst = smem_u32(tiles) + (unsigned)(s * STAGE_BYTES);
+                    mbar_expect_tx(bar, (unsigned)STAGE_BYTES);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (a.a_im2col)
+                            tma_load_im2col_4d(dst + h * A_BYTES, &tmA, bar, kc * 128, iw0[h], ih0[h], in0[h],
+                                               (unsigned short)(kx * a.dX), (unsigned short)(ky * a.dY));
+                        else
+                            tma_load_2d(dst + h * A_BYTES, &tmA, bar, kcoord, m0[h]);
+                    }
+                    tma_load_2d(dst + 2 * A_BYTES, &tmB, bar, kcoord, n0);
+                    if (++s == PAIR_STAGES) { s = 0; ph ^= 1u; }
+                    if (++kc == kchunks) {
+                        kc = 0;
+                        kcoord += a.Cin - (kchunks - 1) * 128;
+                        if (++kx == a.kW) { kx = 0; ++ky; }
+                    } else {
+                        kcoord += 128;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const unsigned desc_hi = (unsigned)(make_smem_desc(0u, 128) >> 32);
+            const unsigned t_lo0 = (smem_u32(tiles) & 0x3ffffu) >> 4;
+            const unsigned stage16 = (unsigned)(STAGE_BYTES >> 4), a16 = (unsigned)(A_BYTES >> 4);
+            int s = 0;
+            unsigned ph = 0, pit = 0, a_lo = t_lo0;
+            bool ok = true;
+            for (int pt = blockIdx.x; pt < num_pt && ok; pt += gridDim.x, ++pit) {
+                const unsigned aph = pit & 1u;
+                if (!mbar_wait(tempty0, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                if (!mbar_wait(tempty0 + 8u, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned b_lo = a_lo + 2u * a16;
+                    const unsigned acc = kb ? 1u : 0u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const unsigned d_tmem = tmem_base + (unsigned)(h * 256);
+                        const unsigned al = a_lo + (unsigned)h * a16;
+                        tc_mma_i8_lohi(d_tmem, al, b_lo, desc_hi, a.idesc, acc);
+                        tc_mma_i8_lohi(d_tmem, al + 2u, b_lo + 2u, desc_hi, a.idesc, 1u);
+                        tc_mma_i8_lohi(d_tmem, al + 4u, b_lo + 4u, desc_hi, a.idesc, 1u);
+                        tc_mma_i8_lohi(d_tmem, al + 6u, b_lo + 6u, desc_hi, a.idesc, 1u);
+                    }
+                    tc_commit(empty0 + 8u * s);
+                    a_lo += stage16;
+                    if (++s == PAIR_STAGES) { s = 0; ph ^= 1u; a_lo = t_lo0; }
+                }
+                if (ok) {
+                    tc_commit(tfull0);
+                    tc_commit(tfull0 + 8u);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        pdl_wait();
+        const int ew = warp - EPI_WARP0;
+        const int quad = warp & 3;
+        const int part = ew >> 2;                        // a quarter of the 256 columns
+        const int cbase = part * 64;
+        const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
+        const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * PAIR_REGION);
+        const unsigned region = smem_u32(stage_out + (size_t)ew * PAIR_REGION);
+        // the launch keeps every CTA on one column block: its constants are staged once
+        const int n0 = ((int)blockIdx.x % a.num_n_tiles) * 256;
+        for (int i = ew * 32 + lane; i < FAST_NP * 256; i += 32 * NUM_EPI_WARPS) {
+            const int prm = i >> 8, c = i & 255;
+            par[i] = (n0 + c < a.cpad) ? __ldg(a.fq + (size_t)prm * a.cpad + n0 + c) : 0;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pready);
+        bool ok = mbar_wait_warp(pready, 0, abort_flag, a.status, 5, lane);
+        unsigned pit = 0;
+        int m_pair = (int)blockIdx.x / a.num_n_tiles;
+        const int gx = n0 + cbase;
+        for (int pt = blockIdx.x; pt < num_pt && ok; pt += gridDim.x, ++pit) {
+            const int pair_now = m_pair;
+            {
+                // same stepping as the producer; the column block stays
+                const int n_tile = (int)blockIdx.x % a.num_n_tiles;
+                m_pair += a.step_m + ((n_tile + a.step_n >= a.num_n_tiles) ? 1 : 0);
+            }
+#pragma unroll 1
+            for (int h = 0; h < 2 && ok; ++h) {
+                const int gy = a.m_base + (2 * pair_now + h) * BM + quad * 32;
+                const bool active = gx < a.N && gy < m_end;
+                if (!mbar_wait_warp(tfull0 + 8u * h, pit & 1u, abort_flag, a.status, 4, lane)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(h * 256 + cbase);
+#pragma unroll 1
+                for (int pass = 0; pass < 2; ++pass) {
+                    if (lane == 0) bulk_wait_read_all();   // the previous store has finished reading the region
+                    __syncwarp();
+                    if (active) {
+                        unsigned va[16], vb[16];
+                        tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(32 * pass), va, vb);
+                        if (a.out_unsigned)
+                            frag_block<4, false, CLAMP, false, EF_OUT_UNSIGNED>(va, vb, par_off, cbase + 32 * pass, region_off, 32, 0,
+                                                                                lane, 0, 0, 0u);
+                        else
+                            frag_block<4, false, CLAMP, false, 0>(va, vb, par_off, cbase + 32 * pass, region_off, 32, 0, lane, 0,
+                                                                  0, 0u);
+                    }
+                    if (pass == 1) {
+                        // the accumulator is drained: hand it back before the store goes out
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty0 + 8u * h);
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && active) {
+                        tma_store_2d(&tmO32, region, gx + 32 * pass, gy);
+                        bulk_commit();
+                    }
+                }
+            }
+        }
+        if (lane == 0) bulk_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // ----------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -420,7 +649,8 @@ static size_t igemm_smem_bytes(int stages, int BK, int BN, int with_res, size_t 
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
-                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why)
+                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
+                    int force_pair)
 {
     static const char* kWhy = "";
     *why = kWhy;
@@ -445,7 +675,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
         // a layer with few output pixels (the classifier, late stages at small batch) would leave most
         // SMs without a tile: narrower column blocks give more tiles
         const long long m_tiles = ((long long)g.B * g.oH * g.oW + BM - 1) / BM;
-        while (bn > 64 && m_tiles * ((g.O + bn - 1) / bn) < num_sms) bn >>= 1;
+        while (!force_pair && bn > 64 && m_tiles * ((g.O + bn - 1) / bn) < num_sms) bn >>= 1;
     }
     plan->BN = bn;
     plan->a_unsigned = in_unsigned;
@@ -537,6 +767,21 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
             if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the residual matrix"; return -1; }
         }
         plan->has_out_maps = 1;
+        // 256-row variant: 256-column tiles, 128-byte K slabs, no residual, weights not resident, and enough
+        // work per CTA that halving the weight traffic pays for the un-overlapped epilogue
+        const int num_kb = plan->taps * (g.C / 128);
+        if (plan->BN == 256 && plan->BK == 128 && !res && !plan->b_resident && g.O % 32 == 0
+            && (force_pair || (num_kb >= 8 && (long long)num_m_tiles * num_n_tiles >= 4ll * num_sms))) {
+            const cuuint32_t box32[2] = {32, 32};
+            rc = g_encode_tiled(&plan->tmO32, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)out, dims, strides, box32, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (rc == CUDA_SUCCESS) {
+                plan->pair = 1;
+                plan->pair_smem_bytes = 1024 + (size_t)PAIR_STAGES * (2 * BM * 128 + 256 * 128) + NUM_EPI_WARPS * PAIR_REGION
+                                      + (2 * PAIR_STAGES + 6) * 8 + 32 + FAST_NP * 256 * 4 + 64;
+            }
+        }
     }
     return 0;
 }
@@ -598,6 +843,27 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     if (a.b_resident && tiles > grid && a.num_n_tiles > 1 && grid % a.num_n_tiles != 0) return cudaErrorInvalidConfiguration;
     a.step_m = grid / a.num_n_tiles;
     a.step_n = grid % a.num_n_tiles;
+    if (plan.pair && use_fast && !r.ptr && !fast.wide) {
+        typedef void (*PairKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
+        static const PairKernel pair_kernels[2] = {igemm_pair_i8_tcgen05_kernel<false>, igemm_pair_i8_tcgen05_kernel<true>};
+        static bool pair_attr_set[64] = {false};
+        if (dev >= 0 && dev < 64 && !pair_attr_set[dev]) {
+            for (PairKernel k : pair_kernels) {
+                cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+                if (e != cudaSuccess) return e;
+            }
+            pair_attr_set[dev] = true;
+        }
+        const int pair_tiles = ((a.num_m_tiles + 1) / 2) * a.num_n_tiles;
+        int pgrid = plan.grid < pair_tiles ? plan.grid : pair_tiles;
+        if (pair_tiles > pgrid && a.num_n_tiles > 1 && pgrid > a.num_n_tiles) pgrid -= pgrid % a.num_n_tiles;
+        if (pair_tiles <= pgrid || a.num_n_tiles == 1 || pgrid % a.num_n_tiles == 0) {
+            a.step_m = pgrid / a.num_n_tiles;
+            a.step_n = pgrid % a.num_n_tiles;
+            return launch_pdl(pair_kernels[fast.need_clamp ? 1 : 0], pgrid, NUM_THREADS, plan.pair_smem_bytes, s, plan.tmA,
+                              plan.tmB, plan.tmO32, a);
+        }
+    }
     typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
     static const Kernel kernels[6] = {igemm_i8_tcgen05_kernel<0>, igemm_i8_tcgen05_kernel<1>, igemm_i8_tcgen05_kernel<2>,
                                       igemm_i8_tcgen05_kernel<3>, igemm_i8_tcgen05_kernel<4>, igemm_i8_tcgen05_kernel<5>};

@@ -123,6 +123,9 @@ struct IgemmPlan {
     int BN;               // tile N: 64, 128 or 256
     int stages;
     int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
+    int pair;             // large-K layer with 256-column tiles: CTAs take two 128-row tiles per weight slab
+    CUtensorMap tmO32;    // output [M][N] bytes, box = 32 rows x 32 columns (the pair kernel's two-pass store)
+    size_t pair_smem_bytes;
     int a_unsigned;
     // im2col geometry
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
@@ -130,8 +133,10 @@ struct IgemmPlan {
     size_t smem_bytes;
 };
 // Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
+// force_pair: take the 256-row variant wherever its structure allows, whatever the layer's size (tests)
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
-                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why);
+                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
+                    int force_pair = 0);
 // m_base: first output row (pixel) of this call within the tensors the plan was encoded for; `out` and the
 // residual stay the tensors' base pointers
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,

@@ -882,7 +882,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             const void* out_ptr = net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
             const void* res_ptr = c.residual >= 0 ? tensor_ptr(net, c.residual, nullptr) : nullptr;
             if (igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
-                                (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why) == 0) {
+                                (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
+                                (flags & N2D2B_FORCE_PAIR) ? 1 : 0) == 0) {
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
                 c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
@@ -963,7 +964,8 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
             gb.B = net->max_batch;
             const char* why = "";
             if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? out : nullptr, r.ptr, gb, tin.is_unsigned,
-                                (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why))
+                                (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
+                                (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
             c.plan_input = in0;
         }
@@ -1190,7 +1192,12 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
 {
     if (!net || cell < 0 || cell >= (int)net->cells.size()) return "";
     switch (net->cells[cell].engine) {
-    case ENG_TCGEN05: return "tcgen05";
+    case ENG_TCGEN05: {
+        const CellRec& c = net->cells[cell];
+        const bool pair = c.plan.pair && c.fast.enabled && !c.fast.wide && c.residual < 0
+                          && net->tensors[c.output].dtype == DT_I8 && c.geom.O % 32 == 0;
+        return pair ? "tcgen05-pair" : "tcgen05";
+    }
     case ENG_SIMT: return "simt";
     case ENG_DEPTHWISE: return "depthwise";
     case ENG_POOL: return "pool";

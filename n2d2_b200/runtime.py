@@ -20,6 +20,7 @@ KEEP_ALL_OUTPUTS = 1
 NO_FUSION = 2
 FORCE_SIMT = 4
 FORCE_IM2COL = 8
+FORCE_PAIR = 32
 EXACT64_EPILOGUE = 16
 
 

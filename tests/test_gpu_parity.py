@@ -72,6 +72,22 @@ def test_depthwise_3x3(case, mode):
     compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='depthwise')
 
 
+# (C, H, W, O, k, stride, pad, input unsigned, builder keywords): layers the 256-row variant can take
+# (weight blocks beyond the resident limit, 128-byte K slabs, 256-column tiles, no residual)
+PAIR_CASES = [(512, 9, 9, 256, 1, 1, 0, True, {}), (256, 14, 14, 256, 3, 1, 1, True, {}),
+              (128, 15, 15, 512, 3, 2, 1, True, {}), (512, 19, 19, 256, 1, 1, 0, False, {}),
+              (1024, 7, 7, 512, 1, 1, 0, True, {'unsigned_relu': False}), (128, 20, 11, 256, 3, 1, 1, True, {})]
+
+
+@pytest.mark.parametrize('case', PAIR_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_s%d' % c[:6])
+@pytest.mark.parametrize('mode', ['double', 'single'])
+def test_256_row_tiles(case, mode):
+    C, H, W, O, k, s, p, uns, kw = case
+    net = single_conv_net(C, H, W, O, k, s, p, in_unsigned=uns, mode=mode, **kw)
+    compare_net(net, 3, flags=KEEP | R.FORCE_PAIR, want_engine='tcgen05-pair')
+    compare_net(net, 5, flags=KEEP | R.FORCE_PAIR, want_engine='tcgen05-pair')   # another (odd) number of row tiles
+
+
 pytestmark = pytest.mark.gpu
 R = runtime
 
