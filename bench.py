@@ -25,7 +25,7 @@ sys.path.insert(0, ROOT)
 
 # DRAM bytes one launch of the implicit-GEMM kernel moves per image (average over the 53 launches of a
 # ResNet-50 forward): 4950.6 MB / 53 launches / 256 images, from the ncu capture summarised under profiles/.
-IGEMM_DRAM_BYTES_PER_IMAGE_PER_LAUNCH = 4678.85e6 / 47 / 256
+IGEMM_DRAM_BYTES_PER_IMAGE_PER_LAUNCH = 4671.45e6 / 47 / 256
 
 METRIC = 'int8_resnet50_images_per_sec'
 UNIT = 'images/s'
@@ -275,7 +275,7 @@ def main():
     peaks = measured_peaks()
     int8_peak = 2.0 * peaks['bf16_sustained']
     achieved = tc_ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
-    roofline = {'bound': 'tensor', 'kernel': 'igemm_i8_tcgen05_kernel', 'achieved': achieved, 'peak': int8_peak,
+    roofline = {'bound': 'tensor', 'kernel': 'igemm_i8_tcgen05_kernel (with its 256-row variant igemm_pair_i8_tcgen05_kernel)', 'achieved': achieved, 'peak': int8_peak,
                 'unit': 'TOP/s', 'frac': achieved / int8_peak, 'traffic': IGEMM_DRAM_BYTES_PER_IMAGE_PER_LAUNCH * B,
                 'traffic_note': 'dram__bytes_read+write per launch, averaged over the 47 launches of one forward; '
                                 'captured with ncu at batch 256 and scaled by batch (traffic grows in proportion); '
