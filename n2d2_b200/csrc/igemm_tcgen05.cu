@@ -252,6 +252,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         unsigned acc_it = 0;
         unsigned stage_it = 0;
         EpiState est;
+        frag_rowbase(est.rb, a.BN >> 2, lane);
         int staged_n_tile = -1;
         int* par = epi_params;
         bool ok = true;
@@ -536,6 +537,8 @@ igemm_pair_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
         const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * PAIR_REGION);
         const unsigned region = smem_u32(stage_out + (size_t)ew * PAIR_REGION);
+        unsigned rb[4];
+        frag_rowbase(rb, 32, lane);
         // the launch keeps every CTA on one column block: its constants are staged once
         const int n0 = ((int)blockIdx.x % a.num_n_tiles) * 256;
         for (int i = ew * 32 + lane; i < FAST_NP * 256; i += 32 * NUM_EPI_WARPS) {
@@ -570,10 +573,10 @@ igemm_pair_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                         unsigned va[16], vb[16];
                         tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(32 * pass), va, vb);
                         if (a.out_unsigned)
-                            frag_block<4, false, CLAMP, false, EF_OUT_UNSIGNED>(va, vb, par_off, cbase + 32 * pass, region_off, 32, 0,
+                            frag_block<4, false, CLAMP, false, EF_OUT_UNSIGNED>(va, vb, par_off, cbase + 32 * pass, region_off, rb, 0,
                                                                                 lane, 0, 0, 0u);
                         else
-                            frag_block<4, false, CLAMP, false, 0>(va, vb, par_off, cbase + 32 * pass, region_off, 32, 0, lane, 0,
+                            frag_block<4, false, CLAMP, false, 0>(va, vb, par_off, cbase + 32 * pass, region_off, rb, 0, lane, 0,
                                                                   0, 0u);
                     }
                     if (pass == 1) {

@@ -51,11 +51,13 @@ struct PatchArgs {
 template <bool CLAMP, int EF>
 __device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int BN, int lane)
 {
+    unsigned rb[4];
+    frag_rowbase(rb, BN, lane);
 #pragma unroll 1
     for (int cb = 0; cb < BN; cb += 32) {
         unsigned va[16], vb[16];
         tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
-        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, cb, region_off, BN, cb, lane, 0, 0, 0u);
+        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, cb, region_off, rb, cb, lane, 0, 0, 0u);
     }
 }
 

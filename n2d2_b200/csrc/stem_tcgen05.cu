@@ -288,6 +288,7 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         const int cp = (ew >> 2) & 1;           // column half of the tile
         unsigned acc_it = 0;
         EpiState est;
+        frag_rowbase(est.rb, a.BN >> 1, lane);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
             const unsigned as = acc_it & 1u, aph = (acc_it >> 1) & 1u;
             EpiTile e;

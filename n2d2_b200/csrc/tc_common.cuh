@@ -77,7 +77,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     // waiting warp leaves the issue slots to the warps that work
     const unsigned long long t0 = globaltimer_ns();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        // a few polls per look at the abort flag and the clock: each failed try_wait has already slept in hardware
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
             *abort_flag = 1;
@@ -93,6 +96,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
 __device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, volatile int* abort_flag,
                                                int* status, int code, int lane)
 {
+    // the common case, a phase that completed long ago, costs one poll of the whole warp
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
     unsigned ok = 1;
     if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1u : 0u;
     ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -313,19 +318,32 @@ static constexpr int EF_WIDE = 16;          // first rescale in 64 bits: x * mul
 // bytes beside it, a = [t0, t1, r0, r1], and b = [m2, 0, m2, 0] (resp. [0, m2, 0, m2]) selects one
 // column.  When t and r differ in signedness the unsigned pair is flipped to signed by xor 0x80 and the
 // host adds 128 * m2 to add2.
+// Row terms of the staging addresses of one lane: rb[k] = (tr + 8k) * wb + (tc ^ x(row)), without the region and
+// the column block.  They depend on the lane and the row width only, so a kernel computes them once.
+__device__ __forceinline__ void frag_rowbase(unsigned* rb, int wb, int lane)
+{
+    const int tr = lane >> 2, tc = (lane & 3) * 2;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const unsigned ro = (unsigned)((tr + 8 * k) * wb);
+        const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
+        rb[k] = ro + ((unsigned)tc ^ xm);
+    }
+}
+
 template <int NG, bool RES, bool CLAMP, bool DP, int EF>
-__device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, unsigned par_off, int pcol0, unsigned region_off, int wb,
-                                           int col0, int lane, int t_lo, int t_hi, unsigned dp_xor)
+__device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* vB, unsigned par_off, int pcol0, unsigned region_off,
+                                           const unsigned* rb, int col0, int lane, int t_lo, int t_hi, unsigned dp_xor)
 {
     unsigned char* const sm = dyn_smem();
     constexpr int NK = 4;   // rows tr + 8k: k = 0, 1 from vA (TMEM lanes 0-15), k = 2, 3 from vB (lanes 16-31)
-    const int tr = lane >> 2, tc = (lane & 3) * 2;
+    const int tc = (lane & 3) * 2;
     unsigned base[NK], base16[NK];
 #pragma unroll
     for (int k = 0; k < NK; ++k) {
-        const unsigned ro = (unsigned)((tr + 8 * k) * wb);
-        const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
-        base[k] = region_off + ro + ((unsigned)(col0 | tc) ^ xm);
+        // col0 (a multiple of 16 below the row width) occupies bits the row offset leaves clear, and the
+        // region is 1024-byte aligned: the column block enters the address as an xor
+        base[k] = (region_off + rb[k]) ^ (unsigned)col0;
         // group i sits at base ^ 8i: bit 3 of base is clear (tc <= 6, col0 a multiple of 16, the swizzle term
         // touches bits 4-6 only), so odd groups are +8 (an immediate offset) and groups 2-3 one xor away
         base16[k] = base[k] ^ 16u;
@@ -455,24 +473,26 @@ struct EpiState {
     unsigned t = 0;          // tiles handled so far (selects the staging region of a residual cell)
     unsigned used0 = 0, used1 = 0;   // completed waits per residual barrier (its parity)
     bool prefetched = false; // the current tile's residual load was issued during the previous tile
+    unsigned rb[4] = {0, 0, 0, 0};   // frag_rowbase of this lane for the warp's row width (set once by the kernel)
 };
 
 // The accumulator slice of one warp: 32 rows, wp columns in blocks of 32 (or one block of 16)
 template <bool RES, bool CLAMP, bool DP, int EF>
-__device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, int lane)
+__device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, const unsigned* rb,
+                                          int lane)
 {
     if (e.wp >= 32) {
 #pragma unroll 1
         for (int cb = 0; cb < e.wp; cb += 32) {
             unsigned va[16], vb[16];
             tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
-            frag_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, e.wp, cb, lane, e.t_lo, e.t_hi,
+            frag_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, rb, cb, lane, e.t_lo, e.t_hi,
                                               e.dp_xor);
         }
     } else {
         unsigned va[8], vb[8];
         tc_ld_2x16x256b_x2_wait(tbase, va, vb);
-        frag_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, e.wp, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
+        frag_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, rb, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
     }
 }
 
@@ -519,32 +539,32 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
         // one branch per tile selects the arithmetic variant; inside, nothing depends on a run-time flag
         if (!RES) {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_WIDE)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
-            case EF_OUT_UNSIGNED: epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane); break;
-            case EF_WIDE: epi_drain<RES, false, DP, EF_WIDE>(e, tbase, cbase, region_off, lane); break;
-            default: epi_drain<RES, false, DP, EF_WIDE | EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_OUT_UNSIGNED: epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE: epi_drain<RES, false, DP, EF_WIDE>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, false, DP, EF_WIDE | EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         } else if (!DP) {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED | EF_WIDE)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, lane); break;
-            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, lane); break;
-            case 3: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, lane); break;
-            case EF_WIDE | 0: epi_drain<RES, false, DP, EF_WIDE | 0>(e, tbase, cbase, region_off, lane); break;
-            case EF_WIDE | 1: epi_drain<RES, false, DP, EF_WIDE | 1>(e, tbase, cbase, region_off, lane); break;
-            case EF_WIDE | 2: epi_drain<RES, false, DP, EF_WIDE | 2>(e, tbase, cbase, region_off, lane); break;
-            default: epi_drain<RES, false, DP, EF_WIDE | 3>(e, tbase, cbase, region_off, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 3: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 0: epi_drain<RES, false, DP, EF_WIDE | 0>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 1: epi_drain<RES, false, DP, EF_WIDE | 1>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 2: epi_drain<RES, false, DP, EF_WIDE | 2>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, false, DP, EF_WIDE | 3>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         } else {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_T_UNSIGNED | EF_DP_A_SIGNED)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, lane); break;
-            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, lane); break;
-            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, lane); break;
-            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, lane); break;
-            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, lane); break;
-            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, lane); break;
-            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         }
     }
