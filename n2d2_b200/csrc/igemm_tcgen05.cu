@@ -36,6 +36,7 @@ static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
+    int res_slots;          // staging regions per epilogue warp of a residual cell (2 or 4)
     int m_base;         // first output row of this call within the tensors (a batch slice starts at image img0)
     int b_resident;     // the CTA's whole weight block stays in shared memory (its column block never changes)
     int oW, oH, kW, sX, sY, pL, pT, dX, dY;
@@ -83,10 +84,10 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     unsigned char* tiles = smem + (a.b_resident ? (size_t)num_kb * b_stage_bytes : 0);
     unsigned char* stage_out = tiles + (size_t)a.stages * stage_bytes;
     // output staging: one region per epilogue warp (32 rows x up to 64 bytes, swizzled for TMA)
-    // cells with a fused residual keep two regions per warp so that the next tile's residual can arrive early
-    const int regions_per_warp = RES ? 2 : 1;
+    // cells with a fused residual keep two or four regions per warp so that the residual of the next tiles arrives early
+    const int regions_per_warp = RES ? a.res_slots : 1;
     unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES * regions_per_warp);
-    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[2 * NUM_EPI_WARPS],
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[4 * NUM_EPI_WARPS],
     //       resident weights
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
@@ -94,8 +95,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const unsigned tempty0 = tfull0 + 16u;
     const unsigned pready0 = tempty0 + 16u;
     const unsigned rbar0 = pready0 + 16u;
-    const unsigned bfull = rbar0 + 8u * (2 * NUM_EPI_WARPS);
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 2 * NUM_EPI_WARPS + 2);
+    const unsigned bfull = rbar0 + 8u * (4 * NUM_EPI_WARPS);
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 4 * NUM_EPI_WARPS + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -114,7 +115,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
             mbar_init(pready0 + 8u * s, NUM_EPI_WARPS);
         }
-        for (int w = 0; w < 2 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
+        for (int w = 0; w < 4 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
         mbar_init(bfull, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -257,6 +258,13 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         int* par = epi_params;
         bool ok = true;
         int m_next = (int)blockIdx.x / a.num_n_tiles, n_next = (int)blockIdx.x % a.num_n_tiles;
+        // residual loads run ahead of the tiles: pf_* walk the same tile sequence, res_slots - 1 tiles in front
+        int pf_tile = blockIdx.x, pf_m = m_next, pf_n = n_next;
+        unsigned pf_it = 0;
+        const unsigned slot_shift = a.res_slots == 4 ? 2u : 1u;
+        const unsigned lookahead = a.res_slots == 4 ? 3u : 2u;
+        const unsigned my_regions = (unsigned)(stage_out - smem_raw) + (unsigned)((warp - EPI_WARP0) * REGION_BYTES * regions_per_warp);
+        const unsigned my_rbar = rbar0 + 32u * (unsigned)(warp - EPI_WARP0);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
             const int n_tile = n_next, m_tile = m_next;
             m_next += a.step_m;
@@ -291,19 +299,32 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int cbase = part * cols_per_warp;
             if (FAST) {
                 // fragment-layout epilogue with swizzled staging, TMA store and TMA residual load
-                const int ew = warp - EPI_WARP0;
                 EpiTile e;
                 e.tmem_acc = tmem_base + as * (unsigned)a.BN;
                 e.BN = a.BN; e.N = a.N; e.M = a.m_base + a.M; e.m0 = m0; e.n0 = n0;
                 e.wp = a.BN >> 2;
                 e.par_off = (unsigned)((unsigned char*)par - smem_raw);
-                e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * REGION_BYTES * regions_per_warp);
+                e.region_off = my_regions;
                 e.region_stride = RES ? REGION_BYTES : 0;
-                e.rbar = rbar0 + 16u * ew;
-                {
-                    const int nt = tile + (int)gridDim.x;
-                    e.next_m0 = nt < num_tiles ? a.m_base + m_next * BM : -1;
-                    e.next_n0 = nt < num_tiles ? n_next * a.BN : 0;
+                e.slot_shift = slot_shift;
+                e.rbar = my_rbar;
+                if (RES) {
+                    if (lane == 0) {
+                        // two regions: the previous tile's store has finished reading, its region takes the next
+                        // tile.  Four regions: the store before that one has, its region takes the tile two ahead,
+                        // and nobody waits on a store that has only just been issued.
+                        if (a.res_slots == 4) bulk_wait_read_1(); else bulk_wait_read_all();
+                        while (pf_it < acc_it + lookahead && pf_tile < num_tiles) {
+                            epi_issue_residual(&tmR, my_regions, REGION_BYTES, my_rbar, pf_it & ((1u << slot_shift) - 1u),
+                                               pf_n * a.BN + part * e.wp, a.m_base + pf_m * BM + quad * 32, a.N, e.M, e.wp);
+                            ++pf_it;
+                            pf_tile += (int)gridDim.x;
+                            pf_m += a.step_m;
+                            pf_n += a.step_n;
+                            if (pf_n >= a.num_n_tiles) { pf_n -= a.num_n_tiles; ++pf_m; }
+                        }
+                    }
+                    __syncwarp();
                 }
                 e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
                 e.abort_flag = abort_flag; e.status = a.status;
@@ -644,11 +665,12 @@ static CUtensorMapSwizzle swizzle_for(int bk)
 }
 
 // resident_b = bytes of the weight block kept in shared memory for the whole launch (0: weights ride the ring)
-static size_t igemm_smem_bytes(int stages, int BK, int BN, int with_res, size_t resident_b)
+// regions = staging regions per epilogue warp (1; 2 or 4 with a fused residual)
+static size_t igemm_smem_bytes(int stages, int BK, int BN, int regions, size_t resident_b)
 {
     return 1024 /*alignment slack*/ + resident_b + (size_t)stages * (BM + (resident_b ? 0 : BN)) * BK
-         + NUM_EPI_WARPS * REGION_BYTES * (with_res ? 2 : 1)
-         + (2 * stages + 8 + 2 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+         + NUM_EPI_WARPS * REGION_BYTES * regions
+         + (2 * stages + 8 + 4 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
@@ -695,16 +717,33 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     // a small-K layer are then activations only.
     const size_t wblock = (size_t)plan->taps * ((g.C + plan->BK - 1) / plan->BK) * plan->BK * plan->BN;
     plan->b_resident = (wblock <= 96 * 1024 && (num_n_tiles == 1 || num_sms > num_n_tiles)) ? 1 : 0;
-    int stages = 8;
-    const size_t resident = plan->b_resident ? wblock : 0;
-    while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, resident) > 226 * 1024) --stages;
-    if (plan->b_resident && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, resident) > 226 * 1024) {
+    const int num_kb = plan->taps * ((g.C + plan->BK - 1) / plan->BK);
+    auto depth = [&](int regions, size_t resident) {
+        int st = 8;
+        while (st > 2 && igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident) > 226 * 1024) --st;
+        return st;
+    };
+    auto fits = [&](int st, int regions, size_t resident) {
+        return igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident) <= 226 * 1024;
+    };
+    // A residual cell stages the residual of up to three tiles ahead when that leaves the ring deep enough
+    // (four regions per epilogue warp instead of two): its loads then have two tile times to arrive.
+    int regions = with_res ? 4 : 1;
+    size_t resident = plan->b_resident ? wblock : 0;
+    int stages = depth(regions, resident);
+    const int want = num_kb + 1 < 4 ? num_kb + 1 : 4;
+    if (with_res && (!fits(stages, regions, resident) || stages < want)) {
+        regions = 2;
+        stages = depth(regions, resident);
+    }
+    if (plan->b_resident && !fits(stages, regions, resident)) {
         plan->b_resident = 0;
-        stages = 8;
-        while (stages > 2 && igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, 0) > 226 * 1024) --stages;
+        resident = 0;
+        stages = depth(regions, 0);
     }
     plan->stages = stages;
-    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, with_res, plan->b_resident ? wblock : 0);
+    plan->res_slots = with_res ? regions : 0;
+    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, regions, resident);
 
     const CUtensorMapSwizzle swz = swizzle_for(plan->BK);
     CUresult rc;
@@ -799,6 +838,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.M = plan.M; a.N = plan.N; a.Cin = plan.Cin; a.taps = plan.taps; a.BK = plan.BK; a.BN = plan.BN;
     a.b_resident = plan.b_resident;
     a.stages = plan.stages; a.a_im2col = plan.a_im2col;
+    a.res_slots = plan.res_slots ? plan.res_slots : 2;
     a.oW = plan.oW; a.oH = plan.oH; a.kW = plan.kW; a.sX = plan.sX; a.sY = plan.sY;
     a.pL = plan.pL; a.pT = plan.pT; a.dX = plan.dX; a.dY = plan.dY;
     a.num_m_tiles = (plan.M + BM - 1) / BM;

@@ -123,6 +123,7 @@ struct IgemmPlan {
     int BN;               // tile N: 64, 128 or 256
     int stages;
     int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
+    int res_slots;        // fused residual: staging regions per epilogue warp (2 or 4), 0 without a residual
     int pair;             // large-K layer with 256-column tiles: CTAs take two 128-row tiles per weight slab
     CUtensorMap tmO32;    // output [M][N] bytes, box = 32 rows x 32 columns (the pair kernel's two-pass store)
     size_t pair_smem_bytes;

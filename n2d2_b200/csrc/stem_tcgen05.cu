@@ -295,10 +295,10 @@ stem_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             e.tmem_acc = tmem_base + as * (unsigned)a.BN;
             e.BN = a.BN; e.N = a.N; e.M = a.M; e.m0 = tile * SBM; e.n0 = 0;
             e.wp = a.BN >> 1;
-            e.next_m0 = -1; e.next_n0 = 0;
             e.par_off = (unsigned)((unsigned char*)par - smem_raw);
             e.region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
             e.region_stride = 0;
+            e.slot_shift = 0;
             e.rbar = 0;
             e.tfull = tfull0 + 8u * as; e.tfull_parity = aph; e.tempty = tempty0 + 8u * as;
             e.abort_flag = abort_flag; e.status = a.status;

@@ -224,6 +224,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, unsigned src
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until the bulk stores of this thread have finished *reading* shared memory
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -455,11 +456,11 @@ struct EpiTile {
     unsigned tmem_acc;      // TMEM address of the accumulator stage (lane 0, first column)
     int BN, N, M, m0, n0;
     int wp;                 // columns per warp: BN / (epilogue warps per TMEM quadrant); 64, 32 or 16
-    int next_m0, next_n0;   // the tile this warp handles next (next_m0 < 0: none): its residual is prefetched
     unsigned par_off;       // staged per-channel constants of this column block (byte offset in dynamic shared memory)
     unsigned region_off;    // this warp's staging region(s) (1024-byte aligned; byte offset in dynamic shared memory)
-    unsigned region_stride; // distance to the second region (residual cells double-buffer), 0 = one region
-    unsigned rbar;          // this warp's residual-arrival mbarriers (two, 8 bytes apart)
+    unsigned region_stride; // distance between the regions of a residual cell, 0 = one region
+    unsigned slot_shift;    // residual cells: log2 of the number of regions (1 or 2)
+    unsigned rbar;          // this warp's residual-arrival mbarriers (one per region, 8 bytes apart)
     unsigned tfull, tfull_parity, tempty;
     volatile int* abort_flag;
     int* status;
@@ -470,9 +471,7 @@ struct EpiTile {
 
 // Per-warp state carried from tile to tile.
 struct EpiState {
-    unsigned t = 0;          // tiles handled so far (selects the staging region of a residual cell)
-    unsigned used0 = 0, used1 = 0;   // completed waits per residual barrier (its parity)
-    bool prefetched = false; // the current tile's residual load was issued during the previous tile
+    unsigned t = 0;          // tiles handled so far (selects the staging region and barrier phase of a residual cell)
     unsigned rb[4] = {0, 0, 0, 0};   // frag_rowbase of this lane for the warp's row width (set once by the kernel)
 };
 
@@ -496,6 +495,21 @@ __device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int 
     }
 }
 
+// One lane starts the residual load of the warp's slice (32 rows at gy, wp columns at gx) of some tile into
+// region `slot`.  A slice outside the tensor arrives on the barrier without a load, so that every tile completes
+// one phase per region and the waits need no bookkeeping.
+__device__ __forceinline__ void epi_issue_residual(const CUtensorMap* tmR, unsigned region_off0, unsigned region_stride,
+                                                   unsigned rbar, unsigned slot, int gx, int gy, int N, int M, int wp)
+{
+    const unsigned bar = rbar + 8u * slot;
+    if (gx < N && gy < M) {
+        mbar_expect_tx(bar, (unsigned)(32 * wp));
+        tma_load_2d(smem_u32(dyn_smem() + region_off0 + slot * region_stride), tmR, bar, gx, gy);
+    } else {
+        mbar_arrive(bar);
+    }
+}
+
 template <bool RES, bool CLAMP, bool DP>
 __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
                                                    int cp, int lane, EpiState& st)
@@ -504,34 +518,18 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
     const int cbase = cp * wp;
     const int gx = e.n0 + cbase, gy = e.m0 + quad * 32;
     const bool active = gx < e.N && gy < e.M;
-    const unsigned b = (RES && e.region_stride) ? (st.t & 1u) : 0u;
+    // a residual cell cycles through its staging regions; the caller issued this tile's residual load
+    // (epi_issue_residual) into region t mod slots, after the store that last used the region had drained
+    const unsigned b = RES ? (st.t & ((1u << e.slot_shift) - 1u)) : 0u;
     const unsigned region_off = e.region_off + b * e.region_stride;
     const unsigned region = smem_u32(dyn_smem() + region_off);
-    bool next_issued = false;   // same decision on every lane: does the next tile's residual travel early?
-    if (RES && e.region_stride && e.next_m0 >= 0)
-        next_issued = e.next_n0 + cbase < e.N && e.next_m0 + quad * 32 < e.M;
-    if (lane == 0) {
-        bulk_wait_read_all();   // earlier stores have finished reading both regions
-        if (RES) {
-            if (active && !st.prefetched) {
-                mbar_expect_tx(e.rbar + 8u * b, (unsigned)(32 * wp));
-                tma_load_2d(region, tmR, e.rbar + 8u * b, gx, gy);
-            }
-            // the next tile's slice of the residual travels while this tile is computed
-            if (next_issued) {
-                const unsigned nb = b ^ 1u;
-                mbar_expect_tx(e.rbar + 8u * nb, (unsigned)(32 * wp));
-                tma_load_2d(smem_u32(dyn_smem() + e.region_off + nb * e.region_stride), tmR, e.rbar + 8u * nb,
-                            e.next_n0 + cbase, e.next_m0 + quad * 32);
-            }
-        }
+    if (!RES) {
+        if (lane == 0) bulk_wait_read_all();   // the earlier store has finished reading the region
+        __syncwarp();
     }
-    __syncwarp();
-    if (RES) st.prefetched = next_issued;
     if (!mbar_wait_warp(e.tfull, e.tfull_parity, e.abort_flag, e.status, 4, lane)) return false;
-    if (RES && active) {
-        if (!mbar_wait_warp(e.rbar + 8u * b, (b ? st.used1 : st.used0) & 1u, e.abort_flag, e.status, 7, lane)) return false;
-        if (b) ++st.used1; else ++st.used0;
+    if (RES) {
+        if (!mbar_wait_warp(e.rbar + 8u * b, (st.t >> e.slot_shift) & 1u, e.abort_flag, e.status, 7, lane)) return false;
     }
     tc_fence_after();
     if (active) {
