@@ -76,12 +76,17 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     // try_wait suspends the thread in hardware until the phase completes or a time limit passes, so a
     // waiting warp leaves the issue slots to the warps that work
     const unsigned long long t0 = globaltimer_ns();
+    unsigned rounds = 0;
     while (true) {
-        // a few polls per look at the abort flag and the clock: each failed try_wait has already slept in hardware
+        // a few polls per look at the abort flag and the clock
 #pragma unroll
         for (int i = 0; i < 4; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
+        // A failed try_wait comes back within tens of cycles, so a long wait (an issuer whose accumulators the
+        // epilogue still holds, an epilogue warp whose residual is still on its way from DRAM) would fill the issue
+        // slots of the warps that work: after a short tight phase the waiter sleeps between polls.
+        if (++rounds > 8) __nanosleep(128);
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
