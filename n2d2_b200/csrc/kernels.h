@@ -98,6 +98,8 @@ struct PatchPlan {
     int patch_bytes;      // bytes of one patch load
     int patch_alloc;      // bytes reserved per patch buffer
     int b_stream;         // weights stream through a ring (too large to stay resident)
+    int bring;            // slots of that ring (one filter tap each)
+    int stage_cols;       // columns an epilogue warp stages per pass
     int in_unsigned;
     int num_sms;
     size_t smem_bytes;

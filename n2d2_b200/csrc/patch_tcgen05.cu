@@ -26,7 +26,8 @@ static constexpr int P_SLOTS = 4;            // TMEM accumulators = epilogue gro
 static constexpr int P_ISSUERS = 2;           // MMA-issuing warps: tiles alternate between them
 static constexpr int P_EPI_WARP0 = 1 + P_ISSUERS;
 static constexpr int P_THREADS = 32 * (P_EPI_WARP0 + P_EPI_WARPS);
-static constexpr int P_BRING = 4;             // weight ring slots (one filter tap each) when the weights stream
+static constexpr int P_BRING_MIN = 4;         // weight ring slots (one filter tap each) when the weights stream:
+static constexpr int P_BRING_MAX = 8;         // as many as shared memory holds between these two
 
 struct PatchArgs {
     int B, oH, oW, N, BN, C;
@@ -38,6 +39,8 @@ struct PatchArgs {
     int patch_bytes;        // bytes one patch load delivers (the full TMA box)
     int patch_alloc;        // bytes reserved per patch buffer (box + the rows a last tile may read past it)
     int b_stream;           // weights too large to stay resident: their tap blocks stream through a ring
+    int bring;              // slots of that ring
+    int stage_cols;         // columns an epilogue warp stages per pass (BN, or 32 to leave room for the ring)
     unsigned rcp_Wp;        // ceil(2^32 / Wp)
     unsigned idesc, tmem_cols;
     void* out;
@@ -48,16 +51,17 @@ struct PatchArgs {
     int wide;               // 64-bit first rescale (see EF_WIDE)
 };
 
+// Columns [c0, c0 + ncols) of a warp's 32 accumulator rows into its staging region (rows of ncols bytes)
 template <bool CLAMP, int EF>
-__device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int BN, int lane)
+__device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int c0, int ncols, int lane)
 {
     unsigned rb[4];
-    frag_rowbase(rb, BN, lane);
+    frag_rowbase(rb, ncols, lane);
 #pragma unroll 1
-    for (int cb = 0; cb < BN; cb += 32) {
+    for (int cb = 0; cb < ncols; cb += 32) {
         unsigned va[16], vb[16];
-        tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
-        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, cb, region_off, rb, cb, lane, 0, 0, 0u);
+        tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(c0 + cb), va, vb);
+        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, c0 + cb, region_off, rb, cb, lane, 0, 0, 0u);
     }
 }
 
@@ -78,6 +82,22 @@ __device__ __forceinline__ void issue_tile(unsigned d_tmem, unsigned a_lo, unsig
                                desc_hi, idesc, (ky | kx | k) ? 1u : 0u);
 }
 
+// The MMAs of one filter tap of one tile (C / 32 K steps), unrolled for the channel counts the kernel takes
+template <int KS>
+__device__ __forceinline__ void issue_tap_n(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc, unsigned first)
+{
+    tc_mma_i8_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+#pragma unroll
+    for (int k = 1; k < KS; ++k) tc_mma_i8_lohi(d_tmem, a_lo + 2u * k, b_lo + 2u * k, desc_hi, idesc, 1u);
+}
+__device__ __forceinline__ void issue_tap(int ksteps, unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
+                                          unsigned first)
+{
+    if (ksteps == 4) issue_tap_n<4>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+    else if (ksteps == 2) issue_tap_n<2>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+    else issue_tap_n<1>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+}
+
 // SHAPE: 0 = any filter (loops), 1 / 2 / 3 = 3x3 filter with 32 / 64 / 128 channels (unrolled issue)
 template <bool CLAMP, int SHAPE>
 __global__ void __launch_bounds__(P_THREADS, 1)
@@ -87,20 +107,20 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int taps = a.taps_y * a.taps_x;
     const int b_tap_bytes = a.BN * a.C;
-    unsigned char* res_b = smem;                                              // [taps][BN][C], or a ring of P_BRING taps
-    unsigned char* patch0 = smem + (((size_t)(a.b_stream ? P_BRING : taps) * b_tap_bytes + 1023) & ~(size_t)1023);
-    unsigned char* stage_out = patch0 + 2 * (size_t)a.patch_alloc;             // [16 warps][32 rows][BN]
-    const int region_bytes = 32 * a.BN;
+    unsigned char* res_b = smem;                                              // [taps][BN][C], or a ring of a.bring taps
+    unsigned char* patch0 = smem + (((size_t)(a.b_stream ? a.bring : taps) * b_tap_bytes + 1023) & ~(size_t)1023);
+    unsigned char* stage_out = patch0 + 2 * (size_t)a.patch_alloc;             // [16 warps][32 rows][stage_cols]
+    const int region_bytes = 32 * a.stage_cols;
     unsigned long long* bars = (unsigned long long*)(stage_out + (size_t)P_EPI_WARPS * region_bytes);
-    // bars: patch_full[2], patch_empty[2], tmem_full[4], tmem_empty[4], weights, (spare), ring_full[4], ring_empty[4]
+    // bars: patch_full[2], patch_empty[2], tmem_full[4], tmem_empty[4], weights, (spare), ring_full[8], ring_empty[8]
     const unsigned pfull0 = smem_u32(bars);
     const unsigned pempty0 = pfull0 + 16u;
     const unsigned tfull0 = pempty0 + 16u;
     const unsigned tempty0 = tfull0 + 8u * P_SLOTS;
     const unsigned bfull = tempty0 + 8u * P_SLOTS;
     const unsigned rfull0 = bfull + 16u;
-    const unsigned rempty0 = rfull0 + 8u * P_BRING;
-    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * P_SLOTS + 2 + 2 * P_BRING);
+    const unsigned rempty0 = rfull0 + 8u * P_BRING_MAX;
+    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * P_SLOTS + 2 + 2 * P_BRING_MAX);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256]
 
@@ -118,7 +138,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             mbar_init(tempty0 + 8u * s, 4);
         }
         mbar_init(bfull, 1);
-        for (int r = 0; r < P_BRING; ++r) {
+        for (int r = 0; r < P_BRING_MAX; ++r) {
             mbar_init(rfull0 + 8u * r, 1);
             mbar_init(rempty0 + 8u * r, P_ISSUERS);
         }
@@ -170,7 +190,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                         if (!mbar_wait(rempty0 + 8u * rs, rph ^ 1u, abort_flag, a.status, 5)) { ok = false; break; }
                         mbar_expect_tx(rfull0 + 8u * rs, (unsigned)b_tap_bytes);
                         tma_load_2d(smem_u32(res_b + (size_t)rs * b_tap_bytes), &tmB, rfull0 + 8u * rs, t * a.C, 0);
-                        if (++rs == P_BRING) { rs = 0; rph ^= 1u; }
+                        if (++rs == a.bring) { rs = 0; rph ^= 1u; }
                     }
                     if (!ok) break;
                 }
@@ -204,33 +224,34 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 tc_fence_after();
                 unsigned a_lo = patch_lo + pb * (unsigned)(a.patch_alloc >> 4);
                 if (a.b_stream) {
-                    // At most P_ISSUERS tiles per item: this thread owns tile `me` and walks the taps as their
-                    // weights arrive; a thread without a tile still releases every ring slot.
-                    const bool mine = (int)me < T;
-                    const unsigned myseq = seq + me;
-                    const unsigned slot = myseq & (P_SLOTS - 1), sph = (myseq / P_SLOTS) & 1u;
-                    if (mine && !mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    // At most P_SLOTS tiles per item, each with its own accumulator: this thread owns tiles `me` and
+                    // `me + P_ISSUERS` and walks the taps as their weights arrive, so one pass of the weights serves
+                    // the whole band; a thread without a tile still releases every ring slot.
+                    const bool mine0 = (int)me < T, mine1 = (int)me + P_ISSUERS < T;
+                    const unsigned seq0 = seq + me, seq1 = seq0 + P_ISSUERS;
+                    const unsigned slot0 = seq0 & (P_SLOTS - 1), slot1 = seq1 & (P_SLOTS - 1);
+                    if (mine0 && !mbar_wait(tempty0 + 8u * slot0, ((seq0 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    if (mine1 && !mbar_wait(tempty0 + 8u * slot1, ((seq1 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
-                    const unsigned d_tmem = tmem_base + slot * (unsigned)a.BN;
+                    const unsigned d0 = tmem_base + slot0 * (unsigned)a.BN, d1 = tmem_base + slot1 * (unsigned)a.BN;
+                    const unsigned tile2 = (unsigned)P_ISSUERS * tile_step;
                     unsigned ar = a_lo + me * tile_step, first = 0;
                     for (int ky = 0; ky < a.taps_y && ok; ++ky, ar += row_step) {
                         unsigned ac = ar;
                         for (int kx = 0; kx < a.taps_x; ++kx, ac += col_step) {
                             if (!mbar_wait(rfull0 + 8u * rs, rph, abort_flag, a.status, 6)) { ok = false; break; }
                             tc_fence_after();
-                            if (mine) {
-                                const unsigned bt = res_b_lo + (unsigned)rs * btap;
-                                for (int k = 0; k < ksteps; ++k) {
-                                    tc_mma_i8_lohi(d_tmem, ac + 2u * k, bt + 2u * k, desc_hi, a.idesc, first);
-                                    first = 1u;
-                                }
-                            }
+                            const unsigned bt = res_b_lo + (unsigned)rs * btap;
+                            if (mine0) issue_tap(ksteps, d0, ac, bt, desc_hi, a.idesc, first);
+                            if (mine1) issue_tap(ksteps, d1, ac + tile2, bt, desc_hi, a.idesc, first);
+                            first = 1u;
                             tc_commit(rempty0 + 8u * rs);
-                            if (++rs == P_BRING) { rs = 0; rph ^= 1u; }
+                            if (++rs == a.bring) { rs = 0; rph ^= 1u; }
                         }
                     }
                     if (!ok) break;
-                    if (mine) tc_commit(tfull0 + 8u * slot);
+                    if (mine0) tc_commit(tfull0 + 8u * slot0);
+                    if (mine1) tc_commit(tfull0 + 8u * slot1);
                     seq += (unsigned)T;
                     tc_commit(pempty0 + 8u * pb);
                     band += step_b;
@@ -275,7 +296,8 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
         const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
-        const unsigned swz_mask = (unsigned)(a.BN / 16 - 1);
+        const int SC = a.stage_cols;
+        const unsigned swz_mask = (unsigned)(SC / 16 - 1);
         unsigned seq = 0;
         int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
         const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
@@ -289,46 +311,55 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
-                if (a.wide) {
-                    if (a.out_unsigned) patch_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
-                    else patch_drain<false, EF_WIDE>(tbase, par_off, region_off, a.BN, lane);
-                } else if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
-                else patch_drain<CLAMP, 0>(tbase, par_off, region_off, a.BN, lane);
-                // the accumulator is drained: hand it back, then copy this warp's 32 rows out
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8u * group);
-                // Copy the warp's 32 rows out in 16-byte units, consecutive lanes on consecutive units of a pixel and
-                // then on the next pixel: a store instruction covers whole contiguous runs of the NHWC output.
-                const int nch = a.N >> 4;                       // 16-byte units per pixel
                 const unsigned pix0 = (unsigned)(t * PBM + quad * 32);
-                if ((nch & (nch - 1)) == 0) {
-                    const int lg = 31 - __clz(nch);
-                    for (int u = lane; u < 32 * nch; u += 32) {
-                        const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
-                        const unsigned p = pix0 + r;            // position within the band
+                // stage_cols columns per pass: drained into the staging region, then copied out
+#pragma unroll 1
+                for (int c0 = 0; c0 < a.BN; c0 += SC) {
+                    if (a.wide) {
+                        if (a.out_unsigned) patch_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, c0, SC, lane);
+                        else patch_drain<false, EF_WIDE>(tbase, par_off, region_off, c0, SC, lane);
+                    } else if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, c0, SC, lane);
+                    else patch_drain<CLAMP, 0>(tbase, par_off, region_off, c0, SC, lane);
+                    if (c0 + SC >= a.BN) {
+                        // the accumulator is drained: hand it back before the last copy
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty0 + 8u * group);
+                    } else {
+                        __syncwarp();
+                    }
+                    // Copy the warp's 32 rows out in 16-byte units, consecutive lanes on consecutive units of a pixel and
+                    // then on the next pixel: a store instruction covers whole contiguous runs of the NHWC output.
+                    const int left = a.N - c0;
+                    const int nch = (left < SC ? left : SC) >> 4;   // 16-byte units per pixel in this pass
+                    if (nch > 0 && (nch & (nch - 1)) == 0) {
+                        const int lg = 31 - __clz(nch);
+                        for (int u = lane; u < 32 * nch; u += 32) {
+                            const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
+                            const unsigned p = pix0 + r;            // position within the band
+                            const unsigned yy = __umulhi(p, a.rcp_Wp);
+                            const unsigned x = p - yy * (unsigned)a.Wp;
+                            if (x < (unsigned)a.oW && yy < (unsigned)rows) {
+                                uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N) + c0;
+                                const unsigned ro = r * (unsigned)SC;
+                                const unsigned xm = (ro >> 7) & swz_mask;
+                                *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
+                            }
+                        }
+                    } else if (nch > 0) {
+                        const unsigned p = pix0 + (unsigned)lane;
                         const unsigned yy = __umulhi(p, a.rcp_Wp);
                         const unsigned x = p - yy * (unsigned)a.Wp;
                         if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
-                            const unsigned ro = r * (unsigned)a.BN;
+                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N) + c0;
+                            const unsigned ro = (unsigned)(lane * SC);
                             const unsigned xm = (ro >> 7) & swz_mask;
-                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
+                            for (int c = 0; c < nch; ++c)
+                                *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
                         }
                     }
-                } else {
-                    const unsigned p = pix0 + (unsigned)lane;
-                    const unsigned yy = __umulhi(p, a.rcp_Wp);
-                    const unsigned x = p - yy * (unsigned)a.Wp;
-                    if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                        uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
-                        const unsigned ro = (unsigned)(lane * a.BN);
-                        const unsigned xm = (ro >> 7) & swz_mask;
-                        for (int c = 0; c < nch; ++c)
-                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
-                    }
+                    __syncwarp();   // the region is rewritten by the next pass or tile
                 }
-                __syncwarp();   // the region is rewritten by the next tile of this group
             }
             n += step_n;
             band += step_b;
@@ -350,16 +381,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// weights of up to this size stay resident; larger ones stream tap by tap through a ring of P_BRING blocks
+// weights of up to this size stay resident; larger ones stream tap by tap through a ring of `bring` blocks, and
+// the epilogue then stages 32 columns per pass so that the ring can be deep: its loads cross the L2 with a
+// latency of thousands of cycles, and what is in flight bounds what arrives
 static constexpr size_t P_RESIDENT_MAX = 96 * 1024;
 static bool patch_streams(int taps, int C, int BN) { return (size_t)taps * BN * C > P_RESIDENT_MAX; }
 
-static size_t patch_smem_bytes(int taps, int C, int BN, int patch_alloc)
+static int patch_stage_cols(int taps, int C, int BN) { return patch_streams(taps, C, BN) ? 32 : BN; }
+
+static size_t patch_smem_bytes(int taps, int C, int BN, int patch_alloc, int bring = P_BRING_MIN)
 {
-    const int blocks = patch_streams(taps, C, BN) ? P_BRING : taps;
+    const int blocks = patch_streams(taps, C, BN) ? bring : taps;
     const size_t b = (((size_t)blocks * BN * C) + 1023) & ~(size_t)1023;
-    return 1024 + b + 2 * (size_t)patch_alloc + (size_t)P_EPI_WARPS * 32 * BN + (4 + 2 * P_SLOTS + 2 + 2 * P_BRING) * 8 + 32
-         + FAST_NP * 256 * 4 + 64;
+    return 1024 + b + 2 * (size_t)patch_alloc + (size_t)P_EPI_WARPS * 32 * patch_stage_cols(taps, C, BN)
+         + (4 + 2 * P_SLOTS + 2 + 2 * P_BRING_MAX) * 8 + 32 + FAST_NP * 256 * 4 + 64;
 }
 
 // bytes a patch buffer must hold for bands of R rows: the tiles of a band read 128-row operands that start
@@ -414,8 +449,9 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     for (int R = 1; R <= g.oH; ++R) {
         if (R + (g.kH - 1) * g.dY > 256) break;
         if (patch_smem_bytes(taps, g.C, plan->BN, patch_alloc_bytes(g, plan->Wp, R)) > 226 * 1024) break;
-        // streamed weights: every tile of a band accumulates while the taps pass, one tile per issuing warp
-        if (plan->b_stream && (R * plan->Wp + PBM - 1) / PBM > P_ISSUERS) break;
+        // streamed weights: every tile of a band accumulates while the taps pass, so a band has at most as many
+        // tiles as there are accumulators
+        if (plan->b_stream && (R * plan->Wp + PBM - 1) / PBM > P_SLOTS) break;
         const int full = g.oH / R, rest = g.oH % R;
         const long long tiles = (long long)full * ((R * plan->Wp + PBM - 1) / PBM)
                               + (rest ? (rest * plan->Wp + PBM - 1) / PBM : 0);
@@ -427,7 +463,12 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     const int box_rows = best_R + (g.kH - 1) * g.dY;
     plan->patch_bytes = box_rows * plan->Wp * g.C;
     plan->patch_alloc = patch_alloc_bytes(g, plan->Wp, best_R);
-    plan->smem_bytes = patch_smem_bytes(taps, g.C, plan->BN, plan->patch_alloc);
+    plan->stage_cols = patch_stage_cols(taps, g.C, plan->BN);
+    plan->bring = P_BRING_MIN;
+    while (plan->b_stream && plan->bring < P_BRING_MAX
+           && patch_smem_bytes(taps, g.C, plan->BN, plan->patch_alloc, plan->bring + 1) <= 226 * 1024)
+        ++plan->bring;
+    plan->smem_bytes = patch_smem_bytes(taps, g.C, plan->BN, plan->patch_alloc, plan->bring);
     const CUtensorMapSwizzle swz = g.C == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                               : (g.C == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUresult rc;
@@ -466,6 +507,8 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, c
     a.n_base = n_base;
     a.patch_bytes = plan.patch_bytes; a.patch_alloc = plan.patch_alloc;
     a.b_stream = plan.b_stream;
+    a.bring = plan.bring;
+    a.stage_cols = plan.stage_cols;
     a.rcp_Wp = (unsigned)(((1ull << 32) + (unsigned)plan.Wp - 1) / (unsigned)plan.Wp);
     a.idesc = (2u << 4) | ((plan.in_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
             | ((unsigned)(PBM >> 4) << 24);

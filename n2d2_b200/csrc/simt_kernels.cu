@@ -406,6 +406,30 @@ __global__ void pool_max_row_kernel(const uint8_t* __restrict__ in, PoolGeom g, 
             const int kx_lo = ix0 < 0 ? -ix0 : 0;
             const int kx_hi = (g.W - ix0) < g.pW ? (g.W - ix0) : g.pW;
             uint4 m = make_uint4(0u, 0u, 0u, 0u);
+            if (g.pH == 3 && g.pW == 3 && ky_lo == 0 && ky_hi == 3 && kx_lo == 0 && kx_hi == 3) {
+                // a whole 3x3 window: nine independent loads in flight, then the maxima (the general loop below
+                // would wait for each load in turn)
+                const uint8_t* p = img + ((size_t)iy0 * g.W + ix0) * g.C + c16 * 16;
+                const size_t rs = (size_t)g.W * g.C;
+                uint4 x[9];
+#pragma unroll
+                for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+                    for (int kx = 0; kx < 3; ++kx) x[ky * 3 + kx] = __ldg((const uint4*)(p + ky * rs + (size_t)kx * g.C));
+                m = x[0];
+#pragma unroll
+                for (int i = 1; i < 9; ++i) {
+                    if (UNSIGNED) {
+                        m.x = __vmaxu4(m.x, x[i].x); m.y = __vmaxu4(m.y, x[i].y);
+                        m.z = __vmaxu4(m.z, x[i].z); m.w = __vmaxu4(m.w, x[i].w);
+                    } else {
+                        m.x = __vmaxs4(m.x, x[i].x); m.y = __vmaxs4(m.y, x[i].y);
+                        m.z = __vmaxs4(m.z, x[i].z); m.w = __vmaxs4(m.w, x[i].w);
+                    }
+                }
+                *(uint4*)(orow + (size_t)t * 16) = m;
+                continue;
+            }
             bool first = true;
             for (int ky = ky_lo; ky < ky_hi; ++ky) {
                 const uint8_t* p = img + ((size_t)(iy0 + ky) * g.W + ix0) * g.C + c16 * 16;

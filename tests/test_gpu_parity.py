@@ -16,7 +16,9 @@ PATCH_CASES = [(64, 56, 56, 64, 3, 1, 1, True), (64, 20, 17, 64, 3, 1, 1, True),
                (32, 40, 40, 96, 3, 1, 1, True),
                # weights beyond the resident limit: the tap blocks stream through a ring
                (128, 28, 28, 128, 3, 1, 1, True), (64, 14, 14, 128, 5, 2, 1, True), (128, 9, 33, 96, 3, 1, 1, False),
-               (128, 5, 100, 96, 3, 1, 1, True)]
+               (128, 5, 100, 96, 3, 1, 1, True),
+               # streamed weights, bands of three and four tiles (one weight pass serves the whole band)
+               (64, 30, 14, 128, 5, 2, 1, True), (128, 24, 28, 128, 3, 1, 1, False)]
 
 
 @pytest.mark.parametrize('case', PATCH_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_p%d_d%d' % c[:7])
