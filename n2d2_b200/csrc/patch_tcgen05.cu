@@ -23,7 +23,7 @@ namespace n2d2b {
 static constexpr int PBM = 128;
 static constexpr int P_EPI_WARPS = 16;
 static constexpr int P_SLOTS = 4;            // TMEM accumulators = epilogue groups
-static constexpr int P_ISSUERS = 2;           // MMA-issuing warps: tiles alternate between them
+static constexpr int P_ISSUERS = 4;           // MMA-issuing warps: tiles alternate between them
 static constexpr int P_EPI_WARP0 = 1 + P_ISSUERS;
 static constexpr int P_THREADS = 32 * (P_EPI_WARP0 + P_EPI_WARPS);
 static constexpr int P_BRING_MIN = 4;         // weight ring slots (one filter tap each) when the weights stream:
