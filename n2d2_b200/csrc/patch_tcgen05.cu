@@ -70,7 +70,7 @@ __device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, un
 // short MMA (one of 128 x 64 x 32 takes about 60 cycles of the tensor pipe) would cost more than the MMA.
 template <int KH, int KW, int KS>
 __device__ __forceinline__ void issue_tile(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
-                                           unsigned row_step, unsigned col_step, unsigned btap)
+                                           unsigned row_step, unsigned col_step, unsigned btap, unsigned issue)
 {
 #pragma unroll
     for (int ky = 0; ky < KH; ++ky)
@@ -78,24 +78,25 @@ __device__ __forceinline__ void issue_tile(unsigned d_tmem, unsigned a_lo, unsig
         for (int kx = 0; kx < KW; ++kx)
 #pragma unroll
             for (int k = 0; k < KS; ++k)
-                tc_mma_i8_lohi(d_tmem, a_lo + ky * row_step + kx * col_step + 2u * k, b_lo + (ky * KW + kx) * btap + 2u * k,
-                               desc_hi, idesc, (ky | kx | k) ? 1u : 0u);
+                tc_mma_i8_lohi_p(d_tmem, a_lo + ky * row_step + kx * col_step + 2u * k, b_lo + (ky * KW + kx) * btap + 2u * k,
+                                 desc_hi, idesc, (ky | kx | k) ? 1u : 0u, issue);
 }
 
 // The MMAs of one filter tap of one tile (C / 32 K steps), unrolled for the channel counts the kernel takes
 template <int KS>
-__device__ __forceinline__ void issue_tap_n(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc, unsigned first)
+__device__ __forceinline__ void issue_tap_n(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc, unsigned first,
+                                            unsigned issue)
 {
-    tc_mma_i8_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+    tc_mma_i8_lohi_p(d_tmem, a_lo, b_lo, desc_hi, idesc, first, issue);
 #pragma unroll
-    for (int k = 1; k < KS; ++k) tc_mma_i8_lohi(d_tmem, a_lo + 2u * k, b_lo + 2u * k, desc_hi, idesc, 1u);
+    for (int k = 1; k < KS; ++k) tc_mma_i8_lohi_p(d_tmem, a_lo + 2u * k, b_lo + 2u * k, desc_hi, idesc, 1u, issue);
 }
 __device__ __forceinline__ void issue_tap(int ksteps, unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
-                                          unsigned first)
+                                          unsigned first, unsigned issue)
 {
-    if (ksteps == 4) issue_tap_n<4>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
-    else if (ksteps == 2) issue_tap_n<2>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
-    else issue_tap_n<1>(d_tmem, a_lo, b_lo, desc_hi, idesc, first);
+    if (ksteps == 4) issue_tap_n<4>(d_tmem, a_lo, b_lo, desc_hi, idesc, first, issue);
+    else if (ksteps == 2) issue_tap_n<2>(d_tmem, a_lo, b_lo, desc_hi, idesc, first, issue);
+    else issue_tap_n<1>(d_tmem, a_lo, b_lo, desc_hi, idesc, first, issue);
 }
 
 // SHAPE: 0 = any filter (loops), 1 / 2 / 3 = 3x3 filter with 32 / 64 / 128 channels (unrolled issue)
@@ -203,9 +204,11 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         // ------------------------------------------------------------------ MMA issuers
         // Issuing a tile costs one thread about 100 cycles per MMA, the tensor pipe about 60: two threads take
         // alternate tiles (each tile has its own accumulator, so their MMAs are independent).
-        const unsigned me = (unsigned)(warp - 1);
-        if (lane == 0 && (int)blockIdx.x < items) {
-            bool ok = a.b_stream ? true : mbar_wait(bfull, 0, abort_flag, a.status, 8);
+        // every lane of the warp runs the loop; `issue` selects the lane whose MMAs and commits take effect
+        const unsigned me = (unsigned)__shfl_sync(0xffffffffu, warp - 1, 0);
+        const unsigned issue = lane == 0 ? 1u : 0u;
+        if ((int)blockIdx.x < items) {
+            bool ok = a.b_stream ? true : mbar_wait_uniform(bfull, 0, abort_flag, a.status, 8);
             const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.C) >> 32);
             const unsigned res_b_lo = (smem_u32(res_b) & 0x3ffffu) >> 4, patch_lo = (smem_u32(patch0) & 0x3ffffu) >> 4;
             const int ksteps = a.C / 32;
@@ -220,7 +223,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 const int T = band_tiles(band);
-                if (!mbar_wait(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
+                if (!mbar_wait_uniform(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
                 tc_fence_after();
                 unsigned a_lo = patch_lo + pb * (unsigned)(a.patch_alloc >> 4);
                 if (a.b_stream) {
@@ -230,8 +233,8 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                     const bool mine0 = (int)me < T, mine1 = (int)me + P_ISSUERS < T;
                     const unsigned seq0 = seq + me, seq1 = seq0 + P_ISSUERS;
                     const unsigned slot0 = seq0 & (P_SLOTS - 1), slot1 = seq1 & (P_SLOTS - 1);
-                    if (mine0 && !mbar_wait(tempty0 + 8u * slot0, ((seq0 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
-                    if (mine1 && !mbar_wait(tempty0 + 8u * slot1, ((seq1 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    if (mine0 && !mbar_wait_uniform(tempty0 + 8u * slot0, ((seq0 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    if (mine1 && !mbar_wait_uniform(tempty0 + 8u * slot1, ((seq1 / P_SLOTS) & 1u) ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
                     const unsigned d0 = tmem_base + slot0 * (unsigned)a.BN, d1 = tmem_base + slot1 * (unsigned)a.BN;
                     const unsigned tile2 = (unsigned)P_ISSUERS * tile_step;
@@ -239,21 +242,21 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                     for (int ky = 0; ky < a.taps_y && ok; ++ky, ar += row_step) {
                         unsigned ac = ar;
                         for (int kx = 0; kx < a.taps_x; ++kx, ac += col_step) {
-                            if (!mbar_wait(rfull0 + 8u * rs, rph, abort_flag, a.status, 6)) { ok = false; break; }
+                            if (!mbar_wait_uniform(rfull0 + 8u * rs, rph, abort_flag, a.status, 6)) { ok = false; break; }
                             tc_fence_after();
                             const unsigned bt = res_b_lo + (unsigned)rs * btap;
-                            if (mine0) issue_tap(ksteps, d0, ac, bt, desc_hi, a.idesc, first);
-                            if (mine1) issue_tap(ksteps, d1, ac + tile2, bt, desc_hi, a.idesc, first);
+                            if (mine0) issue_tap(ksteps, d0, ac, bt, desc_hi, a.idesc, first, issue);
+                            if (mine1) issue_tap(ksteps, d1, ac + tile2, bt, desc_hi, a.idesc, first, issue);
                             first = 1u;
-                            tc_commit(rempty0 + 8u * rs);
+                            tc_commit_p(rempty0 + 8u * rs, issue);
                             if (++rs == a.bring) { rs = 0; rph ^= 1u; }
                         }
                     }
                     if (!ok) break;
-                    if (mine0) tc_commit(tfull0 + 8u * slot0);
-                    if (mine1) tc_commit(tfull0 + 8u * slot1);
+                    if (mine0) tc_commit_p(tfull0 + 8u * slot0, issue);
+                    if (mine1) tc_commit_p(tfull0 + 8u * slot1, issue);
                     seq += (unsigned)T;
-                    tc_commit(pempty0 + 8u * pb);
+                    tc_commit_p(pempty0 + 8u * pb, issue);
                     band += step_b;
                     if (band >= a.bands) band -= a.bands;
                     continue;
@@ -261,29 +264,29 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                 for (int t = 0; t < T; ++t, ++seq, a_lo += tile_step) {
                     if ((seq & (P_ISSUERS - 1)) != me) continue;
                     const unsigned slot = seq & (P_SLOTS - 1), sph = (seq / P_SLOTS) & 1u;
-                    if (!mbar_wait(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+                    if (!mbar_wait_uniform(tempty0 + 8u * slot, sph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
                     const unsigned d_tmem = tmem_base + slot * (unsigned)a.BN;
                     // The operand of a tap starts at an arbitrary pixel row.  The swizzle is a function of the
                     // absolute shared-memory address, so the descriptor needs nothing but that address
                     // (measured: with the base-offset field left 0 every start row gives exact results).
-                    if (SHAPE == 1) issue_tile<3, 3, 1>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
-                    else if (SHAPE == 2) issue_tile<3, 3, 2>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
-                    else if (SHAPE == 3) issue_tile<3, 3, 4>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap);
+                    if (SHAPE == 1) issue_tile<3, 3, 1>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap, issue);
+                    else if (SHAPE == 2) issue_tile<3, 3, 2>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap, issue);
+                    else if (SHAPE == 3) issue_tile<3, 3, 4>(d_tmem, a_lo, res_b_lo, desc_hi, a.idesc, row_step, col_step, btap, issue);
                     else {
                         unsigned ar = a_lo, bt = res_b_lo, first = 0;
                         for (int ky = 0; ky < a.taps_y; ++ky, ar += row_step) {
                             unsigned ac = ar;
                             for (int kx = 0; kx < a.taps_x; ++kx, ac += col_step, bt += btap)
                                 for (int k = 0; k < ksteps; ++k) {
-                                    tc_mma_i8_lohi(d_tmem, ac + 2u * k, bt + 2u * k, desc_hi, a.idesc, first);
+                                    tc_mma_i8_lohi_p(d_tmem, ac + 2u * k, bt + 2u * k, desc_hi, a.idesc, first, issue);
                                     first = 1u;
                                 }
                         }
                     }
-                    tc_commit(tfull0 + 8u * slot);
+                    tc_commit_p(tfull0 + 8u * slot, issue);
                 }
-                if (ok) tc_commit(pempty0 + 8u * pb);   // the patch is free once both issuers' MMAs have read it
+                if (ok) tc_commit_p(pempty0 + 8u * pb, issue);   // the patch is free once both issuers' MMAs have read it
                 band += step_b;
                 if (band >= a.bands) band -= a.bands;
             }

@@ -95,6 +95,22 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     }
 }
 
+// Bounded wait of a whole warp with a warp-uniform result (votes), for loops that every lane runs
+__device__ __forceinline__ bool mbar_wait_uniform(unsigned bar, unsigned parity, volatile int* abort_flag, int* status, int code)
+{
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+        if (__any_sync(0xffffffffu, *abort_flag != 0)) return false;
+        if (__any_sync(0xffffffffu, globaltimer_ns() - t0 > WAIT_LIMIT_NS)) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
 // Warp-wide bounded wait: one lane polls (32 lanes polling one word, times many warps, crowd out the
 // arrivals and the shared-memory traffic of the working warps), then every lane observes the completed
 // phase itself, which costs one successful try_wait and gives each lane its own acquire.
@@ -164,6 +180,29 @@ __device__ __forceinline__ void tc_mma_i8_lohi(unsigned d_tmem, unsigned a_lo, u
         "setp.ne.b32 p, %5, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
         ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Forms for an issuing WARP: every lane runs the loop (uniform control flow lets the compiler keep descriptor
+// words, counters and barrier addresses in uniform registers, where the MMA wants them; a loop under
+// `if (lane == 0)` computes them in vector registers and pays a move per operand per MMA), and `issue`
+// (true on one lane) predicates the instruction itself.
+__device__ __forceinline__ void tc_mma_i8_lohi_p(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc,
+                                                 unsigned accumulate, unsigned issue)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
+}
+__device__ __forceinline__ void tc_commit_p(unsigned bar, unsigned issue)
+{
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar), "r"(issue) : "memory");
 }
 __device__ __forceinline__ void tc_commit(unsigned bar)
 {
