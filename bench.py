@@ -25,7 +25,7 @@ sys.path.insert(0, ROOT)
 
 # DRAM bytes one launch of the implicit-GEMM kernel moves per image (average over the 53 launches of a
 # ResNet-50 forward): 4950.6 MB / 53 launches / 256 images, from the ncu capture summarised under profiles/.
-IGEMM_DRAM_BYTES_PER_IMAGE_PER_LAUNCH = 4671.45e6 / 47 / 256
+IGEMM_DRAM_BYTES_PER_IMAGE_PER_LAUNCH = 4668.37e6 / 47 / 256
 
 METRIC = 'int8_resnet50_images_per_sec'
 UNIT = 'images/s'
