@@ -175,7 +175,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags);
 int n2d2b_net_forward(n2d2b_net* net, const void* d_input, int batch, void* d_output, n2d2b_stream stream);
 /* The same with host buffers (the reference's mInputs.synchronizeHToD / mOutputs.synchronizeDToH):
  * copies in, runs, copies out and synchronises the stream.  From 256 images on the upload is cut into
- * slices (about 256 images each, at most 8) on a second stream and the leading cells run per slice while
+ * slices (about 128 images each, at most 8, the last one half as large) on a second stream and the leading cells run per slice while
  * later slices arrive; pinned host memory lets the copies overlap.  The environment variable N2D2B_SLICES
  * (1..8) overrides the number of slices. */
 int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream);

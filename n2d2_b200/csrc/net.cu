@@ -1124,9 +1124,12 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
     const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
     void* d_in = net->d_stage_in;
     void* d_out = net->d_stage_out;
-    // slices of about 256 images: large enough to fill the GPU, small enough that the first one arrives early
-    int nslices = (net->head_cells > 0 && batch >= 256) ? (batch / 256 < 2 ? 2 : (batch / 256 > 8 ? 8 : batch / 256)) : 1;
+    // Slices of about 128 images, at most 8.  The upload is slower than the leading cells, so what the caller
+    // waits for is the upload, then the leading cells of the LAST slice, then the rest of the network: the last
+    // slice is half as large as the others.
+    int nslices = (net->head_cells > 0 && batch >= 256) ? (batch / 128 > 8 ? 8 : batch / 128) : 1;
     if (const char* e = getenv("N2D2B_SLICES")) nslices = atoi(e) > 0 && atoi(e) <= 8 ? atoi(e) : nslices;
+    const int wsum = 2 * nslices - 1;   // weights 2, 2, ..., 2, 1
     if (nslices == 1) {
         CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
         if (int rc = forward_impl(net, d_in, batch, d_out, s, nullptr, 0)) return rc;
@@ -1136,7 +1139,8 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
         CUDA_TRY(cudaStreamWaitEvent(net->copy_stream, net->stage_free, 0));
         const size_t img_bytes = net->tensors[0].bytes_per_image();
         for (int k = 0; k < nslices; ++k) {
-            const int b0 = (int)((long long)batch * k / nslices), b1 = (int)((long long)batch * (k + 1) / nslices);
+            const int b0 = (int)((long long)batch * (2 * k) / wsum);
+            const int b1 = k + 1 == nslices ? batch : (int)((long long)batch * (2 * k + 2) / wsum);
             CUDA_TRY(cudaMemcpyAsync((uint8_t*)d_in + (size_t)b0 * img_bytes, (const uint8_t*)h_input + (size_t)b0 * img_bytes,
                                      (size_t)(b1 - b0) * img_bytes, cudaMemcpyHostToDevice, net->copy_stream));
             CUDA_TRY(cudaEventRecord(net->slice_ready[k], net->copy_stream));
