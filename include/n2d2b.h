@@ -171,14 +171,39 @@ int n2d2b_net_add_scaling(n2d2b_net* net, int input, const n2d2b_quant* quant, i
 int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags);
 
 /* DeepNet::propagate(inference = true) on device buffers: d_input is batch x H x W x C 8-bit values,
- * d_output receives the last cell's output (batch x its size). Asynchronous on `stream`. */
+ * d_output receives the last cell's output (batch x its size).  Asynchronous on `stream`: the call only
+ * enqueues the kernels, so a device-side wait that gave up (N2D2B_ERR_TIMEOUT) is not known when it returns;
+ * n2d2b_net_check reports it. */
 int n2d2b_net_forward(n2d2b_net* net, const void* d_input, int batch, void* d_output, n2d2b_stream stream);
+/* Waits for the work queued on `stream` and returns N2D2B_ERR_TIMEOUT if a kernel of this network gave up on a
+ * bounded wait since the last check (its outputs are then incomplete), N2D2B_ERR_CUDA if the stream failed,
+ * else 0.  The reference's counterpart is the cudaDeviceSynchronize + CHECK_CUDA_STATUS after each cell when
+ * timings are on (src/DeepNet.cpp:2705-2717).  n2d2b_net_forward_host, _wait, _profile and _read_tensor make
+ * the same check themselves. */
+int n2d2b_net_check(n2d2b_net* net, n2d2b_stream stream);
 /* The same with host buffers (the reference's mInputs.synchronizeHToD / mOutputs.synchronizeDToH):
  * copies in, runs, copies out and synchronises the stream.  From 256 images on the upload is cut into
  * slices (about 128 images each, at most 8, the last one half as large) on a second stream and the leading cells run per slice while
- * later slices arrive; pinned host memory lets the copies overlap.  The environment variable N2D2B_SLICES
- * (1..8) overrides the number of slices. */
+ * later slices arrive; pinned host memory lets the copies overlap. */
 int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream);
+/* Number of upload slices n2d2b_net_forward_host uses: 1..8, or 0 for the automatic choice above.  Fewer are
+ * used when the batch has fewer than 2 * nb_slices - 1 images (every slice holds at least one image). */
+int n2d2b_net_set_slices(n2d2b_net* net, int nb_slices);
+/* Streaming form of n2d2b_net_forward_host, for a caller that feeds batch after batch: the reference prepares
+ * the next batch on a second host thread while the current one is inferred (src/utils/Helper.cpp:428-454,
+ * StimuliProvider::future).  n2d2b_net_submit_host enqueues upload, forward pass and download of one batch and
+ * returns at once; the upload goes to one of two staging buffers on a copy stream, so it runs under the forward
+ * pass of the batch submitted before.  h_input must stay valid and h_output is complete only after
+ * n2d2b_net_wait, which waits for everything submitted and returns the status n2d2b_net_check would.  More than
+ * two batches may be submitted back to back: the third upload waits on the device for the first batch to finish.
+ * Use pinned host memory (pageable memory makes the copies synchronous) and one `stream` per network. */
+int n2d2b_net_submit_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream);
+int n2d2b_net_wait(n2d2b_net* net);
+/* Test hook for the bounded device-side waits (no counterpart in the reference): enqueues on `stream` a one-CTA
+ * kernel that waits at most limit_us microseconds (1..100000) on a barrier nobody arrives at, gives up and
+ * raises this network's status word exactly as a pipeline wait of the tensor-core kernels would.  Nothing
+ * faults or traps; the next n2d2b_net_check returns N2D2B_ERR_TIMEOUT and the network stays usable. */
+int n2d2b_net_selftest_wait_timeout(n2d2b_net* net, unsigned limit_us, n2d2b_stream stream);
 
 int n2d2b_net_num_tensors(const n2d2b_net* net);
 int n2d2b_net_tensor_info(const n2d2b_net* net, int tensor_id, n2d2b_tensor_info* info);
@@ -197,6 +222,13 @@ int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_ou
  * src/Scaling_CUDA_Kernels.cu:209-430): d_in is int32 NHWC (nb_pixels x channels), d_out int8. */
 int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t nb_pixels,
                             const n2d2b_quant* quant, n2d2b_stream stream);
+
+/* Issue-rate probe of the int8 tensor pipe (no counterpart in the reference; it gives the roofline denominator
+ * for the convolution kernels): one CTA per multiprocessor issues `reps` tcgen05.mma kind::i8 instructions of
+ * shape 128 x n x 32 back to back from shared-memory operands, no memory traffic.  *tops = dense int8 TOP/s the
+ * whole GPU sustained over the launch (CUDA events), *cycles_per_mma = SM cycles per instruction on one
+ * multiprocessor.  n: multiple of 16 in 16..256; reps: 64..1000000.  Allocates and frees 128 bytes. */
+int n2d2b_probe_i8_mma_rate(int device, int n, int reps, double* tops, double* cycles_per_mma);
 
 /*
  * First-layer convolution that allocates no device memory.  It has no counterpart in the reference.
@@ -228,6 +260,10 @@ int n2d2b_scaling_propagate(int device, const int32_t* d_in, void* d_out, size_t
  *     stream capture begins.  The call copies the small layer constants and waits for that copy
  *     (a stream synchronisation), then enqueues the kernels asynchronously.
  *   - It calls no cudaMalloc, cudaFree or other allocating CUDA routine.
+ *   - The kernels are enqueued asynchronously, so a device-side wait that gave up is not known when the call
+ *     returns.  The status word sits in the same array; the NEXT call on that device reads it during the wait
+ *     it makes anyway and returns N2D2B_ERR_TIMEOUT ("the previous call's kernel gave up...") without
+ *     launching; the call after that runs normally.  The caller's current device is restored on return.
  */
 #define N2D2B_NOALLOC_MAX_PIXELS (8u * 1024u * 1024u)
 #define N2D2B_NOALLOC_SCRATCH_BYTES (128u * 1024u + 4u * N2D2B_NOALLOC_MAX_PIXELS)

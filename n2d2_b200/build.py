@@ -8,7 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 OUT = os.path.join(HERE, 'libn2d2b.so')
-SOURCES = ['net.cu', 'simt_kernels.cu', 'igemm_tcgen05.cu', 'stem_tcgen05.cu', 'patch_tcgen05.cu', 'stem_s2d_tcgen05.cu']
+SOURCES = ['net.cu', 'simt_kernels.cu', 'igemm_tcgen05.cu', 'stem_tcgen05.cu', 'patch_tcgen05.cu', 'stem_s2d_tcgen05.cu',
+           'probe_tcgen05.cu']
 HEADERS = ['common.cuh', 'kernels.h', 'tc_common.cuh', 'host_internal.h', os.path.join('..', '..', 'include', 'n2d2b.h')]
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
               '-Xcompiler', '-fPIC', '-shared', '-diag-suppress', '550']

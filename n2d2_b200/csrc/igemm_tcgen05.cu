@@ -23,6 +23,7 @@
 // *status_word and makes the whole CTA drain and exit, so a wrong descriptor cannot hang the GPU.
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -864,7 +865,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
                           && plan.has_out_maps;
     const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : (fast.dp4a ? 5 : 4)) : (fast.need_clamp ? 1 : 3));
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -889,7 +890,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     if (plan.pair && use_fast && !r.ptr && !fast.wide) {
         typedef void (*PairKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
         static const PairKernel pair_kernels[2] = {igemm_pair_i8_tcgen05_kernel<false>, igemm_pair_i8_tcgen05_kernel<true>};
-        static bool pair_attr_set[64] = {false};
+        static std::atomic<bool> pair_attr_set[64];
         if (dev >= 0 && dev < 64 && !pair_attr_set[dev]) {
             for (PairKernel k : pair_kernels) {
                 cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);

@@ -13,6 +13,7 @@
 #include "../../include/n2d2b.h"
 #include "kernels.h"
 #include "host_internal.h"
+#include "tc_common.cuh"
 
 using namespace n2d2b;
 
@@ -116,6 +117,17 @@ struct n2d2b_net {
     cudaEvent_t slice_ready[8] = {nullptr};
     cudaEvent_t stage_free = nullptr;
     int head_cells = 0;
+    int head_limit = 0;      // cells [0, head_limit) may run slice by slice: the buffer planner keeps their tensors apart
+    int forced_slices = 0;   // n2d2b_net_set_slices: 0 = automatic
+    // streaming host-buffer entry points (submit / wait): two staging sets, so that the upload of one batch runs
+    // under the forward pass of the batch before it
+    void* d_pipe_in[2] = {nullptr, nullptr};
+    void* d_pipe_out[2] = {nullptr, nullptr};
+    cudaEvent_t pipe_uploaded[2] = {nullptr, nullptr};
+    cudaEvent_t pipe_done[2] = {nullptr, nullptr};
+    bool pipe_busy[2] = {false, false};
+    cudaStream_t pipe_stream[2] = {nullptr, nullptr};   // the stream each slot's work was queued on
+    unsigned pipe_next = 0;
 };
 
 static int validate_quant(const n2d2b_quant* qu, int channels, bool accumulators_have_bias, QuantHost& q,
@@ -132,6 +144,8 @@ static int validate_quant(const n2d2b_quant* qu, int channels, bool accumulators
     q.nb_channels = channels;
     if (q.mode < SC_NONE || q.mode > SC_DOUBLE_SHIFT) return fail(N2D2B_ERR_INVALID, "unknown scaling mode %d", q.mode);
     if (q.act < ACT_LINEAR || q.act > ACT_SATURATION) return fail(N2D2B_ERR_INVALID, "unknown activation %d", q.act);
+    if (q.act == ACT_SATURATION && q.sat_thr < 0)
+        return fail(N2D2B_ERR_INVALID, "saturation_threshold must not be negative (got %d)", q.sat_thr);
     if (q.mode != SC_NONE) {
         if (s.nb_channels != channels)
             return fail(N2D2B_ERR_INVALID, "scaling has %d channels, the cell has %d outputs", s.nb_channels, channels);
@@ -251,7 +265,7 @@ static int upload_quant(QuantHost& q)
 // Clipping to [0, clip] before the rescale tightens the same clamp, and the bias is folded in:
 //   y = (clamp(acc, L - b, H - b) * m + (b * m + half)) >> s.
 // Returns false when some intermediate could leave 32 bits or the configuration is outside this
-// form (float mode, negative multipliers, clip <= 0, out_bits != 8, Saturation activation); the
+// form (float mode, negative multipliers, clip <= 0, out_bits != 8); the
 // exact 64-bit epilogue is used then.
 static long long ceil_div(long long a, long long b)  // b > 0
 {
@@ -262,7 +276,7 @@ static long long ceil_div(long long a, long long b)  // b > 0
 // pack saturates), so it applies when none is needed for other reasons; the shifted result must fit 32 bits.
 static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out)
 {
-    if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned)) return false;
+    if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned) || q.act == ACT_SATURATION) return false;
     const int C = q.nb_channels;
     out.assign((size_t)5 * cpad, 0);
     for (int c = 0; c < C; ++c) {
@@ -290,11 +304,17 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
 {
     if (q.mode != SC_SINGLE_SHIFT && q.mode != SC_DOUBLE_SHIFT && q.mode != SC_FIXED_MULT16 && q.mode != SC_FIXED_MULT32)
         return false;
-    if (q.out_bits != 8 || q.act == ACT_SATURATION) return false;
+    if (q.out_bits != 8) return false;
     const int C = q.nb_channels;
-    const long long out_hi = q.out_unsigned ? 255 : 127;
+    long long out_hi = q.out_unsigned ? 255 : 127;
     long long out_lo = q.out_unsigned ? 0 : -128;
     if (q.act == ACT_RECTIFIER && out_lo < 0) out_lo = 0;
+    if (q.act == ACT_SATURATION) {
+        // saturate to the output range, then clamp to +-threshold: one clamp to the intersection
+        out_hi = std::min(out_hi, (long long)q.sat_thr);
+        out_lo = std::max(out_lo, -(long long)q.sat_thr);
+        *need_clamp = true;
+    }
     *eff_lo = (int)out_lo;
     *eff_hi = (int)out_hi;
     out.assign((size_t)5 * cpad, 0);
@@ -452,6 +472,22 @@ int prepare_fast_constants(const n2d2b_quant* quant, int channels, const int32_t
 }
 }  // namespace n2d2b
 
+// One CTA waits, with the given limit, on a barrier that nobody ever arrives at: the bounded wait of the
+// tensor-core kernels running out, on purpose and harmlessly (no fault, no trap; the kernel returns).
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns)
+{
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status, 9, limit_ns);
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------------------------ C ABI
 extern "C" {
 
@@ -504,6 +540,12 @@ void n2d2b_net_destroy(n2d2b_net* net)
     for (cudaEvent_t e : net->slice_ready)
         if (e) cudaEventDestroy(e);
     if (net->stage_free) cudaEventDestroy(net->stage_free);
+    for (int k = 0; k < 2; ++k) {
+        cudaFree(net->d_pipe_in[k]);
+        cudaFree(net->d_pipe_out[k]);
+        if (net->pipe_uploaded[k]) cudaEventDestroy(net->pipe_uploaded[k]);
+        if (net->pipe_done[k]) cudaEventDestroy(net->pipe_done[k]);
+    }
     delete net;
 }
 
@@ -709,9 +751,32 @@ static void fuse_residuals(n2d2b_net* net)
     }
 }
 
+// Cells [0, n) that the host-buffer entry point may run slice by slice (a structural rule, applied before the
+// kernels are chosen; the engine-based rule in finalize can only shorten it): image-wise cells with large
+// per-image tensors, up to the first fully-connected cell or stand-alone sum.
+static int head_candidate_prefix(const n2d2b_net* net)
+{
+    int n = 0;
+    for (size_t ci = 0; ci < net->cells.size(); ++ci) {
+        const CellRec& c = net->cells[ci];
+        if (!c.skipped) {
+            if (c.type == CELL_FC || c.type == CELL_SUM || c.type == CELL_SCALING) break;
+            const TensorRec& t = net->tensors[c.output];
+            if ((long long)t.H * t.W < 2048) break;
+        }
+        n = (int)ci + 1;
+    }
+    return n;
+}
+
+// Buffers are shared by lifetime.  Cells of the head run once per batch slice at an image offset, so slice k of
+// a head tensor may be written while slices < k of every other head tensor are complete and still needed: two
+// head tensors share a buffer only when they have the same bytes per image (slice k of one then lies exactly
+// over slice k of the other, which the per-slice order of the cells has already retired).
 static int plan_buffers(n2d2b_net* net)
 {
     const bool keep_all = (net->flags & N2D2B_KEEP_ALL_OUTPUTS) != 0;
+    std::vector<size_t> head_bpi;   // per buffer: bytes per image of the head tensors it has held (0 = none)
     const int nt = (int)net->tensors.size();
     std::vector<int> last_use(nt, -1);
     for (int ci = 0; ci < (int)net->cells.size(); ++ci) {
@@ -729,10 +794,12 @@ static int plan_buffers(n2d2b_net* net)
         if (c.skipped) continue;
         TensorRec& t = net->tensors[c.output];
         const size_t need = ((t.bytes_per_image() * (size_t)net->max_batch + 255) / 256) * 256 + 256;
+        const bool in_head = ci < net->head_limit;
         int pick = -1;
         if (!keep_all) {
             for (size_t f = 0; f < free_list.size(); ++f) {
                 const int b = free_list[f];
+                if (in_head && head_bpi[b] != t.bytes_per_image()) continue;
                 if (sizes[b] >= need && (pick < 0 || sizes[b] < sizes[free_list[pick]])) pick = (int)f;
             }
         }
@@ -742,6 +809,7 @@ static int plan_buffers(n2d2b_net* net)
         } else {
             t.buffer = (int)sizes.size();
             sizes.push_back(need);
+            head_bpi.push_back(in_head ? t.bytes_per_image() : 0);
         }
         if (!keep_all) {
             // release the inputs that die with this cell (never the network input or the final output)
@@ -792,6 +860,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     net->max_batch = max_batch;
     net->flags = flags;
     if (!(flags & N2D2B_NO_FUSION)) fuse_residuals(net);
+    net->head_limit = head_candidate_prefix(net);
     if (int rc = plan_buffers(net)) return rc;
     CUDA_TRY(cudaMalloc(&net->d_status, 64));
     CUDA_TRY(cudaMemset(net->d_status, 0, 64));
@@ -926,8 +995,12 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             const TensorRec& t = net->tensors[c.output];
             if ((long long)t.H * t.W < 2048) sliceable = false;
         }
-        if (!sliceable) break;
+        if (!sliceable || (int)ci >= net->head_limit) break;
         net->head_cells = (int)ci + 1;
+    }
+    for (int k = 0; k < 2; ++k) {
+        CUDA_TRY(cudaEventCreateWithFlags(&net->pipe_uploaded[k], cudaEventDisableTiming));
+        CUDA_TRY(cudaEventCreateWithFlags(&net->pipe_done[k], cudaEventDisableTiming));
     }
     net->finalized = true;
     return 0;
@@ -1101,6 +1174,26 @@ int n2d2b_net_forward(n2d2b_net* net, const void* d_input, int batch, void* d_ou
     return forward_impl(net, d_input, batch, d_output, (cudaStream_t)stream, nullptr, 0);
 }
 
+int n2d2b_net_check(n2d2b_net* net, n2d2b_stream stream)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "check before finalize");
+    CUDA_TRY(cudaSetDevice(net->device));
+    CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return check_status(net);
+}
+
+int n2d2b_net_selftest_wait_timeout(n2d2b_net* net, unsigned limit_us, n2d2b_stream stream)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "selftest before finalize");
+    if (limit_us < 1 || limit_us > 100000) return fail(N2D2B_ERR_INVALID, "limit_us must be in 1..100000");
+    CUDA_TRY(cudaSetDevice(net->device));
+    wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(net->d_status, (unsigned long long)limit_us * 1000ull);
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
 int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_output, float* ms, int nb_cells,
                       n2d2b_stream stream)
 {
@@ -1109,14 +1202,28 @@ int n2d2b_net_profile(n2d2b_net* net, const void* d_input, int batch, void* d_ou
     return check_status(net);
 }
 
-int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream)
+int n2d2b_net_set_slices(n2d2b_net* net, int nb_slices)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (nb_slices < 0 || nb_slices > 8) return fail(N2D2B_ERR_INVALID, "nb_slices must be in 0..8 (0 = automatic)");
+    net->forced_slices = nb_slices;
+    return 0;
+}
+
+static int host_call_checks(n2d2b_net* net, const void* h_input, int batch, void* h_output)
 {
     if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
     if (!net->finalized) return fail(N2D2B_ERR_STATE, "forward before finalize");
     if (batch < 0 || batch > net->max_batch)
         return fail(N2D2B_ERR_TOO_LARGE, "batch %d exceeds the finalized maximum %d", batch, net->max_batch);
+    if (batch > 0 && (!h_input || !h_output)) return fail(N2D2B_ERR_INVALID, "host buffers must not be NULL");
+    return 0;
+}
+
+int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream)
+{
+    if (int rc = host_call_checks(net, h_input, batch, h_output)) return rc;
     if (batch == 0) return 0;
-    if (!h_input || !h_output) return fail(N2D2B_ERR_INVALID, "host buffers must not be NULL");
     CUDA_TRY(cudaSetDevice(net->device));
     cudaStream_t s = (cudaStream_t)stream;
     const size_t in_bytes = net->tensors[0].bytes_per_image() * (size_t)batch;
@@ -1128,7 +1235,8 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
     // waits for is the upload, then the leading cells of the LAST slice, then the rest of the network: the last
     // slice is half as large as the others.
     int nslices = (net->head_cells > 0 && batch >= 256) ? (batch / 128 > 8 ? 8 : batch / 128) : 1;
-    if (const char* e = getenv("N2D2B_SLICES")) nslices = atoi(e) > 0 && atoi(e) <= 8 ? atoi(e) : nslices;
+    if (net->forced_slices > 0 && net->head_cells > 0) nslices = net->forced_slices;
+    while (nslices > 1 && batch < 2 * nslices - 1) --nslices;   // every slice holds at least one image
     const int wsum = 2 * nslices - 1;   // weights 2, 2, ..., 2, 1
     if (nslices == 1) {
         CUDA_TRY(cudaMemcpyAsync(d_in, h_input, in_bytes, cudaMemcpyHostToDevice, s));
@@ -1141,6 +1249,7 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
         for (int k = 0; k < nslices; ++k) {
             const int b0 = (int)((long long)batch * (2 * k) / wsum);
             const int b1 = k + 1 == nslices ? batch : (int)((long long)batch * (2 * k + 2) / wsum);
+            if (b1 <= b0) continue;
             CUDA_TRY(cudaMemcpyAsync((uint8_t*)d_in + (size_t)b0 * img_bytes, (const uint8_t*)h_input + (size_t)b0 * img_bytes,
                                      (size_t)(b1 - b0) * img_bytes, cudaMemcpyHostToDevice, net->copy_stream));
             CUDA_TRY(cudaEventRecord(net->slice_ready[k], net->copy_stream));
@@ -1153,6 +1262,55 @@ int n2d2b_net_forward_host(n2d2b_net* net, const void* h_input, int batch, void*
     }
     CUDA_TRY(cudaMemcpyAsync(h_output, d_out, out_bytes, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaStreamSynchronize(s));
+    return check_status(net);
+}
+
+// Streaming form of the host-buffer entry point.  The reference overlaps the preparation of the next batch with
+// the inference of the current one on a second host thread (src/utils/Helper.cpp:428-454); here the overlap is on
+// the device: the upload of batch k + 1 runs on the copy stream, into the second staging buffer, under the
+// forward pass of batch k.
+int n2d2b_net_submit_host(n2d2b_net* net, const void* h_input, int batch, void* h_output, n2d2b_stream stream)
+{
+    if (int rc = host_call_checks(net, h_input, batch, h_output)) return rc;
+    if (batch == 0) return 0;
+    CUDA_TRY(cudaSetDevice(net->device));
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned slot = net->pipe_next & 1u;
+    const size_t in_cap = net->tensors[0].bytes_per_image() * (size_t)net->max_batch + 256;
+    const int ft = final_tensor_of(net);
+    const size_t out_cap = net->tensors[ft].bytes_per_image() * (size_t)net->max_batch + 256;
+    if (!net->d_pipe_in[slot]) {
+        // the staging sets of this entry point are allocated on first use (callers of the blocking form never pay for them)
+        CUDA_TRY(cudaMalloc(&net->d_pipe_in[slot], in_cap));
+        CUDA_TRY(cudaMalloc(&net->d_pipe_out[slot], out_cap));
+    }
+    // the slot's previous batch (two submissions ago) must have left its staging buffers: its forward pass has
+    // read the input and its download has read the output
+    if (net->pipe_busy[slot]) CUDA_TRY(cudaStreamWaitEvent(net->copy_stream, net->pipe_done[slot], 0));
+    const size_t in_bytes = net->tensors[0].bytes_per_image() * (size_t)batch;
+    const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
+    CUDA_TRY(cudaMemcpyAsync(net->d_pipe_in[slot], h_input, in_bytes, cudaMemcpyHostToDevice, net->copy_stream));
+    CUDA_TRY(cudaEventRecord(net->pipe_uploaded[slot], net->copy_stream));
+    CUDA_TRY(cudaStreamWaitEvent(s, net->pipe_uploaded[slot], 0));
+    if (int rc = forward_impl(net, net->d_pipe_in[slot], batch, net->d_pipe_out[slot], s, nullptr, 0)) return rc;
+    CUDA_TRY(cudaMemcpyAsync(h_output, net->d_pipe_out[slot], out_bytes, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaEventRecord(net->pipe_done[slot], s));
+    net->pipe_busy[slot] = true;
+    net->pipe_stream[slot] = s;
+    net->pipe_next++;
+    return 0;
+}
+
+int n2d2b_net_wait(n2d2b_net* net)
+{
+    if (!net) return fail(N2D2B_ERR_INVALID, "net must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "wait before finalize");
+    CUDA_TRY(cudaSetDevice(net->device));
+    for (int k = 0; k < 2; ++k)
+        if (net->pipe_busy[k]) {
+            CUDA_TRY(cudaEventSynchronize(net->pipe_done[k]));
+            net->pipe_busy[k] = false;
+        }
     return check_status(net);
 }
 

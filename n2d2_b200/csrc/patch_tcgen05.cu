@@ -15,6 +15,7 @@
 // drain every fourth tile: 32-bit requantisation in the fragment layout into a swizzled staging region,
 // then one 16-byte-vector copy per pixel row to the NHWC output.  Every wait is bounded.
 #include <cstring>
+#include <atomic>
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -527,7 +528,7 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, c
         patch_conv_tcgen05_kernel<false, 0>, patch_conv_tcgen05_kernel<false, 1>, patch_conv_tcgen05_kernel<false, 2>,
         patch_conv_tcgen05_kernel<false, 3>, patch_conv_tcgen05_kernel<true, 0>,  patch_conv_tcgen05_kernel<true, 1>,
         patch_conv_tcgen05_kernel<true, 2>,  patch_conv_tcgen05_kernel<true, 3>};
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

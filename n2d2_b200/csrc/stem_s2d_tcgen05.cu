@@ -20,6 +20,7 @@
 // values nobody stores.  Every wait is bounded.
 #include <cstring>
 #include <vector>
+#include <atomic>
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -506,7 +507,7 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     static const Kernel variants[6] = {stem_s2d_tcgen05_kernel<false, 0>, stem_s2d_tcgen05_kernel<false, 1>,
                                        stem_s2d_tcgen05_kernel<false, 2>, stem_s2d_tcgen05_kernel<true, 0>,
                                        stem_s2d_tcgen05_kernel<true, 1>,  stem_s2d_tcgen05_kernel<true, 2>};
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -15,6 +15,8 @@
 // count per tile, not memory, sets the pace: hence the padded image, 8-byte loads where the stride
 // allows, and multiplications by reciprocals instead of divisions.
 #include <cstring>
+#include <atomic>
+#include <mutex>
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "host_internal.h"
@@ -428,7 +430,7 @@ cudaError_t launch_stem(const StemPlan& plan, const void* in4, const ConvGeom& g
     typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
     static const StemKernel variants[4] = {stem_conv_tcgen05_kernel<false, false>, stem_conv_tcgen05_kernel<false, true>,
                                            stem_conv_tcgen05_kernel<true, false>, stem_conv_tcgen05_kernel<true, true>};
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -474,10 +476,13 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_SCRATCH_BYTE
 // In host code the array's name is only a handle; its device address comes from the runtime, once per
 // device, with that device current.
 static unsigned char* g_noalloc_ptr[64] = {nullptr};
+static bool g_noalloc_used[64] = {false};   // the status word of a device means something only after a first call
+static std::mutex g_noalloc_mutex;   // first calls from several host threads look the address up one at a time
 
 static int noalloc_scratch_for(int device, unsigned char** ptr)
 {
     if (device < 0 || device >= 64) return n2d2b::set_error(N2D2B_ERR_INVALID, "device %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
     if (!g_noalloc_ptr[device]) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
@@ -527,6 +532,12 @@ extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int bat
                          (unsigned)N2D2B_NOALLOC_MAX_PIXELS);
     if (stem_weight_bytes(g) > NA_WEIGHT_BYTES)
         return set_error(N2D2B_ERR_TOO_LARGE, "arranged weights exceed the fixed scratch");
+    // the caller's current device is put back on every way out
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+    } guard;
+    if (cudaGetDevice(&guard.prev) != cudaSuccess) guard.prev = -1;
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(e));
     int sms = 148;
@@ -553,8 +564,26 @@ extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int bat
     e = cudaMemcpyAsync(scratch, arranged.data(), arranged.size(), cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(scratch + NA_CONST_OFFSET, consts.data(), consts.size() * 4, cudaMemcpyHostToDevice, s);
+    // The status word of the bounded waits lives in the scratch too (last 16 bytes of the constants area).  It
+    // still holds what the previous call's kernel left: read it behind that kernel, during the wait this call
+    // makes anyway, so a time-out of call k is reported by call k + 1.
+    int* status = (int*)(scratch + NA_PAD_OFFSET - 16);
+    int prev_status = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&prev_status, status, sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "copy of the layer constants failed: %s", cudaGetErrorString(e));
+    bool first_call_here;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        first_call_here = !g_noalloc_used[device];
+        g_noalloc_used[device] = true;
+    }
+    if (!first_call_here && prev_status != 0) {
+        cudaMemsetAsync(status, 0, sizeof(int), s);
+        return set_error(N2D2B_ERR_TIMEOUT,
+                         "the previous call's kernel gave up waiting on a pipeline barrier (role %d); its output is incomplete",
+                         prev_status);
+    }
 
     StemPlan plan;
     const char* why = "";
@@ -570,8 +599,6 @@ extern "C" int n2d2b_first_conv_noalloc(int device, const void* d_input, int bat
     fq.out_unsigned = out_unsigned;
     fq.need_clamp = need_clamp;
     fq.enabled = true;
-    // the status word of the bounded waits also lives in the scratch (last 16 bytes of the constants area)
-    int* status = (int*)(scratch + NA_PAD_OFFSET - 16);
     e = cudaMemsetAsync(status, 0, sizeof(int), s);
     if (e == cudaSuccess) e = launch_stem(plan, in4, g, fq, d_output, status, s);
     if (e != cudaSuccess) return set_error(N2D2B_ERR_CUDA, "first-layer launch failed: %s", cudaGetErrorString(e));

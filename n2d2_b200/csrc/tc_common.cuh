@@ -69,8 +69,8 @@ __device__ __forceinline__ unsigned long long globaltimer_ns()
 }
 // Bounded wait. Returns false (and raises the CTA-wide abort flag) on time-out or when another
 // role already aborted.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
-                                          int* status, int code)
+__device__ __forceinline__ bool mbar_wait_for(unsigned bar, unsigned parity, volatile int* abort_flag,
+                                              int* status, int code, unsigned long long limit_ns)
 {
     if (mbar_try_wait(bar, parity)) return true;
     // try_wait suspends the thread in hardware until the phase completes or a time limit passes, so a
@@ -87,12 +87,17 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
         // epilogue still holds, an epilogue warp whose residual is still on its way from DRAM) would fill the issue
         // slots of the warps that work: after a short tight phase the waiter sleeps between polls.
         if (++rounds > 8) __nanosleep(128);
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
+                                          int* status, int code)
+{
+    return mbar_wait_for(bar, parity, abort_flag, status, code, WAIT_LIMIT_NS);
 }
 
 // Bounded wait of a whole warp with a warp-uniform result (votes), for loops that every lane runs

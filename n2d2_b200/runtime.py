@@ -83,6 +83,11 @@ def load():
         lib.n2d2b_net_finalize.argtypes = [C.c_void_p, C.c_int, C.c_uint]
         lib.n2d2b_net_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         lib.n2d2b_net_forward_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        lib.n2d2b_net_check.argtypes = [C.c_void_p, C.c_void_p]
+        lib.n2d2b_net_set_slices.argtypes = [C.c_void_p, C.c_int]
+        lib.n2d2b_net_submit_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        lib.n2d2b_net_wait.argtypes = [C.c_void_p]
+        lib.n2d2b_net_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
         lib.n2d2b_net_num_tensors.argtypes = [C.c_void_p]
         lib.n2d2b_net_tensor_info.argtypes = [C.c_void_p, C.c_int, C.POINTER(TensorInfo)]
         lib.n2d2b_net_read_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
@@ -91,6 +96,7 @@ def load():
                                           C.c_void_p]
         lib.n2d2b_scaling_propagate.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(Quant),
                                                 C.c_void_p]
+        lib.n2d2b_probe_i8_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]
         lib.n2d2b_first_conv_noalloc.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                  C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.POINTER(Quant),
                                                  C.c_void_p, C.c_void_p]
@@ -231,6 +237,23 @@ class QuantizedNet:
     def forward_host_ptr(self, h_in_ptr, batch, h_out_ptr, stream=0):
         check(self.lib.n2d2b_net_forward_host(self.handle, h_in_ptr, batch, h_out_ptr, stream))
 
+    def check(self, stream=0):
+        """Waits for `stream` and raises if a kernel of this network gave up on a bounded wait."""
+        check(self.lib.n2d2b_net_check(self.handle, stream))
+
+    def set_slices(self, n):
+        check(self.lib.n2d2b_net_set_slices(self.handle, n))
+
+    def submit_host_ptr(self, h_in_ptr, batch, h_out_ptr, stream=0):
+        """Streaming form: returns at once; h_out is complete after wait()."""
+        check(self.lib.n2d2b_net_submit_host(self.handle, h_in_ptr, batch, h_out_ptr, stream))
+
+    def wait(self):
+        check(self.lib.n2d2b_net_wait(self.handle))
+
+    def selftest_wait_timeout(self, limit_us=1000, stream=0):
+        check(self.lib.n2d2b_net_selftest_wait_timeout(self.handle, limit_us, stream))
+
     def read_layer(self, layer_idx, batch):
         """Output of layer `layer_idx` of the last forward as an NHWC integer array (needs KEEP_ALL_OUTPUTS
         unless it is the last layer)."""
@@ -251,6 +274,13 @@ class QuantizedNet:
 def scaling_propagate(x_i32_dev_ptr, out_dev_ptr, nb_pixels, q, channels, device=0, stream=0):
     qq, keep = make_quant(q, channels)
     check(load().n2d2b_scaling_propagate(device, x_i32_dev_ptr, out_dev_ptr, nb_pixels, C.byref(qq), stream))
+
+
+def probe_i8_mma_rate(device=0, n=256, reps=40000):
+    """Measured dense int8 tensor-pipe rate of the GPU: (TOP/s over the whole chip, SM cycles per 128 x n x 32 MMA)."""
+    tops, cyc = C.c_double(), C.c_double()
+    check(load().n2d2b_probe_i8_mma_rate(device, n, reps, C.byref(tops), C.byref(cyc)))
+    return tops.value, cyc.value
 
 
 NOALLOC_MAX_PIXELS = 8 * 1024 * 1024

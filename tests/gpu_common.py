@@ -16,13 +16,16 @@ def single_conv_net(C, H, W, O, k, stride=1, pad=0, in_unsigned=True, act='relu'
     return b.net
 
 
-def compare_net(net, batch, flags=KEEP, flavour='i64', x=None, want_engine=None):
+def compare_net(net, batch, flags=KEEP, flavour='i64', x=None, want_engine=None, slices=0, ref=None):
     """Returns (number of compared layers, engines). Asserts bit-exact equality with the oracle."""
     if x is None:
         x = netdesc.make_input(net, batch)
-    ref = oracle.run_net(net, x, flavour)
+    if ref is None:
+        ref = oracle.run_net(net, x, flavour)
     qn = runtime.QuantizedNet(net, max(batch, 1), flags=flags)
     try:
+        if slices:
+            qn.set_slices(slices)
         out = qn.forward_host(x)
         eng = qn.engines()
         if want_engine is not None:

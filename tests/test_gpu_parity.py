@@ -40,12 +40,11 @@ def test_forced_im2col_keeps_the_implicit_gemm_kernel():
     compare_net(net, 2, flags=runtime.KEEP_ALL_OUTPUTS | runtime.FORCE_IM2COL, want_engine='tcgen05')
 
 
-@pytest.mark.parametrize('slices', ['2', '3', '5'])
-def test_host_entry_point_runs_the_leading_cells_slice_by_slice(slices, monkeypatch):
+@pytest.mark.parametrize('slices', [2, 3, 5])
+def test_host_entry_point_runs_the_leading_cells_slice_by_slice(slices):
     # at batch >= 256 the host-buffer entry point uploads the batch in slices and runs the leading cells
     # (here: all of them - im2col and 1x1 implicit GEMM, patch kernel, fused residual sum, pooling) per slice;
     # uneven slice sizes, every layer compared with the oracle
-    monkeypatch.setenv('N2D2B_SLICES', slices)
     b = netdesc.NetBuilder('sliced', 16, 48, 48, 11, 'double', weight_dist=('normal', 30))
     c0 = b.conv(-1, 64, 3, pad=1, name='c0')
     c1 = b.conv(c0, 64, 3, pad=1, name='c1')
@@ -53,9 +52,9 @@ def test_host_entry_point_runs_the_leading_cells_slice_by_slice(slices, monkeypa
     pj = b.conv(c0, 128, 1, act='linear', name='proj')
     sm = b.sum([x4, pj], act='relu', name='sum')
     b.pool(sm, 'max', 2, 2, name='pool')
-    n, eng = compare_net(b.net, 261, flags=0)
+    n, eng = compare_net(b.net, 261, flags=0, slices=slices)
     assert 'fused' in eng and 'patch-tcgen05' in eng and 'tcgen05' in eng
-    compare_net(b.net, 261)     # and with every cell's output kept and compared
+    compare_net(b.net, 261, slices=slices)     # and with every cell's output kept and compared
 
 
 # (C, H, W, stride, pad, dilation, input unsigned, activation)
@@ -276,3 +275,79 @@ def test_batch_invariance_at_a_large_batch():
     picks = [0, 1, 127, 128, 255, 299]
     ref = oracle.run_net(net, x[picks], 'i64')[-1].reshape(len(picks), -1)
     assert np.array_equal(out[picks], ref)
+
+
+def _saturating(net, thr):
+    """Turns every cell's activation into Saturation(+-thr) (signed outputs)."""
+    for l in net['layers']:
+        if 'quant' in l and l['quant']['mode'] != 'none':
+            l['quant']['act'] = 'saturation'
+            l['quant']['sat_thr'] = thr
+            l['quant']['out_unsigned'] = False
+    return net
+
+
+# one case per kernel family: (what, builder of a one-cell network, engine expected in the shipped configuration)
+SAT_CASES = [
+    ('igemm', lambda m: single_conv_net(64, 9, 9, 80, 3, 1, 1, mode=m), 'tcgen05'),
+    ('igemm_1x1_wide', lambda m: single_conv_net(128, 8, 8, 256, 1, 1, 0, mode=m), 'tcgen05'),
+    ('patch', lambda m: single_conv_net(64, 20, 17, 64, 3, 1, 1, mode=m), 'patch-tcgen05'),
+    ('stem_s2d', lambda m: single_conv_net(3, 32, 32, 64, 7, 2, 3, mode=m), 'stem-tcgen05'),
+    ('stem_gather', lambda m: single_conv_net(4, 17, 19, 64, 5, 1, 2, mode=m), 'stem-tcgen05'),
+    ('depthwise', lambda m: single_conv_net(32, 20, 20, 32, 3, 1, 1, mode=m, groups=32), 'depthwise'),
+    ('direct', lambda m: single_conv_net(3, 17, 13, 5, 3, 2, 1, mode=m), 'simt'),
+]
+
+
+@pytest.mark.parametrize('case', SAT_CASES, ids=lambda c: c[0])
+@pytest.mark.parametrize('mode', ['single', 'double', 'fixed', 'float'])
+def test_saturation_activation_on_every_kernel_family(case, mode):
+    # SaturationActivation: Scaling (saturating to the output range) then a clamp to +-threshold
+    # (include/Activation/SaturationActivation_Frame.hpp:55-80 of the reference)
+    _, build, engine = case
+    for thr in (50, 127):
+        net = _saturating(build(mode), thr)
+        # float scalings and wide fixed-point shifts take the exact 64-bit kernels, whatever the family
+        exact_only = mode == 'float' or (mode == 'fixed' and engine == 'stem-tcgen05')
+        compare_net(net, 3, want_engine=None if exact_only else engine)
+        compare_net(net, 3, flags=KEEP | R.FORCE_SIMT)
+        ref = oracle.run_net(net, netdesc.make_input(net, 3), 'i64')[-1]
+        assert int(np.abs(ref).max()) <= thr
+
+
+def test_saturation_activation_in_a_network_with_fused_sums_fc_and_scaling_cell():
+    b = netdesc.NetBuilder('sat', 64, 12, 12, 9, 'double', weight_dist=('normal', 30))
+    r = b.conv(-1, 128, 1, act='linear')
+    t = b.conv(r, 128, 3, pad=1, act='linear')
+    s = b.sum([t, r], act='linear')
+    y = b.scaling(s, act='linear', mode='fixed')
+    p = b.pool(y, 'avg', (12, 12), 1)
+    b.fc(p, 16, act='linear')
+    net = _saturating(b.net, 90)
+    n, eng = compare_net(net, 3, flags=0)
+    assert 'fused' in eng
+    compare_net(net, 3)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_network_usable():
+    # The device-side waits of the tensor-core kernels give up after a time limit instead of hanging.  A
+    # test hook makes exactly that happen, harmlessly (a one-CTA kernel waits 1 ms on a barrier nobody
+    # arrives at and returns): the asynchronous entry point cannot know, the check reports it once, and
+    # the next forward pass is correct.
+    net = netdesc.resnet50(size=64, classes=100)
+    x = netdesc.make_input(net, 2)
+    ref = oracle.run_net(net, x, 'i64')[-1].reshape(2, -1)
+    qn = runtime.QuantizedNet(net, 2)
+    try:
+        assert np.array_equal(qn.forward_host(x).astype(np.int64), ref)
+        qn.check(0)                                   # nothing pending
+        qn.selftest_wait_timeout(1000, 0)
+        with pytest.raises(runtime.N2D2BError, match='status -4'):
+            qn.check(0)
+        qn.check(0)                                   # reported once, then clear
+        qn.selftest_wait_timeout(500, 0)
+        with pytest.raises(runtime.N2D2BError, match='gave up waiting'):
+            qn.forward_host(x)                        # the blocking entry points make the same check
+        assert np.array_equal(qn.forward_host(x).astype(np.int64), ref)
+    finally:
+        qn.close()

@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 
 from n2d2_b200 import netdesc, runtime
+from oracle import oracle
 
 from gpu_common import single_conv_net
 
@@ -37,6 +38,10 @@ def _both_paths(net, batch, seed):
     runtime.first_conv_noalloc(d_in.data_ptr(), batch, i['H'], i['W'], i['C'], i['unsigned'], layer, d_out.data_ptr())
     torch.cuda.synchronize()
     got = d_out.cpu().numpy().view(want.dtype)
+    # both against the CPU restatement of the reference as well, not only against each other
+    ref = oracle.run_net(net, x, 'i64')[-1].reshape(batch, -1)
+    assert np.array_equal(want.astype(np.int64), ref), 'the allocating path differs from the oracle'
+    assert np.array_equal(got.astype(np.int64), ref), 'the allocation-free entry point differs from the oracle'
     return got, want
 
 
