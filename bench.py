@@ -169,6 +169,10 @@ def launch_groups(net, engines):
         if l.get('weight_bits', 8) == 4:
             w //= 2
         b = sum(elems[j] for j in l['inputs']) + elems[i]
+        if l['type'] == 'conv':
+            # a strided filter that skips pixels (1x1 stride 2) reads only the pixels it uses
+            C = shapes[l['inputs'][0]][0]
+            b = min(elems[l['inputs'][0]], shapes[i][1] * shapes[i][2] * l['kH'] * l['kW'] * C) + elems[i]
         owner[i] = len(groups)
         groups.append({'name': l['name'], 'layers': [i], 'ops': 2.0 * macs[i], 'bytes': float(b), 'wbytes': float(w),
                        'engine': engines[i]})

@@ -15,6 +15,7 @@
 // and errors of the C ABI surface as std::runtime_error like the reference's own.
 #pragma once
 
+#include <algorithm>
 #include <cstdint>
 #include <map>
 #include <memory>
@@ -152,6 +153,7 @@ struct DeepNetExport {
 };
 
 class DeepNet;
+struct Network {};   // the reference's event-simulation context, first argument of its cell factories; empty here
 
 class Cell {
 public:
@@ -167,6 +169,10 @@ public:
     void setActivation(const std::shared_ptr<Activation>& activation) { mActivation = activation; }
     unsigned int getOutputsWidth() const { return mOutputsWidth; }
     unsigned int getOutputsHeight() const { return mOutputsHeight; }
+    // known once the cell is wired into a DeepNet
+    unsigned int getNbChannels() const { return mNbChannels; }
+    unsigned int getChannelsWidth() const { return mChannelsWidth; }
+    unsigned int getChannelsHeight() const { return mChannelsHeight; }
 
     // Signedness of the cell's output as DeepNetExport::isCellOutputUnsigned derives it: unsigned only
     // when unsigned data is allowed and the output range starts at 0 (a Rectifier); may be overridden.
@@ -197,6 +203,7 @@ protected:
     std::size_t mQuantizedNbBits = 0;
     std::shared_ptr<Activation> mActivation;
     unsigned int mOutputsWidth = 0, mOutputsHeight = 0;
+    unsigned int mNbChannels = 0, mChannelsWidth = 0, mChannelsHeight = 0;
     int mForcedSign = -1;
     int mTensorId = -1;
 };
@@ -216,8 +223,38 @@ public:
         if (mPaddingDims.size() == 2) { mPaddingDims.push_back(mPaddingDims[0]); mPaddingDims.push_back(mPaddingDims[1]); }
         mActivation = activation;
     }
+    // The reference's creation signature (include/Cell/ConvCell.hpp:45-55): the event-simulation Network and the
+    // DeepNet arguments carry nothing on this path.
+    ConvCell(Network& /*net*/, const DeepNet& /*deepNet*/, const std::string& name, const std::vector<unsigned int>& kernelDims,
+             unsigned int nbOutputs, const std::vector<unsigned int>& subSampleDims = {1, 1},
+             const std::vector<unsigned int>& strideDims = {1, 1}, const std::vector<int>& paddingDims = {0, 0},
+             const std::vector<unsigned int>& dilationDims = {1, 1},
+             const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
+        : ConvCell(name, kernelDims, nbOutputs, subSampleDims, strideDims, paddingDims, dilationDims, activation)
+    {
+    }
     const char* getType() const override { return "Conv"; }
     void setNbGroups(unsigned int groups) { mGroups = groups; }
+    unsigned int getNbGroups() const { return mGroups; }
+    // One kernel, as ConvCell::setWeight(output, channel, kernel) (include/Cell/ConvCell_Frame_CUDA.hpp:109-198):
+    // kernel = kernelHeight x kernelWidth values, x fastest; channel counts within the output's group.  Valid once
+    // the cell is wired into a DeepNet (the number of channels is known then).
+    void setWeight(unsigned int output, unsigned int channel, const std::vector<std::int8_t>& kernel)
+    {
+        const std::size_t cg = mNbChannels / mGroups, ks = (std::size_t)mKernelDims[0] * mKernelDims[1];
+        if (cg == 0) throw std::runtime_error("ConvCell::setWeight(): add the cell to a DeepNet first");
+        if (output >= mNbOutputs || channel >= cg || kernel.size() != ks) throw std::runtime_error("ConvCell::setWeight(): out of range");
+        if (mWeights.size() != (std::size_t)mNbOutputs * cg * ks) mWeights.assign((std::size_t)mNbOutputs * cg * ks, 0);
+        std::copy(kernel.begin(), kernel.end(), mWeights.begin() + ((std::size_t)output * cg + channel) * ks);
+    }
+    void setBias(unsigned int output, std::int32_t value)
+    {
+        if (output >= mNbOutputs) throw std::runtime_error("ConvCell::setBias(): out of range");
+        if (mBiases.size() != mNbOutputs) mBiases.assign(mNbOutputs, 0);
+        mBiases[output] = value;
+    }
+    const std::vector<std::int8_t>& getWeights() const { return mWeights; }
+    const std::vector<std::int32_t>& getBiases() const { return mBiases; }
     // weights in the reference's memory order: [output][channel][ky][kx] (kx fastest)
     void setWeights(const std::vector<std::int8_t>& oihw) { mWeights = oihw; }
     void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
@@ -249,6 +286,8 @@ public:
     // weights in the reference's order: [output][channel][y][x] over the input tensor
     void setWeights(const std::vector<std::int8_t>& w) { mWeights = w; }
     void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
+    const std::vector<std::int8_t>& getWeights() const { return mWeights; }
+    const std::vector<std::int32_t>& getBiases() const { return mBiases; }
 
 private:
     friend class DeepNet;
@@ -297,29 +336,268 @@ public:
     const char* getType() const override { return "Scaling"; }
 };
 
-// Graph container + executor: cells run in insertion order like DeepNet::propagate.
+// Graph container + executor (src/DeepNet.cpp:74-415,826-854,2622-2768).  The graph lives on the host as in
+// the reference: mLayers (layer 0 is the environment) gives the execution order, mParentLayers the wiring.
+// It can be edited (addCellAfter / Before / Between, removeCell: what the post-training quantization does when
+// it inserts and fuses ScalingCells) until initialize() hands the cells, layer by layer, to the C ABI.
 class DeepNet {
 public:
     DeepNet(unsigned int stimuliChannels, unsigned int stimuliHeight, unsigned int stimuliWidth, int device = 0)
+        : mDevice(device), mStimuli{stimuliChannels, stimuliHeight, stimuliWidth}
     {
-        check(n2d2b_net_create(device, &mNet));
-        int id = 0;
-        check(n2d2b_net_set_input(mNet, (int)stimuliChannels, (int)stimuliHeight, (int)stimuliWidth,
-                                  DeepNetExport::mEnvDataUnsigned() ? 1 : 0, &id));
-        mShapes[id] = {stimuliChannels, stimuliHeight, stimuliWidth};
+        mLayers.push_back(std::vector<std::string>(1, "env"));
     }
-    ~DeepNet() { n2d2b_net_destroy(mNet); }
+    ~DeepNet() { if (mNet) n2d2b_net_destroy(mNet); }
     DeepNet(const DeepNet&) = delete;
     DeepNet& operator=(const DeepNet&) = delete;
 
-    // parents: empty = the stimuli (the reference passes a null parent for the environment)
+    // parents: empty or a null pointer = the stimuli (the reference passes a null parent for the environment)
     void addCell(const std::shared_ptr<Cell>& cell, const std::vector<std::shared_ptr<Cell> >& parents)
     {
+        editable();
         if (mCells.count(cell->getName())) throw std::runtime_error("DeepNet::addCell(): cell " + cell->getName() + " already exists");
+        std::vector<std::shared_ptr<Cell> > ps = parents;
+        if (ps.empty()) ps.push_back(std::shared_ptr<Cell>());
+        std::size_t order = 0;
+        for (const auto& p : ps)
+            if (p) order = std::max(order, layerOf(p->getName()));
+        if (order + 1 >= mLayers.size()) mLayers.resize(order + 2);
+        mLayers[order + 1].push_back(cell->getName());
+        for (const auto& p : ps) mParentLayers.emplace_back(cell->getName(), p ? p->getName() : std::string("env"));
+        mCells[cell->getName()] = cell;
+        inferShapes();
+    }
+
+    // newCell takes `parent` as its input and every child of `parent` is re-wired to newCell
+    void addCellAfter(const std::shared_ptr<Cell>& newCell, const std::shared_ptr<Cell>& parent)
+    {
+        editable();
+        insertNew(newCell);
+        for (auto& link : mParentLayers)
+            if (link.second == parent->getName()) link.second = newCell->getName();
+        mParentLayers.emplace_back(newCell->getName(), parent->getName());
+        mLayers.insert(mLayers.begin() + layerOf(parent->getName()) + 1, std::vector<std::string>(1, newCell->getName()));
+        inferShapes();
+    }
+
+    // newCell takes all the parents of `child`, and `child` takes newCell as its only input
+    void addCellBefore(const std::shared_ptr<Cell>& newCell, const std::shared_ptr<Cell>& child)
+    {
+        editable();
+        insertNew(newCell);
+        std::vector<std::pair<std::string, std::string> > links;
+        bool placed = false;
+        for (const auto& link : mParentLayers) {
+            if (link.first != child->getName()) { links.push_back(link); continue; }
+            links.emplace_back(newCell->getName(), link.second);
+            placed = true;
+        }
+        if (!placed) throw std::runtime_error("The cell '" + child->getName() + "' was not found in the graph.");
+        links.emplace_back(child->getName(), newCell->getName());
+        mParentLayers.swap(links);
+        mLayers.insert(mLayers.begin() + layerOf(child->getName()), std::vector<std::string>(1, newCell->getName()));
+        inferShapes();
+    }
+
+    void addCellBetween(const std::shared_ptr<Cell>& newCell, const std::shared_ptr<Cell>& parent, const std::shared_ptr<Cell>& child)
+    {
+        editable();
+        bool found = false;
+        for (const auto& link : mParentLayers) found = found || (link.first == child->getName() && link.second == parent->getName());
+        if (!found) throw std::runtime_error("The cell '" + parent->getName() + "' isn't a parent of the cell '" + child->getName() + "'.");
+        insertNew(newCell);
+        for (auto& link : mParentLayers)
+            if (link.first == child->getName() && link.second == parent->getName()) { link.second = newCell->getName(); break; }
+        mParentLayers.emplace_back(newCell->getName(), parent->getName());
+        mLayers.insert(mLayers.begin() + layerOf(parent->getName()) + 1, std::vector<std::string>(1, newCell->getName()));
+        inferShapes();
+    }
+
+    // reconnect: the children of `cell` take its parents, in the position `cell` had among their inputs
+    void removeCell(const std::shared_ptr<Cell>& cell, bool reconnect = true)
+    {
+        editable();
+        const std::string name = cell->getName();
+        if (!mCells.count(name)) throw std::runtime_error("DeepNet::removeCell(): layer " + name + " does not exist");
+        std::vector<std::string> parents;
+        for (const auto& link : mParentLayers)
+            if (link.first == name) parents.push_back(link.second);
+        std::vector<std::pair<std::string, std::string> > links;
+        for (const auto& link : mParentLayers) {
+            if (link.first == name) continue;
+            if (link.second != name) { links.push_back(link); continue; }
+            if (reconnect)
+                for (const auto& p : parents) links.emplace_back(link.first, p);
+        }
+        mParentLayers.swap(links);
+        mCells.erase(name);
+        for (std::size_t l = 1; l < mLayers.size();) {
+            auto& layer = mLayers[l];
+            layer.erase(std::remove(layer.begin(), layer.end(), name), layer.end());
+            if (layer.empty()) mLayers.erase(mLayers.begin() + l);
+            else ++l;
+        }
+        inferShapes();
+    }
+
+    std::vector<std::shared_ptr<Cell> > getChildCells(const std::string& name) const
+    {
+        std::vector<std::shared_ptr<Cell> > out;
+        for (const auto& link : mParentLayers)
+            if (link.second == name) out.push_back(mCells.at(link.first));
+        return out;
+    }
+    // a null pointer stands for the environment, as in the reference
+    std::vector<std::shared_ptr<Cell> > getParentCells(const std::string& name) const
+    {
+        std::vector<std::shared_ptr<Cell> > out;
+        for (const auto& link : mParentLayers)
+            if (link.first == name) out.push_back(link.second == "env" ? std::shared_ptr<Cell>() : mCells.at(link.second));
+        return out;
+    }
+    bool hasCell(const std::string& name) const { return mCells.count(name) != 0; }
+    const std::map<std::string, std::shared_ptr<Cell> >& getCells() const { return mCells; }
+
+    template <class T> std::shared_ptr<T> getCell(const std::string& name) const
+    {
+        auto it = mCells.find(name);
+        if (it == mCells.end()) throw std::runtime_error("DeepNet::getCell(): layer " + name + " does not exist");
+        auto p = std::dynamic_pointer_cast<T>(it->second);
+        if (!p) throw std::runtime_error("DeepNet::getCell(): wrong type for layer " + name);
+        return p;
+    }
+    const std::vector<std::vector<std::string> >& getLayers() const { return mLayers; }
+
+    // Cell::initialize() of every cell: hands the graph to the device library in layer order, allocates
+    // activations for up to maxBatch stimuli.  The graph is frozen afterwards.
+    void initialize(unsigned int maxBatch, bool keepAllOutputs = false)
+    {
+        editable();
+        // device resources appear here, as in the reference (Cell::initialize()); without a usable GPU this throws
+        check(n2d2b_net_create(mDevice, &mNet));
+        int id = 0;
+        check(n2d2b_net_set_input(mNet, (int)mStimuli.c, (int)mStimuli.h, (int)mStimuli.w,
+                                  DeepNetExport::mEnvDataUnsigned() ? 1 : 0, &id));
+        for (std::size_t l = 1; l < mLayers.size(); ++l)
+            for (const std::string& name : mLayers[l]) {
+                lower(mCells.at(name));
+                mLast = mCells.at(name);
+            }
+        if (!mLast) throw std::runtime_error("DeepNet::initialize(): the network has no cells");
+        check(n2d2b_net_finalize(mNet, (int)maxBatch, keepAllOutputs ? (N2D2B_KEEP_ALL_OUTPUTS | N2D2B_NO_FUSION) : 0u));
+        mInitialized = true;
+    }
+
+    // DeepNet::test on a batch of stimuli (8-bit, [batch][height][width][channels]); returns the last
+    // cell's outputs as integers, [batch][outputs].
+    std::vector<int> test(const std::vector<std::uint8_t>& stimuli, unsigned int batch)
+    {
+        if (!mInitialized) throw std::runtime_error("DeepNet::test(): initialize() first");
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, mLast->mTensorId, &info));
+        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
+        std::vector<int> out(n);
+        if (info.dtype == N2D2B_I32) {
+            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, out.data(), nullptr));
+        } else {
+            std::vector<std::uint8_t> raw(n);
+            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, raw.data(), nullptr));
+            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
+        }
+        return out;
+    }
+
+    // Outputs of one cell after test() (needs initialize(..., keepAllOutputs = true)), NHWC.
+    std::vector<int> getOutputs(const std::string& name, unsigned int batch)
+    {
+        const auto cell = getCell<Cell>(name);
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, cell->mTensorId, &info));
+        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
+        std::vector<int> out(n);
+        if (info.dtype == N2D2B_I32) {
+            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, out.data(), n * 4));
+        } else {
+            std::vector<std::uint8_t> raw(n);
+            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, raw.data(), n));
+            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
+        }
+        return out;
+    }
+
+private:
+    struct Shape { unsigned int c, h, w; };
+    static void check(int rc)
+    {
+        if (rc < 0) throw std::runtime_error(n2d2b_last_error());
+    }
+    void editable() const
+    {
+        if (mInitialized) throw std::runtime_error("DeepNet: the graph cannot change after initialize()");
+    }
+    void insertNew(const std::shared_ptr<Cell>& cell)
+    {
+        if (mCells.count(cell->getName())) throw std::runtime_error("DeepNet: cell " + cell->getName() + " already exists");
+        mCells[cell->getName()] = cell;
+    }
+    std::size_t layerOf(const std::string& name) const
+    {
+        for (std::size_t l = 0; l < mLayers.size(); ++l)
+            if (std::find(mLayers[l].begin(), mLayers[l].end(), name) != mLayers[l].end()) return l;
+        throw std::runtime_error("The cell '" + name + "' was not found in the graph.");
+    }
+    Shape shapeOf(const std::string& name) const
+    {
+        if (name == "env") return mStimuli;
+        const auto& c = mCells.at(name);
+        return Shape{c->mNbOutputs, c->mOutputsHeight, c->mOutputsWidth};
+    }
+    // Output dimensions of every cell from its parents' (ConvCell_Frame_Kernels.cpp:37-45, PoolCell.cpp:233-239),
+    // so that getOutputsWidth() / getNbChannels() answer before initialize() as they do in the reference.
+    void inferShapes()
+    {
+        for (std::size_t l = 1; l < mLayers.size(); ++l)
+            for (const std::string& name : mLayers[l]) {
+                Cell& cell = *mCells.at(name);
+                Shape in{0, 0, 0};
+                bool first = true;
+                for (const auto& link : mParentLayers) {
+                    if (link.first != name) continue;
+                    if (first) in = shapeOf(link.second);
+                    first = false;
+                }
+                if (first) continue;   // not wired yet
+                cell.mNbChannels = in.c;
+                cell.mChannelsHeight = in.h;
+                cell.mChannelsWidth = in.w;
+                if (auto* conv = dynamic_cast<ConvCell*>(&cell)) {
+                    auto dim = [](int n, int k, int s, int p0, int p1, int d) { return (unsigned)((n + p0 + p1 - d * (k - 1) - 1 + s) / (double)s); };
+                    cell.mOutputsWidth = dim((int)in.w, (int)conv->mKernelDims[0], (int)conv->mStrideDims[0], conv->mPaddingDims[0], conv->mPaddingDims[2], (int)conv->mDilationDims[0]);
+                    cell.mOutputsHeight = dim((int)in.h, (int)conv->mKernelDims[1], (int)conv->mStrideDims[1], conv->mPaddingDims[1], conv->mPaddingDims[3], (int)conv->mDilationDims[1]);
+                } else if (auto* pool = dynamic_cast<PoolCell*>(&cell)) {
+                    auto dim = [](int n, int k, int s, int p) { return (unsigned)((n + 2 * p - k + s) / (double)s); };
+                    cell.mOutputsWidth = dim((int)in.w, (int)pool->mPoolDims[0], (int)pool->mStrideDims[0], (int)pool->mPaddingDims[0]);
+                    cell.mOutputsHeight = dim((int)in.h, (int)pool->mPoolDims[1], (int)pool->mStrideDims[1], (int)pool->mPaddingDims[1]);
+                } else if (dynamic_cast<FcCell*>(&cell)) {
+                    cell.mOutputsWidth = cell.mOutputsHeight = 1;
+                } else {
+                    cell.mOutputsWidth = in.w;
+                    cell.mOutputsHeight = in.h;
+                }
+            }
+    }
+    void lower(const std::shared_ptr<Cell>& cell)
+    {
         std::vector<int> ins;
-        for (const auto& p : parents) ins.push_back(p ? p->mTensorId : 0);
-        if (ins.empty()) ins.push_back(0);
-        const Shape in = mShapes.at(ins[0]);
+        Shape in{0, 0, 0};
+        for (const auto& link : mParentLayers) {
+            if (link.first != cell->getName()) continue;
+            if (link.second != "env" && mCells.at(link.second)->mTensorId < 0)
+                throw std::runtime_error("DeepNet::initialize(): cell " + cell->getName() + " runs before its parent " + link.second);
+            if (ins.empty()) in = shapeOf(link.second);
+            ins.push_back(link.second == "env" ? 0 : mCells.at(link.second)->mTensorId);
+        }
+        if (ins.empty()) throw std::runtime_error("DeepNet::initialize(): cell " + cell->getName() + " has no input");
         n2d2b_quant q;
         cell->describeQuant(q);
         int id = -1;
@@ -368,80 +646,21 @@ public:
         } else if (dynamic_cast<ScalingCell*>(cell.get())) {
             check(n2d2b_net_add_scaling(mNet, ins[0], &q, &id));
         } else {
-            throw std::runtime_error("DeepNet::addCell(): cell type " + std::string(cell->getType()) + " is not on the quantized path");
+            throw std::runtime_error("DeepNet::initialize(): cell type " + std::string(cell->getType()) + " is not on the quantized path");
         }
         n2d2b_tensor_info info;
         check(n2d2b_net_tensor_info(mNet, id, &info));
+        if ((unsigned)info.width != cell->mOutputsWidth || (unsigned)info.height != cell->mOutputsHeight)
+            throw std::runtime_error("DeepNet::initialize(): output dimensions of " + cell->getName() + " disagree with the device library");
         cell->mTensorId = id;
-        cell->mOutputsWidth = (unsigned)info.width;
-        cell->mOutputsHeight = (unsigned)info.height;
-        mShapes[id] = {(unsigned)info.channels, (unsigned)info.height, (unsigned)info.width};
-        mCells[cell->getName()] = cell;
-        mLayers.push_back({cell->getName()});
-        mLast = cell;
     }
 
-    template <class T> std::shared_ptr<T> getCell(const std::string& name) const
-    {
-        auto it = mCells.find(name);
-        if (it == mCells.end()) throw std::runtime_error("DeepNet::getCell(): layer " + name + " does not exist");
-        auto p = std::dynamic_pointer_cast<T>(it->second);
-        if (!p) throw std::runtime_error("DeepNet::getCell(): wrong type for layer " + name);
-        return p;
-    }
-    const std::vector<std::vector<std::string> >& getLayers() const { return mLayers; }
-
-    // Cell::initialize() of every cell: allocates activations for up to maxBatch stimuli.
-    void initialize(unsigned int maxBatch, bool keepAllOutputs = false)
-    {
-        check(n2d2b_net_finalize(mNet, (int)maxBatch, keepAllOutputs ? (N2D2B_KEEP_ALL_OUTPUTS | N2D2B_NO_FUSION) : 0u));
-    }
-
-    // DeepNet::test on a batch of stimuli (8-bit, [batch][height][width][channels]); returns the last
-    // cell's outputs as integers, [batch][outputs].
-    std::vector<int> test(const std::vector<std::uint8_t>& stimuli, unsigned int batch)
-    {
-        n2d2b_tensor_info info;
-        check(n2d2b_net_tensor_info(mNet, mLast->mTensorId, &info));
-        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
-        std::vector<int> out(n);
-        if (info.dtype == N2D2B_I32) {
-            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, out.data(), nullptr));
-        } else {
-            std::vector<std::uint8_t> raw(n);
-            check(n2d2b_net_forward_host(mNet, stimuli.data(), (int)batch, raw.data(), nullptr));
-            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
-        }
-        return out;
-    }
-
-    // Outputs of one cell after test() (needs initialize(..., keepAllOutputs = true)), NHWC.
-    std::vector<int> getOutputs(const std::string& name, unsigned int batch)
-    {
-        const auto cell = getCell<Cell>(name);
-        n2d2b_tensor_info info;
-        check(n2d2b_net_tensor_info(mNet, cell->mTensorId, &info));
-        const std::size_t n = (std::size_t)info.channels * info.height * info.width * batch;
-        std::vector<int> out(n);
-        if (info.dtype == N2D2B_I32) {
-            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, out.data(), n * 4));
-        } else {
-            std::vector<std::uint8_t> raw(n);
-            check(n2d2b_net_read_tensor(mNet, cell->mTensorId, (int)batch, raw.data(), n));
-            for (std::size_t i = 0; i < n; ++i) out[i] = info.is_unsigned ? (int)raw[i] : (int)(std::int8_t)raw[i];
-        }
-        return out;
-    }
-
-private:
-    struct Shape { unsigned int c, h, w; };
-    static void check(int rc)
-    {
-        if (rc < 0) throw std::runtime_error(n2d2b_last_error());
-    }
     n2d2b_net* mNet = nullptr;
+    int mDevice;
+    Shape mStimuli;
+    bool mInitialized = false;
     std::map<std::string, std::shared_ptr<Cell> > mCells;
-    std::map<int, Shape> mShapes;
+    std::vector<std::pair<std::string, std::string> > mParentLayers;   // (cell, parent) in input order; "env" = stimuli
     std::vector<std::vector<std::string> > mLayers;
     std::shared_ptr<Cell> mLast;
 };

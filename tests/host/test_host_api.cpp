@@ -3,7 +3,7 @@
 // computation - here the oracle (test infrastructure), which follows the reference's CPU cells.
 //
 //   test_host_api            runs the mnist24 topology (8-bit, SingleShift) on cuda:0, exit 0 = equal
-//   test_host_api --no-gpu   checks that construction fails loudly without a device
+//   test_host_api --no-gpu   checks that DeepNet::initialize fails loudly without a device
 #include <cstdio>
 #include <cstring>
 #include <numeric>
@@ -48,11 +48,17 @@ int main(int argc, char** argv)
     if (no_gpu) {
         try {
             DeepNet dn(C, H, W);
+            auto lin = std::make_shared<LinearActivation>();
+            lin->setActivationScaling(Scaling::singleShiftScaling(std::vector<unsigned char>(4, 3), false, {}));
+            auto fc = std::make_shared<FcCell>("fc", 4, lin);
+            fc->setWeights(std::vector<int8_t>((size_t)4 * C * H * W, 1));
+            dn.addCell(fc, {});
+            dn.initialize(1);     // device resources are created here: no GPU, no network
         } catch (const std::runtime_error& e) {
             printf("failed loudly as expected: %s\n", e.what());
             return 0;
         }
-        fprintf(stderr, "DeepNet construction succeeded without a GPU\n");
+        fprintf(stderr, "DeepNet::initialize succeeded without a GPU\n");
         return 1;
     }
 
