@@ -205,6 +205,19 @@ int n2d2b_net_wait(n2d2b_net* net);
  * faults or traps; the next n2d2b_net_check returns N2D2B_ERR_TIMEOUT and the network stays usable. */
 int n2d2b_net_selftest_wait_timeout(n2d2b_net* net, unsigned limit_us, n2d2b_stream stream);
 
+/* Output edge, Target top-1 (src/Target/Target_CUDA_kernels.cu:88-104; TargetScore): the class with the highest
+ * score of the last forward pass's final tensor, per image (and per pixel when the tensor is a map); among
+ * equal scores the lowest class index wins, as in the reference.  d_labels (and d_values, optional: the winning
+ * scores) are device buffers of batch x height x width int32.  Asynchronous on `stream`, which must be the stream
+ * of that forward pass (or ordered after it). */
+int n2d2b_net_estimated_labels(n2d2b_net* net, int batch, int32_t* d_labels, int32_t* d_values, n2d2b_stream stream);
+/* Input edge: the transformation quantizeNetwork puts in front of the network (src/DeepNetQuantization.cpp:359-370:
+ * multiply by 2^nb_bits - 1 for unsigned stimuli, 2^(nb_bits-1) - 1 for signed ones, then truncate).  d_in holds
+ * float stimuli in the reference's layout [batch][channel][y][x]; d_out receives 8-bit [batch][y][x][channel], the
+ * layout n2d2b_net_forward takes.  Values outside the 8-bit range of the signedness saturate. */
+int n2d2b_quantize_stimuli(int device, const float* d_in, int batch, int channels, int height, int width, int nb_bits,
+                           int env_unsigned, void* d_out, n2d2b_stream stream);
+
 int n2d2b_net_num_tensors(const n2d2b_net* net);
 int n2d2b_net_tensor_info(const n2d2b_net* net, int tensor_id, n2d2b_tensor_info* info);
 /* Copies a tensor of the last forward (first `batch` images) to the host. */

@@ -10,7 +10,9 @@
 // tcgen05.mma kind::i8 into one of two TMEM accumulators, warps 2-17 drain the other accumulator with
 // tcgen05.ld and run the fused epilogue (bias, per-channel rescale, rounding, saturation, ReLU,
 // optional residual add + second rescale) straight to int8 NHWC: every warp owns the 32 rows of its
-// TMEM lane quadrant and a quarter of the tile's columns.  This replaces the reference's
+// TMEM lane quadrant and a quarter of the tile's columns.  Cells on the 32-bit epilogue store their weight
+// rows permuted inside blocks of 32 (16) output channels, so that the column pairs a TMEM load hands a
+// thread are 8 (4) consecutive channels: constants, residual and output move as 128- and 64-bit accesses.  This replaces the reference's
 // cudnnConvolutionForward + cudnnAddTensor + Scaling kernel + cudnnActivationForward sequence
 // (src/Cell/ConvCell_Frame_CUDA.cpp:1169-1270) and its cublasGemm FC
 // (src/Cell/FcCell_Frame_CUDA.cpp:308-427).
@@ -254,7 +256,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         unsigned acc_it = 0;
         unsigned stage_it = 0;
         EpiState est;
-        frag_rowbase(est.rb, a.BN >> 2, lane);
+        perm_rowbase(est.rb, a.BN >> 2, lane, (a.BN >> 2) >= 32 ? 4 : 2);
         int staged_n_tile = -1;
         int* par = epi_params;
         bool ok = true;
@@ -331,7 +333,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 e.abort_flag = abort_flag; e.status = a.status;
                 e.ef = a.ef;
                 e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
-                if (!fast_epilogue_tile<RES, CLAMP, DP>(&tmO, &tmR, e, quad, part, lane, est)) { ok = false; break; }
+                if (!fast_epilogue_tile<RES, CLAMP, DP, true>(&tmO, &tmR, e, quad, part, lane, est)) { ok = false; break; }
                 continue;
             } else {
                 if (!mbar_wait_warp(tfull0 + 8u * as, aph, abort_flag, a.status, 4, lane)) { ok = false; break; }
@@ -560,7 +562,7 @@ igemm_pair_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * PAIR_REGION);
         const unsigned region = smem_u32(stage_out + (size_t)ew * PAIR_REGION);
         unsigned rb[4];
-        frag_rowbase(rb, 32, lane);
+        perm_rowbase(rb, 32, lane, 4);
         // the launch keeps every CTA on one column block: its constants are staged once
         const int n0 = ((int)blockIdx.x % a.num_n_tiles) * 256;
         for (int i = ew * 32 + lane; i < FAST_NP * 256; i += 32 * NUM_EPI_WARPS) {
@@ -595,11 +597,11 @@ igemm_pair_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                         unsigned va[16], vb[16];
                         tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(32 * pass), va, vb);
                         if (a.out_unsigned)
-                            frag_block<4, false, CLAMP, false, EF_OUT_UNSIGNED>(va, vb, par_off, cbase + 32 * pass, region_off, rb, 0,
-                                                                                lane, 0, 0, 0u);
+                            perm_block<4, false, CLAMP, false, EF_OUT_UNSIGNED | EF_PERM>(va, vb, par_off, cbase + 32 * pass, region_off, rb,
+                                                                                          0, lane, 0, 0, 0u);
                         else
-                            frag_block<4, false, CLAMP, false, 0>(va, vb, par_off, cbase + 32 * pass, region_off, rb, 0, lane, 0,
-                                                                  0, 0u);
+                            perm_block<4, false, CLAMP, false, EF_PERM>(va, vb, par_off, cbase + 32 * pass, region_off, rb, 0, lane,
+                                                                        0, 0, 0u);
                     }
                     if (pass == 1) {
                         // the accumulator is drained: hand it back before the store goes out
@@ -829,6 +831,19 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     return 0;
 }
 
+bool igemm_uses_fast_epilogue(const IgemmPlan& plan, const FastQuant& fast, bool has_residual, int out_dtype)
+{
+    return fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!has_residual || fast.fq2) && plan.has_out_maps;
+}
+
+int igemm_perm_block(const IgemmPlan& plan) { return (plan.BN >> 2) >= 32 ? 32 : 16; }
+
+void igemm_permute_weights(const int8_t* w, int8_t* dst, int N, size_t row_bytes, int perm_block)
+{
+    const int ng = perm_block / 8;
+    for (int n = 0; n < N; ++n) memcpy(dst + (size_t)n * row_bytes, w + (size_t)perm_real_channel(n, ng) * row_bytes, row_bytes);
+}
+
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast, void* out,
                          int out_dtype, int m_base, int* status_word, cudaStream_t s)
 {
@@ -860,10 +875,12 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.out_unsigned = fast.out_unsigned;
     a.dp_xor = fast.dp_xor;
     a.dp_a_signed = fast.dp_a_signed;
+    const bool t_unsigned = fast.dp4a ? fast.dp_t_unsigned : (fast.t_lo == 0);
     a.ef = (fast.out_unsigned ? EF_OUT_UNSIGNED : 0) | (r.is_unsigned ? EF_RES_UNSIGNED : 0)
-         | (fast.t_lo == 0 ? EF_T_UNSIGNED : 0) | (fast.dp_a_signed ? EF_DP_A_SIGNED : 0) | (fast.wide ? EF_WIDE : 0);
-    const bool use_fast = fast.enabled && out_dtype == DT_I8 && (plan.N % 32 == 0) && (!r.ptr || fast.fq2)
-                          && plan.has_out_maps;
+         | (t_unsigned ? EF_T_UNSIGNED : 0) | (fast.dp_a_signed ? EF_DP_A_SIGNED : 0) | (fast.wide ? EF_WIDE : 0);
+    const bool use_fast = igemm_uses_fast_epilogue(plan, fast, r.ptr != nullptr, out_dtype);
+    // the weights of a cell on the 32-bit epilogue are stored permuted (and only those)
+    if (use_fast != (plan.perm != 0)) return cudaErrorInvalidConfiguration;
     const int mode = !use_fast ? 0 : (r.ptr ? (fast.need_clamp ? 2 : (fast.dp4a ? 5 : 4)) : (fast.need_clamp ? 1 : 3));
     static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;

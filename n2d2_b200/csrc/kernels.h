@@ -47,6 +47,11 @@ cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void
 cudaError_t launch_pool_i32(const void* in, const PoolGeom& g, void* out, cudaStream_t s);
 cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, const QuantDev& q,
                                 void* out, int out_dtype, cudaStream_t s);
+// Top-1 class per pixel (first maximum wins) of [pixels][C] scores; values may be nullptr.
+cudaError_t launch_argmax(const void* scores, int dtype, int is_unsigned, size_t pixels, int C, int32_t* labels, int32_t* values,
+                          cudaStream_t s);
+// Float stimuli NCHW -> trunc(x * factor) clamped to [lo, hi], 8-bit NHWC.
+cudaError_t launch_quantize_stimuli(const float* in, int B, int C, int H, int W, float factor, int lo, int hi, void* out, cudaStream_t s);
 // Fully connected on CUDA cores: in [B][K], w [O][K] int8.
 cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, int B, int K, int O,
                              const QuantDev& q, void* out, int out_dtype, cudaStream_t s);
@@ -62,6 +67,7 @@ struct FastQuant {
     bool need_clamp = true;     // false: no product can leave 32 bits and saturation is the final pack's
     bool wide = false;          // first rescale in 64 bits: row 0 of fq holds the upper words of the addends (no clamps)
     bool dp4a = false;          // residual stage as a byte dot product (multipliers <= 255, native 8-bit ranges)
+    bool dp_t_unsigned = false; //   the cell's own output is packed as unsigned bytes (natively, or shifted by +128)
     unsigned dp_xor = 0;        //   bytes to flip from unsigned to signed (0x80 per byte)
     int dp_a_signed = 1;        //   signedness of the (t, r) byte vector
     bool enabled = false;
@@ -126,6 +132,7 @@ struct IgemmPlan {
     int stages;
     int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
     int res_slots;        // fused residual: staging regions per epilogue warp (2 or 4), 0 without a residual
+    int perm;             // weight rows stored permuted inside blocks of this many output channels (32 or 16; 0 = not)
     int pair;             // large-K layer with 256-column tiles: CTAs take two 128-row tiles per weight slab
     CUtensorMap tmO32;    // output [M][N] bytes, box = 32 rows x 32 columns (the pair kernel's two-pass store)
     size_t pair_smem_bytes;
@@ -140,6 +147,11 @@ struct IgemmPlan {
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
                     const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
                     int force_pair = 0);
+// Whether a launch of this plan takes the 32-bit epilogue; such a cell's weight rows must be stored in the
+// permuted order (igemm_permute_weights with igemm_perm_block(plan)) and plan.perm set to that block size.
+bool igemm_uses_fast_epilogue(const IgemmPlan& plan, const FastQuant& fast, bool has_residual, int out_dtype);
+int igemm_perm_block(const IgemmPlan& plan);
+void igemm_permute_weights(const int8_t* w, int8_t* dst, int N, size_t row_bytes, int perm_block);
 // m_base: first output row (pixel) of this call within the tensors the plan was encoded for; `out` and the
 // residual stay the tensors' base pointers
 cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residual& r, const FastQuant& fast,

@@ -124,7 +124,9 @@ struct n2d2b_net {
     void* d_pipe_in[2] = {nullptr, nullptr};
     void* d_pipe_out[2] = {nullptr, nullptr};
     cudaEvent_t pipe_uploaded[2] = {nullptr, nullptr};
+    cudaEvent_t pipe_computed[2] = {nullptr, nullptr};
     cudaEvent_t pipe_done[2] = {nullptr, nullptr};
+    cudaStream_t download_stream = nullptr;
     bool pipe_busy[2] = {false, false};
     cudaStream_t pipe_stream[2] = {nullptr, nullptr};   // the stream each slot's work was queued on
     unsigned pipe_next = 0;
@@ -386,27 +388,43 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     bool with_res = c.residual >= 0;
     if (with_res && !build_fast_quant(c.q2, cpad, 512, f2, &lo2, &hi2, &need_clamp)) return 0;
     if (wide && need_clamp) return 0;   // the 64-bit form has no clamps
-    // Dot-product form of the residual stage (see frag_block): every multiplier of the sum's scaling fits
-    // a byte, both operands have a native 8-bit range and no clamp is needed.
-    bool dp4a = false;
+    // Dot-product form of the residual stage (see perm_block): every multiplier of the sum's scaling fits a byte,
+    // both operands have a native 8-bit range and no clamp is needed.  The four bytes [t, t', r, r'] of a dot
+    // product share one signedness: when the cell's own output is signed and the residual unsigned, the first
+    // rescale produces t + 128 instead (its addend grows by 128 << shift, a multiple of 2^shift, so the shifted
+    // value is exactly 128 larger and the unsigned saturating pack clamps at the same places) and the second
+    // addend drops 128 * m2.
+    bool dp4a = false, dp_t_unsigned = false;
     unsigned dp_xor = 0;
     int dp_a_signed = 1;
     if (with_res && !need_clamp && !wide && residual_dtype_i8) {
         const bool t_uns = (lo1 == 0 && hi1 == 255), t_sig = (lo1 == -128 && hi1 == 127);
-        bool small = true;
-        for (int ch = 0; ch < C; ++ch) small = small && f2[(size_t)2 * cpad + ch] >= 0 && f2[(size_t)2 * cpad + ch] <= 255;
-        if ((t_uns || t_sig) && small) {
+        const bool r_uns = residual_unsigned != 0;
+        bool ok = t_uns || t_sig;
+        for (int ch = 0; ch < C; ++ch) ok = ok && f2[(size_t)2 * cpad + ch] >= 0 && f2[(size_t)2 * cpad + ch] <= 255;
+        if (ok && t_uns && !r_uns) ok = false;   // unsigned output with a signed residual: the exact two-step form
+        const bool shift_t = ok && t_sig && r_uns;
+        if (shift_t) {
+            const long long LIM = (1ll << 31) - 1;
+            for (int ch = 0; ch < C && ok; ++ch) {
+                const long long m = f1[(size_t)2 * cpad + ch], add = f1[(size_t)3 * cpad + ch], sh = f1[(size_t)4 * cpad + ch];
+                const long long nadd = add + (128ll << sh);
+                if (acc_bound * m + std::llabs(nadd) > LIM) ok = false;
+            }
+        }
+        if (ok) {
             dp4a = true;
-            const bool flip = (t_uns != (residual_unsigned != 0));
-            dp_a_signed = (t_uns && residual_unsigned) ? 0 : 1;
-            // the byte vector is [t0, t1, r0, r1]: flip the unsigned pair when the two differ
-            if (flip) dp_xor = t_uns ? 0x00008080u : 0x80800000u;
+            dp_t_unsigned = t_uns || shift_t;
+            dp_a_signed = dp_t_unsigned ? 0 : 1;
             for (int ch = 0; ch < cpad; ++ch) {
                 const long long m2 = f2[(size_t)2 * cpad + ch];
                 // row 0 of the residual set: the multiplier in the byte lanes of this column (even column:
-                // lanes 0 and 2 = t0 and r0; odd column: lanes 1 and 3)
+                // lanes 0 and 2 = t and r; odd column: lanes 1 and 3)
                 f2[(size_t)0 * cpad + ch] = (int32_t)((ch & 1) ? (m2 << 8 | m2 << 24) : (m2 | m2 << 16));
-                if (flip) f2[(size_t)3 * cpad + ch] += (int32_t)(128 * m2);
+                if (shift_t) {
+                    f1[(size_t)3 * cpad + ch] += (int32_t)(128ll << f1[(size_t)4 * cpad + ch]);
+                    f2[(size_t)3 * cpad + ch] -= (int32_t)(128 * m2);
+                }
             }
         }
     }
@@ -423,6 +441,7 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     c.fast.need_clamp = need_clamp;
     c.fast.wide = wide;
     c.fast.dp4a = dp4a;
+    c.fast.dp_t_unsigned = dp_t_unsigned;
     c.fast.dp_xor = dp_xor;
     c.fast.dp_a_signed = dp_a_signed;
     c.fast.enabled = true;
@@ -544,8 +563,10 @@ void n2d2b_net_destroy(n2d2b_net* net)
         cudaFree(net->d_pipe_in[k]);
         cudaFree(net->d_pipe_out[k]);
         if (net->pipe_uploaded[k]) cudaEventDestroy(net->pipe_uploaded[k]);
+        if (net->pipe_computed[k]) cudaEventDestroy(net->pipe_computed[k]);
         if (net->pipe_done[k]) cudaEventDestroy(net->pipe_done[k]);
     }
+    if (net->download_stream) cudaStreamDestroy(net->download_stream);
     delete net;
 }
 
@@ -968,6 +989,17 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                     && patch_make_plan(&c.patch, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
                                        net->num_sms, &why) == 0)
                     c.engine = ENG_PATCH;
+                // a cell that stays on the implicit-GEMM kernel with the 32-bit epilogue stores its weight rows in
+                // the permuted order that epilogue reads (see perm_block)
+                if (c.engine == ENG_TCGEN05
+                    && igemm_uses_fast_epilogue(c.plan, c.fast, c.residual >= 0, net->tensors[c.output].dtype)) {
+                    const int pb = igemm_perm_block(c.plan);
+                    const size_t row_bytes = (size_t)g.kH * g.kW * g.Cg;
+                    std::vector<int8_t> permuted(laid.size());
+                    igemm_permute_weights(laid.data(), permuted.data(), g.O, row_bytes, pb);
+                    CUDA_TRY(cudaMemcpy(c.d_weights, permuted.data(), permuted.size(), cudaMemcpyHostToDevice));
+                    c.plan.perm = pb;
+                }
             }
         }
     }
@@ -1000,8 +1032,10 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     }
     for (int k = 0; k < 2; ++k) {
         CUDA_TRY(cudaEventCreateWithFlags(&net->pipe_uploaded[k], cudaEventDisableTiming));
+        CUDA_TRY(cudaEventCreateWithFlags(&net->pipe_computed[k], cudaEventDisableTiming));
         CUDA_TRY(cudaEventCreateWithFlags(&net->pipe_done[k], cudaEventDisableTiming));
     }
+    CUDA_TRY(cudaStreamCreateWithFlags(&net->download_stream, cudaStreamNonBlocking));
     net->finalized = true;
     return 0;
 }
@@ -1036,10 +1070,12 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
             ConvGeom gb = c.geom;
             gb.B = net->max_batch;
             const char* why = "";
+            const int perm = c.plan.perm;   // a property of the stored weights, not of the tensor maps
             if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? out : nullptr, r.ptr, gb, tin.is_unsigned,
                                 (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
                                 (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
+            c.plan.perm = perm;
             c.plan_input = in0;
         }
         IgemmPlan p = c.plan;
@@ -1285,16 +1321,23 @@ int n2d2b_net_submit_host(n2d2b_net* net, const void* h_input, int batch, void* 
         CUDA_TRY(cudaMalloc(&net->d_pipe_out[slot], out_cap));
     }
     // the slot's previous batch (two submissions ago) must have left its staging buffers: its forward pass has
-    // read the input and its download has read the output
-    if (net->pipe_busy[slot]) CUDA_TRY(cudaStreamWaitEvent(net->copy_stream, net->pipe_done[slot], 0));
+    // read the input (the upload waits for that) and its download has read the output (the forward pass, which
+    // writes the output buffer last, waits for that)
+    if (net->pipe_busy[slot]) {
+        CUDA_TRY(cudaStreamWaitEvent(net->copy_stream, net->pipe_computed[slot], 0));
+        CUDA_TRY(cudaStreamWaitEvent(s, net->pipe_done[slot], 0));
+    }
     const size_t in_bytes = net->tensors[0].bytes_per_image() * (size_t)batch;
     const size_t out_bytes = net->tensors[ft].bytes_per_image() * (size_t)batch;
     CUDA_TRY(cudaMemcpyAsync(net->d_pipe_in[slot], h_input, in_bytes, cudaMemcpyHostToDevice, net->copy_stream));
     CUDA_TRY(cudaEventRecord(net->pipe_uploaded[slot], net->copy_stream));
     CUDA_TRY(cudaStreamWaitEvent(s, net->pipe_uploaded[slot], 0));
     if (int rc = forward_impl(net, net->d_pipe_in[slot], batch, net->d_pipe_out[slot], s, nullptr, 0)) return rc;
-    CUDA_TRY(cudaMemcpyAsync(h_output, net->d_pipe_out[slot], out_bytes, cudaMemcpyDeviceToHost, s));
-    CUDA_TRY(cudaEventRecord(net->pipe_done[slot], s));
+    // the download leaves on a stream of its own, so that `s` holds nothing but forward passes back to back
+    CUDA_TRY(cudaEventRecord(net->pipe_computed[slot], s));
+    CUDA_TRY(cudaStreamWaitEvent(net->download_stream, net->pipe_computed[slot], 0));
+    CUDA_TRY(cudaMemcpyAsync(h_output, net->d_pipe_out[slot], out_bytes, cudaMemcpyDeviceToHost, net->download_stream));
+    CUDA_TRY(cudaEventRecord(net->pipe_done[slot], net->download_stream));
     net->pipe_busy[slot] = true;
     net->pipe_stream[slot] = s;
     net->pipe_next++;
@@ -1312,6 +1355,33 @@ int n2d2b_net_wait(n2d2b_net* net)
             net->pipe_busy[k] = false;
         }
     return check_status(net);
+}
+
+int n2d2b_net_estimated_labels(n2d2b_net* net, int batch, int32_t* d_labels, int32_t* d_values, n2d2b_stream stream)
+{
+    if (!net || !d_labels) return fail(N2D2B_ERR_INVALID, "net and d_labels must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "estimated labels before finalize");
+    if (!net->last_input) return fail(N2D2B_ERR_STATE, "estimated labels before a forward pass");
+    if (batch < 0 || batch > net->max_batch) return fail(N2D2B_ERR_TOO_LARGE, "batch out of range");
+    CUDA_TRY(cudaSetDevice(net->device));
+    const int ft = final_tensor_of(net);
+    const TensorRec& t = net->tensors[ft];
+    CUDA_TRY(launch_argmax(tensor_ptr(net, ft, net->last_input), t.dtype, t.is_unsigned, (size_t)batch * t.H * t.W, t.C, d_labels,
+                           d_values, (cudaStream_t)stream));
+    return 0;
+}
+
+int n2d2b_quantize_stimuli(int device, const float* d_in, int batch, int channels, int height, int width, int nb_bits,
+                           int env_unsigned, void* d_out, n2d2b_stream stream)
+{
+    if (!d_in || !d_out) return fail(N2D2B_ERR_INVALID, "device buffers must not be NULL");
+    if (batch < 0 || channels < 1 || height < 1 || width < 1) return fail(N2D2B_ERR_INVALID, "invalid stimuli dimensions");
+    if (nb_bits < 2 || nb_bits > 8) return fail(N2D2B_ERR_INVALID, "nb_bits must be in 2..8 (the path carries 8-bit stimuli)");
+    CUDA_TRY(cudaSetDevice(device));
+    const int hi = env_unsigned ? (1 << nb_bits) - 1 : (1 << (nb_bits - 1)) - 1;
+    const int lo = env_unsigned ? 0 : -(1 << (nb_bits - 1));
+    CUDA_TRY(launch_quantize_stimuli(d_in, batch, channels, height, width, (float)hi, lo, hi, d_out, (cudaStream_t)stream));
+    return 0;
 }
 
 int n2d2b_net_num_tensors(const n2d2b_net* net) { return net ? (int)net->tensors.size() : fail(N2D2B_ERR_INVALID, "net must not be NULL"); }

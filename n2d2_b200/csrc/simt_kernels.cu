@@ -487,6 +487,39 @@ __global__ void pool_scalar_kernel(const void* __restrict__ in, int in_unsigned,
     }
 }
 
+// Average over the whole feature map (the pooling cell before the classifier): one thread per four channels of
+// an image, so a warp reads 128 consecutive bytes per pixel and every load of the pixel loop is independent of
+// the others.  Bytes are summed as two pairs of 16-bit lanes (signed inputs are biased to unsigned by flipping
+// the top bit and un-biased at the end; up to 257 pixels fit a lane).  Divides by the window size and truncates
+// toward zero like the reference's quantized cell.
+template <bool UNSIGNED>
+__global__ void pool_global_avg_kernel(const uint8_t* __restrict__ in, int pixels, int C, size_t total_words,
+                                       uint8_t* __restrict__ out)
+{
+    const int cw = C / 4;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_words; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t b = idx / cw;
+        const int w = (int)(idx - b * cw);
+        const unsigned* p = (const unsigned*)(in + b * (size_t)pixels * C) + w;
+        unsigned even = 0, odd = 0;   // bytes 0, 2 and bytes 1, 3 as 16-bit lanes
+#pragma unroll 7
+        for (int i = 0; i < pixels; ++i) {
+            unsigned x = __ldg(p + (size_t)i * cw);
+            if (!UNSIGNED) x ^= 0x80808080u;
+            even += x & 0x00ff00ffu;
+            odd += (x >> 8) & 0x00ff00ffu;
+        }
+        int v[4] = {(int)(even & 0xffffu), (int)(odd & 0xffffu), (int)(even >> 16), (int)(odd >> 16)};
+        unsigned o = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (!UNSIGNED) v[j] -= 128 * pixels;
+            o |= ((unsigned)(v[j] / pixels) & 0xffu) << (8 * j);   // C division truncates toward zero
+        }
+        ((unsigned*)out)[idx] = o;
+    }
+}
+
 cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void* out, cudaStream_t s)
 {
     // int8 tensors; int32 tensors go through launch_pool_i32
@@ -499,6 +532,14 @@ cudaError_t launch_pool(const void* in, int in_unsigned, const PoolGeom& g, void
         const unsigned grid = (unsigned)(rows < (1ll << 20) ? rows : (1ll << 20));
         if (in_unsigned) pool_max_row_kernel<true><<<grid, threads, 0, s>>>((const uint8_t*)in, g, (uint8_t*)out);
         else pool_max_row_kernel<false><<<grid, threads, 0, s>>>((const uint8_t*)in, g, (uint8_t*)out);
+    } else if (!g.is_max && g.C % 4 == 0 && g.pH == g.H && g.pW == g.W && g.padY == 0 && g.padX == 0 && g.oH == 1 && g.oW == 1
+               && g.H * g.W <= 257 && ((uintptr_t)in & 3) == 0 && ((uintptr_t)out & 3) == 0) {
+        const size_t total = (size_t)g.B * (g.C / 4);
+        if (total == 0) return cudaSuccess;
+        if (in_unsigned)
+            pool_global_avg_kernel<true><<<grid_for(total, block), block, 0, s>>>((const uint8_t*)in, g.H * g.W, g.C, total, (uint8_t*)out);
+        else
+            pool_global_avg_kernel<false><<<grid_for(total, block), block, 0, s>>>((const uint8_t*)in, g.H * g.W, g.C, total, (uint8_t*)out);
     } else if (g.C % 16 == 0) {
         const size_t total = (size_t)g.B * g.oH * g.oW * (g.C / 16);
         if (total == 0) return cudaSuccess;
@@ -615,6 +656,77 @@ cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, i
         fc_direct_kernel<int8_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, B, K, O, q, out);
     else
         fc_direct_kernel<int32_t><<<grid, block, 0, s>>>((const uint8_t*)in, in_unsigned, w, B, K, O, q, out);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Output edge: estimated label = the class with the highest score, the first one among equals
+// (Target top-1, src/Target/Target_CUDA_kernels.cu:88-104 of the reference: `if (tmp > maxVal)`).
+// One warp per (image, pixel); scores are [pixels][C] int8 or int32.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void argmax_kernel(const T* __restrict__ scores, size_t pixels, int C, int32_t* __restrict__ labels,
+                              int32_t* __restrict__ values)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t p = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < pixels; p += warps) {
+        const T* row = scores + p * (size_t)C;
+        int best = INT32_MIN, idx = 0x7fffffff;
+        for (int c = lane; c < C; c += 32) {
+            const int v = (int)row[c];
+            if (v > best || idx == 0x7fffffff) { best = v; idx = c; }   // ascending c within a lane: the first of equals stays
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const int ob = __shfl_xor_sync(0xffffffffu, best, off), oi = __shfl_xor_sync(0xffffffffu, idx, off);
+            if (oi != 0x7fffffff && (idx == 0x7fffffff || ob > best || (ob == best && oi < idx))) { best = ob; idx = oi; }
+        }
+        if (lane == 0) {
+            labels[p] = idx;
+            if (values) values[p] = best;
+        }
+    }
+}
+
+cudaError_t launch_argmax(const void* scores, int dtype, int is_unsigned, size_t pixels, int C, int32_t* labels, int32_t* values,
+                          cudaStream_t s)
+{
+    if (pixels == 0 || C == 0) return cudaSuccess;
+    const int block = 256;
+    const unsigned grid = grid_for(pixels * 32, block);
+    if (dtype == DT_I32) argmax_kernel<int32_t><<<grid, block, 0, s>>>((const int32_t*)scores, pixels, C, labels, values);
+    else if (is_unsigned) argmax_kernel<uint8_t><<<grid, block, 0, s>>>((const uint8_t*)scores, pixels, C, labels, values);
+    else argmax_kernel<int8_t><<<grid, block, 0, s>>>((const int8_t*)scores, pixels, C, labels, values);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Input edge: what the post-training quantization puts in front of the network
+// (src/DeepNetQuantization.cpp:359-370: RangeAffineTransformation(Multiplies, 2^n - 1 or 2^(n-1) - 1) with
+// Truncate): float stimuli [batch][channel][y][x] -> trunc(x * factor) as 8-bit [batch][y][x][channel].
+// The product is a float32 multiply rounded to nearest, as on the reference's float tensors.
+// ---------------------------------------------------------------------------------------------
+__global__ void quantize_stimuli_kernel(const float* __restrict__ in, int C, int H, int W, size_t total, float factor, int lo, int hi,
+                                        uint8_t* __restrict__ out)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % C);
+        size_t p = idx / C;
+        const int x = (int)(p % W); p /= W;
+        const int y = (int)(p % H);
+        const size_t b = p / H;
+        float v = truncf(__fmul_rn(in[((b * C + c) * H + y) * W + x], factor));
+        v = fminf(fmaxf(v, (float)lo), (float)hi);
+        out[idx] = (uint8_t)(int)v;
+    }
+}
+
+cudaError_t launch_quantize_stimuli(const float* in, int B, int C, int H, int W, float factor, int lo, int hi, void* out, cudaStream_t s)
+{
+    const size_t total = (size_t)B * C * H * W;
+    if (total == 0) return cudaSuccess;
+    quantize_stimuli_kernel<<<grid_for(total, 256), 256, 0, s>>>(in, C, H, W, total, factor, lo, hi, (uint8_t*)out);
     return cudaGetLastError();
 }
 

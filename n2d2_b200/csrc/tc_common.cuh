@@ -350,6 +350,8 @@ static constexpr int EF_RES_UNSIGNED = 2;   // residual operand is unsigned
 static constexpr int EF_T_UNSIGNED = 4;     // DP: the cell's own output saturates to [0,255]
 static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are read as signed
 static constexpr int EF_WIDE = 16;          // first rescale in 64 bits: x * mult + (row 0 : row 3 as a 64-bit addend) >> shift
+static constexpr int EF_DP_XOR = 32;        // DP: some of the packed (t, r) bytes are flipped between unsigned and signed (dp_xor)
+static constexpr int EF_PERM = 64;          // weights stored with permuted output channels (perm_block)
 
 // NG 8-column groups (NG = 4: 32 columns, NG = 2: 16) of a warp's 32 accumulator rows in the fragment layout
 // of the 16x256b TMEM load (thread t: rows t/4 + {0, 8, 16, 24}, column pair 8i + 2(t%4) of group i), through the
@@ -497,6 +499,156 @@ __device__ __forceinline__ void frag_block(const unsigned* vA, const unsigned* v
     }
 }
 
+// ---- the same epilogue on weights whose output channels are permuted inside every block of 8 * NG channels -----------
+// The 16x256b TMEM load hands a thread column pairs that are eight columns apart (8i + 2q + e, q = lane % 4).  When the
+// weight rows of a block are stored in the order
+//     stored row 8i + 2q + e  =  real channel 2 NG q + 2i + e        (i < NG, q < 4, e < 2)
+// those columns are the thread's 2 NG CONSECUTIVE real channels: per row it reads its per-channel constants with
+// 128-bit loads, the residual with one 64-bit (NG = 4) or 32-bit (NG = 2) load, and writes its bytes with one
+// store, instead of one 16-bit access per column pair.  The staging region keeps the real channel order, so the
+// TMA store and the residual load are unchanged.
+__host__ __device__ inline int perm_real_channel(int stored, int ng)
+{
+    const int blk = 8 * ng, j = stored % blk;
+    const int i = j >> 3, q = (j >> 1) & 3, e = j & 1;
+    return stored - j + 2 * ng * q + 2 * i + e;
+}
+
+// Row terms of a lane's staging addresses for the permuted layout: the lane's first byte column is 2 NG q.
+__device__ __forceinline__ void perm_rowbase(unsigned* rb, int wb, int lane, int ng)
+{
+    const int tr = lane >> 2, tc = (lane & 3) * 2 * ng;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const unsigned ro = (unsigned)((tr + 8 * k) * wb);
+        const unsigned xm = ((ro >> 7) & (unsigned)(wb / 16 - 1)) << 4;
+        rb[k] = ro + ((unsigned)tc ^ xm);
+    }
+}
+
+__device__ __forceinline__ unsigned pack4_sat(int y0, int y1, int y2, int y3, bool out_unsigned)
+{
+    unsigned p, w;
+    if (out_unsigned) {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(p) : "r"(y3), "r"(y2), "r"(y2));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(y1), "r"(y0), "r"(p));
+    } else {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(p) : "r"(y3), "r"(y2), "r"(y2));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(y1), "r"(y0), "r"(p));
+    }
+    return w;   // bytes y0, y1, y2, y3 from the low end
+}
+
+template <int NG, bool RES, bool CLAMP, bool DP, int EF>
+__device__ __forceinline__ void perm_block(const unsigned* vA, const unsigned* vB, unsigned par_off, int pcol0, unsigned region_off,
+                                           const unsigned* rb, int col0, int lane, int t_lo, int t_hi, unsigned dp_xor)
+{
+    unsigned char* const sm = dyn_smem();
+    constexpr int NK = 4;          // rows tr + 8k: k = 0, 1 from vA (TMEM lanes 0-15), k = 2, 3 from vB (lanes 16-31)
+    constexpr int NH = NG / 2;     // the thread's channels in halves of four
+    unsigned base[NK];
+#pragma unroll
+    for (int k = 0; k < NK; ++k) base[k] = (region_off + rb[k]) ^ (unsigned)col0;
+    unsigned rres[NK][NH];
+    if (RES) {
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            if (NH == 2) {
+                const uint2 r = *(const uint2*)(sm + base[k]);
+                rres[k][0] = r.x;
+                rres[k][NH - 1] = r.y;
+            } else {
+                rres[k][0] = *(const unsigned*)(sm + base[k]);
+            }
+        }
+    }
+    unsigned outw[NK][NH];
+    const unsigned pbase = par_off + (unsigned)(pcol0 + 2 * NG * (lane & 3)) * 4u;
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        const unsigned pp = pbase + 16u * h;   // channels 4h .. 4h + 3 of this thread
+        const int4 mu = *(const int4*)(sm + pp + 2 * 1024);
+        const int4 ad = *(const int4*)(sm + pp + 3 * 1024);
+        const int4 sh = *(const int4*)(sm + pp + 4 * 1024);
+        int4 lo = make_int4(0, 0, 0, 0), hi = lo;
+        if (CLAMP) {
+            lo = *(const int4*)(sm + pp + 0 * 1024);
+            hi = *(const int4*)(sm + pp + 1 * 1024);
+        } else if (EF & EF_WIDE) {
+            lo = *(const int4*)(sm + pp + 0 * 1024);   // upper words of the 64-bit addends
+        }
+        int4 mu2 = make_int4(0, 0, 0, 0), ad2 = mu2, sh2 = mu2, lo2 = mu2, hi2 = mu2;
+        if (RES) {
+            ad2 = *(const int4*)(sm + pp + (FAST_NP + 3) * 1024);
+            sh2 = *(const int4*)(sm + pp + (FAST_NP + 4) * 1024);
+            if (!DP) mu2 = *(const int4*)(sm + pp + (FAST_NP + 2) * 1024);
+            if (CLAMP) hi2 = *(const int4*)(sm + pp + (FAST_NP + 1) * 1024);
+            if (CLAMP || DP) lo2 = *(const int4*)(sm + pp + (FAST_NP + 0) * 1024);   // DP: byte-lane multiplier words
+        }
+        const int muv[4] = {mu.x, mu.y, mu.z, mu.w}, adv[4] = {ad.x, ad.y, ad.z, ad.w}, shv[4] = {sh.x, sh.y, sh.z, sh.w};
+        const int lov[4] = {lo.x, lo.y, lo.z, lo.w}, hiv[4] = {hi.x, hi.y, hi.z, hi.w};
+        const int mu2v[4] = {mu2.x, mu2.y, mu2.z, mu2.w}, ad2v[4] = {ad2.x, ad2.y, ad2.z, ad2.w};
+        const int sh2v[4] = {sh2.x, sh2.y, sh2.z, sh2.w}, lo2v[4] = {lo2.x, lo2.y, lo2.z, lo2.w}, hi2v[4] = {hi2.x, hi2.y, hi2.z, hi2.w};
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            const unsigned* v = (k < 2) ? vA : vB;
+            int y[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                // thread channel 4h + c = 2i + e  ->  group i = 2h + c / 2, element e = c % 2
+                int x = (int)v[4 * (2 * h + (c >> 1)) + 2 * (k & 1) + (c & 1)];
+                if (CLAMP) x = min(max(x, lov[c]), hiv[c]);
+                if (EF & EF_WIDE) {
+                    const long long p = (long long)x * muv[c] + (long long)(((unsigned long long)(unsigned)lov[c] << 32) | (unsigned)adv[c]);
+                    y[c] = (int)(p >> shv[c]);
+                } else {
+                    y[c] = (x * muv[c] + adv[c]) >> shv[c];
+                }
+            }
+            if (RES && DP) {
+                // [t, t', r, r'] per column pair: the saturating pack of the cell's own output also places the two
+                // residual bytes beside it; one byte dot product per value then gives (t + r) * m2 + add2
+                const unsigned rw = rres[k][h];
+                unsigned a01, a23;
+                if (EF & EF_T_UNSIGNED) {
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(a01) : "r"(y[1]), "r"(y[0]), "r"(rw));
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(a23) : "r"(y[3]), "r"(y[2]), "r"(rw >> 16));
+                } else {
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(a01) : "r"(y[1]), "r"(y[0]), "r"(rw));
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(a23) : "r"(y[3]), "r"(y[2]), "r"(rw >> 16));
+                }
+                if (EF & EF_DP_XOR) {
+                    a01 ^= dp_xor;
+                    a23 ^= dp_xor;
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const unsigned a4 = (c < 2) ? a01 : a23;
+                    int d;
+                    if (EF & EF_DP_A_SIGNED) asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a4), "r"(lo2v[c]), "r"(ad2v[c]));
+                    else asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a4), "r"(lo2v[c]), "r"(ad2v[c]));
+                    y[c] = d >> sh2v[c];
+                }
+            } else if (RES) {
+                const unsigned rw = rres[k][h];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = byte_extend(rw, c, (EF & EF_RES_UNSIGNED) != 0);
+                    int u = min(max(y[c], t_lo), t_hi) + r;
+                    if (CLAMP) u = min(max(u, lo2v[c]), hi2v[c]);
+                    y[c] = (u * mu2v[c] + ad2v[c]) >> sh2v[c];
+                }
+            }
+            outw[k][h] = pack4_sat(y[0], y[1], y[2], y[3], (EF & EF_OUT_UNSIGNED) != 0);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NK; ++k) {
+        if (NH == 2) *(uint2*)(sm + base[k]) = make_uint2(outw[k][0], outw[k][NH - 1]);
+        else *(unsigned*)(sm + base[k]) = outw[k][0];
+    }
+}
+
 // One accumulator tile through the fragment-layout epilogue: residual slice in by TMA (issued one tile
 // ahead when the warp has two staging regions), accumulator slice out of TMEM, requantisation into the
 // swizzled staging region, TMA store.  A warp owns the 32 rows of its TMEM quadrant `quad` and the column
@@ -529,18 +681,23 @@ template <bool RES, bool CLAMP, bool DP, int EF>
 __device__ __forceinline__ void epi_drain(const EpiTile& e, unsigned tbase, int cbase, unsigned region_off, const unsigned* rb,
                                           int lane)
 {
+    constexpr bool PERM = (EF & EF_PERM) != 0;
     if (e.wp >= 32) {
 #pragma unroll 1
         for (int cb = 0; cb < e.wp; cb += 32) {
             unsigned va[16], vb[16];
             tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
-            frag_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, rb, cb, lane, e.t_lo, e.t_hi,
-                                              e.dp_xor);
+            if (PERM)
+                perm_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, rb, cb, lane, e.t_lo, e.t_hi, e.dp_xor);
+            else
+                frag_block<4, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase + cb, region_off, rb, cb, lane, e.t_lo, e.t_hi,
+                                                  e.dp_xor);
         }
     } else {
         unsigned va[8], vb[8];
         tc_ld_2x16x256b_x2_wait(tbase, va, vb);
-        frag_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, rb, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
+        if (PERM) perm_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, rb, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
+        else frag_block<2, RES, CLAMP, DP, EF>(va, vb, e.par_off, cbase, region_off, rb, 0, lane, e.t_lo, e.t_hi, e.dp_xor);
     }
 }
 
@@ -559,10 +716,11 @@ __device__ __forceinline__ void epi_issue_residual(const CUtensorMap* tmR, unsig
     }
 }
 
-template <bool RES, bool CLAMP, bool DP>
+template <bool RES, bool CLAMP, bool DP, bool PERM = false>
 __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
                                                    int cp, int lane, EpiState& st)
 {
+    constexpr int P = PERM ? EF_PERM : 0;
     const int wp = e.wp;
     const int cbase = cp * wp;
     const int gx = e.n0 + cbase, gy = e.m0 + quad * 32;
@@ -586,32 +744,32 @@ __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const
         // one branch per tile selects the arithmetic variant; inside, nothing depends on a run-time flag
         if (!RES) {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_WIDE)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case EF_OUT_UNSIGNED: epi_drain<RES, CLAMP, DP, EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case EF_WIDE: epi_drain<RES, false, DP, EF_WIDE>(e, tbase, cbase, region_off, st.rb, lane); break;
-            default: epi_drain<RES, false, DP, EF_WIDE | EF_OUT_UNSIGNED>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, (0) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_OUT_UNSIGNED: epi_drain<RES, CLAMP, DP, (EF_OUT_UNSIGNED) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE: epi_drain<RES, false, DP, (EF_WIDE) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, false, DP, (EF_WIDE | EF_OUT_UNSIGNED) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         } else if (!DP) {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_RES_UNSIGNED | EF_WIDE)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 2: epi_drain<RES, CLAMP, DP, 2>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 3: epi_drain<RES, CLAMP, DP, 3>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case EF_WIDE | 0: epi_drain<RES, false, DP, EF_WIDE | 0>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case EF_WIDE | 1: epi_drain<RES, false, DP, EF_WIDE | 1>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case EF_WIDE | 2: epi_drain<RES, false, DP, EF_WIDE | 2>(e, tbase, cbase, region_off, st.rb, lane); break;
-            default: epi_drain<RES, false, DP, EF_WIDE | 3>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, (0) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, (1) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 2: epi_drain<RES, CLAMP, DP, (2) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 3: epi_drain<RES, CLAMP, DP, (3) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 0: epi_drain<RES, false, DP, (EF_WIDE | 0) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 1: epi_drain<RES, false, DP, (EF_WIDE | 1) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case EF_WIDE | 2: epi_drain<RES, false, DP, (EF_WIDE | 2) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, false, DP, (EF_WIDE | 3) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         } else {
             switch (e.ef & (EF_OUT_UNSIGNED | EF_T_UNSIGNED | EF_DP_A_SIGNED)) {
-            case 0: epi_drain<RES, CLAMP, DP, 0>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 1: epi_drain<RES, CLAMP, DP, 1>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 4: epi_drain<RES, CLAMP, DP, 4>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 5: epi_drain<RES, CLAMP, DP, 5>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 8: epi_drain<RES, CLAMP, DP, 8>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 9: epi_drain<RES, CLAMP, DP, 9>(e, tbase, cbase, region_off, st.rb, lane); break;
-            case 12: epi_drain<RES, CLAMP, DP, 12>(e, tbase, cbase, region_off, st.rb, lane); break;
-            default: epi_drain<RES, CLAMP, DP, 13>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 0: epi_drain<RES, CLAMP, DP, (0) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 1: epi_drain<RES, CLAMP, DP, (1) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 4: epi_drain<RES, CLAMP, DP, (4) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 5: epi_drain<RES, CLAMP, DP, (5) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 8: epi_drain<RES, CLAMP, DP, (8) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 9: epi_drain<RES, CLAMP, DP, (9) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            case 12: epi_drain<RES, CLAMP, DP, (12) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
+            default: epi_drain<RES, CLAMP, DP, (13) | P>(e, tbase, cbase, region_off, st.rb, lane); break;
             }
         }
     }

@@ -88,6 +88,9 @@ def load():
         lib.n2d2b_net_submit_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         lib.n2d2b_net_wait.argtypes = [C.c_void_p]
         lib.n2d2b_net_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
+        lib.n2d2b_net_estimated_labels.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.n2d2b_quantize_stimuli.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                               C.c_void_p, C.c_void_p]
         lib.n2d2b_net_num_tensors.argtypes = [C.c_void_p]
         lib.n2d2b_net_tensor_info.argtypes = [C.c_void_p, C.c_int, C.POINTER(TensorInfo)]
         lib.n2d2b_net_read_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
@@ -237,6 +240,10 @@ class QuantizedNet:
     def forward_host_ptr(self, h_in_ptr, batch, h_out_ptr, stream=0):
         check(self.lib.n2d2b_net_forward_host(self.handle, h_in_ptr, batch, h_out_ptr, stream))
 
+    def estimated_labels(self, batch, d_labels_ptr, d_values_ptr=None, stream=0):
+        """Top-1 class of the last forward pass's final tensor (first maximum wins), into device int32 buffers."""
+        check(self.lib.n2d2b_net_estimated_labels(self.handle, batch, d_labels_ptr, d_values_ptr, stream))
+
     def check(self, stream=0):
         """Waits for `stream` and raises if a kernel of this network gave up on a bounded wait."""
         check(self.lib.n2d2b_net_check(self.handle, stream))
@@ -274,6 +281,12 @@ class QuantizedNet:
 def scaling_propagate(x_i32_dev_ptr, out_dev_ptr, nb_pixels, q, channels, device=0, stream=0):
     qq, keep = make_quant(q, channels)
     check(load().n2d2b_scaling_propagate(device, x_i32_dev_ptr, out_dev_ptr, nb_pixels, C.byref(qq), stream))
+
+
+def quantize_stimuli(d_in_ptr, batch, channels, height, width, d_out_ptr, nb_bits=8, env_unsigned=True, device=0, stream=0):
+    """Float NCHW stimuli -> trunc(x * (2^n - 1 | 2^(n-1) - 1)) as 8-bit NHWC (the input edge of a quantized network)."""
+    check(load().n2d2b_quantize_stimuli(device, d_in_ptr, batch, channels, height, width, nb_bits, 1 if env_unsigned else 0,
+                                        d_out_ptr, stream))
 
 
 def probe_i8_mma_rate(device=0, n=256, reps=40000):

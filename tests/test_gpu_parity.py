@@ -351,3 +351,46 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_network_usable(
         assert np.array_equal(qn.forward_host(x).astype(np.int64), ref)
     finally:
         qn.close()
+
+
+def test_output_edge_estimated_labels_first_maximum_wins():
+    # Target top-1 (src/Target/Target_CUDA_kernels.cu:88-104 of the reference): strict '>' while scanning the
+    # classes in order, so the lowest index among equal scores wins; int8 logits tie often
+    import torch
+    net = netdesc.resnet18(size=32, classes=1000)
+    batch = 7
+    x = netdesc.make_input(net, batch)
+    ref = oracle.run_net(net, x, 'i64')[-1].reshape(batch, -1)
+    qn = runtime.QuantizedNet(net, batch)
+    try:
+        d_in = torch.from_numpy(x).cuda()
+        d_out = torch.empty((batch, qn.out_elems), dtype=torch.int8, device='cuda')
+        labels = torch.full((batch,), -1, dtype=torch.int32, device='cuda')
+        values = torch.zeros((batch,), dtype=torch.int32, device='cuda')
+        qn.forward_device(d_in.data_ptr(), batch, d_out.data_ptr(), 0)
+        qn.estimated_labels(batch, labels.data_ptr(), values.data_ptr(), 0)
+        qn.check(0)
+        assert np.array_equal(d_out.cpu().numpy().astype(np.int64), ref)
+        assert np.array_equal(labels.cpu().numpy(), ref.argmax(axis=1))       # numpy's argmax is first-maximum too
+        assert np.array_equal(values.cpu().numpy(), ref.max(axis=1))
+        assert (ref == ref.max(axis=1, keepdims=True)).sum(axis=1).max() > 1  # the case does contain ties
+    finally:
+        qn.close()
+
+
+def test_input_edge_quantizes_float_stimuli_like_the_range_transform():
+    # src/DeepNetQuantization.cpp:359-370: x * (2^n - 1) (unsigned) or x * (2^(n-1) - 1) (signed), truncated;
+    # NCHW float in, NHWC 8-bit out
+    import torch
+    rng = np.random.Generator(np.random.PCG64(3))
+    x = rng.integers(0, 256, size=(3, 3, 9, 7)).astype(np.float32) / np.float32(255.0)    # 8-bit images scaled to [0, 1]
+    x[0, 0, 0, :4] = [0.5, 0.999, 1.5, -0.2]                                             # plus values that truncate / saturate
+    d_in = torch.from_numpy(x).cuda()
+    for unsigned, factor, lo, hi, dt in ((True, 255.0, 0, 255, np.uint8), (False, 127.0, -128, 127, np.int8)):
+        xs = x if unsigned else x * 2 - 1
+        d_in = torch.from_numpy(np.ascontiguousarray(xs)).cuda()
+        d_out = torch.zeros((3, 9, 7, 3), dtype=torch.uint8, device='cuda')
+        runtime.quantize_stimuli(d_in.data_ptr(), 3, 3, 9, 7, d_out.data_ptr(), 8, unsigned)
+        torch.cuda.synchronize()
+        want = np.clip(np.trunc(xs.astype(np.float32) * np.float32(factor)), lo, hi).astype(dt).transpose(0, 2, 3, 1)
+        assert np.array_equal(d_out.cpu().numpy().view(dt), want)
