@@ -16,7 +16,9 @@
 #pragma once
 
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
+#include <functional>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -88,6 +90,17 @@ public:
     ScalingMode getMode() const { return mMode; }
     std::size_t getFractionalBits() const { return mNbFractionalBits; }
     bool getIsClipped() const { return mIsClipped; }
+    // payloads (getFloatingPointScaling().getScalingPerOutput() etc. in the reference)
+    const std::vector<Float_T>& getFloatingPointScalingPerOutput() const { return mFloat; }
+    const std::vector<std::int32_t>& getFixedPointScalingPerOutput() const { return mFixed; }
+    const std::vector<unsigned char>& getSingleShiftScalingPerOutput() const { return mShift0; }
+    std::vector<std::pair<unsigned char, unsigned char> > getDoubleShiftScalingPerOutput() const
+    {
+        std::vector<std::pair<unsigned char, unsigned char> > v;
+        for (std::size_t i = 0; i < mShift0.size(); ++i) v.emplace_back(mShift0[i], mShift1[i]);
+        return v;
+    }
+    const std::vector<Float_T>& getClippingPerOutput() const { return mClipping; }
 
     // Fills the C-ABI view (pointers stay valid as long as this object lives).
     void describe(n2d2b_scaling& d, int nbOutputs) const
@@ -174,6 +187,21 @@ public:
     unsigned int getChannelsWidth() const { return mChannelsWidth; }
     unsigned int getChannelsHeight() const { return mChannelsHeight; }
 
+    // Free parameters while the network is still in floating point (before and during post-training
+    // quantization): Multiplicative = weights, Additive = biases (include/Cell/Cell.hpp FreeParametersType).
+    enum FreeParametersType { Additive, Multiplicative, All };
+    virtual void processFreeParameters(const std::function<Float_T(Float_T)>& /*func*/, FreeParametersType /*type*/ = All) {}
+    virtual void processFreeParametersPerOutput(const std::function<Float_T(Float_T)>& /*func*/, std::size_t /*output*/,
+                                                FreeParametersType /*type*/ = All) {}
+    virtual std::pair<Float_T, Float_T> getFreeParametersRange(FreeParametersType /*type*/ = All) const { return std::make_pair(0.0f, 0.0f); }
+    virtual std::pair<Float_T, Float_T> getFreeParametersRangePerOutput(std::size_t /*output*/, FreeParametersType /*type*/ = All) const
+    {
+        return std::make_pair(0.0f, 0.0f);
+    }
+    // Rounds the floating-point parameters and stores them as the integers the device takes; throws when a value
+    // does not fit (weights: nbBits signed; biases: 32 bits).
+    virtual void roundFreeParameters(std::size_t /*nbBits*/) {}
+
     // Signedness of the cell's output as DeepNetExport::isCellOutputUnsigned derives it: unsigned only
     // when unsigned data is allowed and the output range starts at 0 (a Rectifier); may be overridden.
     bool isOutputUnsigned() const
@@ -208,14 +236,77 @@ protected:
     int mTensorId = -1;
 };
 
-class ConvCell : public Cell {
+// Floating-point weights [output][...] and biases [output] with the reference's processing hooks; shared by the
+// convolution and the fully-connected cell.
+class FreeParametersCell : public Cell {
+public:
+    using Cell::Cell;
+    // weights in the reference's memory order, one contiguous run per output; biases may be empty (NoBias)
+    void setFloatWeights(const std::vector<Float_T>& w) { mFloatWeights = w; }
+    void setFloatBiases(const std::vector<Float_T>& b) { mFloatBiases = b; }
+    const std::vector<Float_T>& getFloatWeights() const { return mFloatWeights; }
+    const std::vector<Float_T>& getFloatBiases() const { return mFloatBiases; }
+
+    void processFreeParameters(const std::function<Float_T(Float_T)>& func, FreeParametersType type = All) override
+    {
+        if (type != Additive) for (Float_T& w : mFloatWeights) w = func(w);
+        if (type != Multiplicative) for (Float_T& b : mFloatBiases) b = func(b);
+    }
+    void processFreeParametersPerOutput(const std::function<Float_T(Float_T)>& func, std::size_t output, FreeParametersType type = All) override
+    {
+        const std::size_t per = mFloatWeights.size() / mNbOutputs;
+        if (type != Additive) for (std::size_t i = output * per; i < (output + 1) * per; ++i) mFloatWeights[i] = func(mFloatWeights[i]);
+        if (type != Multiplicative && !mFloatBiases.empty()) mFloatBiases[output] = func(mFloatBiases[output]);
+    }
+    std::pair<Float_T, Float_T> getFreeParametersRange(FreeParametersType type = All) const override
+    {
+        Float_T lo = 0.0f, hi = 0.0f;
+        bool first = true;
+        auto take = [&](Float_T v) { if (first) { lo = hi = v; first = false; } else { lo = std::min(lo, v); hi = std::max(hi, v); } };
+        if (type != Additive) for (Float_T w : mFloatWeights) take(w);
+        if (type != Multiplicative) for (Float_T b : mFloatBiases) take(b);
+        return std::make_pair(lo, hi);
+    }
+    std::pair<Float_T, Float_T> getFreeParametersRangePerOutput(std::size_t output, FreeParametersType type = All) const override
+    {
+        Float_T lo = 0.0f, hi = 0.0f;
+        bool first = true;
+        auto take = [&](Float_T v) { if (first) { lo = hi = v; first = false; } else { lo = std::min(lo, v); hi = std::max(hi, v); } };
+        const std::size_t per = mFloatWeights.size() / mNbOutputs;
+        if (type != Additive) for (std::size_t i = output * per; i < (output + 1) * per; ++i) take(mFloatWeights[i]);
+        if (type != Multiplicative && !mFloatBiases.empty()) take(mFloatBiases[output]);
+        return std::make_pair(lo, hi);
+    }
+
+protected:
+    void roundInto(std::size_t nbBits, std::vector<std::int8_t>& weights, std::vector<std::int32_t>& biases)
+    {
+        if (mFloatWeights.empty()) return;
+        const long long wMax = (1ll << (nbBits - 1)) - 1, wMin = -(1ll << (nbBits - 1));
+        weights.resize(mFloatWeights.size());
+        for (std::size_t i = 0; i < mFloatWeights.size(); ++i) {
+            const long long r = std::llround((double)mFloatWeights[i]);
+            if (r < wMin || r > wMax) throw std::runtime_error("Cell " + mName + ": a rounded weight does not fit " + std::to_string(nbBits) + " bits");
+            weights[i] = (std::int8_t)r;
+        }
+        biases.resize(mFloatBiases.size());
+        for (std::size_t i = 0; i < mFloatBiases.size(); ++i) {
+            const long long r = std::llround((double)mFloatBiases[i]);
+            if (r < INT32_MIN || r > INT32_MAX) throw std::runtime_error("Cell " + mName + ": a rounded bias does not fit 32 bits");
+            biases[i] = (std::int32_t)r;
+        }
+    }
+    std::vector<Float_T> mFloatWeights, mFloatBiases;
+};
+
+class ConvCell : public FreeParametersCell {
 public:
     // kernelDims / strideDims / dilationDims are {x, y}; paddingDims {x, y} or {left, top, right, bottom}
     ConvCell(const std::string& name, const std::vector<unsigned int>& kernelDims, unsigned int nbOutputs,
              const std::vector<unsigned int>& subSampleDims = {1, 1}, const std::vector<unsigned int>& strideDims = {1, 1},
              const std::vector<int>& paddingDims = {0, 0}, const std::vector<unsigned int>& dilationDims = {1, 1},
              const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
-        : Cell(name, nbOutputs), mKernelDims(kernelDims), mStrideDims(strideDims), mPaddingDims(paddingDims),
+        : FreeParametersCell(name, nbOutputs), mKernelDims(kernelDims), mStrideDims(strideDims), mPaddingDims(paddingDims),
           mDilationDims(dilationDims)
     {
         for (unsigned int s : subSampleDims)
@@ -255,6 +346,7 @@ public:
     }
     const std::vector<std::int8_t>& getWeights() const { return mWeights; }
     const std::vector<std::int32_t>& getBiases() const { return mBiases; }
+    void roundFreeParameters(std::size_t nbBits) override { roundInto(nbBits, mWeights, mBiases); }
     // weights in the reference's memory order: [output][channel][ky][kx] (kx fastest)
     void setWeights(const std::vector<std::int8_t>& oihw) { mWeights = oihw; }
     void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
@@ -274,11 +366,11 @@ private:
     std::vector<std::int32_t> mBiases;
 };
 
-class FcCell : public Cell {
+class FcCell : public FreeParametersCell {
 public:
     FcCell(const std::string& name, unsigned int nbOutputs,
            const std::shared_ptr<Activation>& activation = std::shared_ptr<Activation>())
-        : Cell(name, nbOutputs)
+        : FreeParametersCell(name, nbOutputs)
     {
         mActivation = activation;
     }
@@ -288,6 +380,7 @@ public:
     void setBiases(const std::vector<std::int32_t>& biases) { mBiases = biases; }
     const std::vector<std::int8_t>& getWeights() const { return mWeights; }
     const std::vector<std::int32_t>& getBiases() const { return mBiases; }
+    void roundFreeParameters(std::size_t nbBits) override { roundInto(nbBits, mWeights, mBiases); }
 
 private:
     friend class DeepNet;
@@ -305,6 +398,7 @@ public:
     {
     }
     const char* getType() const override { return "Pool"; }
+    Pooling getPooling() const { return mPooling; }
 
 private:
     friend class DeepNet;
@@ -334,6 +428,8 @@ public:
         mActivation->setActivationScaling(std::move(scaling));
     }
     const char* getType() const override { return "Scaling"; }
+    const Scaling& getScaling() const { return mActivation->getActivationScaling(); }
+    void setScaling(Scaling scaling) { mActivation->setActivationScaling(std::move(scaling)); }
 };
 
 // Graph container + executor (src/DeepNet.cpp:74-415,826-854,2622-2768).  The graph lives on the host as in
@@ -454,6 +550,51 @@ public:
         for (const auto& link : mParentLayers)
             if (link.first == name) out.push_back(link.second == "env" ? std::shared_ptr<Cell>() : mCells.at(link.second));
         return out;
+    }
+    // DeepNetExport::isCellOutputUnsigned / isCellInputsUnsigned (src/Export/DeepNetExport.cpp:298-388) on this
+    // graph: a Rectifier's output range starts at 0; pooling and ScalingCells (non-negative factors) hand their
+    // parents' range on (src/Cell/PoolCell.cpp:242-244, src/Cell/ScalingCell.cpp:68-104); everything else is signed.
+    bool isCellOutputUnsigned(const Cell& cell) const
+    {
+        if (!DeepNetExport::mUnsignedData()) return false;
+        if (cell.mForcedSign >= 0) return cell.mForcedSign != 0;
+        const bool passThrough = dynamic_cast<const PoolCell*>(&cell) || dynamic_cast<const ScalingCell*>(&cell);
+        if (!passThrough) return cell.getActivation() && cell.getActivation()->kind() == N2D2B_ACT_RECTIFIER;
+        if (auto* sc = dynamic_cast<const ScalingCell*>(&cell)) {
+            const Scaling& s = sc->getScaling();
+            for (Float_T v : s.getFloatingPointScalingPerOutput()) if (v < 0.0f) return false;
+            for (std::int32_t v : s.getFixedPointScalingPerOutput()) if (v < 0) return false;
+        }
+        bool any = false;
+        for (const auto& link : mParentLayers) {
+            if (link.first != cell.getName()) continue;
+            any = true;
+            if (!(link.second == "env" ? DeepNetExport::mEnvDataUnsigned() : isCellOutputUnsigned(*mCells.at(link.second)))) return false;
+        }
+        return any;
+    }
+    bool isCellInputsUnsigned(const Cell& cell) const
+    {
+        if (!DeepNetExport::mUnsignedData()) return false;
+        bool first = true, uns = false;
+        for (const auto& link : mParentLayers) {
+            if (link.first != cell.getName()) continue;
+            const bool u = link.second == "env" ? DeepNetExport::mEnvDataUnsigned() : isCellOutputUnsigned(*mCells.at(link.second));
+            if (first) { uns = u; first = false; }
+            else if (u != uns)
+                throw std::runtime_error("Unsupported: cell " + cell.getName() + " mixes signed and unsigned inputs. "
+                                         "Try setting DeepNetExport::mUnsignedData to false");
+        }
+        return uns;
+    }
+    // a name nobody has yet: baseName, or baseName_1, baseName_2 ... (DeepNet::generateNewCellName)
+    std::string generateNewCellName(const std::string& baseName) const
+    {
+        if (!mCells.count(baseName)) return baseName;
+        for (std::size_t i = 1;; ++i) {
+            const std::string n = baseName + "_" + std::to_string(i);
+            if (!mCells.count(n)) return n;
+        }
     }
     bool hasCell(const std::string& name) const { return mCells.count(name) != 0; }
     const std::map<std::string, std::shared_ptr<Cell> >& getCells() const { return mCells; }
@@ -600,6 +741,7 @@ private:
         if (ins.empty()) throw std::runtime_error("DeepNet::initialize(): cell " + cell->getName() + " has no input");
         n2d2b_quant q;
         cell->describeQuant(q);
+        q.out_unsigned = isCellOutputUnsigned(*cell) ? 1 : 0;
         int id = -1;
         if (auto* conv = dynamic_cast<ConvCell*>(cell.get())) {
             n2d2b_conv_desc d = n2d2b_conv_desc();
