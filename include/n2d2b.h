@@ -222,9 +222,14 @@ int n2d2b_net_num_tensors(const n2d2b_net* net);
 int n2d2b_net_tensor_info(const n2d2b_net* net, int tensor_id, n2d2b_tensor_info* info);
 /* Copies a tensor of the last forward (first `batch` images) to the host. */
 int n2d2b_net_read_tensor(n2d2b_net* net, int tensor_id, int batch, void* host_dst, size_t bytes);
+/* Bytes of weights the network keeps in HBM (*total_bytes), and how many of them are packed 4-bit weights
+ * (*packed4_bytes: cells given weight_bits = 4 that run on the implicit-GEMM kernel, which expands them tile by
+ * tile in shared memory; other cells hold int8).  Either pointer may be NULL. */
+int n2d2b_net_weight_bytes(const n2d2b_net* net, size_t* total_bytes, size_t* packed4_bytes);
 /* Number of kernel launches one forward of `batch` images issues. */
 int n2d2b_net_launches_per_forward(const n2d2b_net* net);
-/* Name of the kernel family cell `cell` runs on ("tcgen05", "simt", "depthwise", "pool", "sum", "fused"). */
+/* Name of the kernel family cell `cell` runs on ("tcgen05", "tcgen05-pair", "tcgen05-w4", "patch-tcgen05",
+ * "stem-tcgen05", "simt", "depthwise", "pool", "sum", "fused"). */
 const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell);
 /* Device time of every cell of one forward, in milliseconds (CUDA events on `stream`), like the
  * per-cell timings of DeepNet::propagate (src/DeepNet.cpp:2705-2717). ms has one entry per cell. */

@@ -36,6 +36,7 @@ static constexpr int EPI_WARP0 = 2;
 static constexpr int NUM_EPI_WARPS = 16;      // four per TMEM lane quadrant, a quarter of the columns each
 static constexpr int REGION_BYTES = 2048;     // staging per epilogue warp: 32 rows x up to 64 bytes
 static constexpr int NUM_THREADS = 32 * (EPI_WARP0 + NUM_EPI_WARPS);
+static constexpr int W4_UNPACK_WARPS = 4;     // extra warps of the packed-int4 variant
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
@@ -64,8 +65,22 @@ struct IgemmArgs {
 };
 
 // ----------------------------------------------------------------------------- the kernel
-template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// Eight packed 4-bit weights (one 32-bit word: byte i = elements 2i in the high and 2i + 1 in the low nibble) as
+// eight signed bytes holding 16 x the weight: the nibble moves to the top of its byte, which is the value times 16
+// with the right sign and needs no sign extension.  The epilogue's constants absorb the factor (its shift grows by
+// four), so the result is exact.
+__device__ __forceinline__ void expand_int4_x16(unsigned x, unsigned& w0, unsigned& w1)
+{
+    const unsigned hi = x & 0xF0F0F0F0u, lo = (x << 4) & 0xF0F0F0F0u;
+    w0 = __byte_perm(hi, lo, 0x5140);   // hi.b0, lo.b0, hi.b1, lo.b1
+    w1 = __byte_perm(hi, lo, 0x7362);   // hi.b2, lo.b2, hi.b3, lo.b3
+}
+
+// W4: the weights sit in HBM as packed 4-bit values.  The producer's TMA load brings a BN x BK/2-byte packed block
+// into the stage beside the operand tiles; four extra warps expand it into the swizzled int8 B tile the MMA reads
+// (as 16 x the weight, see expand_int4_x16) and signal the issuing thread through one more barrier per stage.
+template <int MODE, bool W4>
+__global__ void __launch_bounds__(W4 ? NUM_THREADS + 32 * W4_UNPACK_WARPS : NUM_THREADS, 1)
 igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
                         const IgemmArgs a)
@@ -79,7 +94,9 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int a_stage_bytes = BM * a.BK;
     const int b_stage_bytes = a.BN * a.BK;
-    const int stage_bytes = a_stage_bytes + (a.b_resident ? 0 : b_stage_bytes);
+    const int p_stage_bytes = W4 ? b_stage_bytes / 2 : 0;                       // packed weights of the stage
+    const int stage_bytes = a_stage_bytes + (a.b_resident ? 0 : b_stage_bytes) + p_stage_bytes;
+    const int tx_bytes = a_stage_bytes + (W4 ? p_stage_bytes : (a.b_resident ? 0 : b_stage_bytes));   // what TMA delivers per stage
     const int kchunks = (a.Cin + a.BK - 1) / a.BK;
     const int num_kb = a.taps * kchunks;
     // resident weights first (one BN x BK block per K block), then the ring of activation (and weight) stages
@@ -99,7 +116,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const unsigned pready0 = tempty0 + 16u;
     const unsigned rbar0 = pready0 + 16u;
     const unsigned bfull = rbar0 + 8u * (4 * NUM_EPI_WARPS);
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 4 * NUM_EPI_WARPS + 2);
+    const unsigned bready0 = bfull + 16u;                                       // W4: expanded weights of a stage are in place
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 4 * NUM_EPI_WARPS + 2 + (W4 ? a.stages : 0));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -120,6 +138,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
         for (int w = 0; w < 4 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
         mbar_init(bfull, 1);
+        if (W4)
+            for (int s = 0; s < a.stages; ++s) mbar_init(bready0 + 8u * s, W4_UNPACK_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -177,14 +197,15 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
                     const unsigned bar = full0 + 8u * s;
                     const unsigned dstA = tiles_s + (unsigned)(s * stage_bytes);
-                    mbar_expect_tx(bar, (unsigned)stage_bytes);
+                    mbar_expect_tx(bar, (unsigned)tx_bytes);
                     if (a.a_im2col) {
                         tma_load_im2col_4d(dstA, &tmA, bar, kc * a.BK, iw0, ih0, in0,
                                            (unsigned short)(kx * a.dX), (unsigned short)(ky * a.dY));
                     } else {
                         tma_load_2d(dstA, &tmA, bar, kcoord, m0);
                     }
-                    if (!a.b_resident) tma_load_2d(dstA + a_stage_bytes, &tmB, bar, kcoord, n0);
+                    if (W4) tma_load_2d(dstA + a_stage_bytes + b_stage_bytes, &tmB, bar, kcoord >> 1, n0);   // packed: two per byte
+                    else if (!a.b_resident) tma_load_2d(dstA + a_stage_bytes, &tmB, bar, kcoord, n0);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
                     if (++kc == kchunks) {
                         kc = 0;
@@ -221,6 +242,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 unsigned b_res = b_res0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8u * s, ph, abort_flag, a.status, 3)) { ok = false; break; }
+                    if (W4 && !mbar_wait(bready0 + 8u * s, ph, abort_flag, a.status, 11)) { ok = false; break; }
                     tc_fence_after();
                     const unsigned b_lo = a.b_resident ? b_res : a_lo + a16;
                     const unsigned acc = kb ? 1u : 0u;
@@ -242,6 +264,37 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     if (++s == a.stages) { s = 0; ph ^= 1u; a_lo = a_lo0; }
                 }
                 if (ok) tc_commit(tfull0 + 8u * as);
+            }
+        }
+    } else if (W4 && warp >= EPI_WARP0 + NUM_EPI_WARPS) {
+        // ------------------------------------------------------------------ int4 expansion warps
+        // Stage s may be rewritten once full[s] has completed for the new fill: the producer only refills a stage
+        // after the MMAs that read its previous contents have committed (empty[s]).
+        const int ut = (warp - (EPI_WARP0 + NUM_EPI_WARPS)) * 32 + lane;
+        const int cpr_shift = a.BK == 128 ? 3 : (a.BK == 64 ? 2 : 1);   // 16-byte chunks per B row: BK / 16
+        const int total_chunks = a.BN << cpr_shift;
+        const int half_bk = a.BK >> 1;
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_warp(full0 + 8u * s, ph, abort_flag, a.status, 12, lane)) { ok = false; break; }
+                unsigned char* bt = tiles + (size_t)s * stage_bytes + a_stage_bytes;
+                const unsigned char* pk = bt + b_stage_bytes;
+#pragma unroll 2
+                for (int id = ut; id < total_chunks; id += 32 * W4_UNPACK_WARPS) {
+                    const int row = id >> cpr_shift, ch = id & ((1 << cpr_shift) - 1);
+                    const uint2 p = *(const uint2*)(pk + row * half_bk + ch * 8);
+                    uint4 o;
+                    expand_int4_x16(p.x, o.x, o.y);
+                    expand_int4_x16(p.y, o.z, o.w);
+                    *(uint4*)(bt + swz_off(row, ch * 16, a.BK)) = o;
+                }
+                fence_async_smem();   // generic-proxy stores, read by the tensor core through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bready0 + 8u * s);
+                if (++s == a.stages) { s = 0; ph ^= 1u; }
             }
         }
     } else {
@@ -351,7 +404,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     for (int j = 0; j < 32; ++j) {
                         const int n = nbase + j;
                         if (n < a.N) {
-                            const long long x = (long long)(int)v[j] + (a.q.bias ? (long long)a.q.bias[n] : 0ll);
+                            // W4: the accumulator holds 16 x the sum (a multiple of 16: the shift is exact)
+                            const long long x = (long long)(W4 ? ((int)v[j] >> 4) : (int)v[j]) + (a.q.bias ? (long long)a.q.bias[n] : 0ll);
                             int t = requant64(x, n, a.q);
                             if (a.r.ptr) {
                                 const long long u = (long long)t
@@ -669,16 +723,17 @@ static CUtensorMapSwizzle swizzle_for(int bk)
 
 // resident_b = bytes of the weight block kept in shared memory for the whole launch (0: weights ride the ring)
 // regions = staging regions per epilogue warp (1; 2 or 4 with a fused residual)
-static size_t igemm_smem_bytes(int stages, int BK, int BN, int regions, size_t resident_b)
+// w4: a stage also holds the packed form of its weight block, and one more barrier
+static size_t igemm_smem_bytes(int stages, int BK, int BN, int regions, size_t resident_b, int w4 = 0)
 {
-    return 1024 /*alignment slack*/ + resident_b + (size_t)stages * (BM + (resident_b ? 0 : BN)) * BK
+    return 1024 /*alignment slack*/ + resident_b + (size_t)stages * ((BM + (resident_b ? 0 : BN)) * BK + (w4 ? BN * BK / 2 : 0))
          + NUM_EPI_WARPS * REGION_BYTES * regions
-         + (2 * stages + 8 + 4 * NUM_EPI_WARPS) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+         + (2 * stages + 8 + 4 * NUM_EPI_WARPS + (w4 ? stages : 0)) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
                     const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
-                    int force_pair)
+                    int force_pair, int w4)
 {
     static const char* kWhy = "";
     *why = kWhy;
@@ -706,6 +761,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
         while (!force_pair && bn > 64 && m_tiles * ((g.O + bn - 1) / bn) < num_sms) bn >>= 1;
     }
     plan->BN = bn;
+    plan->w4 = w4 ? 1 : 0;
     plan->a_unsigned = in_unsigned;
     plan->oW = g.oW; plan->oH = g.oH; plan->kW = g.kW;
     plan->sX = g.sX; plan->sY = g.sY; plan->pL = g.pL; plan->pT = g.pT; plan->dX = g.dX; plan->dY = g.dY;
@@ -719,15 +775,15 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     // A CTA whose column block never changes keeps that block's weights in shared memory: the loads of
     // a small-K layer are then activations only.
     const size_t wblock = (size_t)plan->taps * ((g.C + plan->BK - 1) / plan->BK) * plan->BK * plan->BN;
-    plan->b_resident = (wblock <= 96 * 1024 && (num_n_tiles == 1 || num_sms > num_n_tiles)) ? 1 : 0;
+    plan->b_resident = (!w4 && wblock <= 96 * 1024 && (num_n_tiles == 1 || num_sms > num_n_tiles)) ? 1 : 0;
     const int num_kb = plan->taps * ((g.C + plan->BK - 1) / plan->BK);
     auto depth = [&](int regions, size_t resident) {
         int st = 8;
-        while (st > 2 && igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident) > 226 * 1024) --st;
+        while (st > 2 && igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident, w4) > 226 * 1024) --st;
         return st;
     };
     auto fits = [&](int st, int regions, size_t resident) {
-        return igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident) <= 226 * 1024;
+        return igemm_smem_bytes(st, plan->BK, plan->BN, regions, resident, w4) <= 226 * 1024;
     };
     // A residual cell stages the residual of up to three tiles ahead when that leaves the ring deep enough
     // (four regions per epilogue warp instead of two): its loads then have two tile times to arrive.
@@ -746,19 +802,22 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     }
     plan->stages = stages;
     plan->res_slots = with_res ? regions : 0;
-    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, regions, resident);
+    plan->smem_bytes = igemm_smem_bytes(stages, plan->BK, plan->BN, regions, resident, w4);
+    if (!fits(stages, regions, resident)) { *why = "the tile ring does not fit shared memory"; return -1; }
 
     const CUtensorMapSwizzle swz = swizzle_for(plan->BK);
     CUresult rc;
-    // B: weights [N][Ktot], K fastest
+    // B: weights [N][Ktot], K fastest; packed 4-bit weights: [N][Ktot / 2] bytes, loaded unswizzled (the expansion
+    // warps write the swizzled tile)
     {
-        const cuuint64_t dims[2] = {(cuuint64_t)plan->taps * g.C, (cuuint64_t)g.O};
-        const cuuint64_t strides[1] = {(cuuint64_t)plan->taps * g.C};
-        const cuuint32_t box[2] = {(cuuint32_t)plan->BK, (cuuint32_t)plan->BN};
+        const cuuint64_t kbytes = (cuuint64_t)plan->taps * g.C / (w4 ? 2 : 1);
+        const cuuint64_t dims[2] = {kbytes, (cuuint64_t)g.O};
+        const cuuint64_t strides[1] = {kbytes};
+        const cuuint32_t box[2] = {(cuuint32_t)(plan->BK / (w4 ? 2 : 1)), (cuuint32_t)plan->BN};
         const cuuint32_t estr[2] = {1, 1};
         rc = g_encode_tiled(&plan->tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w, dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, w4 ? CU_TENSOR_MAP_SWIZZLE_NONE : swz,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the weight matrix"; return -1; }
     }
     if (!plan->a_im2col) {
@@ -815,7 +874,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
         // 256-row variant: 256-column tiles, 128-byte K slabs, no residual, weights not resident, and enough
         // work per CTA that halving the weight traffic pays for the un-overlapped epilogue
         const int num_kb = plan->taps * (g.C / 128);
-        if (plan->BN == 256 && plan->BK == 128 && !res && !plan->b_resident && g.O % 32 == 0
+        if (plan->BN == 256 && plan->BK == 128 && !res && !plan->b_resident && !w4 && g.O % 32 == 0
             && (force_pair || (num_kb >= 8 && (long long)num_m_tiles * num_n_tiles >= 4ll * num_sms))) {
             const cuuint32_t box32[2] = {32, 32};
             rc = g_encode_tiled(&plan->tmO32, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)out, dims, strides, box32, estr,
@@ -886,9 +945,12 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        const void* variants[6] = {(const void*)igemm_i8_tcgen05_kernel<0>, (const void*)igemm_i8_tcgen05_kernel<1>,
-                                   (const void*)igemm_i8_tcgen05_kernel<2>, (const void*)igemm_i8_tcgen05_kernel<3>,
-                                   (const void*)igemm_i8_tcgen05_kernel<4>, (const void*)igemm_i8_tcgen05_kernel<5>};
+        const void* variants[12] = {(const void*)igemm_i8_tcgen05_kernel<0, false>, (const void*)igemm_i8_tcgen05_kernel<1, false>,
+                                    (const void*)igemm_i8_tcgen05_kernel<2, false>, (const void*)igemm_i8_tcgen05_kernel<3, false>,
+                                    (const void*)igemm_i8_tcgen05_kernel<4, false>, (const void*)igemm_i8_tcgen05_kernel<5, false>,
+                                    (const void*)igemm_i8_tcgen05_kernel<0, true>, (const void*)igemm_i8_tcgen05_kernel<1, true>,
+                                    (const void*)igemm_i8_tcgen05_kernel<2, true>, (const void*)igemm_i8_tcgen05_kernel<3, true>,
+                                    (const void*)igemm_i8_tcgen05_kernel<4, true>, (const void*)igemm_i8_tcgen05_kernel<5, true>};
         for (const void* fn : variants) {
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return e;
@@ -926,9 +988,13 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
         }
     }
     typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
-    static const Kernel kernels[6] = {igemm_i8_tcgen05_kernel<0>, igemm_i8_tcgen05_kernel<1>, igemm_i8_tcgen05_kernel<2>,
-                                      igemm_i8_tcgen05_kernel<3>, igemm_i8_tcgen05_kernel<4>, igemm_i8_tcgen05_kernel<5>};
-    return launch_pdl(kernels[mode], grid, NUM_THREADS, plan.smem_bytes, s, plan.tmA, plan.tmB, plan.tmO, plan.tmR, a);
+    static const Kernel kernels[2][6] = {
+        {igemm_i8_tcgen05_kernel<0, false>, igemm_i8_tcgen05_kernel<1, false>, igemm_i8_tcgen05_kernel<2, false>,
+         igemm_i8_tcgen05_kernel<3, false>, igemm_i8_tcgen05_kernel<4, false>, igemm_i8_tcgen05_kernel<5, false>},
+        {igemm_i8_tcgen05_kernel<0, true>, igemm_i8_tcgen05_kernel<1, true>, igemm_i8_tcgen05_kernel<2, true>,
+         igemm_i8_tcgen05_kernel<3, true>, igemm_i8_tcgen05_kernel<4, true>, igemm_i8_tcgen05_kernel<5, true>}};
+    return launch_pdl(kernels[plan.w4 ? 1 : 0][mode], grid, NUM_THREADS + (plan.w4 ? 32 * W4_UNPACK_WARPS : 0), plan.smem_bytes, s,
+                      plan.tmA, plan.tmB, plan.tmO, plan.tmR, a);
 }
 
 }  // namespace n2d2b

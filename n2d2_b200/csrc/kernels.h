@@ -132,6 +132,7 @@ struct IgemmPlan {
     int stages;
     int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
     int res_slots;        // fused residual: staging regions per epilogue warp (2 or 4), 0 without a residual
+    int w4;               // weights are packed 4-bit values in HBM ([N][Ktot / 2] bytes, even element in the high nibble)
     int perm;             // weight rows stored permuted inside blocks of this many output channels (32 or 16; 0 = not)
     int pair;             // large-K layer with 256-column tiles: CTAs take two 128-row tiles per weight slab
     CUtensorMap tmO32;    // output [M][N] bytes, box = 32 rows x 32 columns (the pair kernel's two-pass store)
@@ -146,7 +147,7 @@ struct IgemmPlan {
 // force_pair: take the 256-row variant wherever its structure allows, whatever the layer's size (tests)
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
                     const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
-                    int force_pair = 0);
+                    int force_pair = 0, int w4 = 0);
 // Whether a launch of this plan takes the 32-bit epilogue; such a cell's weight rows must be stored in the
 // permuted order (igemm_permute_weights with igemm_perm_block(plan)) and plan.perm set to that block size.
 bool igemm_uses_fast_epilogue(const IgemmPlan& plan, const FastQuant& fast, bool has_residual, int out_dtype);

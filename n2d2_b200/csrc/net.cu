@@ -74,7 +74,9 @@ struct CellRec {
     PoolGeom pgeom{};
     QuantHost q;
     std::vector<int8_t> weights;  // host copy, OHWI int8 (int4 already widened)
+    int wbits = 8;                // storage width the caller gave the weights in (8 or 4)
     int8_t* d_weights = nullptr;
+    size_t d_weight_bytes = 0;    // bytes of weights this cell keeps in HBM
     Engine engine = ENG_SIMT;
     // fused residual sum
     int residual = -1;
@@ -276,7 +278,10 @@ static long long ceil_div(long long a, long long b)  // b > 0
 
 // 64-bit form of the same rescale, for fixed-point scalings whose products leave 32 bits: no clamps (the final
 // pack saturates), so it applies when none is needed for other reasons; the shifted result must fit 32 bits.
-static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out)
+// pre_shift: the kernel's accumulator is the true sum times 2^pre_shift (packed 4-bit weights enter the tensor core
+// as 16 x their value): the shift grows by pre_shift and addend and clamp bounds are scaled, which leaves the
+// result unchanged; x_bound bounds the true sum.
+static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int pre_shift = 0)
 {
     if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned) || q.act == ACT_SATURATION) return false;
     const int C = q.nb_channels;
@@ -286,23 +291,24 @@ static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, st
         if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
         else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
         else { m = q.p0[c]; s = q.p1[c]; }
-        if (m < 0 || m > (1ll << 30) || s > 31) return false;
+        if (m < 0 || m > (1ll << 30) || s + pre_shift > 31) return false;
         const long long half = s > 0 ? (1ll << (s - 1)) : 0;
         const long long b = q.has_bias ? q.bias[c] : 0;
-        if (std::llabs(b) > (1ll << 30)) return false;   // keeps every 64-bit intermediate below 2^61
-        const long long add = b * m + half;                                   // < 2^62
+        if (std::llabs(b) > (1ll << 26)) return false;   // keeps every 64-bit intermediate below 2^61
+        const long long add = b * m + half;                                   // < 2^58
         const long long worst = x_bound * m + std::llabs(add);               // < 2^62 for x_bound < 2^30
         if ((worst >> s) > (1ll << 31) - 2) return false;
-        out[(size_t)0 * cpad + c] = (int32_t)(add >> 32);
+        const long long adds = add << pre_shift;
+        out[(size_t)0 * cpad + c] = (int32_t)(adds >> 32);
         out[(size_t)2 * cpad + c] = (int32_t)m;
-        out[(size_t)3 * cpad + c] = (int32_t)(uint32_t)(add & 0xffffffffll);
-        out[(size_t)4 * cpad + c] = (int32_t)s;
+        out[(size_t)3 * cpad + c] = (int32_t)(uint32_t)(adds & 0xffffffffll);
+        out[(size_t)4 * cpad + c] = (int32_t)(s + pre_shift);
     }
     return true;
 }
 
 static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int* eff_lo,
-                             int* eff_hi, bool* need_clamp)
+                             int* eff_hi, bool* need_clamp, int pre_shift = 0)
 {
     if (q.mode != SC_SINGLE_SHIFT && q.mode != SC_DOUBLE_SHIFT && q.mode != SC_FIXED_MULT16 && q.mode != SC_FIXED_MULT32)
         return false;
@@ -328,7 +334,7 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
         if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
         else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
         else { m = q.p0[c]; s = q.p1[c]; }
-        if (m < 0 || s > 30) return false;
+        if (m < 0 || s + pre_shift > 30) return false;
         const long long half = s > 0 ? (1ll << (s - 1)) : 0;
         long long L = 0, H = 0;
         if (m > 0) {
@@ -348,19 +354,20 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
         // with lo > hi yields hi, which is then on the saturating side as well)
         lo = std::max(lo, -x_bound);
         hi = std::min(hi, x_bound);
-        const long long p0 = lo * m + add, p1 = hi * m + add;
-        if (std::llabs(add) > LIM || std::llabs(p0) > LIM || std::llabs(p1) > LIM) return false;
-        if (x_bound * m + std::llabs(add) > LIM) *need_clamp = true;   // an unclamped product could overflow
-        out[(size_t)0 * cpad + c] = (int32_t)lo;
-        out[(size_t)1 * cpad + c] = (int32_t)hi;
+        const long long p0 = (lo * m + add) << pre_shift, p1 = (hi * m + add) << pre_shift;
+        if ((std::llabs(add) << pre_shift) > LIM || std::llabs(p0) > LIM || std::llabs(p1) > LIM) return false;
+        if (((x_bound * m + std::llabs(add)) << pre_shift) > LIM) *need_clamp = true;   // an unclamped product could overflow
+        out[(size_t)0 * cpad + c] = (int32_t)(lo << pre_shift);
+        out[(size_t)1 * cpad + c] = (int32_t)(hi << pre_shift);
         out[(size_t)2 * cpad + c] = (int32_t)m;
-        out[(size_t)3 * cpad + c] = (int32_t)add;
-        out[(size_t)4 * cpad + c] = (int32_t)s;
+        out[(size_t)3 * cpad + c] = (int32_t)(add << pre_shift);
+        out[(size_t)4 * cpad + c] = (int32_t)(s + pre_shift);
     }
     return true;
 }
 
-static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8 = false, int residual_unsigned = 0)
+static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8 = false, int residual_unsigned = 0,
+                       int pre_shift = 0)
 {
     c.fast = FastQuant{};
     if (tout.dtype != DT_I8) return 0;
@@ -368,17 +375,18 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     const int cpad = ((C + 255) / 256) * 256;
     std::vector<int32_t> f1, f2;
     int lo1, hi1, lo2 = 0, hi2 = 0;
-    // |accumulator| <= K * 255 * 128; the residual stage adds two 8-bit values
-    const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * 128ll;
-    if (acc_bound > (1ll << 30)) return 0;
+    // |accumulator| <= K * 255 * 128 (packed 4-bit weights: K * 255 * 8, entering the tensor core times 16); the
+    // residual stage adds two 8-bit values
+    const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * (pre_shift ? 8ll : 128ll);
+    if ((acc_bound << pre_shift) > (1ll << 30)) return 0;
     bool need_clamp = false, wide = false;
-    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) {
+    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp, pre_shift)) {
         // eff range etc. were set before the failing channel; retry in 64 bits
         need_clamp = false;
         if (c.q.out_bits != 8 || c.q.act == ACT_SATURATION
             || (c.q.mode != SC_SINGLE_SHIFT && c.q.mode != SC_DOUBLE_SHIFT && c.q.mode != SC_FIXED_MULT16
                 && c.q.mode != SC_FIXED_MULT32)
-            || !build_wide_quant(c.q, cpad, acc_bound, f1))
+            || !build_wide_quant(c.q, cpad, acc_bound, f1, pre_shift))
             return 0;
         wide = true;
         lo1 = c.q.out_unsigned ? 0 : -128;
@@ -409,7 +417,7 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
             for (int ch = 0; ch < C && ok; ++ch) {
                 const long long m = f1[(size_t)2 * cpad + ch], add = f1[(size_t)3 * cpad + ch], sh = f1[(size_t)4 * cpad + ch];
                 const long long nadd = add + (128ll << sh);
-                if (acc_bound * m + std::llabs(nadd) > LIM) ok = false;
+                if ((acc_bound << pre_shift) * m + std::llabs(nadd) > LIM) ok = false;
             }
         }
         if (ok) {
@@ -626,6 +634,7 @@ int n2d2b_net_add_conv(n2d2b_net* net, const n2d2b_conv_desc* d, const void* wei
     if (g.oH < 1 || g.oW < 1) return fail(N2D2B_ERR_INVALID, "convolution output would be empty");
     if (int rc = validate_quant(quant, g.O, true, c.q, bias)) return rc;
     unpack_weights(weights, d->weight_bits, (size_t)g.O, (size_t)g.kH * g.kW * g.Cg, c.weights);
+    c.wbits = d->weight_bits;
     TensorRec t;
     t.C = g.O; t.H = g.oH; t.W = g.oW;
     quant_output_type(c.q, &t.dtype, &t.is_unsigned);
@@ -656,6 +665,7 @@ int n2d2b_net_add_fc(n2d2b_net* net, int input, int nb_outputs, int weight_bits,
     g.groups = 1; g.Cg = g.C; g.Og = g.O; g.oH = g.oW = 1;
     if (int rc = validate_quant(quant, g.O, true, c.q, bias)) return rc;
     unpack_weights(weights, weight_bits, (size_t)g.O, (size_t)g.C, c.weights);
+    c.wbits = weight_bits;
     TensorRec t;
     t.C = g.O; t.H = 1; t.W = 1;
     quant_output_type(c.q, &t.dtype, &t.is_unsigned);
@@ -910,6 +920,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 stem_s2d_arrange_weights(g, c.weights.data(), arranged.data());
                 CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
                 CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
+                c.d_weight_bytes = arranged.size();
                 int Hs = 0, Ws = 0;
                 stem_s2d_dims(g, &Hs, &Ws);
                 CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * Hs * Ws * 16 + 256));
@@ -930,6 +941,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 stem_arrange_weights(g, c.weights.data(), arranged.data());
                 CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
                 CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
+                c.d_weight_bytes = arranged.size();
                 const char* why = "";
                 if (stem_make_plan(&c.stem, c.d_weights, g, net->tensors[c.inputs[0]].is_unsigned, net->num_sms, &why) == 0) {
                     int Hp = 0, Wp = 0;
@@ -957,10 +969,20 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
         } else {
             c.engine = ENG_SIMT;
         }
-        CUDA_TRY(cudaMalloc((void**)&c.d_weights, laid.size() + 256));
-        CUDA_TRY(cudaMemset(c.d_weights, 0, laid.size() + 256));
-        CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
-        if (!depthwise && !(flags & N2D2B_FORCE_SIMT) && g.groups == 1 && g.C % 16 == 0) {
+        // Packed 4-bit weights stay packed in HBM when the cell runs on the implicit-GEMM kernel, whose expansion
+        // warps unpack them tile by tile; every other kernel takes them widened to int8.
+        const bool igemm_shape = !depthwise && !(flags & N2D2B_FORCE_SIMT) && g.groups == 1 && g.C % 16 == 0;
+        bool w4 = c.wbits == 4 && igemm_shape;
+        auto pack4 = [](const std::vector<int8_t>& w) {
+            std::vector<int8_t> p(w.size() / 2);
+            for (size_t i = 0; i < p.size(); ++i) p[i] = (int8_t)(((w[2 * i] & 0xF) << 4) | (w[2 * i + 1] & 0xF));
+            return p;
+        };
+        c.d_weight_bytes = w4 ? laid.size() / 2 : laid.size();
+        CUDA_TRY(cudaMalloc((void**)&c.d_weights, c.d_weight_bytes + 256));
+        CUDA_TRY(cudaMemset(c.d_weights, 0, c.d_weight_bytes + 256));
+        if (!w4) CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
+        if (igemm_shape) {
             ConvGeom gb = g;
             gb.B = max_batch;
             const char* why = "";
@@ -971,35 +993,54 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             const void* enc_ptr = in_ptr ? in_ptr : (const void*)placeholder;
             const void* out_ptr = net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
             const void* res_ptr = c.residual >= 0 ? tensor_ptr(net, c.residual, nullptr) : nullptr;
-            if (igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
-                                (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
-                                (flags & N2D2B_FORCE_PAIR) ? 1 : 0) == 0) {
+            int planned = igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
+                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
+                                          (flags & N2D2B_FORCE_PAIR) ? 1 : 0, w4 ? 1 : 0);
+            if (planned != 0 && w4) {
+                // no room for the packed variant: widen the weights after all
+                w4 = false;
+                cudaFree(c.d_weights);
+                c.d_weights = nullptr;
+                c.d_weight_bytes = laid.size();
+                CUDA_TRY(cudaMalloc((void**)&c.d_weights, laid.size() + 256));
+                CUDA_TRY(cudaMemset(c.d_weights, 0, laid.size() + 256));
+                CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
+                planned = igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
+                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
+                                          (flags & N2D2B_FORCE_PAIR) ? 1 : 0, 0);
+            }
+            if (planned == 0) {
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
                 c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
                 if (!(flags & N2D2B_EXACT64_EPILOGUE)) {
                     const bool res_i8 = c.residual >= 0 && net->tensors[c.residual].dtype == DT_I8;
                     if (int rc = upload_fast(c, net->tensors[c.output], res_i8,
-                                             c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0))
+                                             c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0, w4 ? 4 : 0))
                         return rc;
                 }
                 // small-channel stride-1 layers read their input once, from a shared-memory patch
-                if (c.fast.enabled && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
+                if (!w4 && c.fast.enabled && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
                     && !(flags & (N2D2B_FORCE_IM2COL | N2D2B_EXACT64_EPILOGUE)) && patch_eligible(gb)
                     && patch_make_plan(&c.patch, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
                                        net->num_sms, &why) == 0)
                     c.engine = ENG_PATCH;
                 // a cell that stays on the implicit-GEMM kernel with the 32-bit epilogue stores its weight rows in
                 // the permuted order that epilogue reads (see perm_block)
-                if (c.engine == ENG_TCGEN05
-                    && igemm_uses_fast_epilogue(c.plan, c.fast, c.residual >= 0, net->tensors[c.output].dtype)) {
-                    const int pb = igemm_perm_block(c.plan);
-                    const size_t row_bytes = (size_t)g.kH * g.kW * g.Cg;
-                    std::vector<int8_t> permuted(laid.size());
-                    igemm_permute_weights(laid.data(), permuted.data(), g.O, row_bytes, pb);
-                    CUDA_TRY(cudaMemcpy(c.d_weights, permuted.data(), permuted.size(), cudaMemcpyHostToDevice));
-                    c.plan.perm = pb;
+                const bool permute = c.engine == ENG_TCGEN05
+                                     && igemm_uses_fast_epilogue(c.plan, c.fast, c.residual >= 0, net->tensors[c.output].dtype);
+                if (permute || w4) {
+                    std::vector<int8_t> rows = laid;
+                    if (permute) {
+                        const int pb = igemm_perm_block(c.plan);
+                        igemm_permute_weights(laid.data(), rows.data(), g.O, (size_t)g.kH * g.kW * g.Cg, pb);
+                        c.plan.perm = pb;
+                    }
+                    if (w4) rows = pack4(rows);
+                    CUDA_TRY(cudaMemcpy(c.d_weights, rows.data(), rows.size(), cudaMemcpyHostToDevice));
                 }
+            } else if (w4) {
+                return fail(N2D2B_ERR_STATE, "internal: a packed cell without a plan");
             }
         }
     }
@@ -1070,10 +1111,10 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
             ConvGeom gb = c.geom;
             gb.B = net->max_batch;
             const char* why = "";
-            const int perm = c.plan.perm;   // a property of the stored weights, not of the tensor maps
+            const int perm = c.plan.perm, w4 = c.plan.w4;   // properties of the stored weights, not of the tensor maps
             if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? out : nullptr, r.ptr, gb, tin.is_unsigned,
                                 (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
-                                (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0))
+                                (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0, w4))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
             c.plan.perm = perm;
             c.plan_input = in0;
@@ -1414,6 +1455,19 @@ int n2d2b_net_read_tensor(n2d2b_net* net, int id, int batch, void* host_dst, siz
     return check_status(net);
 }
 
+int n2d2b_net_weight_bytes(const n2d2b_net* net, size_t* total_bytes, size_t* packed4_bytes)
+{
+    if (!net || !net->finalized) return fail(N2D2B_ERR_STATE, "the network is not finalized");
+    size_t total = 0, packed = 0;
+    for (const CellRec& c : net->cells) {
+        total += c.d_weight_bytes;
+        if (c.engine == ENG_TCGEN05 && c.plan.w4) packed += c.d_weight_bytes;
+    }
+    if (total_bytes) *total_bytes = total;
+    if (packed4_bytes) *packed4_bytes = packed;
+    return 0;
+}
+
 int n2d2b_net_launches_per_forward(const n2d2b_net* net)
 {
     if (!net || !net->finalized) return fail(N2D2B_ERR_STATE, "the network is not finalized");
@@ -1428,7 +1482,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
         const CellRec& c = net->cells[cell];
         const bool pair = c.plan.pair && c.fast.enabled && !c.fast.wide && c.residual < 0
                           && net->tensors[c.output].dtype == DT_I8 && c.geom.O % 32 == 0;
-        return pair ? "tcgen05-pair" : "tcgen05";
+        return pair ? "tcgen05-pair" : (c.plan.w4 ? "tcgen05-w4" : "tcgen05");
     }
     case ENG_SIMT: return "simt";
     case ENG_DEPTHWISE: return "depthwise";

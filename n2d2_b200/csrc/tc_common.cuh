@@ -61,6 +61,18 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the hardware may park the thread until the phase completes or about `ns`
+// nanoseconds pass, so a long wait costs a handful of instructions instead of a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(unsigned bar, unsigned parity, unsigned ns)
+{
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -76,17 +88,14 @@ __device__ __forceinline__ bool mbar_wait_for(unsigned bar, unsigned parity, vol
     // try_wait suspends the thread in hardware until the phase completes or a time limit passes, so a
     // waiting warp leaves the issue slots to the warps that work
     const unsigned long long t0 = globaltimer_ns();
-    unsigned rounds = 0;
     while (true) {
-        // a few polls per look at the abort flag and the clock
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        // A failed try_wait comes back within tens of cycles, so a long wait (an issuer whose accumulators the
+        // A plain failed try_wait comes back within tens of cycles, so a long wait (an issuer whose accumulators the
         // epilogue still holds, an epilogue warp whose residual is still on its way from DRAM) would fill the issue
-        // slots of the warps that work: after a short tight phase the waiter sleeps between polls.
-        if (++rounds > 8) __nanosleep(128);
+        // slots of the warps that work.  With a suspend-time hint the thread is parked until the phase completes (it
+        // wakes at once then) or the hint runs out, and only then looks at the abort flag and the clock.
+        if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+        if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+        if (*abort_flag) return false;
         if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);

@@ -95,6 +95,7 @@ def load():
         lib.n2d2b_net_tensor_info.argtypes = [C.c_void_p, C.c_int, C.POINTER(TensorInfo)]
         lib.n2d2b_net_read_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
         lib.n2d2b_net_launches_per_forward.argtypes = [C.c_void_p]
+        lib.n2d2b_net_weight_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
         lib.n2d2b_net_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                           C.c_void_p]
         lib.n2d2b_scaling_propagate.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(Quant),
@@ -220,6 +221,12 @@ class QuantizedNet:
 
     def engines(self):
         return [self.lib.n2d2b_net_cell_engine(self.handle, i).decode() for i in range(len(self.desc['layers']))]
+
+    def weight_bytes(self):
+        """(bytes of weights in HBM, bytes among them that are packed 4-bit weights)."""
+        total, packed = C.c_size_t(), C.c_size_t()
+        check(self.lib.n2d2b_net_weight_bytes(self.handle, C.byref(total), C.byref(packed)))
+        return total.value, packed.value
 
     def launches_per_forward(self):
         return check(self.lib.n2d2b_net_launches_per_forward(self.handle))

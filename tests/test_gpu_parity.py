@@ -118,7 +118,7 @@ def test_small_networks_cell_by_cell(name, force):
     n, eng = compare_net(net, 3, flags=KEEP | force)
     assert n == len(net['layers'])
     if not force and 'resnet' in name:
-        assert 'tcgen05' in eng
+        assert any(e.startswith('tcgen05') for e in eng)
 
 
 @pytest.mark.parametrize('name', ['resnet50', 'resnet18', 'mobilenet'])
@@ -394,3 +394,47 @@ def test_input_edge_quantizes_float_stimuli_like_the_range_transform():
         torch.cuda.synchronize()
         want = np.clip(np.trunc(xs.astype(np.float32) * np.float32(factor)), lo, hi).astype(dt).transpose(0, 2, 3, 1)
         assert np.array_equal(d_out.cpu().numpy().view(dt), want)
+
+
+# (C, H, O, k, stride, pad, input unsigned): 4-bit weights, packed two per byte in HBM and expanded in the kernel
+W4_CASES = [(64, 8, 64, 1, 1, 0, True), (128, 8, 256, 1, 1, 0, True), (48, 9, 32, 3, 1, 1, True), (256, 14, 512, 1, 2, 0, False),
+            (64, 30, 64, 3, 1, 1, True), (512, 7, 1024, 1, 1, 0, True), (128, 15, 128, 3, 2, 1, True), (256, 9, 256, 3, 1, 1, True)]
+
+
+@pytest.mark.parametrize('case', W4_CASES, ids=lambda c: 'C%d_H%d_O%d_k%d_s%d' % c[:5])
+@pytest.mark.parametrize('mode', ['double', 'fixed', 'single'])
+def test_packed_int4_weights_on_the_tensor_cores(case, mode):
+    C, H, O, k, s, p, uns = case
+    for clipped in ((False, True) if mode == 'fixed' else (False,)):
+        net = single_conv_net(C, H, H, O, k, s, p, in_unsigned=uns, mode=mode, weight_bits=4, clipped=clipped)
+        compare_net(net, 3, want_engine='tcgen05-w4')
+        compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='tcgen05-w4')
+
+
+def test_packed_int4_weights_stay_packed_in_hbm_and_fuse_residuals():
+    net = netdesc.resnet18(size=64, classes=100, weight_bits=4, clipped=True)
+    n, eng = compare_net(net, 3, flags=0)
+    assert 'fused' in eng
+    qn = runtime.QuantizedNet(net, 3)
+    try:
+        total, packed = qn.weight_bytes()
+        eng = qn.engines()
+    finally:
+        qn.close()
+    w4 = [l for l, e in zip(net['layers'], eng) if e == 'tcgen05-w4']
+    # every convolution but the three-channel first layer, and the classifier, hold half a byte per weight
+    assert len(w4) == sum(1 for l in net['layers'] if l['type'] in ('conv', 'fc')) - 1
+    assert packed == sum(int(l['weights'].size) for l in w4) // 2
+    assert packed > 0.95 * total
+    # a network given the same weights unpacked holds twice as much
+    qn8 = runtime.QuantizedNet(net, 3, pack4=False)
+    try:
+        total8, packed8 = qn8.weight_bytes()
+    finally:
+        qn8.close()
+    assert packed8 == 0 and total8 >= 2 * packed
+    # residual sums in both signedness combinations, unclipped scalings (the dot-product epilogue)
+    for mode in ('double', 'single'):
+        net = netdesc.resnet18(size=48, classes=10, weight_bits=4, scaling=mode)
+        n, eng = compare_net(net, 3, flags=0)
+        assert 'fused' in eng and 'tcgen05-w4' in eng
