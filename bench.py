@@ -156,6 +156,15 @@ def launch_groups(net, engines):
     elems = {k: v[0] * v[1] * v[2] for k, v in shapes.items()}
     groups, owner = [], {}
     for i, l in enumerate(net['layers']):
+        if engines[i] == 'fused' and l['type'] == 'pool':
+            # a max pooling folded into the first-layer kernel: that launch writes the pooled tensor only
+            conv = l['inputs'][0]
+            g = groups[owner[conv]]
+            g['layers'].append(i)
+            g['bytes'] += elems[i] - elems[conv]
+            g['name'] += '+' + l['name']
+            owner[i] = owner[conv]
+            continue
         if engines[i] == 'fused':
             conv = max(j for j in l['inputs'] if j >= 0 and net['layers'][j]['type'] == 'conv' and j in owner)
             g = groups[owner[conv]]

@@ -79,18 +79,23 @@ struct StemS2dPlan {
     const int8_t* w;      // weights in the canonical unswizzled K-major layout (device)
     int BN, KH, KWp, Wp;
     int R, bands;
+    int row_stride;       // convolution rows between bands
+    int pool_k, pool_s, P, pool_oH, pool_oW;   // fused max pooling (P = pooled rows per band; 0 = none)
+    int cbuf_alloc;       // bytes of one band-sized output buffer of the fused pooling
     int band_bytes, band_alloc, w_bytes;
     int in_unsigned;
     int num_sms;
     size_t smem_bytes;
 };
 bool stem_s2d_eligible(const ConvGeom& g);
+bool stem_s2d_pool_eligible(const ConvGeom& g, const PoolGeom& p);
 void stem_s2d_dims(const ConvGeom& g, int* Hs, int* Ws);
 size_t stem_s2d_weight_bytes(const ConvGeom& g);
 void stem_s2d_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* dst);
 cudaError_t launch_s2d_image(const void* in, const ConvGeom& g, int batch, void* out, cudaStream_t s);
+// pool: a max pooling folded into the kernel (stem_s2d_pool_eligible); `out` of the launch is then the pooled tensor
 int stem_s2d_make_plan(StemS2dPlan* plan, const void* d_s2d, const int8_t* d_w_arranged, const ConvGeom& g, int max_batch,
-                       int in_unsigned, int num_sms, const char** why);
+                       int in_unsigned, int num_sms, const char** why, const PoolGeom* pool = nullptr);
 cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_base, const FastQuant& fast, void* out,
                             int* status_word, cudaStream_t s);
 

@@ -86,6 +86,9 @@ struct CellRec {
     // 32-bit epilogue constants (tensor-core cells)
     FastQuant fast{};
     int* d_fast = nullptr;
+    // a max pooling folded into the first-layer kernel (the cell's output then is the pooled tensor)
+    bool pool_fused = false;
+    PoolGeom fused_pool{};
     // first-layer tensor-core kernels
     StemPlan stem{};
     StemS2dPlan stem2{};
@@ -804,6 +807,10 @@ static int head_candidate_prefix(const n2d2b_net* net)
 // a head tensor may be written while slices < k of every other head tensor are complete and still needed: two
 // head tensors share a buffer only when they have the same bytes per image (slice k of one then lies exactly
 // over slice k of the other, which the per-slice order of the cells has already retired).
+// A stride-2 first layer whose only reader is a max pooling writes the pooled tensor directly (the POOL variant of
+// the space-to-depth kernel): the convolution's output, the largest tensor of such a network, is never stored.
+static int fuse_stem_pool(n2d2b_net* net);
+
 static int plan_buffers(n2d2b_net* net)
 {
     const bool keep_all = (net->flags & N2D2B_KEEP_ALL_OUTPUTS) != 0;
@@ -891,6 +898,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     net->max_batch = max_batch;
     net->flags = flags;
     if (!(flags & N2D2B_NO_FUSION)) fuse_residuals(net);
+    if (!(flags & (N2D2B_NO_FUSION | N2D2B_KEEP_ALL_OUTPUTS | N2D2B_FORCE_SIMT | N2D2B_EXACT64_EPILOGUE)))
+        if (int rc = fuse_stem_pool(net)) return rc;
     net->head_limit = head_candidate_prefix(net);
     if (int rc = plan_buffers(net)) return rc;
     CUDA_TRY(cudaMalloc(&net->d_status, 64));
@@ -913,7 +922,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
         const bool stem = !depthwise && c.type == CELL_CONV && !(flags & N2D2B_FORCE_SIMT) && c.residual < 0
                           && stem_eligible(g) && net->tensors[c.output].dtype == DT_I8 && !(flags & N2D2B_EXACT64_EPILOGUE);
         if (stem) {
-            if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+            if (!c.d_fast)
+                if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
             if (c.fast.enabled && stem_s2d_eligible(g)) {
                 // stride 2: space-to-depth image, no gather
                 std::vector<int8_t> arranged(stem_s2d_weight_bytes(g));
@@ -926,11 +936,12 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 CUDA_TRY(cudaMalloc(&c.d_pad4, (size_t)max_batch * Hs * Ws * 16 + 256));
                 const char* why = "";
                 if (stem_s2d_make_plan(&c.stem2, c.d_pad4, c.d_weights, g, max_batch, net->tensors[c.inputs[0]].is_unsigned,
-                                       net->num_sms, &why) == 0) {
+                                       net->num_sms, &why, c.pool_fused ? &c.fused_pool : nullptr) == 0) {
                     net->launches++;
                     c.engine = ENG_STEM_S2D;
                     continue;
                 }
+                if (c.pool_fused) return fail(N2D2B_ERR_STATE, "internal: the fused first layer has no plan (%s)", why);
                 cudaFree(c.d_weights);
                 c.d_weights = nullptr;
                 cudaFree(c.d_pad4);
@@ -1078,6 +1089,39 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     }
     CUDA_TRY(cudaStreamCreateWithFlags(&net->download_stream, cudaStreamNonBlocking));
     net->finalized = true;
+    return 0;
+}
+
+static int fuse_stem_pool(n2d2b_net* net)
+{
+    std::vector<int> consumers(net->tensors.size(), 0);
+    for (const CellRec& c : net->cells)
+        if (!c.skipped)
+            for (int i : c.inputs) consumers[i]++;
+    for (size_t ci = 0; ci < net->cells.size(); ++ci) {
+        CellRec& c = net->cells[ci];
+        if (c.skipped || c.type != CELL_CONV || c.residual >= 0 || c.inputs[0] != 0) continue;
+        if (!stem_eligible(c.geom) || !stem_s2d_eligible(c.geom)) continue;
+        const int t = c.output;
+        if (consumers[t] != 1 || net->tensors[t].dtype != DT_I8) continue;
+        int pj = -1;
+        for (size_t cj = ci + 1; cj < net->cells.size(); ++cj)
+            if (!net->cells[cj].skipped && net->cells[cj].inputs.size() == 1 && net->cells[cj].inputs[0] == t) { pj = (int)cj; break; }
+        if (pj < 0 || net->cells[pj].type != CELL_POOL) continue;
+        CellRec& p = net->cells[pj];
+        if (!stem_s2d_pool_eligible(c.geom, p.pgeom)) continue;
+        // the first-layer kernel needs the 32-bit epilogue
+        if (int rc = upload_fast(c, net->tensors[t])) return rc;
+        if (!c.fast.enabled) continue;
+        c.pool_fused = true;
+        c.fused_pool = p.pgeom;
+        net->tensors[t].readable = false;
+        net->tensors[t].buffer = -2;   // never materialised
+        c.output = p.output;
+        net->tensors[p.output].producer = (int)ci;
+        p.skipped = true;
+        p.engine = ENG_FUSED;
+    }
     return 0;
 }
 
@@ -1490,7 +1534,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
     case ENG_SUM: return "sum";
     case ENG_FUSED: return "fused";
     case ENG_STEM: return "stem-tcgen05";
-    case ENG_STEM_S2D: return "stem-tcgen05";
+    case ENG_STEM_S2D: return net->cells[cell].pool_fused ? "stem-pool-tcgen05" : "stem-tcgen05";
     case ENG_PATCH: return "patch-tcgen05";
     }
     return "";

@@ -18,6 +18,14 @@
 // epilogue warps each drain every fourth 128-position tile (32-bit requantisation in the fragment layout, swizzled staging, one
 // 16-byte-vector copy per pixel row to the NHWC output).  Positions in the halo columns (x >= oW) compute
 // values nobody stores.  Every wait is bounded.
+//
+// POOL variant: the layer is followed by a max pooling (k x k window, stride s, no padding) and nothing else reads
+// its output.  A band then is the (P - 1) s + k convolution rows that P pooling rows need (bands advance by P s
+// rows, so k - s rows are computed twice); the epilogue warps requantise every tile straight into a band-sized
+// buffer in shared memory (one 64- or 128-byte row per position, 16-byte units swizzled like the staging regions),
+// meet on a barrier once the band is complete, and then take the maxima from that buffer and write only the
+// pooled rows.  Two such buffers alternate, so the pooling of one band overlaps the MMAs of the next.  The
+// convolution's own output (the largest tensor of a ResNet) never exists in HBM.
 #include <cstring>
 #include <vector>
 #include <atomic>
@@ -38,6 +46,10 @@ struct S2dArgs {
     int KH, KWp;            // filter rows and (even) filter columns after space-to-depth
     int Wp;                 // pixels per row of the re-laid image = oW + KWp - 1
     int R, bands;           // output rows per band, bands per image
+    int row_stride;         // convolution rows from one band to the next (R, or P * pool_s with a fused pooling)
+    int pool_k, pool_s, P;  // fused max pooling: window, stride, pooled rows per band
+    int pool_oH, pool_oW;
+    int cbuf_alloc;         // bytes of one band-sized output buffer (fused pooling)
     int n_base;             // first image of this call within the re-laid buffer (batch slices)
     int band_bytes;         // bytes one band load delivers (the full TMA box)
     int band_alloc;         // bytes reserved per band buffer
@@ -133,7 +145,7 @@ __device__ __forceinline__ void s2d_drain(unsigned tbase, unsigned par_off, unsi
 }
 
 // SHAPE: 0 = any filter (loops), 1 = 4 x 4 (a 7x7/2 or 8x8/2 filter), 2 = 2 x 2 (a 3x3/2 filter)
-template <bool CLAMP, int SHAPE>
+template <bool CLAMP, int SHAPE, bool POOL>
 __global__ void __launch_bounds__(Z_THREADS, 1)
 stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a)
 {
@@ -141,16 +153,17 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* res_b = smem;
     unsigned char* band0 = smem + (((size_t)a.w_bytes + 1023) & ~(size_t)1023);
-    unsigned char* stage_out = band0 + 2 * (size_t)a.band_alloc;               // [16 warps][32 rows][BN]
+    unsigned char* stage_out = band0 + 2 * (size_t)a.band_alloc;               // [16 warps][32 rows][BN], or two band-sized buffers
     const int region_bytes = 32 * a.BN;
-    unsigned long long* bars = (unsigned long long*)(stage_out + (size_t)Z_EPI_WARPS * region_bytes);
-    // bars: band_full[2], band_empty[2], tmem_full[4], tmem_empty[4], weights
+    unsigned long long* bars = (unsigned long long*)(stage_out + (POOL ? 2 * (size_t)a.cbuf_alloc : (size_t)Z_EPI_WARPS * region_bytes));
+    // bars: band_full[2], band_empty[2], tmem_full[4], tmem_empty[4], weights, (spare), band_complete[2]
     const unsigned pfull0 = smem_u32(bars);
     const unsigned pempty0 = pfull0 + 16u;
     const unsigned tfull0 = pempty0 + 16u;
     const unsigned tempty0 = tfull0 + 8u * Z_SLOTS;
     const unsigned bfull = tempty0 + 8u * Z_SLOTS;
-    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * Z_SLOTS + 2);
+    const unsigned cdone0 = bfull + 16u;
+    unsigned* tmem_slot = (unsigned*)(bars + 4 + 2 * Z_SLOTS + 2 + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* par = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // [FAST_NP][256]
 
@@ -168,6 +181,8 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
             mbar_init(tempty0 + 8u * s, 4);
         }
         mbar_init(bfull, 1);
+        mbar_init(cdone0, Z_EPI_WARPS);
+        mbar_init(cdone0 + 8u, Z_EPI_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -185,7 +200,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     const int items = a.B * a.bands;
-    auto band_rows = [&](int band) { const int r = a.oH - band * a.R; return r < a.R ? r : a.R; };
+    auto band_rows = [&](int band) { const int r = a.oH - band * a.row_stride; return r < a.R ? r : a.R; };
     auto band_tiles = [&](int band) { return (band_rows(band) * a.Wp + ZBM - 1) / ZBM; };
 
     if (warp == 0) {
@@ -201,7 +216,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 if (!mbar_wait(pempty0 + 8u * pb, ph ^ 1u, abort_flag, a.status, 1)) break;
                 mbar_expect_tx(pfull0 + 8u * pb, (unsigned)a.band_bytes);
-                tma_load_3d(smem_u32(band0 + (size_t)pb * a.band_alloc), &tmA, pfull0 + 8u * pb, 0, band * a.R, a.n_base + n);
+                tma_load_3d(smem_u32(band0 + (size_t)pb * a.band_alloc), &tmA, pfull0 + 8u * pb, 0, band * a.row_stride, a.n_base + n);
                 n += step_n;
                 band += step_b;
                 if (band >= a.bands) { band -= a.bands; ++n; }
@@ -266,6 +281,67 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
         const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
         bool ok = true;
+        if (POOL) {
+            const unsigned cbuf0_off = (unsigned)(stage_out - smem_raw);
+            const int epi_tid = ew * 32 + lane;
+            const int nvec = a.N >> 4;                       // 16-byte units per pixel
+            unsigned bandit = 0;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++bandit) {
+                const int T = band_tiles(band);
+                const unsigned cb = bandit & 1u;
+                const unsigned cbuf_off = cbuf0_off + cb * (unsigned)a.cbuf_alloc;
+                for (int t = 0; t < T; ++t, ++seq) {
+                    if ((int)(seq & (Z_SLOTS - 1)) != group) continue;
+                    const unsigned sph = (seq / Z_SLOTS) & 1u;
+                    if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
+                    // this warp's 32 positions of the tile, at their place in the band buffer (a multiple of 32 rows
+                    // from its start, so the swizzle term of a row is the one the staging regions use)
+                    const unsigned dst_off = cbuf_off + (unsigned)((t * ZBM + quad * 32) * a.BN);
+                    if (a.wide) {
+                        if (a.out_unsigned) s2d_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, dst_off, a.BN, lane);
+                        else s2d_drain<false, EF_WIDE>(tbase, par_off, dst_off, a.BN, lane);
+                    } else if (a.out_unsigned) s2d_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, dst_off, a.BN, lane);
+                    else s2d_drain<CLAMP, 0>(tbase, par_off, dst_off, a.BN, lane);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty0 + 8u * group);
+                }
+                if (!ok) break;
+                // every warp has written its tiles of the band: meet, then pool from the complete band
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cdone0 + 8u * cb);
+                if (!mbar_wait_warp(cdone0 + 8u * cb, (bandit >> 1) & 1u, abort_flag, a.status, 13, lane)) { ok = false; break; }
+                const int prow0 = band * a.P;
+                const int np = a.pool_oH - prow0 < a.P ? a.pool_oH - prow0 : a.P;
+                const int units = np * a.pool_oW * nvec;
+                const unsigned char* cbuf = dyn_smem() + cbuf_off;
+                for (int u = epi_tid; u < units; u += 32 * Z_EPI_WARPS) {
+                    const int v = u % nvec;
+                    const int pq = u / nvec;
+                    const int q = pq % a.pool_oW, pr = pq / a.pool_oW;
+                    uint4 m = make_uint4(0, 0, 0, 0);
+                    for (int dy = 0; dy < a.pool_k; ++dy)
+                        for (int dx = 0; dx < a.pool_k; ++dx) {
+                            const unsigned pos = (unsigned)((pr * a.pool_s + dy) * a.Wp + q * a.pool_s + dx);
+                            const unsigned ro = pos * (unsigned)a.BN;
+                            const uint4 x = *(const uint4*)(cbuf + ro + ((((unsigned)v) ^ ((ro >> 7) & swz_mask)) << 4));
+                            if ((dy | dx) == 0) m = x;
+                            else if (a.out_unsigned) {
+                                m.x = __vmaxu4(m.x, x.x); m.y = __vmaxu4(m.y, x.y); m.z = __vmaxu4(m.z, x.z); m.w = __vmaxu4(m.w, x.w);
+                            } else {
+                                m.x = __vmaxs4(m.x, x.x); m.y = __vmaxs4(m.y, x.y); m.z = __vmaxs4(m.z, x.z); m.w = __vmaxs4(m.w, x.w);
+                            }
+                        }
+                    uint8_t* dst = (uint8_t*)a.out + ((((size_t)n * a.pool_oH + (size_t)(prow0 + pr)) * a.pool_oW + q) * a.N);
+                    *(uint4*)(dst + v * 16) = m;
+                }
+                n += step_n;
+                band += step_b;
+                if (band >= a.bands) { band -= a.bands; ++n; }
+            }
+        } else {
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
             const int rows = band_rows(band);
             const int T = band_tiles(band);
@@ -320,6 +396,7 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
             band += step_b;
             if (band >= a.bands) { band -= a.bands; ++n; }
         }
+        }
     }
 
     tc_fence_before();
@@ -347,11 +424,12 @@ static void s2d_filter(const ConvGeom& g, int* P, int* KH, int* KWp)
     *KWp = (kw + 1) & ~1;   // an MMA covers two pixels
 }
 
-static size_t s2d_smem_bytes(int w_bytes, int BN, int band_alloc)
+// cbuf_alloc: bytes of one band-sized output buffer of the fused-pooling variant (0: per-warp staging regions)
+static size_t s2d_smem_bytes(int w_bytes, int BN, int band_alloc, int cbuf_alloc = 0)
 {
     const size_t b = ((size_t)w_bytes + 1023) & ~(size_t)1023;
-    return 1024 + b + 2 * (size_t)band_alloc + (size_t)Z_EPI_WARPS * 32 * BN + (4 + 2 * Z_SLOTS + 2) * 8 + 32
-         + FAST_NP * 256 * 4 + 64;
+    return 1024 + b + 2 * (size_t)band_alloc + (cbuf_alloc ? 2 * (size_t)cbuf_alloc : (size_t)Z_EPI_WARPS * 32 * BN)
+         + (4 + 2 * Z_SLOTS + 2 + 2) * 8 + 32 + FAST_NP * 256 * 4 + 64;
 }
 
 static int s2d_band_alloc(int Wp, int KH, int KWp, int R)
@@ -430,8 +508,23 @@ cudaError_t launch_s2d_image(const void* in, const ConvGeom& g, int batch, void*
     return cudaGetLastError();
 }
 
+// A max pooling this kernel can fold in: square window, same stride both ways, no padding, 8-bit channels in whole
+// 16-byte units.
+bool stem_s2d_pool_eligible(const ConvGeom& g, const PoolGeom& p)
+{
+    if (!(stem_s2d_eligible(g) && p.is_max && p.pH == p.pW && p.sY == p.sX && p.padY == 0 && p.padX == 0 && p.pH >= 1 && p.pH <= 4
+          && p.sY >= 1 && p.sY <= p.pH && p.H == g.oH && p.W == g.oW && p.C == g.O && g.O % 16 == 0 && p.oH >= 1 && p.oW >= 1))
+        return false;
+    // one pooled row per band must fit shared memory
+    int P0, KH, KWp;
+    s2d_filter(g, &P0, &KH, &KWp);
+    const int Wp = g.oW + KWp - 1, BN = g.O <= 64 ? 64 : 128, R = p.pH;
+    const int cbuf = ((R * Wp + ZBM - 1) / ZBM) * ZBM * BN;
+    return s2d_smem_bytes(KH * BN * KWp * 16, BN, s2d_band_alloc(Wp, KH, KWp, R), cbuf) <= 226 * 1024;
+}
+
 int stem_s2d_make_plan(StemS2dPlan* plan, const void* d_s2d, const int8_t* d_w_arranged, const ConvGeom& g, int max_batch,
-                       int in_unsigned, int num_sms, const char** why)
+                       int in_unsigned, int num_sms, const char** why, const PoolGeom* pool)
 {
     static const char* kWhy = "";
     *why = kWhy;
@@ -453,6 +546,24 @@ int stem_s2d_make_plan(StemS2dPlan* plan, const void* d_s2d, const int8_t* d_w_a
     plan->num_sms = num_sms;
     int best_R = 0;
     long long best_tiles = 0;
+    if (pool) {
+        // the most pooled rows per band that fit: fewer bands recompute fewer overlapping convolution rows
+        if (!stem_s2d_pool_eligible(g, *pool)) { *why = "pooling outside the fused first-layer kernel"; return -1; }
+        for (int P = 1; P <= pool->oH; ++P) {
+            const int R = (P - 1) * pool->sY + pool->pH;
+            if (R + plan->KH - 1 > 256) break;
+            const int cbuf = ((R * plan->Wp + ZBM - 1) / ZBM) * ZBM * plan->BN;
+            if (s2d_smem_bytes(plan->w_bytes, plan->BN, s2d_band_alloc(plan->Wp, plan->KH, plan->KWp, R), cbuf) > 226 * 1024) break;
+            best_R = R;
+            plan->P = P;
+            plan->cbuf_alloc = cbuf;
+        }
+        if (best_R == 0) { *why = "no band of the fused pooling fits shared memory"; return -1; }
+        plan->pool_k = pool->pH; plan->pool_s = pool->sY; plan->pool_oH = pool->oH; plan->pool_oW = pool->oW;
+        plan->R = best_R;
+        plan->row_stride = plan->P * pool->sY;
+        plan->bands = (pool->oH + plan->P - 1) / plan->P;
+    } else {
     for (int R = 1; R <= g.oH; ++R) {
         if (R + plan->KH - 1 > 256) break;
         if (s2d_smem_bytes(plan->w_bytes, plan->BN, s2d_band_alloc(plan->Wp, plan->KH, plan->KWp, R)) > 226 * 1024) break;
@@ -463,11 +574,13 @@ int stem_s2d_make_plan(StemS2dPlan* plan, const void* d_s2d, const int8_t* d_w_a
     }
     if (best_R == 0) { *why = "no band height fits shared memory"; return -1; }
     plan->R = best_R;
+    plan->row_stride = best_R;
     plan->bands = (g.oH + best_R - 1) / best_R;
+    }
     const int box_rows = best_R + plan->KH - 1;
     plan->band_bytes = box_rows * plan->Wp * 16;
     plan->band_alloc = s2d_band_alloc(plan->Wp, plan->KH, plan->KWp, best_R);
-    plan->smem_bytes = s2d_smem_bytes(plan->w_bytes, plan->BN, plan->band_alloc);
+    plan->smem_bytes = s2d_smem_bytes(plan->w_bytes, plan->BN, plan->band_alloc, plan->cbuf_alloc);
     int Hs, Ws;
     stem_s2d_dims(g, &Hs, &Ws);
     // the re-laid image as (8-byte words of a row, rows, images): one box = one band, rows below the image read as zero
@@ -490,6 +603,9 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     a.B = g.B; a.oH = g.oH; a.oW = g.oW; a.N = g.O; a.BN = plan.BN;
     if (a.B == 0) return cudaSuccess;
     a.KH = plan.KH; a.KWp = plan.KWp; a.Wp = plan.Wp; a.R = plan.R; a.bands = plan.bands;
+    a.row_stride = plan.row_stride;
+    a.pool_k = plan.pool_k; a.pool_s = plan.pool_s; a.P = plan.P; a.pool_oH = plan.pool_oH; a.pool_oW = plan.pool_oW;
+    a.cbuf_alloc = plan.cbuf_alloc;
     a.n_base = n_base;
     a.band_bytes = plan.band_bytes; a.band_alloc = plan.band_alloc; a.w_bytes = plan.w_bytes;
     a.rcp_Wp = (unsigned)(((1ull << 32) + (unsigned)plan.Wp - 1) / (unsigned)plan.Wp);
@@ -504,9 +620,12 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     a.out_unsigned = fast.out_unsigned;
     a.wide = fast.wide ? 1 : 0;
     typedef void (*Kernel)(const CUtensorMap, const S2dArgs);
-    static const Kernel variants[6] = {stem_s2d_tcgen05_kernel<false, 0>, stem_s2d_tcgen05_kernel<false, 1>,
-                                       stem_s2d_tcgen05_kernel<false, 2>, stem_s2d_tcgen05_kernel<true, 0>,
-                                       stem_s2d_tcgen05_kernel<true, 1>,  stem_s2d_tcgen05_kernel<true, 2>};
+    static const Kernel variants[12] = {stem_s2d_tcgen05_kernel<false, 0, false>, stem_s2d_tcgen05_kernel<false, 1, false>,
+                                        stem_s2d_tcgen05_kernel<false, 2, false>, stem_s2d_tcgen05_kernel<true, 0, false>,
+                                        stem_s2d_tcgen05_kernel<true, 1, false>,  stem_s2d_tcgen05_kernel<true, 2, false>,
+                                        stem_s2d_tcgen05_kernel<false, 0, true>,  stem_s2d_tcgen05_kernel<false, 1, true>,
+                                        stem_s2d_tcgen05_kernel<false, 2, true>,  stem_s2d_tcgen05_kernel<true, 0, true>,
+                                        stem_s2d_tcgen05_kernel<true, 1, true>,   stem_s2d_tcgen05_kernel<true, 2, true>};
     static std::atomic<bool> attr_set[64];   // set twice by racing first calls at worst: harmless
     int dev = 0;
     cudaGetDevice(&dev);
@@ -520,7 +639,7 @@ cudaError_t launch_stem_s2d(const StemS2dPlan& plan, const ConvGeom& g, int n_ba
     const long long items = (long long)a.B * a.bands;
     const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
     const int shape = (plan.KH == 4 && plan.KWp == 4) ? 1 : ((plan.KH == 2 && plan.KWp == 2) ? 2 : 0);
-    return launch_pdl(variants[(fast.need_clamp ? 3 : 0) + shape], grid, Z_THREADS, plan.smem_bytes, s, plan.tmA, a);
+    return launch_pdl(variants[(plan.P ? 6 : 0) + (fast.need_clamp ? 3 : 0) + shape], grid, Z_THREADS, plan.smem_bytes, s, plan.tmA, a);
 }
 
 }  // namespace n2d2b

@@ -438,3 +438,24 @@ def test_packed_int4_weights_stay_packed_in_hbm_and_fuse_residuals():
         net = netdesc.resnet18(size=48, classes=10, weight_bits=4, scaling=mode)
         n, eng = compare_net(net, 3, flags=0)
         assert 'fused' in eng and 'tcgen05-w4' in eng
+
+
+# (C, H, W, O, k, pad, activation, pooling window, pooling stride, input unsigned)
+STEM_POOL_CASES = [(3, 64, 64, 64, 7, 3, 'relu', 3, 2, True), (3, 224, 224, 64, 7, 3, 'relu', 3, 2, True),
+                   (3, 33, 29, 32, 3, 1, 'relu', 2, 2, True), (1, 24, 24, 32, 4, 0, 'linear', 2, 2, True),
+                   (4, 40, 36, 128, 5, 2, 'linear', 3, 2, False), (3, 50, 50, 96, 7, 3, 'relu', 3, 3, True),
+                   (3, 31, 47, 64, 3, 1, 'relu', 2, 1, True), (2, 20, 20, 64, 8, 0, 'relu', 4, 2, True)]
+
+
+@pytest.mark.parametrize('case', STEM_POOL_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_p%d_%s_pool%d_s%d' % c[:9])
+@pytest.mark.parametrize('mode', ['double', 'single'])
+def test_first_layer_with_the_max_pooling_folded_in(case, mode):
+    # stride-2 first layer + max pooling as one kernel: the pooled tensor is all that reaches HBM
+    C, H, W, O, k, p, act, pk, ps, uns = case
+    b = netdesc.NetBuilder('stempool', C, H, W, 13, mode, input_unsigned=uns, weight_dist=('normal', 30))
+    c = b.conv(-1, O, k, stride=2, pad=p, act=act, name='conv1')
+    b.pool(c, 'max', pk, ps, name='pool1')
+    for batch in (1, 5):
+        n, eng = compare_net(b.net, batch, flags=0)
+        assert eng == ['stem-pool-tcgen05', 'fused']
+    compare_net(b.net, 3)     # and as two cells, every output kept
