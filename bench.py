@@ -233,6 +233,8 @@ def main():
     ap.add_argument('--ref-images', type=int, default=8, help='images per step of the reference arm')
     ap.add_argument('--parity-images', type=int, default=4, help='images of the batch compared with the CPU oracle')
     ap.add_argument('--peak-probe', action='store_true', help='only measure the int8 tensor-pipe issue rate')
+    ap.add_argument('--finalize-flags', type=int, default=0,
+                    help='n2d2b_net_finalize flags (include/n2d2b.h), e.g. 64 = first layer and max pooling as one kernel')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--profile-out', default=None, help='write the per-cell device times here (JSON)')
     args = ap.parse_args()
@@ -264,7 +266,7 @@ def main():
 
     net = build_net(args)
     B = per_gpu_batch(args, world)
-    qn = runtime.QuantizedNet(net, B, device=local_rank)
+    qn = runtime.QuantizedNet(net, B, device=local_rank, flags=args.finalize_flags)
     i = net['input']
     gen = torch.Generator(device='cuda').manual_seed(1000 + rank)
     d_in = torch.randint(0, 256, (B, i['H'], i['W'], i['C']), dtype=torch.uint8, device='cuda', generator=gen)

@@ -67,8 +67,8 @@ struct IgemmArgs {
 // ----------------------------------------------------------------------------- the kernel
 // Eight packed 4-bit weights (one 32-bit word: byte i = elements 2i in the high and 2i + 1 in the low nibble) as
 // eight signed bytes holding 16 x the weight: the nibble moves to the top of its byte, which is the value times 16
-// with the right sign and needs no sign extension.  The epilogue's constants absorb the factor (its shift grows by
-// four), so the result is exact.
+// with the right sign and needs no sign extension.  The accumulator then holds 16 x the sum, a multiple of 16: the
+// epilogue shifts it right by four first, which is exact.
 __device__ __forceinline__ void expand_int4_x16(unsigned x, unsigned& w0, unsigned& w1)
 {
     const unsigned hi = x & 0xF0F0F0F0u, lo = (x << 4) & 0xF0F0F0F0u;
@@ -386,7 +386,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 e.abort_flag = abort_flag; e.status = a.status;
                 e.ef = a.ef;
                 e.t_lo = a.t_lo; e.t_hi = a.t_hi; e.dp_xor = a.dp_xor;
-                if (!fast_epilogue_tile<RES, CLAMP, DP, true>(&tmO, &tmR, e, quad, part, lane, est)) { ok = false; break; }
+                if (!fast_epilogue_tile<RES, CLAMP, DP, true, W4>(&tmO, &tmR, e, quad, part, lane, est)) { ok = false; break; }
                 continue;
             } else {
                 if (!mbar_wait_warp(tfull0 + 8u * as, aph, abort_flag, a.status, 4, lane)) { ok = false; break; }

@@ -281,10 +281,7 @@ static long long ceil_div(long long a, long long b)  // b > 0
 
 // 64-bit form of the same rescale, for fixed-point scalings whose products leave 32 bits: no clamps (the final
 // pack saturates), so it applies when none is needed for other reasons; the shifted result must fit 32 bits.
-// pre_shift: the kernel's accumulator is the true sum times 2^pre_shift (packed 4-bit weights enter the tensor core
-// as 16 x their value): the shift grows by pre_shift and addend and clamp bounds are scaled, which leaves the
-// result unchanged; x_bound bounds the true sum.
-static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int pre_shift = 0)
+static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out)
 {
     if (q.is_clipped || (q.act == ACT_RECTIFIER && !q.out_unsigned) || q.act == ACT_SATURATION) return false;
     const int C = q.nb_channels;
@@ -294,24 +291,23 @@ static bool build_wide_quant(const QuantHost& q, int cpad, long long x_bound, st
         if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
         else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
         else { m = q.p0[c]; s = q.p1[c]; }
-        if (m < 0 || m > (1ll << 30) || s + pre_shift > 31) return false;
+        if (m < 0 || m > (1ll << 30) || s > 31) return false;
         const long long half = s > 0 ? (1ll << (s - 1)) : 0;
         const long long b = q.has_bias ? q.bias[c] : 0;
-        if (std::llabs(b) > (1ll << 26)) return false;   // keeps every 64-bit intermediate below 2^61
-        const long long add = b * m + half;                                   // < 2^58
+        if (std::llabs(b) > (1ll << 30)) return false;   // keeps every 64-bit intermediate below 2^61
+        const long long add = b * m + half;                                   // < 2^62
         const long long worst = x_bound * m + std::llabs(add);               // < 2^62 for x_bound < 2^30
         if ((worst >> s) > (1ll << 31) - 2) return false;
-        const long long adds = add << pre_shift;
-        out[(size_t)0 * cpad + c] = (int32_t)(adds >> 32);
+        out[(size_t)0 * cpad + c] = (int32_t)(add >> 32);
         out[(size_t)2 * cpad + c] = (int32_t)m;
-        out[(size_t)3 * cpad + c] = (int32_t)(uint32_t)(adds & 0xffffffffll);
-        out[(size_t)4 * cpad + c] = (int32_t)(s + pre_shift);
+        out[(size_t)3 * cpad + c] = (int32_t)(uint32_t)(add & 0xffffffffll);
+        out[(size_t)4 * cpad + c] = (int32_t)s;
     }
     return true;
 }
 
 static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, std::vector<int32_t>& out, int* eff_lo,
-                             int* eff_hi, bool* need_clamp, int pre_shift = 0)
+                             int* eff_hi, bool* need_clamp)
 {
     if (q.mode != SC_SINGLE_SHIFT && q.mode != SC_DOUBLE_SHIFT && q.mode != SC_FIXED_MULT16 && q.mode != SC_FIXED_MULT32)
         return false;
@@ -337,7 +333,7 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
         if (q.mode == SC_SINGLE_SHIFT) { m = 1; s = q.p0[c]; }
         else if (q.mode == SC_DOUBLE_SHIFT) { m = 1 + (1ll << q.p0[c]); s = q.p1[c]; }
         else { m = q.p0[c]; s = q.p1[c]; }
-        if (m < 0 || s + pre_shift > 30) return false;
+        if (m < 0 || s > 30) return false;
         const long long half = s > 0 ? (1ll << (s - 1)) : 0;
         long long L = 0, H = 0;
         if (m > 0) {
@@ -357,20 +353,21 @@ static bool build_fast_quant(const QuantHost& q, int cpad, long long x_bound, st
         // with lo > hi yields hi, which is then on the saturating side as well)
         lo = std::max(lo, -x_bound);
         hi = std::min(hi, x_bound);
-        const long long p0 = (lo * m + add) << pre_shift, p1 = (hi * m + add) << pre_shift;
-        if ((std::llabs(add) << pre_shift) > LIM || std::llabs(p0) > LIM || std::llabs(p1) > LIM) return false;
-        if (((x_bound * m + std::llabs(add)) << pre_shift) > LIM) *need_clamp = true;   // an unclamped product could overflow
-        out[(size_t)0 * cpad + c] = (int32_t)(lo << pre_shift);
-        out[(size_t)1 * cpad + c] = (int32_t)(hi << pre_shift);
+        const long long p0 = lo * m + add, p1 = hi * m + add;
+        if (std::llabs(add) > LIM || std::llabs(p0) > LIM || std::llabs(p1) > LIM) return false;
+        if (x_bound * m + std::llabs(add) > LIM) *need_clamp = true;   // an unclamped product could overflow
+        out[(size_t)0 * cpad + c] = (int32_t)lo;
+        out[(size_t)1 * cpad + c] = (int32_t)hi;
         out[(size_t)2 * cpad + c] = (int32_t)m;
-        out[(size_t)3 * cpad + c] = (int32_t)(add << pre_shift);
-        out[(size_t)4 * cpad + c] = (int32_t)(s + pre_shift);
+        out[(size_t)3 * cpad + c] = (int32_t)add;
+        out[(size_t)4 * cpad + c] = (int32_t)s;
     }
     return true;
 }
 
+// w4: the cell's weights are 4-bit values (|w| <= 8), which tightens the accumulator bound
 static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8 = false, int residual_unsigned = 0,
-                       int pre_shift = 0)
+                       bool w4 = false)
 {
     c.fast = FastQuant{};
     if (tout.dtype != DT_I8) return 0;
@@ -378,18 +375,18 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
     const int cpad = ((C + 255) / 256) * 256;
     std::vector<int32_t> f1, f2;
     int lo1, hi1, lo2 = 0, hi2 = 0;
-    // |accumulator| <= K * 255 * 128 (packed 4-bit weights: K * 255 * 8, entering the tensor core times 16); the
-    // residual stage adds two 8-bit values
-    const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * (pre_shift ? 8ll : 128ll);
-    if ((acc_bound << pre_shift) > (1ll << 30)) return 0;
+    // |accumulator| <= K * 255 * 128 (4-bit weights: K * 255 * 8; they enter the tensor core times 16 and the
+    // epilogue divides the sum by 16 again before anything else); the residual stage adds two 8-bit values
+    const long long acc_bound = (long long)c.geom.kH * c.geom.kW * c.geom.Cg * 255ll * (w4 ? 8ll : 128ll);
+    if (acc_bound * (w4 ? 16 : 1) > (1ll << 30)) return 0;
     bool need_clamp = false, wide = false;
-    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp, pre_shift)) {
+    if (!build_fast_quant(c.q, cpad, acc_bound, f1, &lo1, &hi1, &need_clamp)) {
         // eff range etc. were set before the failing channel; retry in 64 bits
         need_clamp = false;
         if (c.q.out_bits != 8 || c.q.act == ACT_SATURATION
             || (c.q.mode != SC_SINGLE_SHIFT && c.q.mode != SC_DOUBLE_SHIFT && c.q.mode != SC_FIXED_MULT16
                 && c.q.mode != SC_FIXED_MULT32)
-            || !build_wide_quant(c.q, cpad, acc_bound, f1, pre_shift))
+            || !build_wide_quant(c.q, cpad, acc_bound, f1))
             return 0;
         wide = true;
         lo1 = c.q.out_unsigned ? 0 : -128;
@@ -420,7 +417,7 @@ static int upload_fast(CellRec& c, const TensorRec& tout, bool residual_dtype_i8
             for (int ch = 0; ch < C && ok; ++ch) {
                 const long long m = f1[(size_t)2 * cpad + ch], add = f1[(size_t)3 * cpad + ch], sh = f1[(size_t)4 * cpad + ch];
                 const long long nadd = add + (128ll << sh);
-                if ((acc_bound << pre_shift) * m + std::llabs(nadd) > LIM) ok = false;
+                if (acc_bound * m + std::llabs(nadd) > LIM) ok = false;
             }
         }
         if (ok) {
@@ -898,7 +895,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
     net->max_batch = max_batch;
     net->flags = flags;
     if (!(flags & N2D2B_NO_FUSION)) fuse_residuals(net);
-    if (!(flags & (N2D2B_NO_FUSION | N2D2B_KEEP_ALL_OUTPUTS | N2D2B_FORCE_SIMT | N2D2B_EXACT64_EPILOGUE)))
+    if ((flags & N2D2B_FUSE_FIRST_POOL)
+        && !(flags & (N2D2B_NO_FUSION | N2D2B_KEEP_ALL_OUTPUTS | N2D2B_FORCE_SIMT | N2D2B_EXACT64_EPILOGUE)))
         if (int rc = fuse_stem_pool(net)) return rc;
     net->head_limit = head_candidate_prefix(net);
     if (int rc = plan_buffers(net)) return rc;
@@ -1027,7 +1025,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 if (!(flags & N2D2B_EXACT64_EPILOGUE)) {
                     const bool res_i8 = c.residual >= 0 && net->tensors[c.residual].dtype == DT_I8;
                     if (int rc = upload_fast(c, net->tensors[c.output], res_i8,
-                                             c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0, w4 ? 4 : 0))
+                                             c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0, w4))
                         return rc;
                 }
                 // small-channel stride-1 layers read their input once, from a shared-memory patch

@@ -61,18 +61,6 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// The same with a suspend-time hint: the hardware may park the thread until the phase completes or about `ns`
-// nanoseconds pass, so a long wait costs a handful of instructions instead of a polling loop.
-__device__ __forceinline__ bool mbar_try_wait_hint(unsigned bar, unsigned parity, unsigned ns)
-{
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -88,13 +76,16 @@ __device__ __forceinline__ bool mbar_wait_for(unsigned bar, unsigned parity, vol
     // try_wait suspends the thread in hardware until the phase completes or a time limit passes, so a
     // waiting warp leaves the issue slots to the warps that work
     const unsigned long long t0 = globaltimer_ns();
+    unsigned rounds = 0;
     while (true) {
-        // A plain failed try_wait comes back within tens of cycles, so a long wait (an issuer whose accumulators the
+        // a few polls per look at the abort flag and the clock
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        // A failed try_wait comes back within tens of cycles, so a long wait (an issuer whose accumulators the
         // epilogue still holds, an epilogue warp whose residual is still on its way from DRAM) would fill the issue
-        // slots of the warps that work.  With a suspend-time hint the thread is parked until the phase completes (it
-        // wakes at once then) or the hint runs out, and only then looks at the abort flag and the clock.
-        if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
-        if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+        // slots of the warps that work: after a short tight phase the waiter sleeps between polls.
+        if (++rounds > 8) __nanosleep(128);
         if (*abort_flag) return false;
         if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
@@ -361,6 +352,7 @@ static constexpr int EF_DP_A_SIGNED = 8;    // DP: the packed (t, r) bytes are r
 static constexpr int EF_WIDE = 16;          // first rescale in 64 bits: x * mult + (row 0 : row 3 as a 64-bit addend) >> shift
 static constexpr int EF_DP_XOR = 32;        // DP: some of the packed (t, r) bytes are flipped between unsigned and signed (dp_xor)
 static constexpr int EF_PERM = 64;          // weights stored with permuted output channels (perm_block)
+static constexpr int EF_W4 = 128;           // the accumulator holds 16 x the sum (packed 4-bit weights, see expand_int4_x16)
 
 // NG 8-column groups (NG = 4: 32 columns, NG = 2: 16) of a warp's 32 accumulator rows in the fragment layout
 // of the 16x256b TMEM load (thread t: rows t/4 + {0, 8, 16, 24}, column pair 8i + 2(t%4) of group i), through the
@@ -606,6 +598,7 @@ __device__ __forceinline__ void perm_block(const unsigned* vA, const unsigned* v
             for (int c = 0; c < 4; ++c) {
                 // thread channel 4h + c = 2i + e  ->  group i = 2h + c / 2, element e = c % 2
                 int x = (int)v[4 * (2 * h + (c >> 1)) + 2 * (k & 1) + (c & 1)];
+                if (EF & EF_W4) x >>= 4;   // a multiple of 16: exact
                 if (CLAMP) x = min(max(x, lov[c]), hiv[c]);
                 if (EF & EF_WIDE) {
                     const long long p = (long long)x * muv[c] + (long long)(((unsigned long long)(unsigned)lov[c] << 32) | (unsigned)adv[c]);
@@ -725,11 +718,12 @@ __device__ __forceinline__ void epi_issue_residual(const CUtensorMap* tmR, unsig
     }
 }
 
-template <bool RES, bool CLAMP, bool DP, bool PERM = false>
+template <bool RES, bool CLAMP, bool DP, bool PERM = false, bool W4 = false>
 __device__ __forceinline__ bool fast_epilogue_tile(const CUtensorMap* tmO, const CUtensorMap* tmR, const EpiTile& e, int quad,
                                                    int cp, int lane, EpiState& st)
 {
-    constexpr int P = PERM ? EF_PERM : 0;
+    static_assert(PERM || !W4, "the packed-weight variant uses the permuted epilogue");
+    constexpr int P = (PERM ? EF_PERM : 0) | (W4 ? EF_W4 : 0);
     const int wp = e.wp;
     const int cbase = cp * wp;
     const int gx = e.n0 + cbase, gy = e.m0 + quad * 32;

@@ -22,6 +22,7 @@ FORCE_SIMT = 4
 FORCE_IM2COL = 8
 FORCE_PAIR = 32
 EXACT64_EPILOGUE = 16
+FUSE_FIRST_POOL = 64
 
 
 class N2D2BError(RuntimeError):

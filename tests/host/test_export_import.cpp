@@ -64,6 +64,16 @@ int main(int argc, char** argv)
             try { parseExportedCell("#define X_NB_OUTPUTS 2\nstatic const int32_t x_biases[X_NB_OUTPUTS] = {1, 2, 3};\n"); }
             catch (const std::runtime_error& e) { threw = std::string(e.what()).find("3 biases for 2 outputs") != std::string::npos; }
             std::cout << "malformed.threw " << (threw ? 1 : 0) << '\n';
+            // weights below four bits as the QAT export packs them (first value in the high bits, every run of channels
+            // padded to whole bytes; one-bit weights store -1 as 0)
+            const ExportedCell w2 = parseExportedCell(
+                "#define Q2_NB_OUTPUTS 1\n#define Q2_NB_CHANNELS 5\n#define Q2_KERNEL_WIDTH 1\n#define Q2_KERNEL_HEIGHT 1\n"
+                "static const data<2> q2_weights[Q2_WEIGHTS_SIZE] N2D2_SECTION_ATTRIBUTE(N2D2_SECTION_NN_WEIGHTS) = {0x72, 0x40, \n};\n");
+            line("w2.weights", w2.weights);
+            const ExportedCell w1 = parseExportedCell(
+                "#define Q1_NB_OUTPUTS 1\n#define Q1_NB_CHANNELS 9\n#define Q1_KERNEL_WIDTH 1\n#define Q1_KERNEL_HEIGHT 1\n"
+                "static const data<1> q1_weights[Q1_WEIGHTS_SIZE] N2D2_SECTION_ATTRIBUTE(N2D2_SECTION_NN_WEIGHTS) = {0x9b, 0x80, \n};\n");
+            line("w1.weights", w1.weights);
             return 0;
         }
         if (strcmp(argv[1], "--run") || argc < 6) { fprintf(stderr, "usage: see the top of the source file\n"); return 2; }

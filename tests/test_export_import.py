@@ -95,6 +95,8 @@ def test_headers_and_syntxt_parse_to_the_network_they_were_written_from():
     assert np.array_equal(ints('syntxt.conv1.weights'), w.transpose(0, 3, 1, 2).reshape(-1))
     assert np.array_equal(ints('syntxt.conv1.biases'), layers['conv1']['bias'])
     assert d['malformed.threw'] == ['1']
+    # sub-4-bit storage of the QAT export (src/Export/CPP/CPP_ConvCellExport.cpp:419-607)
+    assert d['w2.weights'] == ['1', '-1', '0', '-2', '1'] and d['w1.weights'] == ['1', '-1', '-1', '1', '1', '-1', '1', '1', '1']
 
 
 @pytest.mark.gpu

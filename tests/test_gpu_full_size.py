@@ -39,6 +39,9 @@ def test_full_size_network_cell_by_cell_and_shipped(name):
     assert n == len(net['layers'])
     compare_net(net, 2, flags=0, x=x[:2], ref=ref64)
     compare_net(net, 3, flags=0, x=x)     # an odd batch in the shipped configuration
+    if 'resnet' in name:
+        n, eng = compare_net(net, 2, flags=runtime.FUSE_FIRST_POOL, x=x[:2], ref=ref64)   # first layer + pooling as one kernel
+        assert 'stem-pool-tcgen05' in eng
 
 
 def _slice_bounds(batch, nslices):

@@ -397,7 +397,7 @@ def test_input_edge_quantizes_float_stimuli_like_the_range_transform():
 
 
 # (C, H, O, k, stride, pad, input unsigned): 4-bit weights, packed two per byte in HBM and expanded in the kernel
-W4_CASES = [(64, 8, 64, 1, 1, 0, True), (128, 8, 256, 1, 1, 0, True), (48, 9, 32, 3, 1, 1, True), (256, 14, 512, 1, 2, 0, False),
+W4_CASES = [(64, 8, 64, 1, 1, 0, True), (128, 8, 256, 1, 1, 0, True), (32, 9, 32, 3, 1, 1, True), (256, 14, 512, 1, 2, 0, False),
             (64, 30, 64, 3, 1, 1, True), (512, 7, 1024, 1, 1, 0, True), (128, 15, 128, 3, 2, 1, True), (256, 9, 256, 3, 1, 1, True)]
 
 
@@ -409,6 +409,13 @@ def test_packed_int4_weights_on_the_tensor_cores(case, mode):
         net = single_conv_net(C, H, H, O, k, s, p, in_unsigned=uns, mode=mode, weight_bits=4, clipped=clipped)
         compare_net(net, 3, want_engine='tcgen05-w4')
         compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='tcgen05-w4')
+
+
+def test_packed_int4_rows_that_tma_cannot_address_are_widened():
+    # a packed row of kH * kW * Cin / 2 bytes must be a multiple of 16 bytes for the tensor map; other cells hold int8
+    net = single_conv_net(48, 9, 9, 32, 3, 1, 1, mode='double', weight_bits=4)
+    n, eng = compare_net(net, 3)
+    assert eng == ['tcgen05']
 
 
 def test_packed_int4_weights_stay_packed_in_hbm_and_fuse_residuals():
@@ -450,12 +457,31 @@ STEM_POOL_CASES = [(3, 64, 64, 64, 7, 3, 'relu', 3, 2, True), (3, 224, 224, 64, 
 @pytest.mark.parametrize('case', STEM_POOL_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d_p%d_%s_pool%d_s%d' % c[:9])
 @pytest.mark.parametrize('mode', ['double', 'single'])
 def test_first_layer_with_the_max_pooling_folded_in(case, mode):
-    # stride-2 first layer + max pooling as one kernel: the pooled tensor is all that reaches HBM
+    # stride-2 first layer + max pooling as one kernel (opt-in): the pooled tensor is all that reaches HBM
     C, H, W, O, k, p, act, pk, ps, uns = case
     b = netdesc.NetBuilder('stempool', C, H, W, 13, mode, input_unsigned=uns, weight_dist=('normal', 30))
     c = b.conv(-1, O, k, stride=2, pad=p, act=act, name='conv1')
     b.pool(c, 'max', pk, ps, name='pool1')
     for batch in (1, 5):
-        n, eng = compare_net(b.net, batch, flags=0)
+        n, eng = compare_net(b.net, batch, flags=R.FUSE_FIRST_POOL)
         assert eng == ['stem-pool-tcgen05', 'fused']
     compare_net(b.net, 3)     # and as two cells, every output kept
+
+
+@pytest.mark.parametrize('bits,unsigned', [(4, True), (4, False), (2, True), (5, False), (1, True)])
+def test_activations_below_eight_bits(bits, unsigned):
+    # mixed-precision networks of the QAT fusion carry their own activation bit width (the saturation range of the
+    # Scaling, include/Activation/RectifierActivation_Frame.hpp:65-66): values stay one per byte on the device
+    b = netdesc.NetBuilder('lowbits', 32, 10, 10, 17, 'fixed', weight_dist=('uniform', 7), weight_bits=4)
+    c1 = b.conv(-1, 64, 3, pad=1, act='relu' if unsigned else 'linear', name='c1')
+    c2 = b.conv(c1, 64, 1, act='relu' if unsigned else 'linear', name='c2')
+    b.pool(c2, 'max', 2, 2, name='p')
+    for l in b.net['layers'][:2]:
+        l['quant']['out_bits'] = bits
+        l['quant']['out_unsigned'] = unsigned
+    x = netdesc.make_input(b.net, 3)
+    ref = oracle.run_net(b.net, x, 'i64')
+    lo, hi = (0, 2 ** bits - 1) if unsigned else (-2 ** (bits - 1), 2 ** (bits - 1) - 1)
+    assert ref[1].min() >= lo and ref[1].max() <= hi and (ref[1].max() == hi or bits > 4)
+    compare_net(b.net, 3, x=x, ref=ref)
+    compare_net(b.net, 3, flags=0, x=x, ref=ref)
