@@ -48,6 +48,8 @@ cudaError_t launch_pool_i32(const void* in, const PoolGeom& g, void* out, cudaSt
 cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, const QuantDev& q,
                                 void* out, int out_dtype, cudaStream_t s);
 // Top-1 class per pixel (first maximum wins) of [pixels][C] scores; values may be nullptr.
+// [rows][ld] bytes -> [rows][C] bytes (C <= ld): drops the zero columns a padded cell computed
+cudaError_t launch_drop_padded_columns(const uint8_t* src, int ld, uint8_t* dst, int C, size_t rows, cudaStream_t s);
 cudaError_t launch_argmax(const void* scores, int dtype, int is_unsigned, size_t pixels, int C, int32_t* labels, int32_t* values,
                           cudaStream_t s);
 // Float stimuli NCHW -> trunc(x * factor) clamped to [lo, hi], 8-bit NHWC.
@@ -116,6 +118,7 @@ struct PatchPlan {
     size_t smem_bytes;
 };
 bool patch_eligible(const ConvGeom& g);
+void patch_permute_weights(const int8_t* w, int8_t* dst, int O, size_t row_bytes);
 int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
                     const char** why);
 // n_base: first image of this call within the tensors the plan was encoded for (`out` = the tensor's base)

@@ -93,6 +93,11 @@ struct CellRec {
     StemPlan stem{};
     StemS2dPlan stem2{};
     void* d_pad4 = nullptr;   // input re-laid with 4 bytes per pixel and its zero padding written out
+    // A cell whose output channels are not a multiple of 32 (a 1000-class classifier) cannot leave through the TMA
+    // store of the 32-bit epilogue (rows of its output are not 16-byte multiples).  It runs with zero weight rows
+    // appended up to pad_O channels into d_colpad ([pixels][pad_O]); a copy kernel then drops the padding.
+    int pad_O = 0;
+    void* d_colpad = nullptr;
     // stride-1 convolution from a shared-memory patch
     PatchPlan patch{};
     // tensor-core plan
@@ -559,6 +564,7 @@ void n2d2b_net_destroy(n2d2b_net* net)
         cudaFree(c.q2.d_blob);
         cudaFree(c.d_fast);
         cudaFree(c.d_pad4);
+        cudaFree(c.d_colpad);
     }
     cudaFree(net->d_status);
     cudaFree(net->d_stage_in);
@@ -987,12 +993,25 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             for (size_t i = 0; i < p.size(); ++i) p[i] = (int8_t)(((w[2 * i] & 0xF) << 4) | (w[2 * i + 1] & 0xF));
             return p;
         };
+        // Output channels that are not a multiple of 32: take the 32-bit epilogue on a padded copy (see pad_O)
+        ConvGeom gplan = g;
+        if (igemm_shape && !w4 && g.O % 32 != 0 && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
+            && !(flags & N2D2B_EXACT64_EPILOGUE)) {
+            if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+            if (c.fast.enabled) {
+                c.pad_O = (g.O + 63) & ~63;
+                gplan.O = c.pad_O;
+                laid.resize((size_t)c.pad_O * g.kH * g.kW * g.Cg, 0);
+                CUDA_TRY(cudaMalloc(&c.d_colpad, (size_t)max_batch * g.oH * g.oW * c.pad_O + 256));
+                net->launches++;
+            }
+        }
         c.d_weight_bytes = w4 ? laid.size() / 2 : laid.size();
         CUDA_TRY(cudaMalloc((void**)&c.d_weights, c.d_weight_bytes + 256));
         CUDA_TRY(cudaMemset(c.d_weights, 0, c.d_weight_bytes + 256));
         if (!w4) CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
         if (igemm_shape) {
-            ConvGeom gb = g;
+            ConvGeom gb = gplan;
             gb.B = max_batch;
             const char* why = "";
             const void* in_ptr = tensor_ptr(net, c.inputs[0], nullptr);
@@ -1000,7 +1019,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             // that is re-encoded on first use
             static char placeholder[16] __attribute__((aligned(16)));
             const void* enc_ptr = in_ptr ? in_ptr : (const void*)placeholder;
-            const void* out_ptr = net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
+            const void* out_ptr = c.pad_O ? c.d_colpad
+                                : net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
             const void* res_ptr = c.residual >= 0 ? tensor_ptr(net, c.residual, nullptr) : nullptr;
             int planned = igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
                                           (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
@@ -1022,14 +1042,14 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 c.engine = ENG_TCGEN05;
                 c.has_plan = true;
                 c.plan_input = in_ptr;  // nullptr = must be re-encoded with the real input
-                if (!(flags & N2D2B_EXACT64_EPILOGUE)) {
+                if (!(flags & N2D2B_EXACT64_EPILOGUE) && !c.pad_O) {
                     const bool res_i8 = c.residual >= 0 && net->tensors[c.residual].dtype == DT_I8;
                     if (int rc = upload_fast(c, net->tensors[c.output], res_i8,
                                              c.residual >= 0 ? net->tensors[c.residual].is_unsigned : 0, w4))
                         return rc;
                 }
                 // small-channel stride-1 layers read their input once, from a shared-memory patch
-                if (!w4 && c.fast.enabled && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
+                if (!w4 && !c.pad_O && c.fast.enabled && c.residual < 0 && net->tensors[c.output].dtype == DT_I8
                     && !(flags & (N2D2B_FORCE_IM2COL | N2D2B_EXACT64_EPILOGUE)) && patch_eligible(gb)
                     && patch_make_plan(&c.patch, enc_ptr, c.d_weights, gb, net->tensors[c.inputs[0]].is_unsigned,
                                        net->num_sms, &why) == 0)
@@ -1038,18 +1058,22 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 // the permuted order that epilogue reads (see perm_block)
                 const bool permute = c.engine == ENG_TCGEN05
                                      && igemm_uses_fast_epilogue(c.plan, c.fast, c.residual >= 0, net->tensors[c.output].dtype);
-                if (permute || w4) {
+                if (c.engine == ENG_PATCH) {
+                    std::vector<int8_t> rows(laid.size());
+                    patch_permute_weights(laid.data(), rows.data(), g.O, (size_t)g.kH * g.kW * g.Cg);
+                    CUDA_TRY(cudaMemcpy(c.d_weights, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+                } else if (permute || w4) {
                     std::vector<int8_t> rows = laid;
                     if (permute) {
                         const int pb = igemm_perm_block(c.plan);
-                        igemm_permute_weights(laid.data(), rows.data(), g.O, (size_t)g.kH * g.kW * g.Cg, pb);
+                        igemm_permute_weights(laid.data(), rows.data(), gplan.O, (size_t)g.kH * g.kW * g.Cg, pb);
                         c.plan.perm = pb;
                     }
                     if (w4) rows = pack4(rows);
                     CUDA_TRY(cudaMemcpy(c.d_weights, rows.data(), rows.size(), cudaMemcpyHostToDevice));
                 }
-            } else if (w4) {
-                return fail(N2D2B_ERR_STATE, "internal: a packed cell without a plan");
+            } else if (w4 || c.pad_O) {
+                return fail(N2D2B_ERR_STATE, "internal: a packed or padded cell without a plan (%s)", why);
             }
         }
     }
@@ -1149,12 +1173,14 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
     }
     switch (c.engine) {
     case ENG_TCGEN05: {
+        void* const gemm_out = c.pad_O ? c.d_colpad : out;
         if (c.plan_input != in0) {
             ConvGeom gb = c.geom;
             gb.B = net->max_batch;
+            if (c.pad_O) gb.O = c.pad_O;
             const char* why = "";
             const int perm = c.plan.perm, w4 = c.plan.w4;   // properties of the stored weights, not of the tensor maps
-            if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? out : nullptr, r.ptr, gb, tin.is_unsigned,
+            if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? gemm_out : nullptr, r.ptr, gb, tin.is_unsigned,
                                 (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
                                 (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0, w4))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
@@ -1163,7 +1189,12 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
         }
         IgemmPlan p = c.plan;
         p.M = batch * c.geom.oH * c.geom.oW;
-        CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, out, tout.dtype, img0 * c.geom.oH * c.geom.oW, net->d_status, s));
+        CUDA_TRY(launch_igemm(p, c.q.dev, r, c.fast, gemm_out, tout.dtype, img0 * c.geom.oH * c.geom.oW, net->d_status, s));
+        if (c.pad_O) {
+            const size_t row0 = (size_t)img0 * c.geom.oH * c.geom.oW;
+            CUDA_TRY(launch_drop_padded_columns((const uint8_t*)c.d_colpad + row0 * c.pad_O, c.pad_O,
+                                                (uint8_t*)out + row0 * c.geom.O, c.geom.O, (size_t)p.M, s));
+        }
         break;
     }
     case ENG_PATCH: {

@@ -56,13 +56,15 @@ struct PatchArgs {
 template <bool CLAMP, int EF>
 __device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int c0, int ncols, int lane)
 {
+    // the caller stores the weight rows permuted inside blocks of 32 output channels (patch_permute_weights): a
+    // thread's columns of the fragment are eight consecutive channels (see perm_block)
     unsigned rb[4];
-    frag_rowbase(rb, ncols, lane);
+    perm_rowbase(rb, ncols, lane, 4);
 #pragma unroll 1
     for (int cb = 0; cb < ncols; cb += 32) {
         unsigned va[16], vb[16];
         tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(c0 + cb), va, vb);
-        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, c0 + cb, region_off, rb, cb, lane, 0, 0, 0u);
+        perm_block<4, false, CLAMP, false, EF | EF_PERM>(va, vb, par_off, c0 + cb, region_off, rb, cb, lane, 0, 0, 0u);
     }
 }
 
@@ -424,6 +426,12 @@ bool patch_eligible(const ConvGeom& g)
     if ((g.kH - 1) * g.dY + 1 > 256) return false;
     // at least one output row per band must fit
     return patch_smem_bytes(g.kH * g.kW, g.C, BN, patch_alloc_bytes(g, Wp, 1)) <= 226 * 1024;
+}
+
+// Weight rows ([O][taps * C] bytes) in the order the kernel's epilogue expects
+void patch_permute_weights(const int8_t* w, int8_t* dst, int O, size_t row_bytes)
+{
+    for (int n = 0; n < O; ++n) memcpy(dst + (size_t)n * row_bytes, w + (size_t)perm_real_channel(n, 4) * row_bytes, row_bytes);
 }
 
 int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,

@@ -3,6 +3,7 @@
 // and a direct fully-connected kernel that accept any geometry.  Every kernel ends in the same
 // requantisation epilogue (common.cuh), so no float tensor or separate Scaling pass exists between
 // layers.  Activations are NHWC int8 (signed or unsigned per tensor) or int32.
+#include <algorithm>
 #include "kernels.h"
 
 namespace n2d2b {
@@ -664,6 +665,31 @@ cudaError_t launch_fc_direct(const void* in, int in_unsigned, const int8_t* w, i
 // (Target top-1, src/Target/Target_CUDA_kernels.cu:88-104 of the reference: `if (tmp > maxVal)`).
 // One warp per (image, pixel); scores are [pixels][C] int8 or int32.
 // ---------------------------------------------------------------------------------------------
+// 8 bytes per thread when both row lengths allow it, bytes otherwise
+template <typename V>
+__global__ void drop_padded_columns_kernel(const V* __restrict__ src, int ld, V* __restrict__ dst, int C, size_t rows)
+{
+    const size_t total = rows * (size_t)C;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (size_t)C;
+        dst[i] = src[r * (size_t)ld + (i - r * (size_t)C)];
+    }
+}
+
+cudaError_t launch_drop_padded_columns(const uint8_t* src, int ld, uint8_t* dst, int C, size_t rows, cudaStream_t s)
+{
+    if (rows == 0) return cudaSuccess;
+    const bool vec = (C % 8 == 0) && (ld % 8 == 0) && !((uintptr_t)src & 7) && !((uintptr_t)dst & 7);
+    const size_t total = vec ? rows * (size_t)(C / 8) : rows * (size_t)C;
+    const int threads = 256;
+    const int blocks = (int)std::min<size_t>((total + threads - 1) / threads, 148 * 8);
+    if (vec)
+        drop_padded_columns_kernel<uint2><<<blocks, threads, 0, s>>>((const uint2*)src, ld / 8, (uint2*)dst, C / 8, rows);
+    else
+        drop_padded_columns_kernel<uint8_t><<<blocks, threads, 0, s>>>(src, ld, dst, C, rows);
+    return cudaGetLastError();
+}
+
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ scores, size_t pixels, int C, int32_t* __restrict__ labels,
                               int32_t* __restrict__ values)

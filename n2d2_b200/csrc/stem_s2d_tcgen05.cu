@@ -134,13 +134,15 @@ __device__ __forceinline__ void s2d_issue_tile(unsigned d_tmem, unsigned a_lo, u
 template <bool CLAMP, int EF>
 __device__ __forceinline__ void s2d_drain(unsigned tbase, unsigned par_off, unsigned region_off, int BN, int lane)
 {
+    // the weight rows are stored permuted inside blocks of 32 channels (stem_s2d_arrange_weights): a thread's
+    // columns of the fragment are eight consecutive channels
     unsigned rb[4];
-    frag_rowbase(rb, BN, lane);
+    perm_rowbase(rb, BN, lane, 4);
 #pragma unroll 1
     for (int cb = 0; cb < BN; cb += 32) {
         unsigned va[16], vb[16];
         tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
-        frag_block<4, false, CLAMP, false, EF>(va, vb, par_off, cb, region_off, rb, cb, lane, 0, 0, 0u);
+        perm_block<4, false, CLAMP, false, EF | EF_PERM>(va, vb, par_off, cb, region_off, rb, cb, lane, 0, 0, 0u);
     }
 }
 
@@ -365,18 +367,30 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
                 const int nch = a.N >> 4;                       // 16-byte units per pixel
                 const unsigned pix0 = (unsigned)(t * ZBM + quad * 32);
                 if ((nch & (nch - 1)) == 0) {
+                    // four units per lane at a time: the shared-memory loads first, then the stores, so that neither
+                    // waits for the other
                     const int lg = 31 - __clz(nch);
-                    for (int u = lane; u < 32 * nch; u += 32) {
-                        const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
-                        const unsigned p = pix0 + r;            // position within the band
-                        const unsigned yy = __umulhi(p, a.rcp_Wp);
-                        const unsigned x = p - yy * (unsigned)a.Wp;
-                        if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)n * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
+                    uint8_t* const img_out = (uint8_t*)a.out + ((size_t)n * a.oH + (size_t)(band * a.R)) * a.oW * a.N;
+                    for (int u0 = lane; u0 < 32 * nch; u0 += 128) {
+                        uint4 v[4];
+                        unsigned off[4];
+                        bool live[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int u = u0 + 32 * j;
+                            const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
+                            const unsigned p = pix0 + r;            // position within the band
+                            const unsigned yy = __umulhi(p, a.rcp_Wp);
+                            const unsigned x = p - yy * (unsigned)a.Wp;
+                            live[j] = u < 32 * nch && x < (unsigned)a.oW && yy < (unsigned)rows;
+                            off[j] = (yy * (unsigned)a.oW + x) * (unsigned)a.N + c * 16u;   // within the band: below 2^32
                             const unsigned ro = r * (unsigned)a.BN;
                             const unsigned xm = (ro >> 7) & swz_mask;
-                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
+                            if (live[j]) v[j] = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
                         }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (live[j]) *(uint4*)(img_out + off[j]) = v[j];
                     }
                 } else {
                     const unsigned p = pix0 + (unsigned)lane;
@@ -473,7 +487,8 @@ size_t stem_s2d_weight_bytes(const ConvGeom& g)
 }
 
 // OHWI int8 weights -> per filter row of the re-laid problem a BN x (KWp*16) block in the canonical
-// unswizzled K-major order [n / 8][k / 16][n % 8][k % 16], k = X * 16 + (dy * 2 + dx) * 4 + c
+// unswizzled K-major order [n / 8][k / 16][n % 8][k % 16], k = X * 16 + (dy * 2 + dx) * 4 + c.  Row n of a block holds
+// output channel perm_real_channel(n, 4): the order the epilogue's fragment layout wants (see perm_block).
 void stem_s2d_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* dst)
 {
     int P, KH, KWp;
@@ -482,17 +497,20 @@ void stem_s2d_arrange_weights(const ConvGeom& g, const int8_t* w_ohwi, int8_t* d
     const int offy = P - g.pT, offx = P - g.pL;
     const size_t row_block = (size_t)BN * KWp * 16;
     memset(dst, 0, (size_t)KH * row_block);
-    for (int o = 0; o < g.O; ++o)
+    for (int n = 0; n < BN; ++n) {
+        const int o = perm_real_channel(n, 4);
+        if (o >= g.O) continue;
         for (int ky = 0; ky < g.kH; ++ky)
             for (int kx = 0; kx < g.kW; ++kx)
                 for (int c = 0; c < g.C; ++c) {
                     const int yy = ky + offy, xx = kx + offx;       // tap position in the shifted image
                     const int Y = yy >> 1, dy = yy & 1, X = xx >> 1, dx = xx & 1;
                     const int k = X * 16 + (dy * 2 + dx) * 4 + c;
-                    const size_t off = (size_t)Y * row_block + (size_t)(o / 8) * (KWp * 128) + (size_t)(k / 16) * 128
-                                     + (size_t)(o % 8) * 16 + (size_t)(k % 16);
+                    const size_t off = (size_t)Y * row_block + (size_t)(n / 8) * (KWp * 128) + (size_t)(k / 16) * 128
+                                     + (size_t)(n % 8) * 16 + (size_t)(k % 16);
                     dst[off] = w_ohwi[(((size_t)o * g.kH + ky) * g.kW + kx) * g.C + c];
                 }
+    }
 }
 
 cudaError_t launch_s2d_image(const void* in, const ConvGeom& g, int batch, void* out, cudaStream_t s)

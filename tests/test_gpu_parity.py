@@ -485,3 +485,31 @@ def test_activations_below_eight_bits(bits, unsigned):
     assert ref[1].min() >= lo and ref[1].max() <= hi and (ref[1].max() == hi or bits > 4)
     compare_net(b.net, 3, x=x, ref=ref)
     compare_net(b.net, 3, flags=0, x=x, ref=ref)
+
+
+# (C, H, W, O, k, pad): output channels that are not a multiple of 32 (and of 16, and of 8)
+ODD_O_CASES = [(64, 20, 20, 40, 1, 0), (64, 9, 9, 36, 1, 0), (32, 12, 12, 100, 3, 1), (128, 7, 7, 1000, 1, 0),
+               (16, 10, 10, 7, 3, 1)]
+
+
+@pytest.mark.parametrize('case', ODD_O_CASES, ids=lambda c: 'C%d_%dx%d_O%d_k%d' % c[:5])
+@pytest.mark.parametrize('mode', ['double', 'fixed'])
+def test_output_channels_that_tma_stores_cannot_address_run_padded(case, mode):
+    # such a cell takes the 32-bit epilogue on zero-padded weight rows and a copy kernel drops the padding
+    C, H, W, O, k, pad = case
+    net = single_conv_net(C, H, W, O, k, 1, pad, mode=mode)
+    n, eng = compare_net(net, 5)
+    assert eng == ['tcgen05']
+    qn = runtime.QuantizedNet(net, 5)
+    try:
+        assert qn.launches_per_forward() == 2
+    finally:
+        qn.close()
+    # the exact 64-bit epilogue needs no padding
+    n, eng = compare_net(net, 5, flags=KEEP | R.EXACT64_EPILOGUE)
+    assert eng == ['tcgen05']
+
+
+def test_padded_output_channels_in_upload_slices():
+    net = single_conv_net(16, 48, 48, 24, 3, 1, 1, mode='double')
+    compare_net(net, 7, slices=3)
