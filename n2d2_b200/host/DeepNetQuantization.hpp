@@ -14,17 +14,24 @@
 //                                                    re-scale the cell's parameters to absorb their error)
 //   rounding of the parameters, setQuantized :347-349
 //
-// What the reference takes from its calibration run (Histogram / RangeStats: the activation threshold of every
-// cell, DeepNetQuantization::getCellThreshold :1179-1198) is an input here: a map from cell name to threshold,
-// however it was obtained (value range, MSE, KL divergence, quantile).  Arithmetic on the scalings is done in
-// long double / double / float exactly where the reference does.
+//   clipWeights                           :63-107    weights clamped to the MSE / KL threshold of their histogram
+//   reportOutputsRange / reportOutputsHistogram :150-281 calibration statistics of every cell's float outputs
+//   getCellThreshold                      :1181-1198 threshold of a cell from those statistics
+//
+// The float network itself runs in the caller's framework: its outputs are fed, cell by cell and batch by batch,
+// to reportOutputsRange / reportOutputsHistogram (Calibration.hpp holds RangeStats and Histogram), and
+// quantizeNetwork takes the statistics like the reference's.  A second form takes a map from cell name to threshold,
+// however it was obtained.  Arithmetic on the scalings is done in long double / double / float exactly where the
+// reference does.
 #pragma once
 
 #include <cassert>
 #include <cmath>
+#include <functional>
 #include <limits>
 #include <unordered_map>
 
+#include "Calibration.hpp"
 #include "N2D2.hpp"
 
 namespace N2D2 {
@@ -33,14 +40,41 @@ class DeepNetQuantization {
 public:
     explicit DeepNetQuantization(DeepNet& deepNet) : mDeepNet(deepNet) {}
 
+    // The statistics name of a cell and whether its clipping mode applies -> its activation threshold
+    typedef std::function<double(const Cell& cell, const std::string& cellStatsName, bool clip)> ThresholdFn;
+
+    // src/DeepNetQuantization.cpp:285-388, with the reference's arguments
+    void quantizeNetwork(const std::unordered_map<std::string, Histogram>& outputsHistogram,
+                         const std::unordered_map<std::string, RangeStats>& outputsRange, std::size_t nbBits,
+                         ClippingMode actClippingMode, ScalingMode actScalingMode, bool rescalePerOutputChannel,
+                         double quantileValue = 0.9999)
+    {
+        quantizeNetwork([&](const Cell&, const std::string& cellStatsName, bool clip) {
+            return getCellThreshold(cellStatsName, outputsHistogram, outputsRange, nbBits,
+                                    clip ? actClippingMode : ClippingMode::NONE, quantileValue);
+        }, nbBits, actScalingMode, rescalePerOutputChannel);
+    }
+
     // outputsThreshold: for every cell with an activation (and every element-wise cell) the value
     // getCellThreshold would return: max |output| for ClippingMode::NONE, or the calibrated clipping threshold.
+    // (With a clipping mode and a max pooling as the only child the reference takes the pooling cell's statistics,
+    // :724-737; a map expresses that by the value it holds for the cell.)
     void quantizeNetwork(const std::unordered_map<std::string, double>& outputsThreshold, std::size_t nbBits,
                          ScalingMode actScalingMode, bool rescalePerOutputChannel)
     {
+        quantizeNetwork([&](const Cell& cell, const std::string&, bool) {
+            auto it = outputsThreshold.find(cell.getName());
+            if (it == outputsThreshold.end())
+                throw std::runtime_error("quantizeActivations(): no calibration threshold for cell '" + cell.getName() + "'");
+            return it->second;
+        }, nbBits, actScalingMode, rescalePerOutputChannel);
+    }
+
+    void quantizeNetwork(const ThresholdFn& threshold, std::size_t nbBits, ScalingMode actScalingMode, bool rescalePerOutputChannel)
+    {
         std::unordered_map<std::string, long double> biasScalings
             = rescalePerOutputChannel ? quantizeFreeParemetersPerOutputCh(nbBits) : quantizeFreeParemeters(nbBits);
-        quantizeActivations(outputsThreshold, biasScalings, nbBits);
+        quantizeActivations(threshold, biasScalings, nbBits);
 
         const std::vector<std::vector<std::string> > layers = mDeepNet.getLayers();
         for (std::size_t l = 1; l < layers.size(); ++l)
@@ -176,8 +210,91 @@ public:
         return biasScalings;
     }
 
-    void quantizeActivations(const std::unordered_map<std::string, double>& outputsThreshold,
-                             std::unordered_map<std::string, long double>& biasScalings, std::size_t nbBits)
+    // ---- calibration (src/DeepNetQuantization.cpp:63-107,150-281,1181-1198) -----------------------------------------
+    // Weights beyond the MSE / KL threshold of their own histogram are clamped to it, cell by cell.
+    void clipWeights(std::size_t nbBits, ClippingMode wtClippingMode)
+    {
+        if (wtClippingMode == ClippingMode::NONE) return;
+        const std::size_t nbBins = getNbBinsForClippingMode(nbBits, wtClippingMode);
+        const std::vector<std::vector<std::string> > layers = mDeepNet.getLayers();
+        for (std::size_t l = 1; l < layers.size(); ++l)
+            for (const std::string& name : layers[l]) {
+                std::shared_ptr<Cell> cell = mDeepNet.getCell<Cell>(name);
+                const std::pair<Float_T, Float_T> range = cell->getFreeParametersRange(Cell::Multiplicative);
+                const Float_T maxWeight = std::max(std::abs(range.first), std::abs(range.second));
+                if (maxWeight == 0) continue;
+                Histogram hist(-maxWeight, maxWeight, nbBins);
+                cell->processFreeParameters([&](Float_T wt) { hist(wt); return wt; }, Cell::Multiplicative);
+                Float_T threshold;
+                switch (wtClippingMode) {
+                case ClippingMode::KL_DIVERGENCE: threshold = (Float_T)hist.calibrateKLDivergence(nbBits); break;
+                case ClippingMode::MSE: threshold = (Float_T)hist.calibrateMSE(nbBits); break;
+                default: throw std::runtime_error("Unsupported clipping mode.");
+                }
+                cell->processFreeParameters([&](Float_T wt) { return std::min(std::max(wt, -threshold), threshold); },
+                                            Cell::Multiplicative);
+            }
+    }
+
+    // One batch of float outputs of a cell (or of the stimuli, cellName "env") into its range statistics
+    void reportOutputsRange(std::unordered_map<std::string, RangeStats>& outputsRange, const std::string& cellName,
+                            const Float_T* outputs, std::size_t count) const
+    {
+        if (outputsRange.empty()) {
+            const std::vector<std::vector<std::string> > layers = mDeepNet.getLayers();
+            for (const std::vector<std::string>& layer : layers)
+                for (const std::string& name : layer) outputsRange.insert(std::make_pair(name, RangeStats()));
+        }
+        RangeStats& rangeStats = outputsRange.at(cellName);
+        for (std::size_t i = 0; i < count; ++i) rangeStats(outputs[i]);
+    }
+
+    // The same batch into the cell's histogram (second calibration pass: the ranges are complete).  On first use every
+    // histogram is created over [-max|range|, max|range|], or [0, max|range|] for a cell with unsigned outputs, at
+    // least 0.1 wide; later batches enlarge it by whole bins if the range has grown.
+    void reportOutputsHistogram(std::unordered_map<std::string, Histogram>& outputsHistogram,
+                                const std::unordered_map<std::string, RangeStats>& outputsRange, const std::string& cellName,
+                                const Float_T* outputs, std::size_t count, std::size_t nbBits, ClippingMode actClippingMode,
+                                bool envDataUnsigned = true) const
+    {
+        if (actClippingMode == ClippingMode::NONE) return;
+        if (outputsHistogram.empty()) {
+            const std::size_t nbBins = getNbBinsForClippingMode(nbBits, actClippingMode);
+            const std::vector<std::vector<std::string> > layers = mDeepNet.getLayers();
+            for (std::size_t l = 0; l < layers.size(); ++l)
+                for (const std::string& name : layers[l]) {
+                    const RangeStats& range = outputsRange.at(name);
+                    const bool isCellOutputUnsigned
+                        = (l == 0) ? envDataUnsigned : mDeepNet.isCellOutputUnsigned(*mDeepNet.getCell<Cell>(name));
+                    double val = std::max(std::fabs(range.minVal()), std::fabs(range.maxVal()));
+                    val = std::max(val, 0.1);
+                    outputsHistogram.insert(std::make_pair(name, Histogram(isCellOutputUnsigned ? 0 : -val, val, nbBins)));
+                }
+        }
+        Histogram& hist = outputsHistogram.at(cellName);
+        const RangeStats& range = outputsRange.at(cellName);
+        const bool enlargeSymetric = hist.getMinVal() < 0.0;
+        hist.enlarge(std::max(std::fabs(range.minVal()), std::fabs(range.maxVal())), enlargeSymetric);
+        for (std::size_t i = 0; i < count; ++i) hist(outputs[i]);
+    }
+
+    static double getCellThreshold(const std::string& cellName, const std::unordered_map<std::string, Histogram>& outputsHistogram,
+                                   const std::unordered_map<std::string, RangeStats>& outputsRange, std::size_t nbBits,
+                                   ClippingMode actClippingMode, double quantileValue = 0.9999)
+    {
+        switch (actClippingMode) {
+        case ClippingMode::KL_DIVERGENCE: return outputsHistogram.at(cellName).calibrateKLDivergence(nbBits);
+        case ClippingMode::MSE: return outputsHistogram.at(cellName).calibrateMSE(nbBits);
+        case ClippingMode::QUANTILE: return outputsHistogram.at(cellName).getQuantileValue(quantileValue);
+        default: {
+            const RangeStats& range = outputsRange.at(cellName);
+            return std::max(std::fabs(range.minVal()), std::fabs(range.maxVal()));
+        }
+        }
+    }
+
+    void quantizeActivations(const ThresholdFn& threshold, std::unordered_map<std::string, long double>& biasScalings,
+                             std::size_t nbBits)
     {
         std::unordered_map<std::string, long double> activationScalings;
         const std::vector<std::vector<std::string> > layers = mDeepNet.getLayers();
@@ -191,13 +308,16 @@ public:
                 if (dynamic_cast<PoolCell*>(cell.get()) || dynamic_cast<ScalingCell*>(cell.get())) {
                     activationScalings[cell->getName()] = prevActivationScaling;
                     continue;
-                } else if (isElemWise || cell->getActivation()) {
-                    // with a clipping mode and a max pooling as the only child, the reference takes the pooling cell's
-                    // statistics (:724-732); the caller's threshold map expresses that by the value it holds for the cell
-                    auto it = outputsThreshold.find(cell->getName());
-                    if (it == outputsThreshold.end())
-                        throw std::runtime_error("quantizeActivations(): no calibration threshold for cell '" + cell->getName() + "'");
-                    activationScaling = it->second;
+                } else if (isElemWise) {
+                    activationScaling = threshold(*cell, cell->getName(), false);
+                } else if (cell->getActivation()) {
+                    // clipping modes apply to cells with more than two outputs; when the only child is a max pooling,
+                    // its statistics stand for the cell's (:716-737)
+                    const bool clip = cell->getNbOutputs() > 2;
+                    const std::vector<std::shared_ptr<Cell> > childrenCells = mDeepNet.getChildCells(cell->getName());
+                    const PoolCell* childPool = childrenCells.size() == 1 ? dynamic_cast<const PoolCell*>(childrenCells[0].get()) : nullptr;
+                    const bool isNextCellMaxPool = childPool && childPool->getPooling() == PoolCell::Max;
+                    activationScaling = threshold(*cell, clip && isNextCellMaxPool ? childrenCells[0]->getName() : cell->getName(), clip);
                 } else {
                     throw std::runtime_error("Quantization of cell '" + cell->getName() + "' of type '" + cell->getType() + "' is not supported yet.");
                 }

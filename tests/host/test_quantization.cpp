@@ -6,6 +6,7 @@
 //                                          from value-range calibration, runs the integer networks on cuda:0 and compares
 //                                          them with the float networks computed by the CPU oracle, the way the reference
 //                                          tests its quantization: by how well the quantized network tracks the float one
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <random>
@@ -192,7 +193,103 @@ static int graph_rewrite()
     return 0;
 }
 
-static int run(const char* mode_name, bool per_channel)
+// Calibration statistics of one float run, fed the way a caller's float framework would (two passes: ranges, then
+// histograms over those ranges)
+struct Stats {
+    std::unordered_map<std::string, RangeStats> range;
+    std::unordered_map<std::string, Histogram> hist;
+};
+static Stats collect_stats(DeepNet& dn, const FloatNet& n, const std::vector<float>& x, const FloatOutputs& o, ClippingMode mode,
+                           bool envUnsigned)
+{
+    Stats st;
+    DeepNetQuantization q(dn);
+    std::vector<std::pair<std::string, const std::vector<float>*> > outs
+        = {{"env", &x}, {"conv1", &o.c1}, {"conv2", &o.c2}, {"pool", &o.pool}, {"fc", &o.fc}};
+    if (n.residual) outs.push_back({"sum", &o.sum});
+    // two halves, as two calibration batches (the second one may enlarge the histograms)
+    for (int half = 0; half < 2; ++half)
+        for (auto& kv : outs) {
+            const size_t h = kv.second->size() / 2;
+            q.reportOutputsRange(st.range, kv.first, kv.second->data() + half * h, half ? kv.second->size() - h : h);
+        }
+    for (int half = 0; half < 2; ++half)
+        for (auto& kv : outs) {
+            const size_t h = kv.second->size() / 2;
+            q.reportOutputsHistogram(st.hist, st.range, kv.first, kv.second->data() + half * h, half ? kv.second->size() - h : h, 8,
+                                     mode, envUnsigned);
+        }
+    return st;
+}
+
+// CPU checks of the statistics-driven front-end
+static int stats_frontend()
+{
+    for (int variant = 0; variant < 2; ++variant) {
+        const bool residual = variant == 1;
+        DeepNetExport::mUnsignedData() = !residual;
+        DeepNetExport::mEnvDataUnsigned() = !residual;
+        const FloatNet n = draw_net(residual, 21 + variant);
+        const int B = 8;
+        std::mt19937 g(5);
+        std::vector<float> x((size_t)B * n.C * n.H * n.W);
+        for (auto& v : x) v = (float)(g() & 0xff) / 255.0f;
+        const FloatOutputs ref = float_forward(n, x, B);
+        DeepNet dn(n.C, n.H, n.W);
+        build_graph(dn, n);
+        Stats st = collect_stats(dn, n, x, ref, ClippingMode::MSE, !residual);
+        // ranges are the extreme values, histograms hold every value, unsigned cells start at 0
+        CHECK(near(st.range.at("conv2").maxVal(), *std::max_element(ref.c2.begin(), ref.c2.end())));
+        CHECK(near(st.range.at("conv2").minVal(), *std::min_element(ref.c2.begin(), ref.c2.end())));
+        CHECK(st.hist.at("conv1").getNbValues() == ref.c1.size());
+        CHECK(st.hist.at("conv1").getNbBins() >= 16384);   // min(2^8 * 64, 65536), possibly enlarged
+        CHECK((st.hist.at("conv1").getMinVal() == 0.0) == !residual);
+        CHECK(st.hist.at("conv2").getMinVal() < 0.0 || !residual);   // a Linear activation in a signed network
+        CHECK(near(DeepNetQuantization::getCellThreshold("fc", st.hist, st.range, 8, ClippingMode::NONE), max_abs(ref.fc)));
+        const double mse = DeepNetQuantization::getCellThreshold("conv1", st.hist, st.range, 8, ClippingMode::MSE);
+        const double kl = DeepNetQuantization::getCellThreshold("conv1", st.hist, st.range, 8, ClippingMode::KL_DIVERGENCE);
+        const double qt = DeepNetQuantization::getCellThreshold("conv1", st.hist, st.range, 8, ClippingMode::QUANTILE, 0.999);
+        CHECK(mse > 0 && mse <= st.hist.at("conv1").getMaxVal() && kl > 0 && kl <= st.hist.at("conv1").getMaxVal());
+        CHECK(qt > 0 && qt < max_abs(ref.c1));
+        // which statistics quantizeActivations asks for: the max pooling's for the cell above it, with clipping on
+        // cells of more than two outputs only
+        std::vector<std::string> asked;
+        DeepNetQuantization(dn).quantizeNetwork([&](const Cell& cell, const std::string& statsName, bool clip) {
+            asked.push_back(cell.getName() + ":" + statsName + ":" + (clip ? "1" : "0"));
+            return DeepNetQuantization::getCellThreshold(statsName, st.hist, st.range, 8, ClippingMode::NONE);
+        }, 8, ScalingMode::FIXED_MULT32, false);
+        const std::string tail = residual ? "sum:sum:0" : "conv2:pool:1";
+        CHECK(std::find(asked.begin(), asked.end(), tail) != asked.end());
+        CHECK(std::find(asked.begin(), asked.end(), "conv1:conv1:1") != asked.end());
+        CHECK(std::find(asked.begin(), asked.end(), "fc:fc:1") != asked.end());
+        // clipWeights: no weight beyond the threshold of its cell's histogram, and some weights did move
+        DeepNet dn2(n.C, n.H, n.W);
+        build_graph(dn2, n);
+        const auto before = dn2.getCell<Cell>("conv2")->getFreeParametersRange(Cell::Multiplicative);
+        DeepNetQuantization(dn2).clipWeights(8, ClippingMode::MSE);
+        const auto after = dn2.getCell<Cell>("conv2")->getFreeParametersRange(Cell::Multiplicative);
+        CHECK(after.second <= before.second && after.first >= before.first);
+        CHECK(after.second < before.second || after.first > before.first);
+        // state files round-trip
+        const std::string dir = "/tmp";
+        RangeStats::saveOutputsRange(dir + "/n2d2b_test_range.bin", st.range);
+        Histogram::saveOutputsHistogram(dir + "/n2d2b_test_hist.bin", st.hist);
+        std::unordered_map<std::string, RangeStats> r2;
+        std::unordered_map<std::string, Histogram> h2;
+        RangeStats::loadOutputsRange(dir + "/n2d2b_test_range.bin", r2);
+        Histogram::loadOutputsHistogram(dir + "/n2d2b_test_hist.bin", h2);
+        CHECK(r2.size() == st.range.size() && h2.size() == st.hist.size());
+        CHECK(r2.at("fc").maxVal() == st.range.at("fc").maxVal() && r2.at("fc").moments() == st.range.at("fc").moments());
+        CHECK(h2.at("conv2").getBins() == st.hist.at("conv2").getBins() && h2.at("conv2").getMaxVal() == st.hist.at("conv2").getMaxVal());
+        remove((dir + "/n2d2b_test_range.bin").c_str());
+        remove((dir + "/n2d2b_test_hist.bin").c_str());
+    }
+    return 0;
+}
+
+// clip: 0 = thresholds given as a map of value ranges; 1 / 2 / 3 = calibration statistics with no clipping, MSE,
+// KL divergence
+static int run(const char* mode_name, bool per_channel, int clip = 0)
 {
     const ScalingMode mode = !strcmp(mode_name, "fixed") ? ScalingMode::FIXED_MULT32
                              : (!strcmp(mode_name, "single") ? ScalingMode::SINGLE_SHIFT : ScalingMode::DOUBLE_SHIFT);
@@ -225,11 +322,19 @@ static int run(const char* mode_name, bool per_channel)
         if (residual) thr["sum"] = max_abs(ref.sum);
         DeepNet dn(n.C, n.H, n.W);
         build_graph(dn, n);
-        DeepNetQuantization(dn).quantizeNetwork(thr, 8, mode, per_channel);
+        double out_threshold = max_abs(ref.fc);
+        if (clip == 0) {
+            DeepNetQuantization(dn).quantizeNetwork(thr, 8, mode, per_channel);
+        } else {
+            const ClippingMode cm = clip == 1 ? ClippingMode::NONE : (clip == 2 ? ClippingMode::MSE : ClippingMode::KL_DIVERGENCE);
+            Stats st = collect_stats(dn, n, x, ref, cm == ClippingMode::NONE ? ClippingMode::MSE : cm, !residual);
+            out_threshold = DeepNetQuantization::getCellThreshold("fc", st.hist, st.range, 8, cm);
+            DeepNetQuantization(dn).quantizeNetwork(st.hist, st.range, 8, cm, mode, per_channel);
+        }
         dn.initialize(B);
         const std::vector<int> logits = dn.test(stimuli, B);
         // the integer logits track the float ones: y_int ~ y_float / threshold * 127 (signed 8-bit output)
-        const double scale = max_abs(ref.fc) / 127.0;
+        const double scale = out_threshold / 127.0;
         double err = 0, norm = 0;
         int agree = 0;
         for (int b = 0; b < B; ++b) {
@@ -244,11 +349,12 @@ static int run(const char* mode_name, bool per_channel)
             agree += (am_i == am_f);
         }
         const double rel = std::sqrt(err / norm);
-        printf("%s per_channel=%d %s: relative error %.4f, top-1 agreement %d / %d, %zu layers\n", mode_name, (int)per_channel,
+        printf("%s per_channel=%d clip=%d %s: relative error %.4f, top-1 agreement %d / %d, %zu layers\n", mode_name, (int)per_channel, clip,
                residual ? "residual" : "chain", rel, agree, B, dn.getLayers().size() - 1);
         // 8 bits leave a few percent of noise; shift scalings are as exact as fixed-point ones because the parameters
         // absorb the approximation
-        if (!(rel < 0.08) || agree < B * 85 / 100) ++failures;
+        // (clipped thresholds saturate the largest logits: compare top-1 only there)
+        if ((clip < 2 && !(rel < 0.08)) || agree < B * 85 / 100) ++failures;
     }
     return failures;
 }
@@ -262,7 +368,12 @@ int main(int argc, char** argv)
             printf("known answers ok\n");
             return 0;
         }
-        if (argc >= 4 && !strcmp(argv[1], "--run")) return run(argv[2], atoi(argv[3]) != 0);
+        if (argc >= 2 && !strcmp(argv[1], "--stats")) {
+            if (int rc = stats_frontend()) return rc;
+            printf("statistics front-end ok\n");
+            return 0;
+        }
+        if (argc >= 4 && !strcmp(argv[1], "--run")) return run(argv[2], atoi(argv[3]) != 0, argc >= 5 ? atoi(argv[4]) : 0);
     } catch (const std::exception& e) {
         fprintf(stderr, "error: %s\n", e.what());
         return 1;

@@ -19,7 +19,7 @@ def _build():
     oracle.build()
     src = os.path.join(ROOT, 'tests', 'host', 'test_quantization.cpp')
     deps = [src, runtime.LIB_PATH, os.path.join(ROOT, 'include', 'n2d2b.h')] + [
-        os.path.join(ROOT, 'n2d2_b200', 'host', f) for f in ('N2D2.hpp', 'DeepNetQuantization.hpp')]
+        os.path.join(ROOT, 'n2d2_b200', 'host', f) for f in ('N2D2.hpp', 'DeepNetQuantization.hpp', 'Calibration.hpp')]
     if os.path.exists(EXE) and all(os.path.getmtime(EXE) > os.path.getmtime(d) for d in deps):
         return
     env = {k: v for k, v in os.environ.items() if k not in ('CC', 'CXX')}
@@ -41,4 +41,23 @@ def test_scaling_approximations_and_graph_rewrite_known_answers():
 def test_quantized_networks_track_the_float_networks(mode, per_channel):
     _build()
     out = subprocess.run([EXE, '--run', mode, str(per_channel)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_statistics_driven_front_end_on_cpu():
+    """Ranges and histograms fed batch by batch, the thresholds quantizeActivations asks for (a max pooling's
+    statistics stand for the cell above it), weight clipping, state files."""
+    _build()
+    out = subprocess.run([EXE, '--stats'], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert 'statistics front-end ok' in out.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('mode,per_channel,clip', [('fixed', 0, 1), ('double', 1, 1), ('fixed', 0, 2), ('single', 1, 2),
+                                                   ('fixed', 1, 3)])
+def test_networks_quantized_from_calibration_statistics(mode, per_channel, clip):
+    # clip: 1 = statistics without clipping (must equal the value-range run), 2 = MSE, 3 = KL divergence
+    _build()
+    out = subprocess.run([EXE, '--run', mode, str(per_channel), str(clip)], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
