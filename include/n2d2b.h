@@ -212,6 +212,13 @@ int n2d2b_net_selftest_wait_timeout(n2d2b_net* net, unsigned limit_us, n2d2b_str
  * scores) are device buffers of batch x height x width int32.  Asynchronous on `stream`, which must be the stream
  * of that forward pass (or ordered after it). */
 int n2d2b_net_estimated_labels(n2d2b_net* net, int batch, int32_t* d_labels, int32_t* d_values, n2d2b_stream stream);
+/* Target top-N (src/Target/Target_CUDA_kernels.cu:44-86): the top_n classes per image (and pixel) by descending
+ * score, d_labels / d_values = batch x top_n x height x width int32 like the reference's estimatedLabels.  Among
+ * equal scores the reference's exchange sort leaves the classes in an order that is neither by index nor stable;
+ * this entry point returns exactly that order (evaluated in closed form, not by the quadratic sort).  top_n = 1 is
+ * n2d2b_net_estimated_labels.  Up to 16384 classes. */
+int n2d2b_net_estimated_labels_topn(n2d2b_net* net, int batch, int top_n, int32_t* d_labels, int32_t* d_values,
+                                    n2d2b_stream stream);
 /* Input edge: the transformation quantizeNetwork puts in front of the network (src/DeepNetQuantization.cpp:359-370:
  * multiply by 2^nb_bits - 1 for unsigned stimuli, 2^(nb_bits-1) - 1 for signed ones, then truncate).  d_in holds
  * float stimuli in the reference's layout [batch][channel][y][x]; d_out receives 8-bit [batch][y][x][channel], the

@@ -31,15 +31,33 @@ def needs_build():
 
 
 def build_library(force=False, verbose=False):
+    """One nvcc process per source file (in parallel), objects under n2d2_b200/_build/, then one link step whose
+    output replaces the library atomically."""
     if not force and not needs_build():
         return OUT
-    cmd = [_nvcc()] + NVCC_FLAGS + (['-Xptxas', '-v'] if verbose else []) + ['-o', OUT] + \
-          [os.path.join(CSRC, s) for s in SOURCES]
+    from concurrent.futures import ThreadPoolExecutor
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a compiler wrapper without its support files
     env.pop('CC', None)
     env.pop('CXX', None)
-    subprocess.check_call(cmd, env=env)
+    objdir = os.path.join(HERE, '_build')
+    os.makedirs(objdir, exist_ok=True)
+    newest_header = max(os.path.getmtime(os.path.join(CSRC, h)) for h in HEADERS)
+    flags = [f for f in NVCC_FLAGS if f != '-shared'] + (['-Xptxas', '-v'] if verbose else [])
+
+    def compile_one(src):
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + '.o')
+        path = os.path.join(CSRC, src)
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(path), newest_header):
+            return obj
+        subprocess.check_call([_nvcc()] + flags + ['-c', path, '-o', obj], env=env)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
+    tmp = OUT + '.tmp'
+    subprocess.check_call([_nvcc(), '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', '-o', tmp] + objs, env=env)
+    os.replace(tmp, OUT)
     return OUT
 
 

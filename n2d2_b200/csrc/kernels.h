@@ -50,6 +50,9 @@ cudaError_t launch_elemwise_sum(const SumInputs& ins, size_t pixels, int C, cons
 // Top-1 class per pixel (first maximum wins) of [pixels][C] scores; values may be nullptr.
 // [rows][ld] bytes -> [rows][C] bytes (C <= ld): drops the zero columns a padded cell computed
 cudaError_t launch_drop_padded_columns(const uint8_t* src, int ld, uint8_t* dst, int C, size_t rows, cudaStream_t s);
+// labels / values: [images][topN][hw]; pixels = images * hw score vectors of C entries; C <= 16384
+cudaError_t launch_topn(const void* scores, int dtype, int is_unsigned, size_t pixels, size_t hw, int C, int topN, int32_t* labels,
+                        int32_t* values, cudaStream_t s);
 cudaError_t launch_argmax(const void* scores, int dtype, int is_unsigned, size_t pixels, int C, int32_t* labels, int32_t* values,
                           cudaStream_t s);
 // Float stimuli NCHW -> trunc(x * factor) clamped to [lo, hi], 8-bit NHWC.

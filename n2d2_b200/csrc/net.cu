@@ -1485,6 +1485,26 @@ int n2d2b_net_estimated_labels(n2d2b_net* net, int batch, int32_t* d_labels, int
     return 0;
 }
 
+int n2d2b_net_estimated_labels_topn(n2d2b_net* net, int batch, int top_n, int32_t* d_labels, int32_t* d_values, n2d2b_stream stream)
+{
+    if (!net || !d_labels) return fail(N2D2B_ERR_INVALID, "net and d_labels must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "estimated labels before finalize");
+    if (!net->last_input) return fail(N2D2B_ERR_STATE, "estimated labels before a forward pass");
+    if (batch < 0 || batch > net->max_batch) return fail(N2D2B_ERR_TOO_LARGE, "batch out of range");
+    const int ft = final_tensor_of(net);
+    const TensorRec& t = net->tensors[ft];
+    if (top_n < 1 || top_n > t.C) return fail(N2D2B_ERR_INVALID, "top_n must be in 1..%d (the number of classes)", t.C);
+    if (t.C > 16384) return fail(N2D2B_ERR_TOO_LARGE, "top-N handles up to 16384 classes");
+    CUDA_TRY(cudaSetDevice(net->device));
+    const void* scores = tensor_ptr(net, ft, net->last_input);
+    if (top_n == 1)   // the reference's top-1 branch: first maximum; the layouts coincide
+        CUDA_TRY(launch_argmax(scores, t.dtype, t.is_unsigned, (size_t)batch * t.H * t.W, t.C, d_labels, d_values, (cudaStream_t)stream));
+    else
+        CUDA_TRY(launch_topn(scores, t.dtype, t.is_unsigned, (size_t)batch * t.H * t.W, (size_t)t.H * t.W, t.C, top_n, d_labels,
+                             d_values, (cudaStream_t)stream));
+    return 0;
+}
+
 int n2d2b_quantize_stimuli(int device, const float* d_in, int batch, int channels, int height, int width, int nb_bits,
                            int env_unsigned, void* d_out, n2d2b_stream stream)
 {

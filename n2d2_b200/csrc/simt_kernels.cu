@@ -727,6 +727,111 @@ cudaError_t launch_argmax(const void* scores, int dtype, int is_unsigned, size_t
     return cudaGetLastError();
 }
 
+// Target top-N (src/Target/Target_CUDA_kernels.cu:44-86).  The reference orders a pixel's scores with an exchange
+// sort, "for x: for y: if (v[y] < v[x]) swap(x, y)", quadratic in the number of classes; among equal scores (int8
+// logits tie all the time) the classes end in the order those exchanges leave.  That order has a closed form, which
+// this kernel evaluates in O(topN x classes) per pixel:
+//   * pass x = 0 leaves the minimum at position 0; every position where the running minimum dropped receives the
+//     element the minimum displaced;
+//   * every later pass x inserts element x into the descending prefix behind its equals, and each group of equal,
+//     smaller scores gives its first element to the group below and takes the element coming from above, i.e. the
+//     group is rotated by one.
+// So a group of equal scores r, read in position order after pass 0, is a queue that appends on a score == r and
+// moves its head to its tail on a score > r (when it holds more than one element).  The groups are emitted from the
+// highest score down until topN entries are out.  One warp per pixel; the sequential parts run on lane 0.
+// Shared memory: three int arrays of C entries.  Output [image][k][pixel of the image], like the reference.
+template <typename T>
+__global__ void topn_kernel(const T* __restrict__ scores, size_t pixels, size_t hw, int C, int topN, int32_t* __restrict__ labels,
+                            int32_t* __restrict__ values)
+{
+    extern __shared__ int topn_smem[];
+    int* val = topn_smem;
+    int* ids = val + C;
+    int* buf = ids + C;
+    const int lane = threadIdx.x;
+    for (size_t p = blockIdx.x; p < pixels; p += gridDim.x) {
+        const T* row = scores + p * (size_t)C;
+        for (int c = lane; c < C; c += 32) { val[c] = (int)row[c]; ids[c] = c; }
+        __syncwarp();
+        if (lane == 0) {
+            int cur = val[0], curid = 0;
+            for (int y = 1; y < C; ++y) {
+                const int v = val[y];
+                if (v < cur) { val[y] = cur; ids[y] = curid; cur = v; curid = y; }
+            }
+            val[0] = cur;
+            ids[0] = curid;
+        }
+        __syncwarp();
+        const size_t img = p / hw, pix = p - img * hw;
+        int32_t* lab = labels + img * (size_t)topN * hw + pix;
+        int32_t* vout = values ? values + img * (size_t)topN * hw + pix : nullptr;
+        int emitted = 0;
+        long long prev = (long long)INT32_MAX + 1;
+        while (emitted < topN) {
+            // next group: the highest score below the previous group's, and its size
+            int r = INT32_MIN, found = 0;
+            for (int c = lane; c < C; c += 32) {
+                const int v = val[c];
+                if ((long long)v < prev && (!found || v > r)) { r = v; found = 1; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const int orr = __shfl_xor_sync(0xffffffffu, r, off), of = __shfl_xor_sync(0xffffffffu, found, off);
+                if (of && (!found || orr > r)) { r = orr; found = 1; }
+            }
+            if (!found) break;   // fewer than topN classes
+            int cnt = 0;
+            for (int c = lane; c < C; c += 32) cnt += (val[c] == r);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+            if (lane == 0) {
+                int h = 0, L = 0;   // head and length of the queue in buf[0, cnt)
+                for (int x = 0; x < C; ++x) {
+                    const int v = val[x];
+                    if (v == r) {
+                        int t = h + L; if (t >= cnt) t -= cnt;
+                        buf[t] = ids[x];
+                        ++L;
+                    } else if (v > r && L > 1) {
+                        int t = h + L; if (t >= cnt) t -= cnt;
+                        buf[t] = buf[h];
+                        if (++h == cnt) h = 0;
+                    }
+                }
+                for (int k = 0; k < cnt && emitted + k < topN; ++k) {
+                    int t = h + k; if (t >= cnt) t -= cnt;
+                    lab[(size_t)(emitted + k) * hw] = buf[t];
+                    if (vout) vout[(size_t)(emitted + k) * hw] = r;
+                }
+            }
+            emitted += cnt;
+            prev = r;
+            __syncwarp();
+        }
+        __syncwarp();
+    }
+}
+
+cudaError_t launch_topn(const void* scores, int dtype, int is_unsigned, size_t pixels, size_t hw, int C, int topN, int32_t* labels,
+                        int32_t* values, cudaStream_t s)
+{
+    if (pixels == 0 || C == 0 || topN == 0) return cudaSuccess;
+    const size_t smem = (size_t)3 * C * sizeof(int);
+    const unsigned grid = (unsigned)std::min<size_t>(pixels, 148 * 16);
+#define N2D2B_TOPN(T)                                                                                                   \
+    do {                                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(topn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        if (e != cudaSuccess) return e;                                                                                 \
+        topn_kernel<T><<<grid, 32, smem, s>>>((const T*)scores, pixels, hw, C, topN, labels, values);                   \
+    } while (0)
+    if (dtype == DT_I32) N2D2B_TOPN(int32_t);
+    else if (is_unsigned) N2D2B_TOPN(uint8_t);
+    else N2D2B_TOPN(int8_t);
+#undef N2D2B_TOPN
+    return cudaGetLastError();
+}
+
 // ---------------------------------------------------------------------------------------------
 // Input edge: what the post-training quantization puts in front of the network
 // (src/DeepNetQuantization.cpp:359-370: RangeAffineTransformation(Multiplies, 2^n - 1 or 2^(n-1) - 1) with

@@ -90,6 +90,7 @@ def load():
         lib.n2d2b_net_wait.argtypes = [C.c_void_p]
         lib.n2d2b_net_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
         lib.n2d2b_net_estimated_labels.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.n2d2b_net_estimated_labels_topn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.n2d2b_quantize_stimuli.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                C.c_void_p, C.c_void_p]
         lib.n2d2b_net_num_tensors.argtypes = [C.c_void_p]
@@ -247,6 +248,10 @@ class QuantizedNet:
 
     def forward_host_ptr(self, h_in_ptr, batch, h_out_ptr, stream=0):
         check(self.lib.n2d2b_net_forward_host(self.handle, h_in_ptr, batch, h_out_ptr, stream))
+
+    def estimated_labels_topn(self, batch, top_n, d_labels_ptr, d_values_ptr=None, stream=0):
+        """Target top-N of the last forward pass: labels / values [batch][top_n][height][width] int32 on the device."""
+        check(self.lib.n2d2b_net_estimated_labels_topn(self.handle, batch, top_n, d_labels_ptr, d_values_ptr, stream))
 
     def estimated_labels(self, batch, d_labels_ptr, d_values_ptr=None, stream=0):
         """Top-1 class of the last forward pass's final tensor (first maximum wins), into device int32 buffers."""

@@ -21,6 +21,7 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "n2d2_oracle.h"
 
 static inline int imax(int a, int b) { return a > b ? a : b; }
@@ -82,4 +83,39 @@ int n2d2o_num_threads(void)
 #else
     return 1;
 #endif
+}
+
+/* src/Target/Target_CUDA_kernels.cu:44-86 (cudaGetEstimatedTarget_kernel, topN > 1): the scores of a pixel and their
+ * class indices go through an exchange sort, "for x: for y: if (v[y] < v[x]) swap(x, y)", which orders the values
+ * descending; among equal scores the order is whatever those exchanges leave, neither by class nor stable, so the
+ * loops are restated literally.  topN == 1 (:88-104): the first maximum. */
+void n2d2o_estimated_labels_topn(const int64_t* scores, size_t pixels, int nbClass, int topN, int32_t* labels, int64_t* values)
+{
+#pragma omp parallel for schedule(dynamic)
+    for (long long p = 0; p < (long long)pixels; ++p) {
+        const int64_t* in = scores + (size_t)p * nbClass;
+        if (topN == 1) {
+            int best = 0;
+            for (int c = 1; c < nbClass; ++c)
+                if (in[c] > in[best]) best = c;
+            labels[p] = best;
+            values[p] = in[best];
+            continue;
+        }
+        int64_t* v = (int64_t*)malloc(sizeof(int64_t) * (size_t)nbClass);
+        int32_t* idx = (int32_t*)malloc(sizeof(int32_t) * (size_t)nbClass);
+        for (int c = 0; c < nbClass; ++c) { v[c] = in[c]; idx[c] = c; }
+        for (int x = 0; x < nbClass; ++x)
+            for (int y = 0; y < nbClass; ++y)
+                if (v[y] < v[x]) {
+                    const int64_t tv = v[x]; v[x] = v[y]; v[y] = tv;
+                    const int32_t ti = idx[x]; idx[x] = idx[y]; idx[y] = ti;
+                }
+        for (int k = 0; k < topN; ++k) {
+            labels[(size_t)p * topN + k] = idx[k];
+            values[(size_t)p * topN + k] = v[k];
+        }
+        free(v);
+        free(idx);
+    }
 }

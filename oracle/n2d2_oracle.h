@@ -9,6 +9,9 @@ extern "C" {
 
 int n2d2o_conv_out_dim(int in, int k, int stride, int pad0, int pad1, int dil);
 int n2d2o_pool_out_dim(int in, int pool, int stride, int pad);
+/* Target top-N of one score vector per pixel (src/Target/Target_CUDA_kernels.cu:44-86): scores [pixels][nbClass]
+ * (class fastest), labels / values [pixels][topN].  topN == 1 takes the first maximum (:88-104). */
+void n2d2o_estimated_labels_topn(const int64_t* scores, size_t pixels, int nbClass, int topN, int32_t* labels, int64_t* values);
 int n2d2o_num_threads(void);
 void n2d2o_set_num_threads(int n);
 

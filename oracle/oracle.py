@@ -172,6 +172,18 @@ def unpack_weights(layer):
     return np.asarray(layer['weights'], np.int8)
 
 
+def estimated_labels_topn(scores, top_n):
+    """Target top-N of the reference (src/Target/Target_CUDA_kernels.cu:44-104) on integer scores [pixels][classes]:
+    returns (labels, values), each [pixels][top_n]."""
+    sc = np.ascontiguousarray(scores, np.int64)
+    pixels, nb_class = sc.shape
+    labels = np.zeros((pixels, top_n), np.int32)
+    values = np.zeros((pixels, top_n), np.int64)
+    lib().n2d2o_estimated_labels_topn(sc.ctypes.data_as(C.c_void_p), C.c_size_t(pixels), nb_class, top_n,
+                                      labels.ctypes.data_as(C.c_void_p), values.ctypes.data_as(C.c_void_p))
+    return labels, values
+
+
 def run_net(net, x_nhwc, flavour='f32'):
     """Runs the network on x_nhwc ([B][H][W][C], 8-bit) cell by cell. Returns the list of per-layer
     outputs as NHWC int64 arrays (exactly-integer values in both flavours)."""

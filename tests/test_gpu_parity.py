@@ -513,3 +513,58 @@ def test_output_channels_that_tma_stores_cannot_address_run_padded(case, mode):
 def test_padded_output_channels_in_upload_slices():
     net = single_conv_net(16, 48, 48, 24, 3, 1, 1, mode='double')
     compare_net(net, 7, slices=3)
+
+
+@pytest.mark.parametrize('classes,top_n,size', [(1000, 5, 32), (10, 10, 32), (37, 3, 48), (1000, 1, 32)])
+def test_output_edge_top_n_in_the_order_the_reference_sort_leaves(classes, top_n, size):
+    # Target top-N (src/Target/Target_CUDA_kernels.cu:44-86): an exchange sort whose order among equal scores is
+    # neither by class nor stable; the oracle replays it literally, the device evaluates it in closed form
+    import torch
+    net = netdesc.resnet18(size=size, classes=classes)
+    batch = 9
+    x = netdesc.make_input(net, batch)
+    ref = oracle.run_net(net, x, 'i64')[-1].reshape(batch, -1)
+    want_l, want_v = oracle.estimated_labels_topn(ref, top_n)
+    qn = runtime.QuantizedNet(net, batch)
+    try:
+        d_in = torch.from_numpy(x).cuda()
+        d_out = torch.empty((batch, qn.out_elems), dtype=torch.int8, device='cuda')
+        labels = torch.full((batch, top_n), -1, dtype=torch.int32, device='cuda')
+        values = torch.zeros((batch, top_n), dtype=torch.int32, device='cuda')
+        qn.forward_device(d_in.data_ptr(), batch, d_out.data_ptr(), 0)
+        qn.estimated_labels_topn(batch, top_n, labels.data_ptr(), values.data_ptr(), 0)
+        qn.check(0)
+        assert np.array_equal(values.cpu().numpy(), want_v)
+        assert np.array_equal(labels.cpu().numpy(), want_l)
+        if top_n > 1 and classes > 100:
+            # the case does contain ties inside the top-N, and their order is not the ascending class order
+            tied = [(want_v[b][:-1] == want_v[b][1:]).any() for b in range(batch)]
+            assert any(tied)
+        with pytest.raises(runtime.N2D2BError):
+            qn.estimated_labels_topn(batch, classes + 1, labels.data_ptr(), values.data_ptr(), 0)
+    finally:
+        qn.close()
+
+
+def test_output_edge_top_n_per_pixel_of_a_score_map():
+    # a fully convolutional head: top-N per pixel, output [image][k][y][x]; int8 maps with few levels tie everywhere
+    import torch
+    net = single_conv_net(16, 12, 10, 21, 3, 1, 1, mode='single', act='linear')
+    batch, top_n = 4, 4
+    x = netdesc.make_input(net, batch)
+    ref = oracle.run_net(net, x, 'i64')[-1]                      # [B][C][H][W]
+    B, Cn, H, W = ref.shape
+    want_l, want_v = oracle.estimated_labels_topn(ref.transpose(0, 2, 3, 1).reshape(B * H * W, Cn), top_n)
+    qn = runtime.QuantizedNet(net, batch)
+    try:
+        qn.forward_host(x)
+        labels = torch.full((B, top_n, H, W), -1, dtype=torch.int32, device='cuda')
+        values = torch.zeros((B, top_n, H, W), dtype=torch.int32, device='cuda')
+        qn.estimated_labels_topn(batch, top_n, labels.data_ptr(), values.data_ptr(), 0)
+        qn.check(0)
+        got_l = labels.cpu().numpy().transpose(0, 2, 3, 1).reshape(B * H * W, top_n)
+        got_v = values.cpu().numpy().transpose(0, 2, 3, 1).reshape(B * H * W, top_n)
+        assert np.array_equal(got_v, want_v)
+        assert np.array_equal(got_l, want_l)
+    finally:
+        qn.close()
