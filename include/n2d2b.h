@@ -219,6 +219,9 @@ int n2d2b_net_estimated_labels(n2d2b_net* net, int batch, int32_t* d_labels, int
  * n2d2b_net_estimated_labels.  Up to 16384 classes. */
 int n2d2b_net_estimated_labels_topn(n2d2b_net* net, int batch, int top_n, int32_t* d_labels, int32_t* d_values,
                                     n2d2b_stream stream);
+/* The same into host buffers, blocking (for a caller without device memory of its own, after
+ * n2d2b_net_forward_host or n2d2b_net_wait); h_values may be NULL. */
+int n2d2b_net_estimated_labels_topn_host(n2d2b_net* net, int batch, int top_n, int32_t* h_labels, int32_t* h_values);
 /* Input edge: the transformation quantizeNetwork puts in front of the network (src/DeepNetQuantization.cpp:359-370:
  * multiply by 2^nb_bits - 1 for unsigned stimuli, 2^(nb_bits-1) - 1 for signed ones, then truncate).  d_in holds
  * float stimuli in the reference's layout [batch][channel][y][x]; d_out receives 8-bit [batch][y][x][channel], the

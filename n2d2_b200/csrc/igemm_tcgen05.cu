@@ -40,6 +40,7 @@ static constexpr int W4_UNPACK_WARPS = 4;     // extra warps of the packed-int4 
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
+    int grouped;        // block-diagonal layer (depthwise as groups of BN channels): a column block reads its own input channels
     int res_slots;          // staging regions per epilogue warp of a residual cell (2 or 4)
     int m_base;         // first output row of this call within the tensors (a batch slice starts at image img0)
     int b_resident;     // the CTA's whole weight block stays in shared memory (its column block never changes)
@@ -199,7 +200,7 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     const unsigned dstA = tiles_s + (unsigned)(s * stage_bytes);
                     mbar_expect_tx(bar, (unsigned)tx_bytes);
                     if (a.a_im2col) {
-                        tma_load_im2col_4d(dstA, &tmA, bar, kc * a.BK, iw0, ih0, in0,
+                        tma_load_im2col_4d(dstA, &tmA, bar, kc * a.BK + (a.grouped ? n0 : 0), iw0, ih0, in0,
                                            (unsigned short)(kx * a.dX), (unsigned short)(ky * a.dY));
                     } else {
                         tma_load_2d(dstA, &tmA, bar, kcoord, m0);
@@ -731,13 +732,48 @@ static size_t igemm_smem_bytes(int stages, int BK, int BN, int regions, size_t r
          + (2 * stages + 8 + 4 * NUM_EPI_WARPS + (w4 ? stages : 0)) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
+// Channels per block-diagonal group of a depthwise layer this kernel takes (0: not such a layer): groups of 64
+// channels = one 64-column tile each, or a single group of 32
+int igemm_dw_group(const ConvGeom& g)
+{
+    if (g.groups <= 1 || g.groups != g.C || g.O != g.C || g.Cg != 1 || g.Og != 1) return 0;
+    if (g.C % 64 == 0) return 64;
+    if (g.C == 32) return 32;
+    return 0;
+}
+
+size_t igemm_dw_weight_bytes(const ConvGeom& g) { return (size_t)g.C * g.kH * g.kW * igemm_dw_group(g); }
+
+// Depthwise weights [C][taps] as the block-diagonal matrix [C][taps][group channels] (real channel order)
+void igemm_dw_arrange_weights(const ConvGeom& g, const int8_t* w_ct, int8_t* dst)
+{
+    const int cg = igemm_dw_group(g), taps = g.kH * g.kW;
+    const size_t row_bytes = (size_t)taps * cg;
+    memset(dst, 0, (size_t)g.C * row_bytes);
+    for (int o = 0; o < g.C; ++o)
+        for (int t = 0; t < taps; ++t) dst[(size_t)o * row_bytes + (size_t)t * cg + (o % cg)] = w_ct[(size_t)o * taps + t];
+}
+
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,
-                    const ConvGeom& g, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
+                    const ConvGeom& g0, int in_unsigned, int force_im2col, int force_bn, int num_sms, const char** why,
                     int force_pair, int w4)
 {
     static const char* kWhy = "";
     *why = kWhy;
     if (load_driver_entry_points(why)) return -1;
+    // A depthwise layer runs as block-diagonal groups: per 64-column tile a dense layer over the tile's own 64 input
+    // channels (weights [C][taps * 64], zeros off the diagonal); the activation loads take the group's channel slice.
+    ConvGeom g = g0;
+    const int Ct = g0.C;          // channels per pixel of the input tensor
+    int grouped = 0;
+    if (const int cg = igemm_dw_group(g0)) {
+        if (w4 || res) { *why = "block-diagonal groups take neither packed weights nor a residual"; return -1; }
+        g.C = cg; g.groups = 1; g.Cg = cg; g.Og = g0.O;
+        grouped = Ct > cg ? 1 : 0;
+        force_im2col = 1;
+        force_bn = 64;
+        force_pair = 0;
+    }
     if (g.groups != 1) { *why = "grouped convolution is not a dense contraction"; return -1; }
     if (g.C % 16 != 0) { *why = "input channels must be a multiple of 16 for the TMA path"; return -1; }
     if (((uintptr_t)in & 15) || ((uintptr_t)w & 15)) { *why = "operands must be 16-byte aligned"; return -1; }
@@ -761,6 +797,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
         while (!force_pair && bn > 64 && m_tiles * ((g.O + bn - 1) / bn) < num_sms) bn >>= 1;
     }
     plan->BN = bn;
+    plan->grouped = grouped;
     plan->w4 = w4 ? 1 : 0;
     plan->a_unsigned = in_unsigned;
     plan->oW = g.oW; plan->oH = g.oH; plan->kW = g.kW;
@@ -832,8 +869,8 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
     } else {
         // NHWC activations as a (C, W, H, N) tensor; the base pixel of output (ox, oy) is
         // (ox*sX - pL, oy*sY - pT) and the filter tap is passed as an offset per load.
-        const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
-        const cuuint64_t strides[3] = {(cuuint64_t)g.C, (cuuint64_t)g.C * g.W, (cuuint64_t)g.C * g.W * g.H};
+        const cuuint64_t dims[4] = {(cuuint64_t)Ct, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)Ct, (cuuint64_t)Ct * g.W, (cuuint64_t)Ct * g.W * g.H};
         const int lower[2] = {-g.pL, -g.pT};
         // last base pixel = (oW-1)*sX - pL  ->  upper corner relative to the tensor edge
         const int upper[2] = {(g.oW - 1) * g.sX - g.pL - (g.W - 1), (g.oH - 1) * g.sY - g.pT - (g.H - 1)};
@@ -847,7 +884,7 @@ int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void
         // documented remedy used by NVIDIA's own open-source templates.
         int drv = 0;
         if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010) {
-            const size_t bytes = (size_t)g.C * g.W * g.H * g.B;
+            const size_t bytes = (size_t)Ct * g.W * g.H * g.B;
             if (bytes < 131072) reinterpret_cast<unsigned long long*>(&plan->tmA)[1] &= ~(1ull << 21);
         }
     }
@@ -913,6 +950,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     a.M = plan.M; a.N = plan.N; a.Cin = plan.Cin; a.taps = plan.taps; a.BK = plan.BK; a.BN = plan.BN;
     a.b_resident = plan.b_resident;
     a.stages = plan.stages; a.a_im2col = plan.a_im2col;
+    a.grouped = plan.grouped;
     a.res_slots = plan.res_slots ? plan.res_slots : 2;
     a.oW = plan.oW; a.oH = plan.oH; a.kW = plan.kW; a.sX = plan.sX; a.sY = plan.sY;
     a.pL = plan.pL; a.pT = plan.pT; a.dX = plan.dX; a.dY = plan.dY;

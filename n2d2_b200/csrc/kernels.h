@@ -118,9 +118,15 @@ struct PatchPlan {
     int stage_cols;       // columns an epilogue warp stages per pass
     int in_unsigned;
     int num_sms;
+    int G;                // channel groups: 1, or the block-diagonal groups of a depthwise layer
     size_t smem_bytes;
 };
+// dense stride-1 layers with 32 / 64 / 128 input channels, and depthwise stride-1 layers whose channels are a
+// multiple of 32 (run as block-diagonal groups of 64 or 32 channels)
 bool patch_eligible(const ConvGeom& g);
+int patch_groups(const ConvGeom& g);
+size_t patch_dw_weight_bytes(const ConvGeom& g);
+void patch_dw_arrange_weights(const ConvGeom& g, const int8_t* w_ct, int8_t* dst);
 void patch_permute_weights(const int8_t* w, int8_t* dst, int O, size_t row_bytes);
 int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
                     const char** why);
@@ -141,6 +147,7 @@ struct IgemmPlan {
     int BK;               // bytes of K per pipeline stage: 32, 64 or 128 (also the swizzle width)
     int BN;               // tile N: 64, 128 or 256
     int stages;
+    int grouped;          // depthwise layer as block-diagonal groups: column block n reads input channels [n * BN, (n + 1) * BN)
     int b_resident;       // weights of the CTA's column block stay in shared memory for the whole launch
     int res_slots;        // fused residual: staging regions per epilogue warp (2 or 4), 0 without a residual
     int w4;               // weights are packed 4-bit values in HBM ([N][Ktot / 2] bytes, even element in the high nibble)
@@ -154,6 +161,11 @@ struct IgemmPlan {
     int grid;             // CTAs to launch
     size_t smem_bytes;
 };
+// depthwise layers the kernel takes as block-diagonal groups (channels a multiple of 64, or 32): channels per group,
+// bytes and layout of the block-diagonal weight matrix [C][taps][group]
+int igemm_dw_group(const ConvGeom& g);
+size_t igemm_dw_weight_bytes(const ConvGeom& g);
+void igemm_dw_arrange_weights(const ConvGeom& g, const int8_t* w_ct, int8_t* dst);
 // Encodes the tensor maps for `in`/`w` and fills the tiling. Returns 0, or -1 with `why` set.
 // force_pair: take the 256-row variant wherever its structure allows, whatever the layer's size (tests)
 int igemm_make_plan(IgemmPlan* plan, const void* in, const int8_t* w, const void* out, const void* res,

@@ -119,6 +119,8 @@ struct n2d2b_net {
     int* d_status = nullptr;
     int launches = 0;
     const void* last_input = nullptr;
+    void* d_labels_scratch = nullptr;   // device labels / scores of the host-buffer top-N entry point
+    size_t labels_scratch_bytes = 0;
     void* d_stage_in = nullptr;   // device staging of the host-buffer entry point
     void* d_stage_out = nullptr;
     // host-buffer entry point: the upload is cut into slices on its own stream so that the leading
@@ -567,6 +569,7 @@ void n2d2b_net_destroy(n2d2b_net* net)
         cudaFree(c.d_colpad);
     }
     cudaFree(net->d_status);
+    cudaFree(net->d_labels_scratch);
     cudaFree(net->d_stage_in);
     cudaFree(net->d_stage_out);
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
@@ -977,6 +980,55 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             c.engine = ENG_DEPTHWISE;
             if (!(flags & N2D2B_EXACT64_EPILOGUE))
                 if (int rc = upload_fast(c, net->tensors[c.output])) return rc;
+            // Stride-1 layers whose channels come in whole groups of 32 run on the tensor cores as block-diagonal
+            // groups (patch kernel); it needs the 32-bit epilogue
+            ConvGeom gb = g;
+            gb.B = max_batch;
+            if (c.fast.enabled && !(flags & N2D2B_FORCE_SIMT) && patch_eligible(gb)) {
+                std::vector<int8_t> arranged(patch_dw_weight_bytes(g));
+                patch_dw_arrange_weights(g, c.weights.data(), arranged.data());
+                CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
+                CUDA_TRY(cudaMemcpy(c.d_weights, arranged.data(), arranged.size(), cudaMemcpyHostToDevice));
+                c.d_weight_bytes = arranged.size();
+                const char* why = "";
+                const void* in_ptr = tensor_ptr(net, c.inputs[0], nullptr);
+                static char dw_placeholder[16] __attribute__((aligned(16)));
+                if (patch_make_plan(&c.patch, in_ptr ? in_ptr : (const void*)dw_placeholder, c.d_weights, gb,
+                                    net->tensors[c.inputs[0]].is_unsigned, net->num_sms, &why) == 0) {
+                    c.engine = ENG_PATCH;
+                    c.plan_input = in_ptr;   // nullptr = re-encoded with the real input at the first forward pass
+                    continue;
+                }
+                cudaFree(c.d_weights);
+                c.d_weights = nullptr;
+            }
+            // Strided ones (and whatever else the patch kernel leaves) take the implicit-GEMM kernel the same way: one
+            // 64-column tile per group of 64 channels, im2col loads of the group's channel slice
+            if (c.fast.enabled && !(flags & (N2D2B_FORCE_SIMT | N2D2B_EXACT64_EPILOGUE)) && igemm_dw_group(gb)) {
+                std::vector<int8_t> arranged(igemm_dw_weight_bytes(g));
+                igemm_dw_arrange_weights(g, c.weights.data(), arranged.data());
+                CUDA_TRY(cudaMalloc((void**)&c.d_weights, arranged.size() + 256));
+                c.d_weight_bytes = arranged.size();
+                const char* why = "";
+                const void* in_ptr = tensor_ptr(net, c.inputs[0], nullptr);
+                static char dwg_placeholder[16] __attribute__((aligned(16)));
+                if (igemm_make_plan(&c.plan, in_ptr ? in_ptr : (const void*)dwg_placeholder, c.d_weights,
+                                    tensor_ptr(net, c.output, nullptr), nullptr, gb, net->tensors[c.inputs[0]].is_unsigned, 1, 0,
+                                    net->num_sms, &why, 0, 0) == 0
+                    && igemm_uses_fast_epilogue(c.plan, c.fast, false, DT_I8)) {
+                    const int pb = igemm_perm_block(c.plan);
+                    std::vector<int8_t> rows(arranged.size());
+                    igemm_permute_weights(arranged.data(), rows.data(), g.C, arranged.size() / (size_t)g.C, pb);
+                    c.plan.perm = pb;
+                    CUDA_TRY(cudaMemcpy(c.d_weights, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+                    c.engine = ENG_TCGEN05;
+                    c.has_plan = true;
+                    c.plan_input = in_ptr;
+                    continue;
+                }
+                cudaFree(c.d_weights);
+                c.d_weights = nullptr;
+            }
             // [C][kH][kW] -> [kH][kW][C] so that 16 channels of a tap are one 128-bit load
             const int taps = g.kH * g.kW;
             for (int ch = 0; ch < g.C; ++ch)
@@ -1505,6 +1557,32 @@ int n2d2b_net_estimated_labels_topn(n2d2b_net* net, int batch, int top_n, int32_
     return 0;
 }
 
+int n2d2b_net_estimated_labels_topn_host(n2d2b_net* net, int batch, int top_n, int32_t* h_labels, int32_t* h_values)
+{
+    if (!net || !h_labels) return fail(N2D2B_ERR_INVALID, "net and h_labels must not be NULL");
+    if (!net->finalized) return fail(N2D2B_ERR_STATE, "estimated labels before finalize");
+    if (batch < 0 || batch > net->max_batch) return fail(N2D2B_ERR_TOO_LARGE, "batch out of range");
+    const TensorRec& t = net->tensors[final_tensor_of(net)];
+    if (top_n < 1 || top_n > t.C) return fail(N2D2B_ERR_INVALID, "top_n must be in 1..%d (the number of classes)", t.C);
+    CUDA_TRY(cudaSetDevice(net->device));
+    const size_t n = (size_t)batch * top_n * t.H * t.W;
+    if (n == 0) return 0;
+    if (net->labels_scratch_bytes < 2 * n * sizeof(int32_t)) {
+        cudaFree(net->d_labels_scratch);
+        net->d_labels_scratch = nullptr;
+        net->labels_scratch_bytes = 0;
+        CUDA_TRY(cudaMalloc(&net->d_labels_scratch, 2 * n * sizeof(int32_t)));
+        net->labels_scratch_bytes = 2 * n * sizeof(int32_t);
+    }
+    int32_t* d_labels = (int32_t*)net->d_labels_scratch;
+    int32_t* d_values = d_labels + n;
+    // the legacy stream orders this after the forward pass on any blocking stream
+    if (int rc = n2d2b_net_estimated_labels_topn(net, batch, top_n, d_labels, d_values, nullptr)) return rc;
+    CUDA_TRY(cudaMemcpy(h_labels, d_labels, n * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (h_values) CUDA_TRY(cudaMemcpy(h_values, d_values, n * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 int n2d2b_quantize_stimuli(int device, const float* d_in, int batch, int channels, int height, int width, int nb_bits,
                            int env_unsigned, void* d_out, n2d2b_stream stream)
 {
@@ -1575,6 +1653,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
         const CellRec& c = net->cells[cell];
         const bool pair = c.plan.pair && c.fast.enabled && !c.fast.wide && c.residual < 0
                           && net->tensors[c.output].dtype == DT_I8 && c.geom.O % 32 == 0;
+        if (c.geom.groups > 1) return "depthwise-tcgen05";
         return pair ? "tcgen05-pair" : (c.plan.w4 ? "tcgen05-w4" : "tcgen05");
     }
     case ENG_SIMT: return "simt";
@@ -1584,7 +1663,7 @@ const char* n2d2b_net_cell_engine(const n2d2b_net* net, int cell)
     case ENG_FUSED: return "fused";
     case ENG_STEM: return "stem-tcgen05";
     case ENG_STEM_S2D: return net->cells[cell].pool_fused ? "stem-pool-tcgen05" : "stem-tcgen05";
-    case ENG_PATCH: return "patch-tcgen05";
+    case ENG_PATCH: return net->cells[cell].geom.groups > 1 ? "depthwise-tcgen05" : "patch-tcgen05";
     }
     return "";
 }

@@ -10,6 +10,12 @@
 // no data moves, and the MMAs of a tile (taps x C/32 of them) are issued back to back.  Positions in the
 // halo columns (x >= oW) compute values nobody stores.  The weights of all taps stay resident.
 //
+// Depthwise 3x3 layers take the same route as block-diagonal groups: the channels are cut into groups of 64 (32), a
+// CTA works on one group for its whole life (CTA b on group b mod G, so the group's weight block - its own taps on
+// the diagonal, zeros elsewhere - stays resident), the patch load takes the group's channel slice of the NHWC tensor
+// and the output rows are written into that slice.  The tensor core multiplies 64 times more than the layer needs,
+// and still outruns the CUDA cores, where a byte dot product issues at a quarter of the integer rate.
+//
 // Warp 0 loads (weights once, patches double-buffered), warps 1-2 issue tcgen05.mma kind::i8 for alternate
 // tiles into a ring of four TMEM accumulators, and four groups of four epilogue warps (one warp per TMEM lane quadrant) each
 // drain every fourth tile: 32-bit requantisation in the fragment layout into a swizzled staging region,
@@ -31,7 +37,9 @@ static constexpr int P_BRING_MIN = 4;         // weight ring slots (one filter t
 static constexpr int P_BRING_MAX = 8;         // as many as shared memory holds between these two
 
 struct PatchArgs {
-    int B, oH, oW, N, BN, C;
+    int B, oH, oW, N, BN, C;   // N, C: output and input channels of one group (= of the layer when G == 1)
+    int G;                  // channel groups (block-diagonal layers); CTA b works on group b % G
+    int ldo;                // output channels per pixel of the whole tensor
     int taps_y, taps_x, dY, dX, pT, pL;
     int Wp;                 // patch width in pixels: oW + (kW-1)*dX
     int R;                  // output rows per band
@@ -154,9 +162,12 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                      ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // this CTA's channel group, and its place among the CTAs of that group
+    const int grp = (int)blockIdx.x % a.G, cta = (int)blockIdx.x / a.G, nctas = (int)gridDim.x / a.G;
+    const int ch0 = grp * a.N;                       // first output channel (= first input channel) of the group
     for (int i = threadIdx.x; i < FAST_NP * 256; i += P_THREADS) {
         const int prm = i >> 8, c = i & 255;
-        par[i] = (c < a.cpad) ? __ldg(a.fq + (size_t)prm * a.cpad + c) : 0;
+        par[i] = (ch0 + c < a.cpad) ? __ldg(a.fq + (size_t)prm * a.cpad + ch0 + c) : 0;
     }
     tc_fence_before();
     __syncthreads();
@@ -169,31 +180,31 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && (int)blockIdx.x < items) {
+        if (lane == 0 && cta < items) {
             if (!a.b_stream) {
                 mbar_expect_tx(bfull, (unsigned)(taps * b_tap_bytes));
                 for (int t = 0; t < taps; ++t)
-                    tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, 0);
+                    tma_load_2d(smem_u32(res_b + (size_t)t * b_tap_bytes), &tmB, bfull, t * a.C, ch0);
             }
             pdl_wait();   // weights are constants; the activations are the previous kernel's output
             unsigned it = 0;
             int rs = 0;              // weight ring slot and its phase
             unsigned rph = 0;
             bool ok = true;
-            int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
-            const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
-            for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
+            int n = cta / a.bands, band = cta % a.bands;
+            const int step_n = nctas / a.bands, step_b = nctas % a.bands;
+            for (int item = cta; item < items; item += nctas, ++it) {
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 if (!mbar_wait(pempty0 + 8u * pb, ph ^ 1u, abort_flag, a.status, 1)) break;
                 mbar_expect_tx(pfull0 + 8u * pb, (unsigned)a.patch_bytes);
-                tma_load_4d(smem_u32(patch0 + (size_t)pb * a.patch_alloc), &tmA, pfull0 + 8u * pb, 0, -a.pL,
+                tma_load_4d(smem_u32(patch0 + (size_t)pb * a.patch_alloc), &tmA, pfull0 + 8u * pb, grp * a.C, -a.pL,
                             band * a.R - a.pT, a.n_base + n);
                 if (a.b_stream) {
                     // every item walks all taps once: its weights follow the patch through the ring
                     for (int t = 0; t < taps && ok; ++t) {
                         if (!mbar_wait(rempty0 + 8u * rs, rph ^ 1u, abort_flag, a.status, 5)) { ok = false; break; }
                         mbar_expect_tx(rfull0 + 8u * rs, (unsigned)b_tap_bytes);
-                        tma_load_2d(smem_u32(res_b + (size_t)rs * b_tap_bytes), &tmB, rfull0 + 8u * rs, t * a.C, 0);
+                        tma_load_2d(smem_u32(res_b + (size_t)rs * b_tap_bytes), &tmB, rfull0 + 8u * rs, t * a.C, ch0);
                         if (++rs == a.bring) { rs = 0; rph ^= 1u; }
                     }
                     if (!ok) break;
@@ -210,7 +221,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         // every lane of the warp runs the loop; `issue` selects the lane whose MMAs and commits take effect
         const unsigned me = (unsigned)__shfl_sync(0xffffffffu, warp - 1, 0);
         const unsigned issue = lane == 0 ? 1u : 0u;
-        if ((int)blockIdx.x < items) {
+        if (cta < items) {
             bool ok = a.b_stream ? true : mbar_wait_uniform(bfull, 0, abort_flag, a.status, 8);
             const unsigned desc_hi = (unsigned)(make_smem_desc(0u, a.C) >> 32);
             const unsigned res_b_lo = (smem_u32(res_b) & 0x3ffffu) >> 4, patch_lo = (smem_u32(patch0) & 0x3ffffu) >> 4;
@@ -218,12 +229,12 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             const unsigned row_step = (unsigned)((a.dY * a.Wp * a.C) >> 4), col_step = (unsigned)((a.dX * a.C) >> 4);
             const unsigned btap = (unsigned)(b_tap_bytes >> 4);
             unsigned it = 0, seq = 0;
-            int band = (int)blockIdx.x % a.bands;
-            const int step_b = (int)gridDim.x % a.bands;
+            int band = cta % a.bands;
+            const int step_b = nctas % a.bands;
             const unsigned tile_step = (unsigned)((PBM * a.C) >> 4);
             int rs = 0;              // weight ring slot and its phase (streamed weights)
             unsigned rph = 0;
-            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
+            for (int item = cta; item < items && ok; item += nctas, ++it) {
                 const unsigned pb = it & 1u, ph = (it >> 1) & 1u;
                 const int T = band_tiles(band);
                 if (!mbar_wait_uniform(pfull0 + 8u * pb, ph, abort_flag, a.status, 3)) { ok = false; break; }
@@ -305,10 +316,10 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         const int SC = a.stage_cols;
         const unsigned swz_mask = (unsigned)(SC / 16 - 1);
         unsigned seq = 0;
-        int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
-        const int step_n = (int)gridDim.x / a.bands, step_b = (int)gridDim.x % a.bands;
+        int n = cta / a.bands, band = cta % a.bands;
+        const int step_n = nctas / a.bands, step_b = nctas % a.bands;
         bool ok = true;
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        for (int item = cta; item < items && ok; item += nctas) {
             const int rows = band_rows(band);
             const int T = band_tiles(band);
             for (int t = 0; t < T; ++t, ++seq) {
@@ -346,7 +357,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                             const unsigned yy = __umulhi(p, a.rcp_Wp);
                             const unsigned x = p - yy * (unsigned)a.Wp;
                             if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                                uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N) + c0;
+                                uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.ldo) + ch0 + c0;
                                 const unsigned ro = r * (unsigned)SC;
                                 const unsigned xm = (ro >> 7) & swz_mask;
                                 *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
@@ -357,7 +368,7 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                         const unsigned yy = __umulhi(p, a.rcp_Wp);
                         const unsigned x = p - yy * (unsigned)a.Wp;
                         if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N) + c0;
+                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.ldo) + ch0 + c0;
                             const unsigned ro = (unsigned)(lane * SC);
                             const unsigned xm = (ro >> 7) & swz_mask;
                             for (int c = 0; c < nch; ++c)
@@ -414,8 +425,30 @@ static int patch_alloc_bytes(const ConvGeom& g, int Wp, int R)
     return (rows * g.C + 1023) & ~1023;
 }
 
-bool patch_eligible(const ConvGeom& g)
+// Channels per block-diagonal group of a depthwise layer (0: not a layer this kernel takes as groups)
+static int patch_dw_group(const ConvGeom& g)
 {
+    if (g.groups <= 1 || g.groups != g.C || g.O != g.C || g.Cg != 1 || g.Og != 1) return 0;
+    if (g.C % 64 == 0) return 64;
+    if (g.C % 32 == 0) return 32;
+    return 0;
+}
+
+// The geometry of one group of a depthwise layer as the dense layer the kernel sees
+static ConvGeom patch_group_geom(const ConvGeom& g)
+{
+    ConvGeom e = g;
+    const int cg = patch_dw_group(g);
+    if (cg) { e.C = cg; e.O = cg; e.groups = 1; e.Cg = cg; e.Og = cg; }
+    return e;
+}
+
+int patch_groups(const ConvGeom& g) { const int cg = patch_dw_group(g); return cg ? g.C / cg : 1; }
+
+bool patch_eligible(const ConvGeom& g0)
+{
+    if (g0.groups != 1 && (!patch_dw_group(g0) || patch_groups(g0) > 64)) return false;
+    const ConvGeom g = patch_group_geom(g0);
     if (g.groups != 1 || g.sX != 1 || g.sY != 1) return false;
     if (g.C != 32 && g.C != 64 && g.C != 128) return false;
     if (g.O % 32 != 0 || g.O > 128) return false;
@@ -434,12 +467,28 @@ void patch_permute_weights(const int8_t* w, int8_t* dst, int O, size_t row_bytes
     for (int n = 0; n < O; ++n) memcpy(dst + (size_t)n * row_bytes, w + (size_t)perm_real_channel(n, 4) * row_bytes, row_bytes);
 }
 
-int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g, int in_unsigned, int num_sms,
+// Depthwise weights [C][taps] as the block-diagonal matrix of the grouped form: row o = [taps][group channels] with
+// the tap's weight at column o % group and zeros elsewhere; rows in the epilogue's order.
+size_t patch_dw_weight_bytes(const ConvGeom& g) { return (size_t)g.C * g.kH * g.kW * patch_dw_group(g); }
+void patch_dw_arrange_weights(const ConvGeom& g, const int8_t* w_ct, int8_t* dst)
+{
+    const int cg = patch_dw_group(g), taps = g.kH * g.kW;
+    const size_t row_bytes = (size_t)taps * cg;
+    memset(dst, 0, (size_t)g.C * row_bytes);
+    for (int n = 0; n < g.C; ++n) {
+        const int o = perm_real_channel(n, 4);
+        for (int t = 0; t < taps; ++t) dst[(size_t)n * row_bytes + (size_t)t * cg + (o % cg)] = w_ct[(size_t)o * taps + t];
+    }
+}
+
+int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const ConvGeom& g0, int in_unsigned, int num_sms,
                     const char** why)
 {
     static const char* kWhy = "";
     *why = kWhy;
-    if (!patch_eligible(g)) { *why = "geometry outside the patch kernel"; return -1; }
+    if (!patch_eligible(g0)) { *why = "geometry outside the patch kernel"; return -1; }
+    const ConvGeom g = patch_group_geom(g0);   // one group (the layer itself when it is dense)
+    const int Ct = g0.C;                       // channels per pixel of the input tensor, rows of the weight matrix
     if (((uintptr_t)in & 15) || ((uintptr_t)w & 15)) { *why = "operands must be 16-byte aligned"; return -1; }
     cudaDriverEntryPointQueryResult qr;
     void* fn = nullptr;
@@ -453,6 +502,7 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     plan->Wp = g.oW + (g.kW - 1) * g.dX;
     plan->in_unsigned = in_unsigned;
     plan->num_sms = num_sms;
+    plan->G = patch_groups(g0);
     // rows per band: among the heights that fit shared memory (and the 256-row TMA box), the one that
     // wastes the fewest 128-position tiles per image; ties go to the taller band (fewer halo rows re-read)
     int best_R = 0;
@@ -485,7 +535,7 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
                                               : (g.C == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUresult rc;
     {   // weights [O][taps*C], one box = one tap of all outputs (rows beyond O read as zero)
-        const cuuint64_t dims[2] = {(cuuint64_t)taps * g.C, (cuuint64_t)g.O};
+        const cuuint64_t dims[2] = {(cuuint64_t)taps * g.C, (cuuint64_t)g0.O};
         const cuuint64_t strides[1] = {(cuuint64_t)taps * g.C};
         const cuuint32_t box[2] = {(cuuint32_t)g.C, (cuuint32_t)plan->BN};
         const cuuint32_t estr[2] = {1, 1};
@@ -495,8 +545,8 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
         if (rc != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the weights"; return -1; }
     }
     {   // NHWC activations as (C, W, H, B); one box = a whole patch, zero-filled outside the image
-        const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
-        const cuuint64_t strides[3] = {(cuuint64_t)g.C, (cuuint64_t)g.C * g.W, (cuuint64_t)g.C * g.W * g.H};
+        const cuuint64_t dims[4] = {(cuuint64_t)Ct, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+        const cuuint64_t strides[3] = {(cuuint64_t)Ct, (cuuint64_t)Ct * g.W, (cuuint64_t)Ct * g.W * g.H};
         const cuuint32_t box[4] = {(cuuint32_t)g.C, (cuuint32_t)plan->Wp, (cuuint32_t)box_rows, 1};
         const cuuint32_t estr[4] = {1, 1, 1, 1};
         rc = ((EncodeTiledFn)fn)(&plan->tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)in, dims, strides, box, estr,
@@ -507,12 +557,14 @@ int patch_make_plan(PatchPlan* plan, const void* in, const int8_t* w, const Conv
     return 0;
 }
 
-cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, const FastQuant& fast, void* out,
+cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g0, int n_base, const FastQuant& fast, void* out,
                          int* status_word, cudaStream_t s)
 {
+    const ConvGeom g = patch_group_geom(g0);
     PatchArgs a;
     memset(&a, 0, sizeof(a));
     a.B = g.B; a.oH = g.oH; a.oW = g.oW; a.N = g.O; a.BN = plan.BN; a.C = g.C;
+    a.G = plan.G; a.ldo = g0.O;
     if (a.B == 0) return cudaSuccess;
     a.taps_y = g.kH; a.taps_x = g.kW; a.dY = g.dY; a.dX = g.dX; a.pT = g.pT; a.pL = g.pL;
     a.Wp = plan.Wp; a.R = plan.R; a.bands = plan.bands;
@@ -546,8 +598,10 @@ cudaError_t launch_patch(const PatchPlan& plan, const ConvGeom& g, int n_base, c
         }
         attr_set[dev] = true;
     }
+    // a multiple of the group count: CTA b works on group b % G
     const long long items = (long long)a.B * a.bands;
-    const int grid = (int)(items < plan.num_sms ? items : plan.num_sms);
+    const long long per_group = plan.num_sms / plan.G > 0 ? plan.num_sms / plan.G : 1;
+    const int grid = (int)((items < per_group ? items : per_group) * plan.G);
     const int shape = (g.kH == 3 && g.kW == 3 && !plan.b_stream) ? (g.C == 32 ? 1 : (g.C == 64 ? 2 : 3)) : 0;
     return launch_pdl(variants[(fast.need_clamp ? 4 : 0) + shape], grid, P_THREADS, plan.smem_bytes, s, plan.tmA, plan.tmB, a);
 }

@@ -631,6 +631,21 @@ public:
 
     // DeepNet::test on a batch of stimuli (8-bit, [batch][height][width][channels]); returns the last
     // cell's outputs as integers, [batch][outputs].
+    // Target top-N of the last test() call (Target::process / TargetScore with the reference's getEstimatedLabels
+    // kernel, src/Target/Target_CUDA_kernels.cu:24-104): labels (and scores) [batch][topN][height][width]; equal
+    // scores come in the order the reference's sort leaves them, topN = 1 takes the first maximum.
+    std::vector<int> getEstimatedLabels(unsigned int batch, unsigned int topN = 1, std::vector<int>* scores = nullptr)
+    {
+        if (!mInitialized) throw std::runtime_error("DeepNet::getEstimatedLabels(): initialize() and test() first");
+        n2d2b_tensor_info info;
+        check(n2d2b_net_tensor_info(mNet, mLast->mTensorId, &info));
+        const std::size_t n = (std::size_t)batch * topN * info.height * info.width;
+        std::vector<int> labels(n);
+        if (scores) scores->resize(n);
+        check(n2d2b_net_estimated_labels_topn_host(mNet, (int)batch, (int)topN, labels.data(), scores ? scores->data() : nullptr));
+        return labels;
+    }
+
     std::vector<int> test(const std::vector<std::uint8_t>& stimuli, unsigned int batch)
     {
         if (!mInitialized) throw std::runtime_error("DeepNet::test(): initialize() first");

@@ -91,6 +91,7 @@ def load():
         lib.n2d2b_net_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
         lib.n2d2b_net_estimated_labels.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.n2d2b_net_estimated_labels_topn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.n2d2b_net_estimated_labels_topn_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         lib.n2d2b_quantize_stimuli.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                C.c_void_p, C.c_void_p]
         lib.n2d2b_net_num_tensors.argtypes = [C.c_void_p]
@@ -201,6 +202,7 @@ class QuantizedNet:
             self.tensor_of_layer[idx] = tid.value
         check(self.lib.n2d2b_net_finalize(self.handle, max_batch, flags))
         out = self.tensor_info(self.tensor_of_layer[len(net['layers']) - 1])
+        self.out_info = out
         self.out_elems = out.channels * out.height * out.width
         self.out_dtype = np.int32 if out.dtype == 1 else (np.uint8 if out.is_unsigned else np.int8)
         self.in_elems = i['C'] * i['H'] * i['W']
@@ -252,6 +254,14 @@ class QuantizedNet:
     def estimated_labels_topn(self, batch, top_n, d_labels_ptr, d_values_ptr=None, stream=0):
         """Target top-N of the last forward pass: labels / values [batch][top_n][height][width] int32 on the device."""
         check(self.lib.n2d2b_net_estimated_labels_topn(self.handle, batch, top_n, d_labels_ptr, d_values_ptr, stream))
+
+    def estimated_labels_topn_host(self, batch, top_n):
+        """Target top-N of the last forward pass as numpy arrays (labels, values), each [batch][top_n][height][width]."""
+        t = self.out_info
+        labels = np.empty((batch, top_n, t.height, t.width), np.int32)
+        values = np.empty((batch, top_n, t.height, t.width), np.int32)
+        check(self.lib.n2d2b_net_estimated_labels_topn_host(self.handle, batch, top_n, _ptr(labels), _ptr(values)))
+        return labels, values
 
     def estimated_labels(self, batch, d_labels_ptr, d_values_ptr=None, stream=0):
         """Top-1 class of the last forward pass's final tensor (first maximum wins), into device int32 buffers."""

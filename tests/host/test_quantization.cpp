@@ -333,6 +333,21 @@ static int run(const char* mode_name, bool per_channel, int clip = 0)
         }
         dn.initialize(B);
         const std::vector<int> logits = dn.test(stimuli, B);
+        {   // Target top-1 / top-3 of the host classes: first maximum, descending scores that are the labels' logits
+            const std::vector<int> top1 = dn.getEstimatedLabels(B, 1);
+            std::vector<int> scores3;
+            const std::vector<int> top3 = dn.getEstimatedLabels(B, 3, &scores3);
+            for (int b = 0; b < B; ++b) {
+                int am = 0;
+                for (int c = 1; c < n.classes; ++c)
+                    if (logits[(size_t)b * n.classes + c] > logits[(size_t)b * n.classes + am]) am = c;
+                if (top1[b] != am) { fprintf(stderr, "top-1 of image %d: %d, expected %d\n", b, top1[b], am); return 1; }
+                for (int k = 0; k < 3; ++k) {
+                    if (scores3[(size_t)b * 3 + k] != logits[(size_t)b * n.classes + top3[(size_t)b * 3 + k]]) return 1;
+                    if (k && scores3[(size_t)b * 3 + k] > scores3[(size_t)b * 3 + k - 1]) return 1;
+                }
+            }
+        }
         // the integer logits track the float ones: y_int ~ y_float / threshold * 127 (signed 8-bit output)
         const double scale = out_threshold / 127.0;
         double err = 0, norm = 0;

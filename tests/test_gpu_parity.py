@@ -69,8 +69,42 @@ def test_depthwise_3x3(case, mode):
     # the dot-product kernel (32-bit epilogue) and, with the exact-epilogue flag, the 64-bit kernel
     C, H, W, s, p, d, uns, act = case
     net = single_conv_net(C, H, W, C, 3, s, p, in_unsigned=uns, act=act, mode=mode, dil=d, groups=C)
-    compare_net(net, 3, want_engine='depthwise')
+    # layers with whole groups of 64 (or one of 32) channels, and stride-1 layers with groups of 32, run on the tensor
+    # cores as block-diagonal groups
+    on_tensor_cores = C % 64 == 0 or C == 32 or (s == 1 and C % 32 == 0)
+    # (fixed-point scalings with wide shifts have no 32-bit epilogue and stay on the exact CUDA-core kernel)
+    want = 'depthwise' if not on_tensor_cores else (('depthwise-tcgen05', 'depthwise') if mode == 'fixed' else 'depthwise-tcgen05')
+    compare_net(net, 3, want_engine=want)
+    compare_net(net, 3, flags=KEEP | R.FORCE_SIMT, want_engine='depthwise')
     compare_net(net, 3, flags=KEEP | R.EXACT64_EPILOGUE, want_engine='depthwise')
+
+
+# (C, H, W, k, pad, dilation, batch): depthwise layers as block-diagonal groups on the tensor cores - several bands
+# and images per CTA, more groups than fit the grid evenly, 5x5 and dilated filters, one group of 32
+# (C, H, W, k, stride, pad, dilation, batch): the strided ones through im2col loads of the group's channel slice
+DW_TC_STRIDED_CASES = [(64, 112, 112, 3, 2, 1, 1, 3), (128, 56, 56, 3, 2, 1, 1, 5), (256, 28, 28, 3, 2, 1, 1, 9),
+                       (512, 14, 14, 3, 2, 1, 1, 37), (1024, 9, 7, 3, 2, 1, 1, 4), (32, 30, 30, 3, 2, 1, 1, 3),
+                       (192, 17, 23, 5, 3, 2, 1, 3), (64, 40, 40, 3, 1, 0, 1, 2)]
+
+
+@pytest.mark.parametrize('case', DW_TC_STRIDED_CASES, ids=lambda c: 'C%d_%dx%d_k%d_s%d_p%d_d%d_b%d' % c)
+@pytest.mark.parametrize('mode', ['double', 'single'])
+def test_strided_depthwise_as_block_diagonal_groups(case, mode):
+    C, H, W, k, st, p, d, batch = case
+    net = single_conv_net(C, H, W, C, k, st, p, mode=mode, dil=d, groups=C)
+    compare_net(net, batch, want_engine='depthwise-tcgen05')
+
+
+DW_TC_CASES = [(128, 56, 56, 3, 1, 1, 5), (512, 14, 14, 3, 1, 1, 37), (1024, 7, 7, 3, 1, 1, 9), (32, 112, 112, 3, 1, 1, 3),
+               (96, 30, 17, 3, 1, 1, 4), (64, 20, 20, 5, 2, 1, 3), (192, 24, 24, 3, 2, 2, 3), (256, 28, 28, 3, 0, 1, 2)]
+
+
+@pytest.mark.parametrize('case', DW_TC_CASES, ids=lambda c: 'C%d_%dx%d_k%d_p%d_d%d_b%d' % c)
+@pytest.mark.parametrize('mode', ['double', 'single'])
+def test_depthwise_as_block_diagonal_groups_on_the_tensor_cores(case, mode):
+    C, H, W, k, p, d, batch = case
+    net = single_conv_net(C, H, W, C, k, 1, p, mode=mode, dil=d, groups=C)
+    compare_net(net, batch, want_engine='depthwise-tcgen05')
 
 
 # (C, H, W, O, k, stride, pad, input unsigned, builder keywords): layers the 256-row variant can take
@@ -294,7 +328,9 @@ SAT_CASES = [
     ('patch', lambda m: single_conv_net(64, 20, 17, 64, 3, 1, 1, mode=m), 'patch-tcgen05'),
     ('stem_s2d', lambda m: single_conv_net(3, 32, 32, 64, 7, 2, 3, mode=m), 'stem-tcgen05'),
     ('stem_gather', lambda m: single_conv_net(4, 17, 19, 64, 5, 1, 2, mode=m), 'stem-tcgen05'),
-    ('depthwise', lambda m: single_conv_net(32, 20, 20, 32, 3, 1, 1, mode=m, groups=32), 'depthwise'),
+    ('depthwise', lambda m: single_conv_net(48, 20, 20, 48, 3, 2, 1, mode=m, groups=48), 'depthwise'),
+    ('depthwise-tc-strided', lambda m: single_conv_net(128, 20, 20, 128, 3, 2, 1, mode=m, groups=128), 'depthwise-tcgen05'),
+    ('depthwise-tc', lambda m: single_conv_net(64, 20, 20, 64, 3, 1, 1, mode=m, groups=64), 'depthwise-tcgen05'),
     ('direct', lambda m: single_conv_net(3, 17, 13, 5, 3, 2, 1, mode=m), 'simt'),
 ]
 
@@ -308,7 +344,7 @@ def test_saturation_activation_on_every_kernel_family(case, mode):
     for thr in (50, 127):
         net = _saturating(build(mode), thr)
         # float scalings and wide fixed-point shifts take the exact 64-bit kernels, whatever the family
-        exact_only = mode == 'float' or (mode == 'fixed' and engine in ('stem-tcgen05', 'patch-tcgen05'))
+        exact_only = mode == 'float' or (mode == 'fixed' and engine in ('stem-tcgen05', 'patch-tcgen05', 'depthwise-tcgen05'))
         compare_net(net, 3, want_engine=None if exact_only else engine)
         compare_net(net, 3, flags=KEEP | R.FORCE_SIMT)
         ref = oracle.run_net(net, netdesc.make_input(net, 3), 'i64')[-1]
@@ -562,6 +598,9 @@ def test_output_edge_top_n_per_pixel_of_a_score_map():
         values = torch.zeros((B, top_n, H, W), dtype=torch.int32, device='cuda')
         qn.estimated_labels_topn(batch, top_n, labels.data_ptr(), values.data_ptr(), 0)
         qn.check(0)
+        # the host-buffer form returns the same arrays
+        host_l, host_v = qn.estimated_labels_topn_host(batch, top_n)
+        assert np.array_equal(host_l, labels.cpu().numpy()) and np.array_equal(host_v, values.cpu().numpy())
         got_l = labels.cpu().numpy().transpose(0, 2, 3, 1).reshape(B * H * W, top_n)
         got_v = values.cpu().numpy().transpose(0, 2, 3, 1).reshape(B * H * W, top_n)
         assert np.array_equal(got_v, want_v)
