@@ -223,7 +223,7 @@ static Stats collect_stats(DeepNet& dn, const FloatNet& n, const std::vector<flo
 }
 
 // CPU checks of the statistics-driven front-end
-static int stats_frontend()
+static int stats_frontend(const std::string& dir)
 {
     for (int variant = 0; variant < 2; ++variant) {
         const bool residual = variant == 1;
@@ -271,7 +271,6 @@ static int stats_frontend()
         CHECK(after.second <= before.second && after.first >= before.first);
         CHECK(after.second < before.second || after.first > before.first);
         // state files round-trip
-        const std::string dir = "/tmp";
         RangeStats::saveOutputsRange(dir + "/n2d2b_test_range.bin", st.range);
         Histogram::saveOutputsHistogram(dir + "/n2d2b_test_hist.bin", st.hist);
         std::unordered_map<std::string, RangeStats> r2;
@@ -384,7 +383,8 @@ int main(int argc, char** argv)
             return 0;
         }
         if (argc >= 2 && !strcmp(argv[1], "--stats")) {
-            if (int rc = stats_frontend()) return rc;
+            if (argc < 3) { fprintf(stderr, "--stats needs a scratch directory\n"); return 2; }
+            if (int rc = stats_frontend(argv[2])) return rc;
             printf("statistics front-end ok\n");
             return 0;
         }

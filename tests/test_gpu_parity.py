@@ -588,9 +588,10 @@ def test_output_edge_top_n_per_pixel_of_a_score_map():
     net = single_conv_net(16, 12, 10, 21, 3, 1, 1, mode='single', act='linear')
     batch, top_n = 4, 4
     x = netdesc.make_input(net, batch)
-    ref = oracle.run_net(net, x, 'i64')[-1]                      # [B][C][H][W]
-    B, Cn, H, W = ref.shape
-    want_l, want_v = oracle.estimated_labels_topn(ref.transpose(0, 2, 3, 1).reshape(B * H * W, Cn), top_n)
+    ref = oracle.run_net(net, x, 'i64')[-1]                      # [B][H][W][C]
+    B, H, W, Cn = ref.shape
+    assert (H, W, Cn) == (12, 10, 21)
+    want_l, want_v = oracle.estimated_labels_topn(ref.reshape(B * H * W, Cn), top_n)
     qn = runtime.QuantizedNet(net, batch)
     try:
         qn.forward_host(x)

@@ -48,7 +48,9 @@ def test_statistics_driven_front_end_on_cpu():
     """Ranges and histograms fed batch by batch, the thresholds quantizeActivations asks for (a max pooling's
     statistics stand for the cell above it), weight clipping, state files."""
     _build()
-    out = subprocess.run([EXE, '--stats'], capture_output=True, text=True)
+    scratch = os.path.join(ROOT, 'tests', 'host', '_tmp')
+    os.makedirs(scratch, exist_ok=True)
+    out = subprocess.run([EXE, '--stats', scratch], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
     assert 'statistics front-end ok' in out.stdout
 
