@@ -76,17 +76,37 @@ def per_gpu_batch(args, world):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event reasons while the timed region runs: NVML read-outs every few milliseconds
+    from a thread (read-only queries), or nvidia-smi in a loop where the NVML binding is missing."""
     FIELDS = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
               'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
               'clocks_event_reasons.sw_power_cap')
+    REASONS = (('hw_slowdown', 0x8), ('hw_thermal_slowdown', 0x40), ('sw_thermal_slowdown', 0x20), ('sw_power_cap', 0x4))
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
+        self.samples = []      # (time, sm MHz, max MHz, set of reasons)
         self.proc = None
+        self.nvml = None
+        self.stop_flag = False
 
     def start(self):
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = 'GPU-' + str(torch.cuda.get_device_properties(self.index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
@@ -96,28 +116,41 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                get = getattr(n, 'nvmlDeviceGetCurrentClocksEventReasons', None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = int(get(self.handle))
+                self.samples.append((time.time(), mhz, self.max_mhz, {name for name, bit in self.REASONS if mask & bit}))
+            except Exception:
+                pass
+            time.sleep(0.004)
+
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append((time.time(), line.strip()))
-
-    def stop(self, t0, t1):
-        if not self.proc:
-            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
-        time.sleep(0.15)
-        self.proc.terminate()
-        rows = [l for (t, l) in self.samples if t0 <= t <= t1 + 0.1] or [l for (_, l) in self.samples[-3:]]
-        sm, mx, reasons = [], [], set()
-        for l in rows:
-            p = [x.strip() for x in l.split(',')]
+            p = [x.strip() for x in line.split(',')]
             try:
-                sm.append(float(p[0])); mx.append(float(p[1]))
+                reasons = {name for (name, _), v in zip(self.REASONS, p[3:7]) if v.lower().startswith('active')}
+                self.samples.append((time.time(), float(p[0]), float(p[1]), reasons))
             except (ValueError, IndexError):
                 continue
-            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), p[3:7]):
-                if v.lower().startswith('active'):
-                    reasons.add(name)
-        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
-                'reasons': sorted(reasons), 'samples': len(sm)}
+
+    def stop(self, t0, t1):
+        if not self.proc and not self.nvml:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no clock read-out available']}
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+        self.stop_flag = True
+        rows = [r for r in self.samples if t0 <= r[0] <= t1] or self.samples[-3:]
+        reasons = set()
+        for r in rows:
+            reasons |= r[3]
+        sm = [r[1] for r in rows]
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(r[2] for r in rows) if rows else None,
+                'reasons': sorted(reasons), 'samples': len(sm), 'source': 'nvml' if self.nvml else 'nvidia-smi'}
 
 
 def measured_peaks():
