@@ -134,7 +134,6 @@ typedef struct n2d2b_tensor_info {
 #define N2D2B_FORCE_IM2COL 8u     /* tensor-core convolutions always load activations through the im2col map */
 #define N2D2B_EXACT64_EPILOGUE 16u /* tensor-core cells always use the 64-bit requantisation (cross-check of the 32-bit form) */
 #define N2D2B_FORCE_PAIR 32u      /* 256-row tiles wherever their structure allows, whatever the layer's size (tests) */
-#define N2D2B_RESIDUAL_TILES_128 128u /* cells with a fused residual sum take 128-column tiles (four accumulator stages) instead of 256-column ones (tuning switch) */
 #define N2D2B_FUSE_FIRST_POOL 64u /* a stride-2 first layer whose only reader is an unpadded max pooling writes the pooled tensor itself (its own output never reaches HBM); off by default: measured slower than the two kernels on one GPU */
 
 const char* n2d2b_last_error(void);

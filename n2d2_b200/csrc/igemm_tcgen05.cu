@@ -40,7 +40,6 @@ static constexpr int W4_UNPACK_WARPS = 4;     // extra warps of the packed-int4 
 
 struct IgemmArgs {
     int M, N, Cin, taps, BK, BN, stages, a_im2col;
-    unsigned nacc_mask, nacc_shift;   // TMEM accumulator stages - 1 (1 or 3: two stages of 256 columns, four of up to 128) and their log2
     int grouped;        // block-diagonal layer (depthwise as groups of BN channels): a column block reads its own input channels
     int res_slots;          // staging regions per epilogue warp of a residual cell (2 or 4)
     int m_base;         // first output row of this call within the tensors (a batch slice starts at image img0)
@@ -109,17 +108,17 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // cells with a fused residual keep two or four regions per warp so that the residual of the next tiles arrives early
     const int regions_per_warp = RES ? a.res_slots : 1;
     unsigned long long* bars = (unsigned long long*)(stage_out + NUM_EPI_WARPS * REGION_BYTES * regions_per_warp);
-    // bars: full[stages], empty[stages], tmem_full[4], tmem_empty[4], params_ready[2], residual[4 * NUM_EPI_WARPS],
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2], params_ready[2], residual[4 * NUM_EPI_WARPS],
     //       resident weights
     const unsigned full0 = smem_u32(bars);
     const unsigned empty0 = full0 + 8u * a.stages;
     const unsigned tfull0 = empty0 + 8u * a.stages;
-    const unsigned tempty0 = tfull0 + 32u;
-    const unsigned pready0 = tempty0 + 32u;
+    const unsigned tempty0 = tfull0 + 16u;
+    const unsigned pready0 = tempty0 + 16u;
     const unsigned rbar0 = pready0 + 16u;
     const unsigned bfull = rbar0 + 8u * (4 * NUM_EPI_WARPS);
     const unsigned bready0 = bfull + 16u;                                       // W4: expanded weights of a stage are in place
-    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 10 + 4 * NUM_EPI_WARPS + 2 + (W4 ? a.stages : 0));
+    unsigned* tmem_slot = (unsigned*)(bars + 2 * a.stages + 6 + 4 * NUM_EPI_WARPS + 2 + (W4 ? a.stages : 0));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // [2 buffers][2 quant sets][FAST_NP][256], 16-byte aligned for vector loads
     int* epi_params = (int*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);
@@ -133,11 +132,11 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(full0 + 8u * s, 1);
             mbar_init(empty0 + 8u * s, 1);
         }
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbar_init(tfull0 + 8u * s, 1);
             mbar_init(tempty0 + 8u * s, NUM_EPI_WARPS);
+            mbar_init(pready0 + 8u * s, NUM_EPI_WARPS);
         }
-        for (int s = 0; s < 2; ++s) mbar_init(pready0 + 8u * s, NUM_EPI_WARPS);
         for (int w = 0; w < 4 * NUM_EPI_WARPS; ++w) mbar_init(rbar0 + 8u * w, 1);
         mbar_init(bfull, 1);
         if (W4)
@@ -236,8 +235,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const unsigned b16 = (unsigned)(b_stage_bytes >> 4);
             unsigned a_lo = a_lo0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
-                const unsigned as = acc_it & a.nacc_mask;
-                const unsigned aph = (acc_it >> a.nacc_shift) & 1u;
+                const unsigned as = acc_it & 1u;
+                const unsigned aph = (acc_it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * as, aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + as * (unsigned)a.BN;
@@ -329,8 +328,8 @@ igemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             n_next += a.step_n;
             if (n_next >= a.num_n_tiles) { n_next -= a.num_n_tiles; ++m_next; }
             const int m0 = a.m_base + m_tile * BM, n0 = n_tile * a.BN;
-            const unsigned as = acc_it & a.nacc_mask;
-            const unsigned aph = (acc_it >> a.nacc_shift) & 1u;
+            const unsigned as = acc_it & 1u;
+            const unsigned aph = (acc_it >> 1) & 1u;
             if (FAST && n_tile != staged_n_tile) {
                 // stage this column block's per-channel constants (once per CTA when the grid is a
                 // multiple of the number of column blocks).  Two buffers: the other one may still be
@@ -730,7 +729,7 @@ static size_t igemm_smem_bytes(int stages, int BK, int BN, int regions, size_t r
 {
     return 1024 /*alignment slack*/ + resident_b + (size_t)stages * ((BM + (resident_b ? 0 : BN)) * BK + (w4 ? BN * BK / 2 : 0))
          + NUM_EPI_WARPS * REGION_BYTES * regions
-         + (2 * stages + 12 + 4 * NUM_EPI_WARPS + (w4 ? stages : 0)) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
+         + (2 * stages + 8 + 4 * NUM_EPI_WARPS + (w4 ? stages : 0)) * 8 + 32 + 2 * 2 * FAST_NP * 256 * 4 + 64;
 }
 
 // Channels per block-diagonal group of a depthwise layer this kernel takes (0: not such a layer): groups of 64
@@ -960,11 +959,7 @@ cudaError_t launch_igemm(const IgemmPlan& plan, const QuantDev& q, const Residua
     // instruction descriptor: D = s32, A = u8/s8, B = s8, both K-major, N and M extents
     a.idesc = (2u << 4) | ((plan.a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((unsigned)(plan.BN >> 3) << 17)
             | ((unsigned)(BM >> 4) << 24);
-    // accumulator stages: all 512 TMEM columns for tiles of 128 or 256 columns, 256 of them for 64-column tiles
-    const unsigned nacc = plan.BN <= 128 ? 4u : 2u;
-    a.nacc_mask = nacc - 1u;
-    a.nacc_shift = nacc == 4u ? 2u : 1u;
-    unsigned cols = nacc * plan.BN;
+    unsigned cols = 2u * plan.BN;
     unsigned p2 = 32;
     while (p2 < cols) p2 <<= 1;
     a.tmem_cols = p2;

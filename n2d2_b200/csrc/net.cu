@@ -1074,9 +1074,8 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
             const void* out_ptr = c.pad_O ? c.d_colpad
                                 : net->tensors[c.output].dtype == DT_I8 ? tensor_ptr(net, c.output, nullptr) : nullptr;
             const void* res_ptr = c.residual >= 0 ? tensor_ptr(net, c.residual, nullptr) : nullptr;
-            const int force_bn = (res_ptr && (flags & N2D2B_RESIDUAL_TILES_128) && gb.O >= 128) ? 128 : 0;
             int planned = igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
-                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, force_bn, net->num_sms, &why,
+                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
                                           (flags & N2D2B_FORCE_PAIR) ? 1 : 0, w4 ? 1 : 0);
             if (planned != 0 && w4) {
                 // no room for the packed variant: widen the weights after all
@@ -1088,7 +1087,7 @@ int n2d2b_net_finalize(n2d2b_net* net, int max_batch, unsigned flags)
                 CUDA_TRY(cudaMemset(c.d_weights, 0, laid.size() + 256));
                 CUDA_TRY(cudaMemcpy(c.d_weights, laid.data(), laid.size(), cudaMemcpyHostToDevice));
                 planned = igemm_make_plan(&c.plan, enc_ptr, c.d_weights, out_ptr, res_ptr, gb, net->tensors[c.inputs[0]].is_unsigned,
-                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, force_bn, net->num_sms, &why,
+                                          (flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
                                           (flags & N2D2B_FORCE_PAIR) ? 1 : 0, 0);
             }
             if (planned == 0) {
@@ -1234,7 +1233,7 @@ static int run_cell(n2d2b_net* net, CellRec& c, const void* d_input, int batch, 
             const char* why = "";
             const int perm = c.plan.perm, w4 = c.plan.w4;   // properties of the stored weights, not of the tensor maps
             if (igemm_make_plan(&c.plan, in0, c.d_weights, tout.dtype == DT_I8 ? gemm_out : nullptr, r.ptr, gb, tin.is_unsigned,
-                                (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, c.plan.BN, net->num_sms, &why,
+                                (net->flags & N2D2B_FORCE_IM2COL) ? 1 : 0, 0, net->num_sms, &why,
                                 (net->flags & N2D2B_FORCE_PAIR) ? 1 : 0, w4))
                 return fail(N2D2B_ERR_INVALID, "tensor-core plan failed: %s", why);
             c.plan.perm = perm;

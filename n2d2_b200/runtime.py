@@ -23,7 +23,6 @@ FORCE_IM2COL = 8
 FORCE_PAIR = 32
 EXACT64_EPILOGUE = 16
 FUSE_FIRST_POOL = 64
-RESIDUAL_TILES_128 = 128
 
 
 class N2D2BError(RuntimeError):
