@@ -15,8 +15,8 @@
 //
 // Roles as in the patch kernel: warp 0 loads (weights once, bands double-buffered), warps 1-2 issue
 // tcgen05.mma kind::i8 for alternate tiles into a ring of four TMEM accumulators, four groups of four
-// epilogue warps each drain every fourth 128-position tile (32-bit requantisation in the fragment layout, swizzled staging, one
-// 16-byte-vector copy per pixel row to the NHWC output).  Positions in the halo columns (x >= oW) compute
+// epilogue warps each drain every fourth 128-position tile (32-bit requantisation in the fragment layout, the bytes going
+// from the registers straight to the NHWC output, eight consecutive channels per lane).  Positions in the halo columns (x >= oW) compute
 // values nobody stores.  Every wait is bounded.
 //
 // POOL variant: the layer is followed by a max pooling (k x k window, stride s, no padding) and nothing else reads
@@ -277,7 +277,6 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
-        const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
         const unsigned swz_mask = (unsigned)(a.BN / 16 - 1);
         unsigned seq = 0;
         int n = (int)blockIdx.x / a.bands, band = (int)blockIdx.x % a.bands;
@@ -347,64 +346,39 @@ stem_s2d_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const S2dArgs a
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
             const int rows = band_rows(band);
             const int T = band_tiles(band);
+            uint8_t* const band_out = (uint8_t*)a.out + ((size_t)n * a.oH + (size_t)(band * a.R)) * a.oW * a.N;
             for (int t = 0; t < T; ++t, ++seq) {
                 if ((int)(seq & (Z_SLOTS - 1)) != group) continue;
                 const unsigned sph = (seq / Z_SLOTS) & 1u;
                 if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
-                if (a.wide) {
-                    if (a.out_unsigned) s2d_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
-                    else s2d_drain<false, EF_WIDE>(tbase, par_off, region_off, a.BN, lane);
-                } else if (a.out_unsigned) s2d_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, a.BN, lane);
-                else s2d_drain<CLAMP, 0>(tbase, par_off, region_off, a.BN, lane);
-                // the accumulator is drained: hand it back, then copy this warp's 32 rows out
+                // This lane's four rows of the fragment (positions of the band's raster) and where they go: the bytes leave
+                // the registers for global memory directly, eight channels per lane, a 32-byte sector per four lanes
+                unsigned rowoff[4];   // byte offsets within the band: below 2^32
+                unsigned rowok = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const unsigned p = (unsigned)(t * ZBM + quad * 32 + (lane >> 2) + 8 * k);
+                    const unsigned yy = __umulhi(p, a.rcp_Wp);
+                    const unsigned x = p - yy * (unsigned)a.Wp;
+                    if (x < (unsigned)a.oW && yy < (unsigned)rows) rowok |= 1u << k;
+                    rowoff[k] = (yy * (unsigned)a.oW + x) * (unsigned)a.N;
+                }
+#pragma unroll 1
+                for (int cb = 0; cb < a.N; cb += 32) {
+                    unsigned va[16], vb[16];
+                    tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
+                    if (a.wide) {
+                        if (a.out_unsigned) perm_block_global<false, EF_WIDE | EF_OUT_UNSIGNED>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                        else perm_block_global<false, EF_WIDE>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                    } else if (a.out_unsigned) perm_block_global<CLAMP, EF_OUT_UNSIGNED>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                    else perm_block_global<CLAMP, 0>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                }
+                // the accumulator is drained: hand it back
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8u * group);
-                // Copy the warp's 32 rows out in 16-byte units, consecutive lanes on consecutive units of a pixel and
-                // then on the next pixel: a store instruction covers whole contiguous runs of the NHWC output.
-                const int nch = a.N >> 4;                       // 16-byte units per pixel
-                const unsigned pix0 = (unsigned)(t * ZBM + quad * 32);
-                if ((nch & (nch - 1)) == 0) {
-                    // four units per lane at a time: the shared-memory loads first, then the stores, so that neither
-                    // waits for the other
-                    const int lg = 31 - __clz(nch);
-                    uint8_t* const img_out = (uint8_t*)a.out + ((size_t)n * a.oH + (size_t)(band * a.R)) * a.oW * a.N;
-                    for (int u0 = lane; u0 < 32 * nch; u0 += 128) {
-                        uint4 v[4];
-                        unsigned off[4];
-                        bool live[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int u = u0 + 32 * j;
-                            const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
-                            const unsigned p = pix0 + r;            // position within the band
-                            const unsigned yy = __umulhi(p, a.rcp_Wp);
-                            const unsigned x = p - yy * (unsigned)a.Wp;
-                            live[j] = u < 32 * nch && x < (unsigned)a.oW && yy < (unsigned)rows;
-                            off[j] = (yy * (unsigned)a.oW + x) * (unsigned)a.N + c * 16u;   // within the band: below 2^32
-                            const unsigned ro = r * (unsigned)a.BN;
-                            const unsigned xm = (ro >> 7) & swz_mask;
-                            if (live[j]) v[j] = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (live[j]) *(uint4*)(img_out + off[j]) = v[j];
-                    }
-                } else {
-                    const unsigned p = pix0 + (unsigned)lane;
-                    const unsigned yy = __umulhi(p, a.rcp_Wp);
-                    const unsigned x = p - yy * (unsigned)a.Wp;
-                    if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                        uint8_t* dst = (uint8_t*)a.out + ((((size_t)n * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.N);
-                        const unsigned ro = (unsigned)(lane * a.BN);
-                        const unsigned xm = (ro >> 7) & swz_mask;
-                        for (int c = 0; c < nch; ++c)
-                            *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
-                    }
-                }
-                __syncwarp();   // the region is rewritten by the next tile of this group
             }
             n += step_n;
             band += step_b;

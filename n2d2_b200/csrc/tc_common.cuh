@@ -651,6 +651,57 @@ __device__ __forceinline__ void perm_block(const unsigned* vA, const unsigned* v
     }
 }
 
+// The same block (no residual) written straight to global memory: with the permuted layout a thread holds eight
+// consecutive channels of a row, four neighbouring lanes a whole 32-byte sector of it, so the bytes need no detour
+// through a staging region when the rows' addresses have no regular pattern a TMA store could follow (the band
+// kernels, whose rows are pixels of a padded raster).  out + rowoff[k] = address of channel pcol0's byte of row tr + 8k
+// in the output, rowok bit k = that row exists.
+template <bool CLAMP, int EF>
+__device__ __forceinline__ void perm_block_global(const unsigned* vA, const unsigned* vB, unsigned par_off, int pcol0,
+                                                  uint8_t* out, const unsigned (&rowoff)[4], unsigned rowok, int lane)
+{
+    unsigned char* const sm = dyn_smem();
+    constexpr int NK = 4, NH = 2;
+    unsigned outw[NK][NH];
+    const unsigned pbase = par_off + (unsigned)(pcol0 + 8 * (lane & 3)) * 4u;
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        const unsigned pp = pbase + 16u * h;
+        const int4 mu = *(const int4*)(sm + pp + 2 * 1024);
+        const int4 ad = *(const int4*)(sm + pp + 3 * 1024);
+        const int4 sh = *(const int4*)(sm + pp + 4 * 1024);
+        int4 lo = make_int4(0, 0, 0, 0), hi = lo;
+        if (CLAMP) {
+            lo = *(const int4*)(sm + pp + 0 * 1024);
+            hi = *(const int4*)(sm + pp + 1 * 1024);
+        } else if (EF & EF_WIDE) {
+            lo = *(const int4*)(sm + pp + 0 * 1024);
+        }
+        const int muv[4] = {mu.x, mu.y, mu.z, mu.w}, adv[4] = {ad.x, ad.y, ad.z, ad.w}, shv[4] = {sh.x, sh.y, sh.z, sh.w};
+        const int lov[4] = {lo.x, lo.y, lo.z, lo.w}, hiv[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            const unsigned* v = (k < 2) ? vA : vB;
+            int y[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                int x = (int)v[4 * (2 * h + (c >> 1)) + 2 * (k & 1) + (c & 1)];
+                if (CLAMP) x = min(max(x, lov[c]), hiv[c]);
+                if (EF & EF_WIDE) {
+                    const long long p = (long long)x * muv[c] + (long long)(((unsigned long long)(unsigned)lov[c] << 32) | (unsigned)adv[c]);
+                    y[c] = (int)(p >> shv[c]);
+                } else {
+                    y[c] = (x * muv[c] + adv[c]) >> shv[c];
+                }
+            }
+            outw[k][h] = pack4_sat(y[0], y[1], y[2], y[3], (EF & EF_OUT_UNSIGNED) != 0);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NK; ++k)
+        if (rowok & (1u << k)) *(uint2*)(out + rowoff[k] + 8 * (lane & 3)) = make_uint2(outw[k][0], outw[k][1]);
+}
+
 // One accumulator tile through the fragment-layout epilogue: residual slice in by TMA (issued one tile
 // ahead when the warp has two staging regions), accumulator slice out of TMEM, requantisation into the
 // swizzled staging region, TMA store.  A warp owns the 32 rows of its TMEM quadrant `quad` and the column
