@@ -255,7 +255,7 @@ public:
     void reportOutputsHistogram(std::unordered_map<std::string, Histogram>& outputsHistogram,
                                 const std::unordered_map<std::string, RangeStats>& outputsRange, const std::string& cellName,
                                 const Float_T* outputs, std::size_t count, std::size_t nbBits, ClippingMode actClippingMode,
-                                bool envDataUnsigned = true) const
+                                bool envDataUnsigned = DeepNetExport::mEnvDataUnsigned()) const
     {
         if (actClippingMode == ClippingMode::NONE) return;
         if (outputsHistogram.empty()) {
