@@ -18,8 +18,8 @@
 //
 // Warp 0 loads (weights once, patches double-buffered), warps 1-2 issue tcgen05.mma kind::i8 for alternate
 // tiles into a ring of four TMEM accumulators, and four groups of four epilogue warps (one warp per TMEM lane quadrant) each
-// drain every fourth tile: 32-bit requantisation in the fragment layout into a swizzled staging region,
-// then one 16-byte-vector copy per pixel row to the NHWC output.  Every wait is bounded.
+// drain every fourth tile: 32-bit requantisation in the fragment layout, the bytes going from the registers straight to
+// the NHWC output (eight consecutive channels per lane).  Every wait is bounded.
 #include <cstring>
 #include <atomic>
 #include "kernels.h"
@@ -59,22 +59,6 @@ struct PatchArgs {
     int out_unsigned;
     int wide;               // 64-bit first rescale (see EF_WIDE)
 };
-
-// Columns [c0, c0 + ncols) of a warp's 32 accumulator rows into its staging region (rows of ncols bytes)
-template <bool CLAMP, int EF>
-__device__ __forceinline__ void patch_drain(unsigned tbase, unsigned par_off, unsigned region_off, int c0, int ncols, int lane)
-{
-    // the caller stores the weight rows permuted inside blocks of 32 output channels (patch_permute_weights): a
-    // thread's columns of the fragment are eight consecutive channels (see perm_block)
-    unsigned rb[4];
-    perm_rowbase(rb, ncols, lane, 4);
-#pragma unroll 1
-    for (int cb = 0; cb < ncols; cb += 32) {
-        unsigned va[16], vb[16];
-        tc_ld_2x16x256b_x4_wait(tbase + (unsigned)(c0 + cb), va, vb);
-        perm_block<4, false, CLAMP, false, EF | EF_PERM>(va, vb, par_off, c0 + cb, region_off, rb, cb, lane, 0, 0, 0u);
-    }
-}
 
 // The MMAs of one tile with compile-time tap counts: a straight run of address adds and MMAs.  The issuing
 // thread pays the latency of every instruction it executes, so loop control and address arithmetic around a
@@ -312,9 +296,6 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         const int quad = warp & 3;          // TMEM lane quadrant this warp may read
         const int group = ew >> 2;          // drains the tiles whose sequence number is `group` modulo 4
         const unsigned par_off = (unsigned)((unsigned char*)par - smem_raw);
-        const unsigned region_off = (unsigned)(stage_out - smem_raw) + (unsigned)(ew * region_bytes);
-        const int SC = a.stage_cols;
-        const unsigned swz_mask = (unsigned)(SC / 16 - 1);
         unsigned seq = 0;
         int n = cta / a.bands, band = cta % a.bands;
         const int step_n = nctas / a.bands, step_b = nctas % a.bands;
@@ -322,61 +303,39 @@ patch_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         for (int item = cta; item < items && ok; item += nctas) {
             const int rows = band_rows(band);
             const int T = band_tiles(band);
+            uint8_t* const band_out = (uint8_t*)a.out + ((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R)) * a.oW * a.ldo + ch0;
             for (int t = 0; t < T; ++t, ++seq) {
                 if ((int)(seq & (P_SLOTS - 1)) != group) continue;
                 const unsigned sph = (seq / P_SLOTS) & 1u;
                 if (!mbar_wait_warp(tfull0 + 8u * group, sph, abort_flag, a.status, 4, lane)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned tbase = tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(group * a.BN);
-                const unsigned pix0 = (unsigned)(t * PBM + quad * 32);
-                // stage_cols columns per pass: drained into the staging region, then copied out
-#pragma unroll 1
-                for (int c0 = 0; c0 < a.BN; c0 += SC) {
-                    if (a.wide) {
-                        if (a.out_unsigned) patch_drain<false, EF_WIDE | EF_OUT_UNSIGNED>(tbase, par_off, region_off, c0, SC, lane);
-                        else patch_drain<false, EF_WIDE>(tbase, par_off, region_off, c0, SC, lane);
-                    } else if (a.out_unsigned) patch_drain<CLAMP, EF_OUT_UNSIGNED>(tbase, par_off, region_off, c0, SC, lane);
-                    else patch_drain<CLAMP, 0>(tbase, par_off, region_off, c0, SC, lane);
-                    if (c0 + SC >= a.BN) {
-                        // the accumulator is drained: hand it back before the last copy
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty0 + 8u * group);
-                    } else {
-                        __syncwarp();
-                    }
-                    // Copy the warp's 32 rows out in 16-byte units, consecutive lanes on consecutive units of a pixel and
-                    // then on the next pixel: a store instruction covers whole contiguous runs of the NHWC output.
-                    const int left = a.N - c0;
-                    const int nch = (left < SC ? left : SC) >> 4;   // 16-byte units per pixel in this pass
-                    if (nch > 0 && (nch & (nch - 1)) == 0) {
-                        const int lg = 31 - __clz(nch);
-                        for (int u = lane; u < 32 * nch; u += 32) {
-                            const unsigned r = (unsigned)u >> lg, c = (unsigned)u & (unsigned)(nch - 1);
-                            const unsigned p = pix0 + r;            // position within the band
-                            const unsigned yy = __umulhi(p, a.rcp_Wp);
-                            const unsigned x = p - yy * (unsigned)a.Wp;
-                            if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                                uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.ldo) + ch0 + c0;
-                                const unsigned ro = r * (unsigned)SC;
-                                const unsigned xm = (ro >> 7) & swz_mask;
-                                *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + ((c ^ xm) << 4));
-                            }
-                        }
-                    } else if (nch > 0) {
-                        const unsigned p = pix0 + (unsigned)lane;
-                        const unsigned yy = __umulhi(p, a.rcp_Wp);
-                        const unsigned x = p - yy * (unsigned)a.Wp;
-                        if (x < (unsigned)a.oW && yy < (unsigned)rows) {
-                            uint8_t* dst = (uint8_t*)a.out + ((((size_t)(a.n_base + n) * a.oH + (size_t)(band * a.R) + yy) * a.oW + x) * a.ldo) + ch0 + c0;
-                            const unsigned ro = (unsigned)(lane * SC);
-                            const unsigned xm = (ro >> 7) & swz_mask;
-                            for (int c = 0; c < nch; ++c)
-                                *(uint4*)(dst + c * 16) = *(const uint4*)(dyn_smem() + region_off + ro + (((unsigned)c ^ xm) << 4));
-                        }
-                    }
-                    __syncwarp();   // the region is rewritten by the next pass or tile
+                // This lane's four rows of the fragment (positions of the band's raster) and where they go: the bytes leave
+                // the registers for global memory directly, eight channels per lane, a 32-byte sector per four lanes
+                unsigned rowoff[4];   // byte offsets within the band: below 2^32
+                unsigned rowok = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const unsigned p = (unsigned)(t * PBM + quad * 32 + (lane >> 2) + 8 * k);
+                    const unsigned yy = __umulhi(p, a.rcp_Wp);
+                    const unsigned x = p - yy * (unsigned)a.Wp;
+                    if (x < (unsigned)a.oW && yy < (unsigned)rows) rowok |= 1u << k;
+                    rowoff[k] = (yy * (unsigned)a.oW + x) * (unsigned)a.ldo;
                 }
+#pragma unroll 1
+                for (int cb = 0; cb < a.N; cb += 32) {
+                    unsigned va[16], vb[16];
+                    tc_ld_2x16x256b_x4_wait(tbase + (unsigned)cb, va, vb);
+                    if (a.wide) {
+                        if (a.out_unsigned) perm_block_global<false, EF_WIDE | EF_OUT_UNSIGNED>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                        else perm_block_global<false, EF_WIDE>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                    } else if (a.out_unsigned) perm_block_global<CLAMP, EF_OUT_UNSIGNED>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                    else perm_block_global<CLAMP, 0>(va, vb, par_off, cb, band_out + cb, rowoff, rowok, lane);
+                }
+                // the accumulator is drained: hand it back
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8u * group);
             }
             n += step_n;
             band += step_b;
