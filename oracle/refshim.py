@@ -110,3 +110,28 @@ def run_net(net, x_nhwc):
         outs[idx] = y
         res.append(np.transpose(np.rint(y).astype(np.int64), (0, 2, 3, 1)))
     return res
+
+
+# ---- the reference's Target top-N CUDA kernel (src/Target/Target_CUDA_kernels.cu), GPU boxes only -------------------
+TARGET_SO = os.path.join(_HERE, '_ref', 'libn2d2_targetshim.so')
+_TARGET_LIB = None
+
+
+def target_available():
+    return os.path.exists(TARGET_SO)
+
+
+def estimated_target(scores_nchw, top_n):
+    """cudaGetEstimatedTarget of the reference on float scores [batch][class][y][x] (run on the current GPU):
+    returns (labels int32, values float32), each [batch][top_n][y][x]."""
+    global _TARGET_LIB
+    if _TARGET_LIB is None:
+        _TARGET_LIB = C.CDLL(TARGET_SO)
+    s = np.ascontiguousarray(scores_nchw, np.float32)
+    B, Cn, H, W = s.shape
+    labels = np.zeros((B, top_n, H, W), np.int32)
+    values = np.zeros((B, top_n, H, W), np.float32)
+    rc = _TARGET_LIB.refshim_estimated_target(top_n, Cn, H, W, B, _p(s), _p(values), _p(labels))
+    if rc != 0:
+        raise RuntimeError(f'refshim_estimated_target failed ({rc})')
+    return labels, values

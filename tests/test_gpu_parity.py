@@ -608,3 +608,49 @@ def test_output_edge_top_n_per_pixel_of_a_score_map():
         assert np.array_equal(got_l, want_l)
     finally:
         qn.close()
+
+
+def _identity_scores_net(classes, H, W):
+    """A network whose final tensor is its (signed 8-bit) input: a 1x1 convolution with identity weights, no bias and
+    a shift of zero."""
+    net = single_conv_net(classes, H, W, classes, 1, 1, 0, in_unsigned=False, act='linear', mode='single', bias=False)
+    l = net['layers'][0]
+    l['weights'] = np.eye(classes, dtype=np.int8).reshape(classes, 1, 1, classes)
+    l['bias'] = None
+    l['quant']['shift0'] = np.zeros(classes, np.uint8)
+    l['quant']['out_unsigned'] = False
+    return net
+
+
+@pytest.mark.parametrize('classes,top_n,hw', [(1000, 5, (1, 1)), (10, 10, (1, 1)), (21, 4, (12, 10)), (150, 3, (5, 7))])
+def test_top_n_order_against_the_reference_kernel_itself(classes, top_n, hw):
+    # The reference's cudaGetEstimatedTarget kernel, compiled from the reference tree where that tree is, run here on
+    # int8-like scores full of ties: the oracle's literal replay of its sort and the device's closed form must both
+    # return its labels.
+    from oracle import refshim
+    if not refshim.target_available():
+        pytest.skip('the reference tree was not compiled for this machine')
+    import torch
+    H, W = hw
+    rng = np.random.default_rng(classes * 7 + top_n)
+    B = 6
+    levels = 9 if classes > 100 else 5                       # few score levels: ties in every top-N
+    scores = rng.integers(-levels, levels + 1, (B, H, W, classes)).astype(np.int64)
+    ref_l, ref_v = refshim.estimated_target(scores.transpose(0, 3, 1, 2).astype(np.float32), top_n)
+    ora_l, ora_v = oracle.estimated_labels_topn(scores.reshape(B * H * W, classes), top_n)
+    ora_l = ora_l.reshape(B, H, W, top_n).transpose(0, 3, 1, 2)
+    ora_v = ora_v.reshape(B, H, W, top_n).transpose(0, 3, 1, 2)
+    assert np.array_equal(ref_v.astype(np.int64), ora_v)
+    assert np.array_equal(ref_l, ora_l)
+    # the device entry point works on a network's final tensor: a 1x1 convolution that copies its input (identity
+    # weights, unit scaling) puts exactly these scores there
+    net = _identity_scores_net(classes, H, W)
+    qn = runtime.QuantizedNet(net, B)
+    try:
+        out = qn.forward_host(scores.astype(np.int8))
+        assert np.array_equal(out.reshape(B, H, W, classes).astype(np.int64), scores)
+        got_l, got_v = qn.estimated_labels_topn_host(B, top_n)
+        assert np.array_equal(got_v.astype(np.int64), ora_v)
+        assert np.array_equal(got_l, ref_l)
+    finally:
+        qn.close()
