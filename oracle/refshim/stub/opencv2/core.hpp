@@ -19,9 +19,23 @@
 #define CV_32FC1 CV_MAKETYPE(CV_32F, 1)
 #define CV_64FC1 CV_MAKETYPE(CV_64F, 1)
 namespace cv {
+struct Point { int x, y; };
+struct Rect {
+    Rect();
+    Rect(int x, int y, int width, int height);
+    Point tl() const;
+    Point br() const;
+    int x, y, width, height;
+};
+struct Scalar {
+    Scalar();
+    Scalar(double v0, double v1 = 0, double v2 = 0, double v3 = 0);
+    double val[4];
+};
 class Mat {
 public:
     Mat();
+    Mat operator()(const Rect& roi) const;
     Mat(int rows, int cols, int type);
     Mat(int rows, int cols, int type, void* data, std::size_t step = 0);
     Mat(const Mat&);

@@ -193,6 +193,56 @@ static int graph_rewrite()
     return 0;
 }
 
+// The committed vectors of the reference's own approximateScalingWithPowerOf2Divs / approximateScalingWithFixedPoint
+// (tests/golden/quantization_golden.txt, written by tests/golden/make_quantization_golden.py): every value must be equal
+static int golden(const char* path)
+{
+    typedef DeepNetQuantization Q;
+    FILE* f = fopen(path, "r");
+    if (!f) { fprintf(stderr, "cannot open %s\n", path); return 2; }
+    char line[8192];
+    int cases = 0;
+    while (fgets(line, sizeof line, f)) {
+        if (line[0] == '#' || line[0] == '\n') continue;
+        char* bar = strchr(line, '|');
+        if (!bar) { fclose(f); return 2; }
+        *bar = 0;
+        std::vector<std::string> in, out;
+        for (char* t = strtok(line, " \n"); t; t = strtok(nullptr, " \n")) in.push_back(t);
+        for (char* t = strtok(bar + 1, " \n"); t; t = strtok(nullptr, " \n")) out.push_back(t);
+        if (in[0] == "p2") {
+            const float scaling = (float)strtod(in[1].c_str(), nullptr);
+            const std::size_t nb = (std::size_t)atoi(in[2].c_str());
+            const auto r = Q::approximateScalingWithPowerOf2Divs(scaling, nb);
+            bool ok = r.second == strtod(out[0].c_str(), nullptr) && r.first.size() == nb && out.size() == nb + 1;
+            for (std::size_t i = 0; ok && i < nb; ++i) ok = r.first[i] == (unsigned char)atoi(out[1 + i].c_str());
+            if (!ok) { fprintf(stderr, "power-of-two case %s x%zu differs: precision %a\n", in[1].c_str(), nb, r.second); fclose(f); return 1; }
+        } else if (in[0] == "fx") {
+            ScalingMode mode = atoi(in[1].c_str()) == 2 ? ScalingMode::FIXED_MULT16 : ScalingMode::FIXED_MULT32;
+            std::vector<Float_T> sc;
+            for (std::size_t i = 2; i < in.size(); ++i) sc.push_back((Float_T)strtod(in[i].c_str(), nullptr));
+            const int wantFrac = atoi(out[0].c_str());
+            bool threw = false;
+            std::pair<std::size_t, std::vector<std::int32_t> > r;
+            try { r = Q::approximateScalingWithFixedPoint(mode, sc); } catch (const std::runtime_error&) { threw = true; }
+            bool ok = threw == (wantFrac < 0);
+            if (ok && !threw) {
+                ok = (int)r.first == wantFrac && (int)(mode == ScalingMode::FIXED_MULT16 ? 2 : 3) == atoi(out[1].c_str())
+                     && r.second.size() == sc.size() && out.size() == sc.size() + 2;
+                for (std::size_t i = 0; ok && i < sc.size(); ++i) ok = r.second[i] == (std::int32_t)atoll(out[2 + i].c_str());
+            }
+            if (!ok) { fprintf(stderr, "fixed-point case differs (mode %s, first scaling %s)\n", in[1].c_str(), in[2].c_str()); fclose(f); return 1; }
+        } else {
+            fclose(f);
+            return 2;
+        }
+        ++cases;
+    }
+    fclose(f);
+    printf("%d golden cases ok\n", cases);
+    return cases > 0 ? 0 : 2;
+}
+
 // Calibration statistics of one float run, fed the way a caller's float framework would (two passes: ranges, then
 // histograms over those ranges)
 struct Stats {
@@ -382,6 +432,7 @@ int main(int argc, char** argv)
             printf("known answers ok\n");
             return 0;
         }
+        if (argc >= 3 && !strcmp(argv[1], "--golden")) return golden(argv[2]);
         if (argc >= 2 && !strcmp(argv[1], "--stats")) {
             if (argc < 3) { fprintf(stderr, "--stats needs a scratch directory\n"); return 2; }
             if (int rc = stats_frontend(argv[2])) return rc;

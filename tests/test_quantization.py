@@ -63,3 +63,14 @@ def test_networks_quantized_from_calibration_statistics(mode, per_channel, clip)
     _build()
     out = subprocess.run([EXE, '--run', mode, str(per_channel), str(clip)], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_scaling_approximations_equal_the_reference_on_committed_vectors():
+    """approximateScalingWithPowerOf2Divs / approximateScalingWithFixedPoint against vectors produced by the reference's
+    own functions (tests/golden/make_quantization_golden.py): exponents, precisions, fractional bits and fixed-point
+    scalings bit for bit, including the fall-back from 16 to 32 bits and the case the reference rejects."""
+    _build()
+    out = subprocess.run([EXE, '--golden', os.path.join(ROOT, 'tests', 'golden', 'quantization_golden.txt')],
+                         capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert 'golden cases ok' in out.stdout
