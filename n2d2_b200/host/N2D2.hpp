@@ -344,6 +344,16 @@ public:
         if (mBiases.size() != mNbOutputs) mBiases.assign(mNbOutputs, 0);
         mBiases[output] = value;
     }
+    // Sparse connection map of the cell (the `mapping` argument of Cell::addInput and Cell::isConnection,
+    // include/Cell/Cell.hpp; the reference's ini files write it as Mapping(...)): mapping[output * nbChannels + channel]
+    // says whether the channel feeds the output.  The reference's kernels skip unconnected channels
+    // (src/Cell/ConvCell_Frame_Kernels.cpp:93-96); here their weights are zero in the dense layer the device runs,
+    // which gives the same integers.  Only without groups.
+    void setMapping(const std::vector<bool>& mapping) { mMapping = mapping; }
+    bool isConnection(unsigned int channel, unsigned int output) const
+    {
+        return mMapping.empty() || mMapping[(std::size_t)output * mNbChannels + channel];
+    }
     const std::vector<std::int8_t>& getWeights() const { return mWeights; }
     const std::vector<std::int32_t>& getBiases() const { return mBiases; }
     void roundFreeParameters(std::size_t nbBits) override { roundInto(nbBits, mWeights, mBiases); }
@@ -362,6 +372,7 @@ private:
     std::vector<int> mPaddingDims;
     std::vector<unsigned int> mDilationDims;
     unsigned int mGroups = 1;
+    std::vector<bool> mMapping;
     std::vector<std::int8_t> mWeights;
     std::vector<std::int32_t> mBiases;
 };
@@ -772,12 +783,16 @@ private:
             // OIHW (reference memory order) -> OHWI (kernel order)
             const std::size_t cg = in.c / conv->mGroups, kh = d.kernel_h, kw = d.kernel_w, O = d.nb_outputs;
             if (conv->mWeights.size() != O * cg * kh * kw) throw std::runtime_error("ConvCell " + cell->getName() + ": wrong number of weights");
+            if (!conv->mMapping.empty() && (conv->mGroups != 1 || conv->mMapping.size() != O * cg))
+                throw std::runtime_error("ConvCell " + cell->getName() + ": a connection map needs nbOutputs x nbChannels entries and no groups");
             std::vector<std::int8_t> ohwi(conv->mWeights.size());
             for (std::size_t o = 0; o < O; ++o)
-                for (std::size_t c = 0; c < cg; ++c)
+                for (std::size_t c = 0; c < cg; ++c) {
+                    const bool connected = conv->mMapping.empty() || conv->mMapping[o * cg + c];
                     for (std::size_t y = 0; y < kh; ++y)
                         for (std::size_t x = 0; x < kw; ++x)
-                            ohwi[((o * kh + y) * kw + x) * cg + c] = conv->mWeights[((o * cg + c) * kh + y) * kw + x];
+                            ohwi[((o * kh + y) * kw + x) * cg + c] = connected ? conv->mWeights[((o * cg + c) * kh + y) * kw + x] : 0;
+                }
             check(n2d2b_net_add_conv(mNet, &d, ohwi.data(), conv->mBiases.empty() ? nullptr : conv->mBiases.data(), &q, &id));
         } else if (auto* fc = dynamic_cast<FcCell*>(cell.get())) {
             const std::size_t K = (std::size_t)in.c * in.h * in.w, O = fc->getNbOutputs();

@@ -171,6 +171,12 @@ class QuantizedNet:
             ins = [self.tensor_of_layer[j] for j in l['inputs']]
             if l['type'] in ('conv', 'fc'):
                 w = np.ascontiguousarray(l['weights'], np.int8)
+                if l.get('maps') is not None:
+                    # sparse connection map [Cout][Cin] of the reference's Cell mapping: unconnected channels get zero
+                    # weights in the dense layer the device runs ([Cout][kH][kW][Cin])
+                    if l['type'] != 'conv' or l['groups'] != 1:
+                        raise ValueError('a connection map needs a convolution without groups')
+                    w = np.ascontiguousarray(w * np.asarray(l['maps'], np.int8)[:, None, None, :])
                 bits = int(l.get('weight_bits', 8))
                 wbuf = pack_int4(w) if (bits == 4 and pack4) else w
                 wbits = bits if (bits == 4 and pack4) else 8

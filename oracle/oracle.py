@@ -196,7 +196,7 @@ def run_net(net, x_nhwc, flavour='f32'):
         if l['type'] == 'conv':
             w = unpack_weights(l)                      # [O][kH][kW][Cg]
             w_oihw = np.transpose(w, (0, 3, 1, 2))
-            y = conv(a, w_oihw, flavour, l['stride'], l['pad'], l['dil'], l['groups'], bias=l['bias'])
+            y = conv(a, w_oihw, flavour, l['stride'], l['pad'], l['dil'], l['groups'], maps=l.get('maps'), bias=l['bias'])
             y = scaling(y, l['quant'], flavour)
         elif l['type'] == 'fc':
             w = unpack_weights(l)                      # [O][K], K in NHWC order of the input

@@ -15,16 +15,8 @@
 
 using N2D2::Tensor;
 
-// The shim only ever passes regular block-diagonal group maps, for which the number of groups is
-// the channel count divided by the number of leading connections of output 0
-// (what Cell::getNbGroups, src/Cell/Cell.cpp:251-300, returns for such maps).
-size_t N2D2::Cell::getNbGroups(const Tensor<bool>& map)
-{
-    const size_t nbChannels = map.dimY();
-    size_t perGroup = 0;
-    while (perGroup < nbChannels && map(0, perGroup)) ++perGroup;
-    return perGroup ? nbChannels / perGroup : 0;
-}
+// Cell::getNbGroups / getNbGroupsHandMade (how a connection map is read as groups) come from the reference's own
+// src/Cell/Cell.cpp; the link step keeps those two functions of that file and drops the rest (see the Makefile).
 
 static Tensor<float> make_tensor(const float* src, std::vector<size_t> dims)
 {

@@ -62,7 +62,18 @@ int main(int argc, char** argv)
         return 1;
     }
 
-    Lcg g(12345);
+    // twice: dense, and with a sparse connection map on the second convolution (the reference's mnist24 model wires
+    // conv2 to conv1 through a Mapping table; this one connects output o to 3-7 consecutive channels starting at o)
+    for (int sparse = 0; sparse < 2; ++sparse) {
+    std::vector<bool> mapping((size_t)24 * 16, false);
+    std::vector<uint8_t> maps((size_t)24 * 16, 0);
+    for (int o = 0; o < 24; ++o)
+        for (int c = 0; c < 16; ++c) {
+            const bool on = ((c - o) % 16 + 16) % 16 < 3 + (o % 5);
+            mapping[(size_t)o * 16 + c] = on;
+            maps[(size_t)o * 16 + c] = on ? 1 : 0;
+        }
+    Lcg g(12345 + sparse);
     Layer l1 = draw(g, 16, 1 * 4 * 4), l2 = draw(g, 24, 16 * 5 * 5), l3 = draw(g, 150, 24 * 4 * 4), l4 = draw(g, 10, 150);
     std::vector<uint8_t> stimuli((size_t)B * H * W * C);
     for (auto& v : stimuli) v = (uint8_t)g.range(0, 255);
@@ -80,6 +91,7 @@ int main(int argc, char** argv)
     auto conv2 = std::make_shared<ConvCell>("conv2", std::vector<unsigned>{5, 5}, 24, std::vector<unsigned>{1, 1},
                                             std::vector<unsigned>{2, 2}, std::vector<int>{0, 0}, std::vector<unsigned>{1, 1}, relu(l2));
     conv2->setWeights(l2.w); conv2->setBiases(l2.b); conv2->setQuantized(8);
+    if (sparse) conv2->setMapping(mapping);
     auto fc1 = std::make_shared<FcCell>("fc1", 150, relu(l3));
     fc1->setWeights(l3.w); fc1->setBiases(l3.b); fc1->setQuantized(8);
     auto lin = std::make_shared<LinearActivation>();
@@ -109,7 +121,7 @@ int main(int argc, char** argv)
       n2d2o_conv_f32(x.data(), W, H, C, B, w.data(), 4, 4, 1, 16, nullptr, 1, 2, 2, 0, 0, 0, 0, 1, 1, 0, 0, t1.data());
       n2d2o_add_bias_f32(t1.data(), 11, 11, 16, B, bb.data()); scale(t1, 16, 121, l1, 1, 1); }
     { auto w = to_f(l2.w), bb = to_f(l2.b);
-      n2d2o_conv_f32(t1.data(), 11, 11, 16, B, w.data(), 5, 5, 16, 24, nullptr, 1, 2, 2, 0, 0, 0, 0, 1, 1, 0, 0, t2.data());
+      n2d2o_conv_f32(t1.data(), 11, 11, 16, B, w.data(), 5, 5, 16, 24, sparse ? maps.data() : nullptr, 1, 2, 2, 0, 0, 0, 0, 1, 1, 0, 0, t2.data());
       n2d2o_add_bias_f32(t2.data(), 4, 4, 24, B, bb.data()); scale(t2, 24, 16, l2, 1, 1); }
     { auto w = to_f(l3.w), bb = to_f(l3.b); n2d2o_fc_f32(t2.data(), 384, B, w.data(), bb.data(), 150, t3.data()); scale(t3, 150, 1, l3, 1, 1); }
     { auto w = to_f(l4.w), bb = to_f(l4.b); n2d2o_fc_f32(t3.data(), 150, B, w.data(), bb.data(), 10, t4.data()); scale(t4, 10, 1, l4, 0, 0); }
@@ -128,6 +140,9 @@ int main(int argc, char** argv)
     threw = false;
     try { deepNet.test(std::vector<uint8_t>((size_t)(B + 1) * H * W), B + 1); } catch (const std::runtime_error&) { threw = true; }
     if (!threw) { fprintf(stderr, "oversize batch did not throw\n"); return 1; }
-    printf("host api: %zu mismatches over %zu logits + %zu inner values\n", bad, t4.size(), t2.size());
-    return bad ? 1 : 0;
+    if (sparse && (conv2->isConnection(5, 0) || !conv2->isConnection(2, 0))) { fprintf(stderr, "isConnection disagrees with the map\n"); return 1; }
+    printf("host api (%s): %zu mismatches over %zu logits + %zu inner values\n", sparse ? "sparse conv2" : "dense", bad, t4.size(), t2.size());
+    if (bad) return 1;
+    }
+    return 0;
 }

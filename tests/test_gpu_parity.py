@@ -654,3 +654,15 @@ def test_top_n_order_against_the_reference_kernel_itself(classes, top_n, hw):
         assert np.array_equal(got_l, ref_l)
     finally:
         qn.close()
+
+
+@pytest.mark.parametrize('C,O,k', [(64, 96, 3), (16, 24, 5), (128, 128, 1), (3, 20, 3)])
+def test_sparse_connection_map(C, O, k):
+    # the reference's Cell mapping (Mapping(...) of its ini files): channels an output is not connected to are skipped
+    # by its kernels; the device runs the dense layer with zero weights there
+    net = single_conv_net(C, 14, 15, O, k, 1, k // 2, mode='double')
+    rng = np.random.default_rng(C + O)
+    maps = (rng.random((O, C)) < 0.35).astype(np.uint8)
+    maps[np.arange(O), rng.integers(0, C, O)] = 1
+    net['layers'][0]['maps'] = maps
+    compare_net(net, 5)

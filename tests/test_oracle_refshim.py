@@ -29,6 +29,29 @@ def test_random_convolutions_match_the_reference_kernel():
         assert np.array_equal(got, want), (C, H, W, O, k, s, p, d, g)
 
 
+def test_sparse_connection_maps_match_the_reference_kernel():
+    # Cell mapping (the ini files' Mapping(...)): unconnected channels are skipped; with a map that is not made of
+    # groups the weight tensor is indexed by the channel itself
+    rng = np.random.default_rng(12)
+    for _ in range(12):
+        C, O = int(rng.choice([3, 8, 16, 24])), int(rng.integers(2, 30))
+        k = int(rng.choice([1, 3, 5]))
+        s = int(rng.integers(1, 3))
+        p = int(rng.integers(0, k))
+        H, W = int(rng.integers(k, 16)), int(rng.integers(k, 16))
+        maps = (rng.random((O, C)) < 0.4).astype(np.uint8)
+        maps[np.arange(O), rng.integers(0, C, O)] = 1            # every output keeps at least one channel
+        x = rng.integers(-128, 256, (2, C, H, W))
+        w = rng.integers(-127, 128, (O, C, k, k))
+        b = rng.integers(-4096, 4097, O)
+        want = refshim.conv(x, w, (s, s), (p, p, p, p), (1, 1), maps, b)
+        got = oracle.conv(x, w, 'f32', (s, s), (p, p, p, p), (1, 1), 1, maps=maps, bias=b, ref_quirks=True)
+        assert np.array_equal(got, want), (C, H, W, O, k, s, p)
+        # the same integers from a dense convolution whose unconnected weights are zero (what the device runs)
+        dense = oracle.conv(x, w * maps[:, :, None, None], 'i64', (s, s), (p, p, p, p), (1, 1), 1, bias=b)
+        assert np.array_equal(dense, oracle.conv(x, w, 'i64', (s, s), (p, p, p, p), (1, 1), 1, maps=maps, bias=b))
+
+
 def test_fp32_rounding_beyond_2_24_matches_the_reference_kernel():
     x = np.full((1, 1024, 5, 5), 255)
     w = np.full((2, 1024, 3, 3), 127)
