@@ -84,7 +84,7 @@ def test_depthwise_3x3(case, mode):
 # (C, H, W, k, stride, pad, dilation, batch): the strided ones through im2col loads of the group's channel slice
 DW_TC_STRIDED_CASES = [(64, 112, 112, 3, 2, 1, 1, 3), (128, 56, 56, 3, 2, 1, 1, 5), (256, 28, 28, 3, 2, 1, 1, 9),
                        (512, 14, 14, 3, 2, 1, 1, 37), (1024, 9, 7, 3, 2, 1, 1, 4), (32, 30, 30, 3, 2, 1, 1, 3),
-                       (192, 17, 23, 5, 3, 2, 1, 3), (64, 40, 40, 3, 1, 0, 1, 2)]
+                       (192, 17, 23, 5, 3, 2, 1, 3), (64, 40, 40, 3, 1, 0, 1, 2), (128, 9, 9, 3, 2, 1, 1, 1)]
 
 
 @pytest.mark.parametrize('case', DW_TC_STRIDED_CASES, ids=lambda c: 'C%d_%dx%d_k%d_s%d_p%d_d%d_b%d' % c)
@@ -96,7 +96,8 @@ def test_strided_depthwise_as_block_diagonal_groups(case, mode):
 
 
 DW_TC_CASES = [(128, 56, 56, 3, 1, 1, 5), (512, 14, 14, 3, 1, 1, 37), (1024, 7, 7, 3, 1, 1, 9), (32, 112, 112, 3, 1, 1, 3),
-               (96, 30, 17, 3, 1, 1, 4), (64, 20, 20, 5, 2, 1, 3), (192, 24, 24, 3, 2, 2, 3), (256, 28, 28, 3, 0, 1, 2)]
+               (96, 30, 17, 3, 1, 1, 4), (64, 20, 20, 5, 2, 1, 3), (192, 24, 24, 3, 2, 2, 3), (256, 28, 28, 3, 0, 1, 2),
+               (64, 9, 9, 3, 1, 1, 1), (1024, 3, 3, 3, 1, 1, 1)]
 
 
 @pytest.mark.parametrize('case', DW_TC_CASES, ids=lambda c: 'C%d_%dx%d_k%d_p%d_d%d_b%d' % c)
