@@ -427,6 +427,7 @@ def main():
     # every launch against the roofline that bounds it: max(ops / int8 peak, algorithmic bytes / HBM peak)
     groups = launch_groups(net, engines)
     rows, bound_sum, meas_sum, tc_alg_bytes = [], 0.0, 0.0, 0.0
+    by_kind = {}
     for g in groups:
         ms = float(sum(prof[j] for j in g['layers']))
         t_tensor = g['ops'] * B / (int8_peak * 1e12) * 1e3
@@ -439,6 +440,10 @@ def main():
             tc_alg_bytes += alg_bytes
         rows.append([g['name'], g['engine'], round(ms, 4), 'tensor' if t_tensor >= t_hbm else 'hbm',
                      round(bound / ms, 3) if ms > 0 else None])
+        # the same per kind of launch: a residual sum folded into the epilogue is its own kind of the implicit-GEMM kernel
+        kind = g['engine'] + (' + fused residual sum' if '+sum' in g['name'] else '')
+        k = by_kind.setdefault(kind, [0, 0.0, 0.0])
+        k[0] += 1; k[1] += ms; k[2] += bound
     roofline = {'bound': 'tensor', 'kernel': 'igemm_i8_tcgen05_kernel (with its 256-row variant igemm_pair_i8_tcgen05_kernel)',
                 'achieved': achieved, 'peak': int8_peak, 'unit': 'TOP/s', 'frac': achieved / int8_peak,
                 'peak_note': f"2 x {peaks['source']} burst bf16 cuBLAS TFLOP/s ({peaks['bf16_burst']}): the kind::i8 pipe "
@@ -457,7 +462,11 @@ def main():
                 'per_launch': {'frac_time_weighted': bound_sum / meas_sum if meas_sum > 0 else None,
                                'what': 'sum over launches of max(ops / int8 peak, algorithmic bytes / measured HBM '
                                        f'{hbm_peak} GB/s) divided by the sum of measured launch times',
-                               'rows': rows, 'columns': ['cell', 'engine', 'ms', 'bound', 'frac']}}
+                               'rows': rows, 'columns': ['cell', 'engine', 'ms', 'bound', 'frac'],
+                               'by_kind': [{'kind': kd, 'launches': v[0], 'ms': round(v[1], 4),
+                                            'share_of_step': round(v[1] / meas_sum, 4) if meas_sum > 0 else None,
+                                            'frac': round(v[2] / v[1], 3) if v[1] > 0 else None}
+                                           for kd, v in sorted(by_kind.items(), key=lambda kv: -kv[1][1])]}}
     if args.profile_out and rank == 0:
         prows = [{'cell': l['name'], 'engine': e, 'ms': float(m), 'macs_per_image': int(mc)}
                  for l, e, m, mc in zip(net['layers'], engines, prof, macs)]
