@@ -107,7 +107,11 @@ typedef struct n2d2b_conv_desc {
     int32_t pad_top, pad_left, pad_bottom, pad_right;
     int32_t dilation_y, dilation_x;
     int32_t groups;       /* 1 = dense, nb_channels = depthwise */
-    int32_t weight_bits;  /* 8, or 4 for packed int4 weights */
+    int32_t weight_bits;  /* 8; or 4, 2, 1 for packed weights as the export's data<N> stores them: 8 / N values per byte,
+                           * the first in the highest bits, rows starting on a byte, two's complement (1 bit: 0 = -1,
+                           * 1 = +1).  3-bit weights come in 4-bit containers and 5- to 7-bit ones in bytes, as the export
+                           * writes them.  4-bit weights stay packed in HBM where the implicit-GEMM kernel runs the cell;
+                           * 2- and 1-bit ones are widened to bytes */
 } n2d2b_conv_desc;
 
 /* PoolCell creation arguments (include/Cell/PoolCell.hpp) */

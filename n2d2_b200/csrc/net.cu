@@ -470,14 +470,21 @@ static void unpack_weights(const void* src, int weight_bits, size_t rows, size_t
         memcpy(dst.data(), src, rows * row_elems);
         return;
     }
-    // packed int4: element 2i in the high nibble of byte i, element 2i+1 in the low nibble
-    const size_t row_bytes = (row_elems + 1) / 2;
+    // Packed sub-byte weights as the reference's export stores them (data<N>, export/CPP_Quantization/include/
+    // typedefs.hpp:359-517): 8 / N values per byte, the first one in the highest bits, every row starting on a byte;
+    // two's complement in N bits, except N = 1 where the bit 0 stands for -1 and 1 for +1.
+    const size_t per_byte = 8 / (size_t)weight_bits;
+    const size_t row_bytes = (row_elems + per_byte - 1) / per_byte;
+    const int mask = (1 << weight_bits) - 1, sign = 1 << (weight_bits - 1);
     const uint8_t* p = (const uint8_t*)src;
     for (size_t r = 0; r < rows; ++r)
         for (size_t i = 0; i < row_elems; ++i) {
-            const uint8_t byte = p[r * row_bytes + i / 2];
-            const int nib = (i % 2 == 0) ? (byte >> 4) : (byte & 0xF);
-            dst[r * row_elems + i] = (int8_t)((nib & 8) ? nib - 16 : nib);
+            const uint8_t byte = p[r * row_bytes + i / per_byte];
+            const int shift = 8 - weight_bits * (int)(i % per_byte + 1);
+            int v = (byte >> shift) & mask;
+            if (weight_bits == 1) v = v ? 1 : -1;
+            else if (v & sign) v -= 1 << weight_bits;
+            dst[r * row_elems + i] = (int8_t)v;
         }
 }
 
@@ -627,7 +634,8 @@ int n2d2b_net_add_conv(n2d2b_net* net, const n2d2b_conv_desc* d, const void* wei
     if (in.C % d->groups || d->nb_outputs % d->groups)
         return fail(N2D2B_ERR_INVALID, "groups (%d) must divide channels (%d) and outputs (%d)", d->groups, in.C,
                     d->nb_outputs);
-    if (d->weight_bits != 8 && d->weight_bits != 4) return fail(N2D2B_ERR_INVALID, "weight_bits must be 8 or 4");
+    if (d->weight_bits != 8 && d->weight_bits != 4 && d->weight_bits != 2 && d->weight_bits != 1)
+        return fail(N2D2B_ERR_INVALID, "weight_bits must be 8, 4, 2 or 1");
     CellRec c;
     c.type = CELL_CONV;
     c.inputs = {d->input};
@@ -663,7 +671,8 @@ int n2d2b_net_add_fc(n2d2b_net* net, int input, int nb_outputs, int weight_bits,
     const TensorRec in = net->tensors[input];
     if (in.dtype != DT_I8) return fail(N2D2B_ERR_INVALID, "a fully-connected cell needs an 8-bit input tensor");
     if (nb_outputs < 1) return fail(N2D2B_ERR_INVALID, "nb_outputs must be positive");
-    if (weight_bits != 8 && weight_bits != 4) return fail(N2D2B_ERR_INVALID, "weight_bits must be 8 or 4");
+    if (weight_bits != 8 && weight_bits != 4 && weight_bits != 2 && weight_bits != 1)
+        return fail(N2D2B_ERR_INVALID, "weight_bits must be 8, 4, 2 or 1");
     CellRec c;
     c.type = CELL_FC;
     c.inputs = {input};

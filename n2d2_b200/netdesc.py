@@ -52,6 +52,28 @@ def pack_int4(w):
     return ((hi << 4) | lo).astype(np.uint8)
 
 
+def pack_bits(w, bits):
+    """Sub-byte weights [rows][...] as the export's data<N> stores them: 8 / bits values per byte, the first in the
+    highest bits, every row starting on a byte; 1-bit weights store -1 as 0
+    (export/CPP_Quantization/include/typedefs.hpp:359-517 of the reference)."""
+    rows = np.asarray(w, np.int64).reshape(w.shape[0], -1)
+    per = 8 // bits
+    if bits == 1:
+        if not np.isin(rows, (-1, 1)).all():
+            raise ValueError('1-bit weights are -1 or +1')
+        v = (rows > 0).astype(np.int64)
+    else:
+        v = rows & ((1 << bits) - 1)
+    pad = (-rows.shape[1]) % per
+    if pad:
+        v = np.concatenate([v, np.zeros((rows.shape[0], pad), np.int64)], axis=1)
+    v = v.reshape(rows.shape[0], -1, per)
+    out = np.zeros(v.shape[:2], np.int64)
+    for j in range(per):
+        out |= v[:, :, j] << (8 - bits * (j + 1))
+    return np.ascontiguousarray(out.astype(np.uint8))
+
+
 class NetBuilder:
     """Builds a network description and draws seeded parameters.
 
@@ -84,6 +106,10 @@ class NetBuilder:
         kind, p = self.weight_dist
         if self.weight_bits == 4:
             return self.rng.integers(-7, 8, size=shape, dtype=np.int64).astype(np.int8)
+        if self.weight_bits == 2:
+            return self.rng.integers(-2, 2, size=shape, dtype=np.int64).astype(np.int8)
+        if self.weight_bits == 1:
+            return (2 * self.rng.integers(0, 2, size=shape, dtype=np.int64) - 1).astype(np.int8)
         if kind == 'uniform':
             return self.rng.integers(-p, p + 1, size=shape, dtype=np.int64).astype(np.int8)
         w = np.rint(self.rng.normal(0.0, p, size=shape))
@@ -93,6 +119,8 @@ class NetBuilder:
         kind, p = self.weight_dist
         if self.weight_bits == 4:
             return 4.3
+        if self.weight_bits in (1, 2):
+            return 1.1
         return p / math.sqrt(3.0) if kind == 'uniform' else float(p)
 
     def _quant(self, channels, act, acc_sigma, target_rms=45.0, mode=None):

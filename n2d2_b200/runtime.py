@@ -11,7 +11,7 @@ import os
 
 import numpy as np
 
-from .netdesc import ACTS, MODES, pack_int4
+from .netdesc import ACTS, MODES, pack_bits, pack_int4
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, 'libn2d2b.so')
@@ -178,8 +178,9 @@ class QuantizedNet:
                         raise ValueError('a connection map needs a convolution without groups')
                     w = np.ascontiguousarray(w * np.asarray(l['maps'], np.int8)[:, None, None, :])
                 bits = int(l.get('weight_bits', 8))
-                wbuf = pack_int4(w) if (bits == 4 and pack4) else w
-                wbits = bits if (bits == 4 and pack4) else 8
+                packed = pack4 and bits in (1, 2, 4)
+                wbuf = (pack_int4(w) if bits == 4 else pack_bits(w, bits)) if packed else w
+                wbits = bits if packed else 8
                 b = None if l.get('bias') is None else np.ascontiguousarray(l['bias'], np.int32)
                 q, keep = make_quant(l['quant'], l['Cout'])
                 if l['type'] == 'conv':

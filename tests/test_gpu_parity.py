@@ -667,3 +667,23 @@ def test_sparse_connection_map(C, O, k):
     maps[np.arange(O), rng.integers(0, C, O)] = 1
     net['layers'][0]['maps'] = maps
     compare_net(net, 5)
+
+
+@pytest.mark.parametrize('bits', [2, 1])
+@pytest.mark.parametrize('case', [(64, 12, 12, 64, 3, 1, 1), (3, 15, 13, 10, 3, 2, 1), (32, 9, 9, 40, 1, 1, 0), (16, 8, 8, 24, 5, 1, 2)],
+                         ids=lambda c: 'C%d_%dx%d_O%d_k%d' % c[:5])
+def test_packed_two_bit_and_one_bit_weights(case, bits):
+    # the export's data<2> / data<1> packing (four / eight weights per byte, first in the highest bits, rows starting on
+    # a byte, 1-bit weights -1 / +1) through the C ABI; rows of 27 or 25 weights end in a partly filled byte
+    C, H, W, O, k, s, p = case
+    net = single_conv_net(C, H, W, O, k, s, p, mode='double', weight_bits=bits)
+    w = net['layers'][0]['weights']
+    assert w.min() >= (-2 if bits == 2 else -1) and w.max() <= 1 and (bits == 2 or not (w == 0).any())
+    compare_net(net, 3)
+
+
+def test_networks_with_two_bit_and_one_bit_weights():
+    for bits in (2, 1):
+        net = netdesc.resnet18(size=32, classes=10, weight_bits=bits, scaling='double')
+        n, eng = compare_net(net, 3, flags=0)
+        assert 'fused' in eng
